@@ -1,0 +1,358 @@
+// A2: FlashAttention backward on tcgen05 / TMEM (sm_100a), causal and non-causal, head_dim 64 / 128.
+//
+// Gradients of O = softmax(Q K^T * scale) V for an arbitrary upstream dO. (The reference's backward,
+// rust-nn src/tensor.rs:1468-1554, assumes a uniform upstream gradient; the oracle here is autograd
+// through dense fp32 softmax attention.)
+//
+// One CTA = one (batch, head, 128-key block), 256 threads, looping over the query blocks that see it.
+// Per query block, five tensor-core products, all operands fed from 128B-swizzled shared memory:
+//   S  = Q K^T            dP = dO V^T                      (K-major x K-major)        -> TMEM
+//   P  = exp2(S*c - lse)  dS = P * (dP - delta)            (tcgen05.ld, registers, bf16 tiles to smem)
+//   dV += P^T dO          dK += dS^T Q                     (MN-major x MN-major, accumulate in TMEM)
+//   dQ  = dS K                                             (K-major x MN-major)       -> TMEM -> fp32 atomics
+// dK / dV stay resident in TMEM for the whole loop. Warp w reads TMEM lanes 32*(w%4).. (its rows) and
+// the column half w/4. Every wait is bounded.
+#include "../common/ptx.cuh"
+#include "../common/tensormap.h"
+#include "flash_sm100.h"
+
+namespace b200 {
+
+struct BwdParams {
+  __nv_bfloat16* dk; long long dk_sb, dk_ss, dk_sh;
+  __nv_bfloat16* dv; long long dv_sb, dv_ss, dv_sh;
+  float* dq_accum;
+  const float* lse; const float* delta;
+  int B, H, Sq, Skv;
+  float scale, scale_log2;
+  uint32_t* status;
+};
+
+// delta[b,h,s] = sum_e dO[b,s,h,e] * O[b,s,h,e]; one warp per row
+__global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, long long o_sb, long long o_ss, long long o_sh,
+                                   const __nv_bfloat16* __restrict__ d, long long d_sb, long long d_ss, long long d_sh,
+                                   float* __restrict__ delta, int B, int H, int S, int hd) {
+  long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)B * H * S;
+  if (w >= total) return;
+  const int s = (int)(w % S); long long r = w / S; const int h = (int)(r % H); const int b = (int)(r / H);
+  const __nv_bfloat16* op = o + b * o_sb + s * o_ss + h * o_sh;
+  const __nv_bfloat16* dp = d + b * d_sb + s * d_ss + h * d_sh;
+  float acc = 0.f;
+  for (int e = 2 * lane; e < hd; e += 64) {
+    float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(op + e));
+    float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dp + e));
+    acc += a.x * c.x + a.y * c.y;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) delta[w] = acc;
+}
+
+// dq[b,s,h,:] (bf16, strided) = dq_accum[b,s,h,:] (fp32, contiguous)
+__global__ void flash_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long sb,
+                                        long long ss, long long sh, int B, int S, int H, int hd) {
+  const long long total = (long long)B * S * H * (hd / 8);
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const int vpr = hd / 8;
+  for (; i < total; i += stride) {
+    const int v = (int)(i % vpr); long long r = i / vpr;
+    const int h = (int)(r % H); r /= H; const int s = (int)(r % S); const int b = (int)(r / S);
+    const float4 a0 = *reinterpret_cast<const float4*>(acc + ((((long long)b * S + s) * H + h) * hd + v * 8));
+    const float4 a1 = *reinterpret_cast<const float4*>(acc + ((((long long)b * S + s) * H + h) * hd + v * 8 + 4));
+    uint4 o = make_uint4(pack_bf16x2(a0.x, a0.y), pack_bf16x2(a0.z, a0.w), pack_bf16x2(a1.x, a1.y), pack_bf16x2(a1.z, a1.w));
+    *reinterpret_cast<uint4*>(dq + b * sb + s * ss + h * sh + v * 8) = o;
+  }
+}
+
+template <int HD, bool CAUSAL>
+__global__ void __launch_bounds__(256, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, BwdParams p) {
+  constexpr int BLK = 128;
+  constexpr int KA = HD / 64;
+  constexpr int STAGES = (HD == 64) ? 2 : 1;
+  constexpr int TILE_BYTES = BLK * HD * 2;       // one Q / dO / K / V tile
+  constexpr int PS_BYTES = BLK * BLK * 2;        // P or dS tile
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DK = 256, COL_DV = 256 + HD;
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE_BYTES;
+  uint8_t* sQ = sV + TILE_BYTES;                 // STAGES
+  uint8_t* sdO = sQ + STAGES * TILE_BYTES;       // STAGES
+  uint8_t* sP = sdO + STAGES * TILE_BYTES;
+  uint8_t* sdS = sP + PS_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + PS_BYTES);
+  uint64_t* kv_bar = bars;            // 1
+  uint64_t* q_bar = bars + 1;         // STAGES (Q and dO of one query block arrive together)
+  uint64_t* sdp_bar = bars + 3;       // 1
+  uint64_t* dq_bar = bars + 4;        // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int quarter = warp & 3, chalf = warp >> 2;
+  const int row = quarter * 32 + lane;          // row of the 128-row tile this thread owns
+  const int n_kv_blocks = (p.Skv + BLK - 1) / BLK;
+  const int m_blocks = (p.Sq + BLK - 1) / BLK;
+  int bid = blockIdx.x;
+  const int jb = bid % n_kv_blocks; bid /= n_kv_blocks;   // early key blocks (most work when causal) first
+  const int h = bid % p.H; const int b = bid / p.H;
+  const int kv0 = jb * BLK;
+
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (tid == 0 && p.status) atomicCAS(p.status, 0u, (uint32_t)ST_BAD_ARGUMENT);
+    return;
+  }
+  if (tid == 0) {
+    mbar_init(kv_bar, 1);
+    for (int s = 0; s < STAGES; ++s) mbar_init(&q_bar[s], 1);
+    mbar_init(sdp_bar, 1); mbar_init(dq_bar, 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmdO);
+  }
+  if (warp == 0) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_row = tmem_base + (uint32_t(quarter * 32) << 16);
+
+  const int i_start = CAUSAL ? (kv0 / BLK) : 0;
+  const int n_iter = m_blocks - i_start;
+
+  constexpr uint32_t idesc_kk = make_idesc(BLK, BLK, CFMT_F32, FMT_BF16, FMT_BF16, 0, 0);   // S, dP
+  constexpr uint32_t idesc_mm = make_idesc(BLK, HD, CFMT_F32, FMT_BF16, FMT_BF16, 1, 1);    // dV, dK
+  constexpr uint32_t idesc_km = make_idesc(BLK, HD, CFMT_F32, FMT_BF16, FMT_BF16, 0, 1);    // dQ
+
+  auto load_q = [&](int it) {
+    const int st = it % STAGES; const int i = i_start + it;
+    mbar_expect_tx(&q_bar[st], 2 * TILE_BYTES);
+#pragma unroll
+    for (int a = 0; a < KA; ++a) {
+      tma_load_4d(sQ + st * TILE_BYTES + a * (BLK * 128), &tmQ, &q_bar[st], a * 64, h, i * BLK, b);
+      tma_load_4d(sdO + st * TILE_BYTES + a * (BLK * 128), &tmdO, &q_bar[st], a * 64, h, i * BLK, b);
+    }
+  };
+  auto issue_s_dp = [&](int it) {
+    const int st = it % STAGES;
+    const uint32_t aQ = smem_u32(sQ + st * TILE_BYTES), adO = smem_u32(sdO + st * TILE_BYTES);
+    const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k) {
+      const int atom = k >> 2, kk = k & 3;
+      umma_f16(tmem_base + COL_S, make_sdesc_sw128(aQ + atom * (BLK * 128) + kk * 32, 0, 1024),
+               make_sdesc_sw128(aK + atom * (BLK * 128) + kk * 32, 0, 1024), idesc_kk, k > 0 ? 1u : 0u);
+    }
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k) {
+      const int atom = k >> 2, kk = k & 3;
+      umma_f16(tmem_base + COL_DP, make_sdesc_sw128(adO + atom * (BLK * 128) + kk * 32, 0, 1024),
+               make_sdesc_sw128(aV + atom * (BLK * 128) + kk * 32, 0, 1024), idesc_kk, k > 0 ? 1u : 0u);
+    }
+    tc_commit(sdp_bar);
+  };
+  auto issue_grads = [&](int it) {
+    const int st = it % STAGES;
+    const uint32_t aQ = smem_u32(sQ + st * TILE_BYTES), adO = smem_u32(sdO + st * TILE_BYTES);
+    const uint32_t aK = smem_u32(sK), aP = smem_u32(sP), adS = smem_u32(sdS);
+    const uint32_t acc = it > 0 ? 1u : 0u;
+#pragma unroll
+    for (int k = 0; k < BLK / 16; ++k) {   // dV += P^T dO   (K dimension = query rows)
+      umma_f16(tmem_base + COL_DV, make_sdesc_sw128(aP + k * 2048, BLK * 128, 1024),
+               make_sdesc_sw128(adO + k * 2048, BLK * 128, 1024), idesc_mm, (k > 0) ? 1u : acc);
+    }
+#pragma unroll
+    for (int k = 0; k < BLK / 16; ++k) {   // dK += dS^T Q
+      umma_f16(tmem_base + COL_DK, make_sdesc_sw128(adS + k * 2048, BLK * 128, 1024),
+               make_sdesc_sw128(aQ + k * 2048, BLK * 128, 1024), idesc_mm, (k > 0) ? 1u : acc);
+    }
+#pragma unroll
+    for (int k = 0; k < BLK / 16; ++k) {   // dQ = dS K      (K dimension = key rows)
+      const int atom = k >> 2, kk = k & 3;
+      umma_f16(tmem_base + COL_S, make_sdesc_sw128(adS + atom * (BLK * 128) + kk * 32, 0, 1024),
+               make_sdesc_sw128(aK + k * 2048, BLK * 128, 1024), idesc_km, k > 0 ? 1u : 0u);
+    }
+    tc_commit(dq_bar);
+  };
+
+  bool ok = true;
+  if (tid == 0 && n_iter > 0) {
+    mbar_expect_tx(kv_bar, 2 * TILE_BYTES);
+#pragma unroll
+    for (int a = 0; a < KA; ++a) {
+      tma_load_4d(sK + a * (BLK * 128), &tmK, kv_bar, a * 64, h, kv0, b);
+      tma_load_4d(sV + a * (BLK * 128), &tmV, kv_bar, a * 64, h, kv0, b);
+    }
+    load_q(0);
+    if (STAGES > 1 && n_iter > 1) load_q(1);
+    ok = mbar_wait(kv_bar, 0, p.status, ST_TIMEOUT_TMA_FULL) && mbar_wait(&q_bar[0], 0, p.status, ST_TIMEOUT_TMA_FULL);
+    if (ok) { tc_fence_after_sync(); issue_s_dp(0); }
+  }
+
+  const float log2e = 1.4426950408889634f;
+  for (int it = 0; it < n_iter; ++it) {
+    const int i = i_start + it;
+    const int q0 = i * BLK;
+    const int q_row = q0 + row;
+    const bool row_ok = q_row < p.Sq;
+    const long long stat_idx = ((long long)b * p.H + h) * p.Sq + q_row;
+    const float lse2 = row_ok ? p.lse[stat_idx] * log2e : 0.f;
+    const float dlt = row_ok ? p.delta[stat_idx] : 0.f;
+    if (!mbar_wait(sdp_bar, it & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    tc_fence_after_sync();
+    const bool need_mask = CAUSAL && (kv0 + BLK - 1 > q0);
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int colbase = chalf * 64 + c * 32;
+      uint32_t sv[32], dv[32];
+      tmem_ld_x32(tmem_row + COL_S + colbase, sv);
+      tmem_ld_x32(tmem_row + COL_DP + colbase, dv);
+      tmem_ld_wait();
+      float pp[32], ds[32];
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        float pr = exp2f(__uint_as_float(sv[e]) * p.scale_log2 - lse2);
+        if (!row_ok || (need_mask && (kv0 + colbase + e > q_row))) pr = 0.f;
+        pp[e] = pr;
+        ds[e] = pr * (__uint_as_float(dv[e]) - dlt);
+      }
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const int cc = (colbase >> 3) + g;
+        const int atom = cc >> 3, chunk = cc & 7;
+        const uint32_t off = atom * (BLK * 128) + sw128_offset(row, chunk);
+        *reinterpret_cast<uint4*>(sP + off) = make_uint4(pack_bf16x2(pp[g * 8 + 0], pp[g * 8 + 1]), pack_bf16x2(pp[g * 8 + 2], pp[g * 8 + 3]),
+                                                         pack_bf16x2(pp[g * 8 + 4], pp[g * 8 + 5]), pack_bf16x2(pp[g * 8 + 6], pp[g * 8 + 7]));
+        *reinterpret_cast<uint4*>(sdS + off) = make_uint4(pack_bf16x2(ds[g * 8 + 0], ds[g * 8 + 1]), pack_bf16x2(ds[g * 8 + 2], ds[g * 8 + 3]),
+                                                          pack_bf16x2(ds[g * 8 + 4], ds[g * 8 + 5]), pack_bf16x2(ds[g * 8 + 6], ds[g * 8 + 7]));
+      }
+    }
+    tc_fence_before_sync();
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (tid == 0) { tc_fence_after_sync(); issue_grads(it); }
+    if (!mbar_wait(dq_bar, it & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    tc_fence_after_sync();
+    // the Q/dO stage of this iteration is free: prefetch a later query block into it
+    if (tid == 0 && it + STAGES < n_iter) load_q(it + STAGES);
+    // dQ rows -> fp32 atomics (scaled)
+    if (true) {
+      float* dst = p.dq_accum + ((((long long)b * p.Sq + q_row) * p.H + h) * HD);
+#pragma unroll
+      for (int c = 0; c < HD / 64; ++c) {
+        const int colbase = chalf * (HD / 2) + c * 32;
+        uint32_t v[32];
+        tmem_ld_x32(tmem_row + COL_S + colbase, v);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            float4 a = make_float4(__uint_as_float(v[e]) * p.scale, __uint_as_float(v[e + 1]) * p.scale,
+                                   __uint_as_float(v[e + 2]) * p.scale, __uint_as_float(v[e + 3]) * p.scale);
+            atomicAdd(reinterpret_cast<float4*>(dst + colbase + e), a);
+          }
+        }
+      }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (tid == 0 && it + 1 < n_iter) {
+      ok = mbar_wait(&q_bar[(it + 1) % STAGES], ((it + 1) / STAGES) & 1, p.status, ST_TIMEOUT_TMA_FULL);
+      if (ok) { tc_fence_after_sync(); issue_s_dp(it + 1); }
+    }
+  }
+
+  // dK / dV: TMEM -> bf16 global. Thread owns key row `row`, column half `chalf`.
+  if (ok && n_iter > 0) {
+    tc_fence_after_sync();
+    const int kv_row = kv0 + row;
+#pragma unroll
+    for (int c = 0; c < HD / 64; ++c) {
+      const int colbase = chalf * (HD / 2) + c * 32;
+      uint32_t vk[32], vv[32];
+      tmem_ld_x32(tmem_row + COL_DK + colbase, vk);
+      tmem_ld_x32(tmem_row + COL_DV + colbase, vv);
+      tmem_ld_wait();
+      if (kv_row < p.Skv) {
+        __nv_bfloat16* dkp = p.dk + (long long)b * p.dk_sb + (long long)kv_row * p.dk_ss + (long long)h * p.dk_sh + colbase;
+        __nv_bfloat16* dvp = p.dv + (long long)b * p.dv_sb + (long long)kv_row * p.dv_ss + (long long)h * p.dv_sh + colbase;
+#pragma unroll
+        for (int e = 0; e < 32; e += 8) {
+          *reinterpret_cast<uint4*>(dkp + e) = make_uint4(
+              pack_bf16x2(__uint_as_float(vk[e]) * p.scale, __uint_as_float(vk[e + 1]) * p.scale),
+              pack_bf16x2(__uint_as_float(vk[e + 2]) * p.scale, __uint_as_float(vk[e + 3]) * p.scale),
+              pack_bf16x2(__uint_as_float(vk[e + 4]) * p.scale, __uint_as_float(vk[e + 5]) * p.scale),
+              pack_bf16x2(__uint_as_float(vk[e + 6]) * p.scale, __uint_as_float(vk[e + 7]) * p.scale));
+          *reinterpret_cast<uint4*>(dvp + e) = make_uint4(
+              pack_bf16x2(__uint_as_float(vv[e]), __uint_as_float(vv[e + 1])), pack_bf16x2(__uint_as_float(vv[e + 2]), __uint_as_float(vv[e + 3])),
+              pack_bf16x2(__uint_as_float(vv[e + 4]), __uint_as_float(vv[e + 5])), pack_bf16x2(__uint_as_float(vv[e + 6]), __uint_as_float(vv[e + 7])));
+        }
+      }
+    }
+  } else if (ok && n_iter <= 0) {
+    // a key block no query attends to (cannot happen for causal self-attention): zero gradients
+    const int kv_row = kv0 + row;
+    if (kv_row < p.Skv) {
+      for (int e = chalf * (HD / 2); e < (chalf + 1) * (HD / 2); ++e) {
+        p.dk[(long long)b * p.dk_sb + (long long)kv_row * p.dk_ss + (long long)h * p.dk_sh + e] = __float2bfloat16(0.f);
+        p.dv[(long long)b * p.dv_sb + (long long)kv_row * p.dv_ss + (long long)h * p.dv_sh + e] = __float2bfloat16(0.f);
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) { tc_fence_after_sync(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+template <int HD, bool CAUSAL>
+static int launch_bwd(const FlashArgs& a, cudaStream_t st) {
+  CUtensorMap tmQ, tmK, tmV, tmdO;
+  const auto BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const auto SW = CU_TENSOR_MAP_SWIZZLE_128B;
+  if (make_tmap_attn(&tmQ, a.q.ptr, BF, 2, a.hd, a.H, a.Sq, a.B, a.q.sh, a.q.ss, a.q.sb, 64, 128, SW)) return 101;
+  if (make_tmap_attn(&tmK, a.k.ptr, BF, 2, a.hd, a.H, a.Skv, a.B, a.k.sh, a.k.ss, a.k.sb, 64, 128, SW)) return 102;
+  if (make_tmap_attn(&tmV, a.v.ptr, BF, 2, a.hd, a.H, a.Skv, a.B, a.v.sh, a.v.ss, a.v.sb, 64, 128, SW)) return 103;
+  if (make_tmap_attn(&tmdO, a.dout.ptr, BF, 2, a.hd, a.H, a.Sq, a.B, a.dout.sh, a.dout.ss, a.dout.sb, 64, 128, SW)) return 104;
+  constexpr int STAGES = (HD == 64) ? 2 : 1;
+  constexpr int SMEM = 2 * 128 * HD * 2 + 2 * STAGES * 128 * HD * 2 + 2 * 128 * 128 * 2 + 128;
+  auto kfn = flash_bwd_kernel<HD, CAUSAL>;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return 105;
+    attr = true;
+  }
+  const long long rows = (long long)a.B * a.H * a.Sq;
+  flash_delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>(
+      (const __nv_bfloat16*)a.o.ptr, a.o.sb, a.o.ss, a.o.sh, (const __nv_bfloat16*)a.dout.ptr, a.dout.sb, a.dout.ss,
+      a.dout.sh, a.delta, a.B, a.H, a.Sq, a.hd);
+  cudaMemsetAsync(a.dq_accum, 0, sizeof(float) * (size_t)a.B * a.Sq * a.H * a.hd, st);
+  BwdParams p;
+  p.dk = (__nv_bfloat16*)a.dk.ptr; p.dk_sb = a.dk.sb; p.dk_ss = a.dk.ss; p.dk_sh = a.dk.sh;
+  p.dv = (__nv_bfloat16*)a.dv.ptr; p.dv_sb = a.dv.sb; p.dv_ss = a.dv.ss; p.dv_sh = a.dv.sh;
+  p.dq_accum = a.dq_accum; p.lse = a.lse; p.delta = a.delta;
+  p.B = a.B; p.H = a.H; p.Sq = a.Sq; p.Skv = a.Skv;
+  p.scale = a.scale; p.scale_log2 = a.scale * 1.4426950408889634f; p.status = a.status;
+  const long long grid = (long long)((a.Skv + 127) / 128) * a.H * a.B;
+  kfn<<<(unsigned)grid, 256, SMEM, st>>>(tmQ, tmK, tmV, tmdO, p);
+  long long total = (long long)a.B * a.Sq * a.H * (a.hd / 8);
+  long long g = (total + 255) / 256; if (g > 148 * 16) g = 148 * 16;
+  flash_dq_convert_kernel<<<(unsigned)g, 256, 0, st>>>(a.dq_accum, (__nv_bfloat16*)a.dq.ptr, a.dq.sb, a.dq.ss, a.dq.sh,
+                                                        a.B, a.Sq, a.H, a.hd);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+}  // namespace b200
+
+extern "C" int b200_flash_bwd(const b200::FlashArgs* a, cudaStream_t st) {
+  using namespace b200;
+  if (a->B <= 0 || a->H <= 0 || a->Sq <= 0 || a->Skv <= 0) return 0;
+  if (a->hd == 64) return a->causal ? launch_bwd<64, true>(*a, st) : launch_bwd<64, false>(*a, st);
+  if (a->hd == 128) return a->causal ? launch_bwd<128, true>(*a, st) : launch_bwd<128, false>(*a, st);
+  return -3;
+}

@@ -1,0 +1,281 @@
+// A1: FlashAttention forward on tcgen05 / TMEM (sm_100a), causal and non-causal, head_dim 64 / 128.
+//
+// Exact softmax(Q K^T * scale) V with an online softmax; the oracle is dense fp32 softmax attention,
+// the same mathematics as rust-nn src/tensor.rs:618-677 and its WGSL shader src/gpu.rs:95-133
+// (which stream keys per query on scalar units).
+//
+// One CTA = one (batch, head, 128-query block); 128 threads; thread t owns query row t = TMEM lane t.
+//   S  = Q K_j^T     tcgen05.mma, both operands K-major 128B-swizzled tiles written by TMA   -> TMEM
+//   P  = exp2(S*c - m)  read back with tcgen05.ld (one row per thread: no shuffles), written to
+//                        shared memory as a bf16 K-major swizzled A operand
+//   PV = P V_j       tcgen05.mma, V consumed MN-major straight from its [kv][hd] layout      -> TMEM
+//   O  = O*alpha + PV   in registers (fp32)
+// K/V tiles are double-buffered by TMA; two CTAs share an SM (TMEM 2 x 256 columns) so one CTA's
+// exponentials overlap the other's MMAs. Every wait is bounded.
+#include "../common/ptx.cuh"
+#include "../common/tensormap.h"
+#include "flash_sm100.h"
+
+namespace b200 {
+
+struct FwdParams {
+  __nv_bfloat16* o; long long o_sb, o_ss, o_sh;
+  float* lse;
+  int B, H, Sq, Skv;
+  float scale_log2;
+  uint32_t* status;
+};
+
+template <int HD, int BN, bool CAUSAL>
+__global__ void __launch_bounds__(128, 2)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, FwdParams p) {
+  constexpr int BMQ = 128;
+  constexpr int KA = HD / 64;                 // 64-element atoms along head_dim
+  constexpr int Q_BYTES = BMQ * HD * 2;
+  constexpr int KV_BYTES = BN * HD * 2;
+  constexpr int P_BYTES = BMQ * BN * 2;
+  constexpr uint32_t TMEM_COLS = 256;
+  constexpr uint32_t PV_COL = 128;
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + Q_BYTES;                 // 2 stages
+  uint8_t* sV = sK + 2 * KV_BYTES;            // 2 stages
+  uint8_t* sP = sV + 2 * KV_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
+  uint64_t* q_bar = bars;          // 1
+  uint64_t* k_bar = bars + 1;      // 2
+  uint64_t* v_bar = bars + 3;      // 2
+  uint64_t* s_bar = bars + 5;      // 1
+  uint64_t* pv_bar = bars + 6;     // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int m_blocks = (p.Sq + BMQ - 1) / BMQ;
+  int bid = blockIdx.x;
+  // heavy (late, causal) query blocks first
+  const int qb = m_blocks - 1 - (bid % m_blocks); bid /= m_blocks;
+  const int h = bid % p.H; const int b = bid / p.H;
+  const int q0 = qb * BMQ;
+
+  if ((smem_u32(smem) & 1023u) != 0) {          // swizzled tiles need 1024-byte alignment
+    if (tid == 0 && p.status) atomicCAS(p.status, 0u, (uint32_t)ST_BAD_ARGUMENT);
+    return;
+  }
+  if (tid == 0) {
+    mbar_init(q_bar, 1);
+    mbar_init(&k_bar[0], 1); mbar_init(&k_bar[1], 1);
+    mbar_init(&v_bar[0], 1); mbar_init(&v_bar[1], 1);
+    mbar_init(s_bar, 1); mbar_init(pv_bar, 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+  }
+  if (warp == 0) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_row = tmem_base + (uint32_t(warp * 32) << 16);
+
+  int n_blocks = (p.Skv + BN - 1) / BN;
+  if (CAUSAL) { int lim = (q0 + BMQ + BN - 1) / BN; if (lim < n_blocks) n_blocks = lim; }
+
+  constexpr uint32_t idesc_s = make_idesc(BMQ, BN, CFMT_F32, FMT_BF16, FMT_BF16, 0, 0);
+  constexpr uint32_t idesc_pv = make_idesc(BMQ, HD, CFMT_F32, FMT_BF16, FMT_BF16, 0, 1);
+
+  auto load_kv = [&](int j) {
+    const int st = j & 1;
+#pragma unroll
+    for (int a = 0; a < KA; ++a) {
+      if (a == 0) mbar_expect_tx(&k_bar[st], KV_BYTES);
+      tma_load_4d(sK + st * KV_BYTES + a * (BN * 128), &tmK, &k_bar[st], a * 64, h, j * BN, b);
+    }
+#pragma unroll
+    for (int a = 0; a < KA; ++a) {
+      if (a == 0) mbar_expect_tx(&v_bar[st], KV_BYTES);
+      tma_load_4d(sV + st * KV_BYTES + a * (BN * 128), &tmV, &v_bar[st], a * 64, h, j * BN, b);
+    }
+  };
+  auto issue_s = [&](int j) {   // S = Q K_j^T
+    const int st = j & 1;
+    const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK + st * KV_BYTES);
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k) {
+      const int atom = k >> 2, kk = k & 3;
+      uint64_t da = make_sdesc_sw128(aQ + atom * (BMQ * 128) + kk * 32, 0, 1024);
+      uint64_t db = make_sdesc_sw128(aK + atom * (BN * 128) + kk * 32, 0, 1024);
+      umma_f16(tmem_base, da, db, idesc_s, k > 0 ? 1u : 0u);
+    }
+    tc_commit(s_bar);
+  };
+  auto issue_pv = [&](int j) {  // PV = P V_j
+    const int st = j & 1;
+    const uint32_t aP = smem_u32(sP), aV = smem_u32(sV + st * KV_BYTES);
+#pragma unroll
+    for (int k = 0; k < BN / 16; ++k) {
+      const int atom = k >> 2, kk = k & 3;
+      uint64_t da = make_sdesc_sw128(aP + atom * (BMQ * 128) + kk * 32, 0, 1024);
+      uint64_t db = make_sdesc_sw128(aV + k * 2048, BN * 128, 1024);
+      umma_f16(tmem_base + PV_COL, da, db, idesc_pv, k > 0 ? 1u : 0u);
+    }
+    tc_commit(pv_bar);
+  };
+
+  bool ok = true;
+  if (tid == 0) {
+    mbar_expect_tx(q_bar, Q_BYTES);
+#pragma unroll
+    for (int a = 0; a < KA; ++a) tma_load_4d(sQ + a * (BMQ * 128), &tmQ, q_bar, a * 64, h, q0, b);
+    load_kv(0);
+    if (n_blocks > 1) load_kv(1);
+    ok = mbar_wait(q_bar, 0, p.status, ST_TIMEOUT_TMA_FULL) && mbar_wait(&k_bar[0], 0, p.status, ST_TIMEOUT_TMA_FULL);
+    if (ok) { tc_fence_after_sync(); issue_s(0); }
+  }
+
+  float m_run = -INFINITY, l_run = 0.f;
+  float o_acc[HD];
+#pragma unroll
+  for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
+  const int q_row = q0 + tid;
+
+  for (int j = 0; j < n_blocks; ++j) {
+    const int st = j & 1;
+    const uint32_t ph_kv = (j >> 1) & 1;
+    if (!mbar_wait(s_bar, j & 1, p.status, ST_TIMEOUT_ACC_FULL)) { ok = false; }
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    tc_fence_after_sync();
+    const int kv0 = j * BN;
+    const bool need_mask = (kv0 + BN > p.Skv) || (CAUSAL && (kv0 + BN - 1 > q0));
+    // pass 1: row maximum
+    float mx = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t v[32];
+      tmem_ld_x32(tmem_row + c * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float s = __uint_as_float(v[i]);
+        if (need_mask) {
+          const int col = kv0 + c * 32 + i;
+          if (col >= p.Skv || (CAUSAL && col > q_row)) s = -INFINITY;
+        }
+        mx = fmaxf(mx, s);
+      }
+    }
+    const float m_new = fmaxf(m_run, mx * p.scale_log2);
+    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+    const float alpha = exp2f(m_run - m_use);
+    // pass 2: exponentials, row sum, bf16 P tile into shared memory (K-major, 128B swizzle)
+    float rs = 0.f;
+#pragma unroll
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t v[32];
+      tmem_ld_x32(tmem_row + c * 32, v);
+      tmem_ld_wait();
+      float e[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float s = __uint_as_float(v[i]);
+        if (need_mask) {
+          const int col = kv0 + c * 32 + i;
+          if (col >= p.Skv || (CAUSAL && col > q_row)) s = -INFINITY;
+        }
+        e[i] = exp2f(s * p.scale_log2 - m_use);
+        rs += e[i];
+      }
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const int cc = c * 4 + g;                 // 16-byte chunk index along kv
+        const int atom = cc >> 3, chunk = cc & 7;
+        uint4 o = make_uint4(pack_bf16x2(e[g * 8 + 0], e[g * 8 + 1]), pack_bf16x2(e[g * 8 + 2], e[g * 8 + 3]),
+                             pack_bf16x2(e[g * 8 + 4], e[g * 8 + 5]), pack_bf16x2(e[g * 8 + 6], e[g * 8 + 7]));
+        *reinterpret_cast<uint4*>(sP + atom * (BMQ * 128) + sw128_offset(tid, chunk)) = o;
+      }
+    }
+    l_run = l_run * alpha + rs;
+    m_run = m_new;
+    tc_fence_before_sync();
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      ok = mbar_wait(&v_bar[st], ph_kv, p.status, ST_TIMEOUT_TMA_FULL);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_pv(j);
+        if (j + 1 < n_blocks) {
+          ok = mbar_wait(&k_bar[st ^ 1], ((j + 1) >> 1) & 1, p.status, ST_TIMEOUT_TMA_FULL);
+          if (ok) issue_s(j + 1);
+        }
+      }
+    }
+    if (!mbar_wait(pv_bar, j & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    tc_fence_after_sync();
+    // K_j / V_j buffers are free now: prefetch block j+2 into them
+    if (tid == 0 && j + 2 < n_blocks) load_kv(j + 2);
+#pragma unroll
+    for (int c = 0; c < HD / 32; ++c) {
+      uint32_t v[32];
+      tmem_ld_x32(tmem_row + PV_COL + c * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha + __uint_as_float(v[i]);
+    }
+    tc_fence_before_sync();
+  }
+
+  if (ok && q_row < p.Sq) {
+    const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+    __nv_bfloat16* op = p.o + (long long)b * p.o_sb + (long long)q_row * p.o_ss + (long long)h * p.o_sh;
+#pragma unroll
+    for (int i = 0; i < HD; i += 8) {
+      uint4 o = make_uint4(pack_bf16x2(o_acc[i] * inv_l, o_acc[i + 1] * inv_l), pack_bf16x2(o_acc[i + 2] * inv_l, o_acc[i + 3] * inv_l),
+                           pack_bf16x2(o_acc[i + 4] * inv_l, o_acc[i + 5] * inv_l), pack_bf16x2(o_acc[i + 6] * inv_l, o_acc[i + 7] * inv_l));
+      *reinterpret_cast<uint4*>(op + i) = o;
+    }
+    if (p.lse) {
+      const float mu = (m_run == -INFINITY) ? 0.f : m_run;
+      p.lse[((long long)b * p.H + h) * p.Sq + q_row] = (mu + log2f(fmaxf(l_run, 1e-37f))) * 0.6931471805599453f;
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) { tc_fence_after_sync(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+template <int HD, int BN, bool CAUSAL>
+static int launch_fwd(const FlashArgs& a, cudaStream_t st) {
+  CUtensorMap tmQ, tmK, tmV;
+  const auto BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if (make_tmap_attn(&tmQ, a.q.ptr, BF, 2, a.hd, a.H, a.Sq, a.B, a.q.sh, a.q.ss, a.q.sb, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return 101;
+  if (make_tmap_attn(&tmK, a.k.ptr, BF, 2, a.hd, a.H, a.Skv, a.B, a.k.sh, a.k.ss, a.k.sb, 64, BN, CU_TENSOR_MAP_SWIZZLE_128B)) return 102;
+  if (make_tmap_attn(&tmV, a.v.ptr, BF, 2, a.hd, a.H, a.Skv, a.B, a.v.sh, a.v.ss, a.v.sb, 64, BN, CU_TENSOR_MAP_SWIZZLE_128B)) return 103;
+  constexpr int SMEM = 128 * HD * 2 + 4 * BN * HD * 2 + 128 * BN * 2 + 128;
+  auto kfn = flash_fwd_kernel<HD, BN, CAUSAL>;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return 104;
+    attr = true;
+  }
+  FwdParams p;
+  p.o = (__nv_bfloat16*)a.o.ptr; p.o_sb = a.o.sb; p.o_ss = a.o.ss; p.o_sh = a.o.sh;
+  p.lse = a.lse; p.B = a.B; p.H = a.H; p.Sq = a.Sq; p.Skv = a.Skv;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.status = a.status;
+  const long long grid = (long long)((a.Sq + 127) / 128) * a.H * a.B;
+  kfn<<<(unsigned)grid, 128, SMEM, st>>>(tmQ, tmK, tmV, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+}  // namespace b200
+
+extern "C" int b200_flash_fwd(const b200::FlashArgs* a, cudaStream_t st) {
+  using namespace b200;
+  if (a->B <= 0 || a->H <= 0 || a->Sq <= 0 || a->Skv <= 0) return 0;
+  if (a->hd == 64) return a->causal ? launch_fwd<64, 128, true>(*a, st) : launch_fwd<64, 128, false>(*a, st);
+  if (a->hd == 128) return a->causal ? launch_fwd<128, 64, true>(*a, st) : launch_fwd<128, 64, false>(*a, st);
+  return -3;
+}

@@ -1,0 +1,332 @@
+// E1: vectorised elementwise / broadcast / reduce family (HBM-bound; 16-byte accesses, grid-stride).
+// Restates the reference's AVX2 elementwise helpers (rust-nn src/simd.rs:214-406), its activation
+// shader (src/gpu.rs:136-153), Dropout (src/nn.rs:231-259), FakeQuantize (src/nn.rs:644-667),
+// softplus/sigmoid/silu ops (src/tensor.rs:948-987) and the bias column-sum of the Linear backward
+// (src/tensor.rs:1592-1709) as CUDA kernels.
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include "../gemm/gemm_sm100.h"
+
+namespace b200 {
+
+template <typename T> struct Vec;
+template <> struct Vec<float> { using V = float4; static constexpr int N = 4; };
+template <> struct Vec<__nv_bfloat16> { using V = uint4; static constexpr int N = 8; };
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
+
+template <typename T, int N> struct alignas(sizeof(T) * N) Pack { T v[N]; };
+
+__device__ __forceinline__ float gelu_f(float v) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  return 0.5f * v * (1.f + tanhf(k0 * (v + k1 * v * v * v)));
+}
+__device__ __forceinline__ float gelu_grad(float s) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float t = tanhf(k0 * (s + k1 * s * s * s));
+  return 0.5f * (1.f + t) + 0.5f * s * (1.f - t * t) * k0 * (1.f + 3.f * k1 * s * s);
+}
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(__expf(v)); }
+
+enum : int {
+  OP_ADD = 0, OP_SUB = 1, OP_MUL = 2, OP_DIV = 3,
+  OP_RELU = 10, OP_GELU = 11, OP_SILU = 12, OP_SIGMOID = 13, OP_TANH = 14, OP_SOFTPLUS = 15,
+  OP_SCALE = 16, OP_EXP = 17, OP_ABS = 18, OP_SQUARE = 19, OP_CLAMP = 20, OP_ROUND = 21, OP_ADD_SCALAR = 22,
+  // backward of a unary op: out = g * f'(saved); saved is the INPUT of the forward op
+  OP_RELU_BWD = 30, OP_GELU_BWD = 31, OP_SILU_BWD = 32, OP_SIGMOID_BWD = 33, OP_TANH_BWD = 34, OP_SOFTPLUS_BWD = 35,
+  // fused: out = a * silu(b)  (Mamba gate) and its two gradients
+  OP_MUL_SILU = 40,
+};
+
+__device__ __forceinline__ float unary_apply(float x, int op, float s0, float s1) {
+  switch (op) {
+    case OP_RELU: return x > 0.f ? x : 0.f;
+    case OP_GELU: return gelu_f(x);
+    case OP_SILU: return x / (1.f + __expf(-x));
+    case OP_SIGMOID: return 1.f / (1.f + __expf(-x));
+    case OP_TANH: return tanhf(x);
+    case OP_SOFTPLUS: return softplus_f(x);
+    case OP_SCALE: return x * s0;
+    case OP_ADD_SCALAR: return x + s0;
+    case OP_EXP: return __expf(x);
+    case OP_ABS: return fabsf(x);
+    case OP_SQUARE: return x * x;
+    case OP_CLAMP: return fminf(fmaxf(x, s0), s1);
+    case OP_ROUND: return rintf(x);
+    default: return x;
+  }
+}
+__device__ __forceinline__ float binary_apply(float a, float b, int op) {
+  switch (op) {
+    case OP_ADD: return a + b;
+    case OP_SUB: return a - b;
+    case OP_MUL: return a * b;
+    case OP_DIV: return a / b;
+    case OP_RELU_BWD: return b > 0.f ? a : 0.f;
+    case OP_GELU_BWD: return a * gelu_grad(b);
+    case OP_SILU_BWD: { float sg = 1.f / (1.f + __expf(-b)); return a * sg * (1.f + b * (1.f - sg)); }
+    case OP_SIGMOID_BWD: { float sg = 1.f / (1.f + __expf(-b)); return a * sg * (1.f - sg); }
+    case OP_TANH_BWD: { float t = tanhf(b); return a * (1.f - t * t); }
+    case OP_SOFTPLUS_BWD: return a / (1.f + __expf(-b));
+    case OP_MUL_SILU: return a * b / (1.f + __expf(-b));
+    default: return a;
+  }
+}
+
+template <typename T>
+__global__ void unary_kernel(const T* __restrict__ x, T* __restrict__ y, long long n, int op, float s0, float s1) {
+  constexpr int N = Vec<T>::N;
+  using P = Pack<T, N>;
+  long long nv = n / N;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  long long stride = (long long)gridDim.x * blockDim.x;
+  for (; i < nv; i += stride) {
+    P in = reinterpret_cast<const P*>(x)[i], out;
+#pragma unroll
+    for (int j = 0; j < N; ++j) out.v[j] = from_f<T>(unary_apply(to_f(in.v[j]), op, s0, s1));
+    reinterpret_cast<P*>(y)[i] = out;
+  }
+  long long tail = nv * N + blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (tail < n) y[tail] = from_f<T>(unary_apply(to_f(x[tail]), op, s0, s1));
+}
+
+// y = a (op) b with b broadcast along rows when b_period > 0 (b has b_period elements, index = i % b_period)
+template <typename T>
+__global__ void binary_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ y, long long n,
+                              int op, long long b_period) {
+  constexpr int N = Vec<T>::N;
+  using P = Pack<T, N>;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  long long stride = (long long)gridDim.x * blockDim.x;
+  if (b_period == 0) {
+    long long nv = n / N;
+    for (long long k = i; k < nv; k += stride) {
+      P pa = reinterpret_cast<const P*>(a)[k], pb = reinterpret_cast<const P*>(b)[k], out;
+#pragma unroll
+      for (int j = 0; j < N; ++j) out.v[j] = from_f<T>(binary_apply(to_f(pa.v[j]), to_f(pb.v[j]), op));
+      reinterpret_cast<P*>(y)[k] = out;
+    }
+    long long tail = nv * N + i;
+    if (tail < n) y[tail] = from_f<T>(binary_apply(to_f(a[tail]), to_f(b[tail]), op));
+  } else {
+    for (long long k = i; k < n; k += stride)
+      y[k] = from_f<T>(binary_apply(to_f(a[k]), to_f(b[k % b_period]), op));
+  }
+}
+
+// cast kernels
+template <typename TI, typename TO>
+__global__ void cast_kernel(const TI* __restrict__ x, TO* __restrict__ y, long long n, float scale) {
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  long long stride = (long long)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) y[i] = from_f<TO>(to_f(x[i]) * scale);
+}
+
+// column sum: out[c] (+)= sum_r x[r, c]   (dbias). Two-stage: each block reduces a slab of rows, atomics to fp32.
+template <typename T>
+__global__ void colsum_kernel(const T* __restrict__ x, float* __restrict__ out, long long rows, int cols,
+                              long long ld, int rows_per_block) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  long long r0 = (long long)blockIdx.y * rows_per_block;
+  long long r1 = r0 + rows_per_block; if (r1 > rows) r1 = rows;
+  if (c >= cols) return;
+  float acc = 0.f;
+  for (long long r = r0; r < r1; ++r) acc += to_f(x[r * ld + c]);
+  atomicAdd(out + c, acc);
+}
+
+// full reduction sum / sum of squares / max / min into fp32 scalar slots (out[0..3])
+template <typename T>
+__global__ void reduce_kernel(const T* __restrict__ x, float* __restrict__ out, long long n, int what) {
+  float acc = (what == 2) ? -INFINITY : (what == 3) ? INFINITY : 0.f;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  long long stride = (long long)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    float v = to_f(x[i]);
+    if (what == 0) acc += v; else if (what == 1) acc += v * v; else if (what == 2) acc = fmaxf(acc, v); else acc = fminf(acc, v);
+  }
+  __shared__ float sh[32];
+  for (int o = 16; o > 0; o >>= 1) {
+    float t = __shfl_xor_sync(0xffffffffu, acc, o);
+    if (what <= 1) acc += t; else if (what == 2) acc = fmaxf(acc, t); else acc = fminf(acc, t);
+  }
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    int nw = blockDim.x >> 5;
+    acc = threadIdx.x < nw ? sh[threadIdx.x] : ((what == 2) ? -INFINITY : (what == 3) ? INFINITY : 0.f);
+    for (int o = 16; o > 0; o >>= 1) {
+      float t = __shfl_xor_sync(0xffffffffu, acc, o);
+      if (what <= 1) acc += t; else if (what == 2) acc = fmaxf(acc, t); else acc = fminf(acc, t);
+    }
+    if (threadIdx.x == 0) {
+      if (what <= 1) atomicAdd(out, acc);
+      else if (what == 2) { int* a = (int*)out; int old = *a, assumed; do { assumed = old; if (__int_as_float(assumed) >= acc) break; old = atomicCAS(a, assumed, __float_as_int(acc)); } while (assumed != old); }
+      else { int* a = (int*)out; int old = *a, assumed; do { assumed = old; if (__int_as_float(assumed) <= acc) break; old = atomicCAS(a, assumed, __float_as_int(acc)); } while (assumed != old); }
+    }
+  }
+}
+
+// Philox-free counter hash (splitmix64) for dropout: stateless, seed + element index.
+__device__ __forceinline__ float u01(uint64_t seed, uint64_t idx) {
+  uint64_t z = seed + idx * 0x9E3779B97F4A7C15ull + 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z = z ^ (z >> 31);
+  return (float)(z >> 40) * (1.0f / 16777216.0f);
+}
+template <typename T>
+__global__ void dropout_kernel(const T* __restrict__ x, T* __restrict__ y, long long n, float p, float scale,
+                               uint64_t seed) {
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  long long stride = (long long)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    float keep = u01(seed, (uint64_t)i) >= p ? scale : 0.f;
+    y[i] = from_f<T>(to_f(x[i]) * keep);
+  }
+}
+
+// fake quantise: y = clamp(round(x / s), qmin, qmax) * s   (gradient is a straight-through mask, computed in python)
+template <typename T>
+__global__ void fake_quant_kernel(const T* __restrict__ x, T* __restrict__ y, long long n, float scale, float qmin,
+                                  float qmax) {
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  long long stride = (long long)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    float q = rintf(to_f(x[i]) / scale);
+    q = fminf(fmaxf(q, qmin), qmax);
+    y[i] = from_f<T>(q * scale);
+  }
+}
+
+// embedding gather: out[t, :] = table[ids[t], :]  (bf16 or f32 rows, 16-byte vector copies)
+template <typename T>
+__global__ void embedding_fwd_kernel(const T* __restrict__ table, const long long* __restrict__ ids,
+                                     T* __restrict__ out, long long tokens, int dim, long long vocab) {
+  constexpr int N = Vec<T>::N;
+  using P = Pack<T, N>;
+  int vec_per_row = dim / N;
+  long long total = tokens * vec_per_row;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  long long stride = (long long)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    long long t = i / vec_per_row; int v = (int)(i % vec_per_row);
+    long long id = ids[t];
+    if (id < 0 || id >= vocab) id = 0;
+    reinterpret_cast<P*>(out + t * dim)[v] = reinterpret_cast<const P*>(table + id * dim)[v];
+  }
+}
+// embedding backward: grad_table[ids[t], :] += g[t, :]  (fp32 accumulation)
+template <typename T>
+__global__ void embedding_bwd_kernel(const T* __restrict__ g, const long long* __restrict__ ids,
+                                     float* __restrict__ grad_table, long long tokens, int dim, long long vocab) {
+  long long total = tokens * dim;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  long long stride = (long long)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    long long t = i / dim; int d = (int)(i % dim);
+    long long id = ids[t];
+    if (id < 0 || id >= vocab) continue;
+    atomicAdd(grad_table + id * dim + d, to_f(g[i]));
+  }
+}
+
+static inline int grid_for(long long work, int block, int max_blocks = 148 * 16) {
+  long long g = (work + block - 1) / block;
+  if (g < 1) g = 1;
+  if (g > max_blocks) g = max_blocks;
+  return (int)g;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_unary(const void* x, void* y, long long n, int op, float s0, float s1, int is_bf16, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (is_bf16) unary_kernel<__nv_bfloat16><<<grid_for(n / 8 + 1, 256), 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, n, op, s0, s1);
+  else unary_kernel<float><<<grid_for(n / 4 + 1, 256), 256, 0, st>>>((const float*)x, (float*)y, n, op, s0, s1);
+  return (int)cudaGetLastError();
+}
+
+int b200_binary(const void* a, const void* b, void* y, long long n, int op, long long b_period, int is_bf16,
+                cudaStream_t st) {
+  if (n <= 0) return 0;
+  long long work = b_period ? n : n / (is_bf16 ? 8 : 4) + 1;
+  if (is_bf16) binary_kernel<__nv_bfloat16><<<grid_for(work, 256), 256, 0, st>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, n, op, b_period);
+  else binary_kernel<float><<<grid_for(work, 256), 256, 0, st>>>((const float*)a, (const float*)b, (float*)y, n, op, b_period);
+  return (int)cudaGetLastError();
+}
+
+// dir: 0 f32->bf16, 1 bf16->f32
+int b200_cast(const void* x, void* y, long long n, float scale, int dir, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (dir == 0) cast_kernel<float, __nv_bfloat16><<<grid_for(n, 256), 256, 0, st>>>((const float*)x, (__nv_bfloat16*)y, n, scale);
+  else cast_kernel<__nv_bfloat16, float><<<grid_for(n, 256), 256, 0, st>>>((const __nv_bfloat16*)x, (float*)y, n, scale);
+  return (int)cudaGetLastError();
+}
+
+// out must be zero-initialised (or hold a running sum) by the caller
+int b200_colsum(const void* x, float* out, long long rows, int cols, long long ld, int is_bf16, cudaStream_t st) {
+  if (rows <= 0 || cols <= 0) return 0;
+  int rpb = 256;
+  dim3 grid((cols + 127) / 128, (unsigned)((rows + rpb - 1) / rpb));
+  if (is_bf16) colsum_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, out, rows, cols, ld, rpb);
+  else colsum_kernel<float><<<grid, 128, 0, st>>>((const float*)x, out, rows, cols, ld, rpb);
+  return (int)cudaGetLastError();
+}
+
+// what: 0 sum, 1 sum of squares, 2 max, 3 min. `out` must be pre-initialised (0, 0, -inf, +inf).
+int b200_reduce(const void* x, float* out, long long n, int what, int is_bf16, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (is_bf16) reduce_kernel<__nv_bfloat16><<<grid_for(n, 256, 592), 256, 0, st>>>((const __nv_bfloat16*)x, out, n, what);
+  else reduce_kernel<float><<<grid_for(n, 256, 592), 256, 0, st>>>((const float*)x, out, n, what);
+  return (int)cudaGetLastError();
+}
+
+int b200_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, int is_bf16, cudaStream_t st) {
+  if (n <= 0) return 0;
+  float scale = p < 1.f ? 1.f / (1.f - p) : 0.f;
+  if (is_bf16) dropout_kernel<__nv_bfloat16><<<grid_for(n, 256), 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, n, p, scale, seed);
+  else dropout_kernel<float><<<grid_for(n, 256), 256, 0, st>>>((const float*)x, (float*)y, n, p, scale, seed);
+  return (int)cudaGetLastError();
+}
+
+int b200_fake_quant(const void* x, void* y, long long n, float scale, float qmin, float qmax, int is_bf16,
+                    cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (is_bf16) fake_quant_kernel<__nv_bfloat16><<<grid_for(n, 256), 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, n, scale, qmin, qmax);
+  else fake_quant_kernel<float><<<grid_for(n, 256), 256, 0, st>>>((const float*)x, (float*)y, n, scale, qmin, qmax);
+  return (int)cudaGetLastError();
+}
+
+int b200_embedding_fwd(const void* table, const long long* ids, void* out, long long tokens, int dim, long long vocab,
+                       int is_bf16, cudaStream_t st) {
+  if (tokens <= 0) return 0;
+  if (is_bf16) {
+    if (dim % 8) return -1;
+    embedding_fwd_kernel<__nv_bfloat16><<<grid_for(tokens * (dim / 8), 256), 256, 0, st>>>((const __nv_bfloat16*)table, ids, (__nv_bfloat16*)out, tokens, dim, vocab);
+  } else {
+    if (dim % 4) return -1;
+    embedding_fwd_kernel<float><<<grid_for(tokens * (dim / 4), 256), 256, 0, st>>>((const float*)table, ids, (float*)out, tokens, dim, vocab);
+  }
+  return (int)cudaGetLastError();
+}
+
+int b200_embedding_bwd(const void* g, const long long* ids, float* grad_table, long long tokens, int dim,
+                       long long vocab, int is_bf16, cudaStream_t st) {
+  if (tokens <= 0) return 0;
+  if (is_bf16) embedding_bwd_kernel<__nv_bfloat16><<<grid_for(tokens * dim, 256), 256, 0, st>>>((const __nv_bfloat16*)g, ids, grad_table, tokens, dim, vocab);
+  else embedding_bwd_kernel<float><<<grid_for(tokens * dim, 256), 256, 0, st>>>((const float*)g, ids, grad_table, tokens, dim, vocab);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -1,0 +1,412 @@
+// G1: persistent, warp-specialised tcgen05 GEMM for sm_100a.
+//
+//   C[b] = epilogue( alpha * A[b] * B[b]^T )          A: logical [M,K]   B: logical [N,K]
+//
+// Either operand may be K-major (stored [rows,K], K contiguous) or MN-major (stored [K,rows],
+// rows contiguous); the transposition is expressed in the TMA tensor map and the tensor-core
+// matrix descriptor, never as a copy. This is the same contract as the reference's packed CPU
+// GEMM, which folds transposes into packing (rust-nn src/blas.rs:104-186, 273-339), and it is the
+// one routine behind Linear forward (NT), dX (NN) and dW (TN) (src/tensor.rs:767-781, 1649-1687).
+//
+// Structure per CTA (192 threads, one CTA per SM, persistent over output tiles):
+//   warp 0    : TMA producer  - cp.async.bulk.tensor into a ring of 128B-swizzled stages
+//   warp 1    : MMA issuer    - one elected thread issues tcgen05.mma (128 x BN x 16), accumulators
+//                               live in TMEM, double-buffered so the epilogue overlaps the next tile
+//   warps 2-5 : epilogue      - tcgen05.ld TMEM -> registers, fused bias / activation / activation
+//                               gradient / residual, direct global stores (bf16, fp32 or fp32 atomic add
+//                               for split-K and gradient accumulation)
+// All waits are bounded; on expiry a code lands in the status word and the CTA unwinds.
+#include "../common/ptx.cuh"
+#include "../common/tensormap.h"
+#include "gemm_sm100.h"
+
+namespace b200 {
+
+constexpr int BM = 128;
+constexpr int GEMM_THREADS = 192;
+constexpr int TILE_K_BYTES = 128;  // one swizzle row
+constexpr int UMMA_K_BYTES = 32;
+
+template <typename T> struct ElemTraits;
+template <> struct ElemTraits<__nv_bfloat16> {
+  static constexpr int BK = 64;
+  static constexpr uint32_t FMT = FMT_BF16;
+  static constexpr bool TF32 = false;
+};
+template <> struct ElemTraits<float> {
+  static constexpr int BK = 32;
+  static constexpr uint32_t FMT = FMT_TF32;
+  static constexpr bool TF32 = true;
+};
+
+__device__ __forceinline__ float act_fwd(float v, int act) {
+  switch (act) {
+    case ACT_RELU: return v > 0.f ? v : 0.f;
+    case ACT_GELU: {
+      const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+      float u = k0 * (v + k1 * v * v * v);
+      return 0.5f * v * (1.f + tanhf(u));
+    }
+    case ACT_SILU: return v / (1.f + __expf(-v));
+    case ACT_SIGMOID: return 1.f / (1.f + __expf(-v));
+    case ACT_TANH: return tanhf(v);
+    default: return v;
+  }
+}
+// derivative of the activation, evaluated at the saved value `s`:
+// the pre-activation for GELU/SiLU, the output for ReLU/sigmoid/tanh.
+__device__ __forceinline__ float act_bwd(float s, int act) {
+  switch (act) {
+    case ACT_RELU: return s > 0.f ? 1.f : 0.f;
+    case ACT_GELU: {
+      const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+      float u = k0 * (s + k1 * s * s * s);
+      float t = tanhf(u);
+      float du = k0 * (1.f + 3.f * k1 * s * s);
+      return 0.5f * (1.f + t) + 0.5f * s * (1.f - t * t) * du;
+    }
+    case ACT_SILU: {
+      float sg = 1.f / (1.f + __expf(-s));
+      return sg * (1.f + s * (1.f - sg));
+    }
+    case ACT_SIGMOID: return s * (1.f - s);
+    case ACT_TANH: return 1.f - s * s;
+    default: return 1.f;
+  }
+}
+
+template <typename T, int BN, bool A_MN, bool B_MN>
+struct GemmSmem {
+  static constexpr int BK = ElemTraits<T>::BK;
+  static constexpr int A_BYTES = BM * TILE_K_BYTES;   // 16 KB
+  static constexpr int B_BYTES = BN * TILE_K_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BUDGET = 200 * 1024;
+  static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment
+};
+
+template <typename T, int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  using S = GemmSmem<T, BN, A_MN, B_MN>;
+  constexpr int BK = S::BK;
+  constexpr int STAGES = S::STAGES;
+  constexpr int ATOM = TILE_K_BYTES / sizeof(T);        // elements per 128-byte row
+  constexpr int UMMA_K = UMMA_K_BYTES / sizeof(T);
+  constexpr int K_STEPS = BK / UMMA_K;                  // 4
+  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+  uint64_t* full_bar = bars;                 // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;       // [STAGES]
+  uint64_t* acc_full = bars + 2 * STAGES;    // [2]
+  uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int m_blocks = (p.M + BM - 1) / BM;
+  const int n_blocks = (p.N + BN - 1) / BN;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int kb_per_split = (num_kb + p.splits - 1) / p.splits;
+  const long long tiles_per_batch = (long long)m_blocks * n_blocks * p.splits;
+  const long long total_tiles = tiles_per_batch * p.batch;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int b = (int)(t / tiles_per_batch);
+        long long r = t % tiles_per_batch;
+        const int split = (int)(r / ((long long)m_blocks * n_blocks));
+        r %= (long long)m_blocks * n_blocks;
+        const int mb = (int)(r / n_blocks), nb = (int)(r % n_blocks);
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(kb0 + kb_per_split, num_kb);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, ST_TIMEOUT_TMA_EMPTY)) { ok = false; break; }
+          uint8_t* sa = smem + stage * S::STAGE_BYTES;
+          uint8_t* sb = sa + S::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
+          if (!A_MN) {
+            tma_load_3d(sa, &tmA, &full_bar[stage], kb * BK, mb * BM, b);
+          } else {
+#pragma unroll
+            for (int a = 0; a < BM / ATOM; ++a)
+              tma_load_3d(sa + a * (BK * TILE_K_BYTES), &tmA, &full_bar[stage], mb * BM + a * ATOM, kb * BK, b);
+          }
+          if (!B_MN) {
+            tma_load_3d(sb, &tmB, &full_bar[stage], kb * BK, nb * BN, b);
+          } else {
+#pragma unroll
+            for (int a = 0; a < BN / ATOM; ++a)
+              tma_load_3d(sb + a * (BK * TILE_K_BYTES), &tmB, &full_bar[stage], nb * BN + a * ATOM, kb * BK, b);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN, CFMT_F32, ElemTraits<T>::FMT, ElemTraits<T>::FMT,
+                                            A_MN ? 1u : 0u, B_MN ? 1u : 0u);
+      // K-major: 8-row groups 1024 B apart.  MN-major: 8-k-row groups 1024 B apart, 128B-row atoms
+      // BK*128 B apart.
+      constexpr uint32_t A_LBO = A_MN ? BK * TILE_K_BYTES : 0, A_SBO = 1024;
+      constexpr uint32_t B_LBO = B_MN ? BK * TILE_K_BYTES : 0, B_SBO = 1024;
+      constexpr uint32_t A_KADV = A_MN ? UMMA_K * TILE_K_BYTES : UMMA_K_BYTES;
+      constexpr uint32_t B_KADV = B_MN ? UMMA_K * TILE_K_BYTES : UMMA_K_BYTES;
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      int it = 0;
+      for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+        long long r = t % tiles_per_batch;
+        const int split = (int)(r / ((long long)m_blocks * n_blocks));
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(kb0 + kb_per_split, num_kb);
+        const int as = it & 1;
+        const uint32_t aphase = (it >> 1) & 1;
+        if (!mbar_wait(&acc_empty[as], aphase ^ 1, p.status, ST_TIMEOUT_ACC_EMPTY)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + as * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, p.status, ST_TIMEOUT_TMA_FULL)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
+          const uint32_t sb = sa + S::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < K_STEPS; ++k) {
+            uint64_t da = make_sdesc_sw128(sa + k * A_KADV, A_LBO, A_SBO);
+            uint64_t db = make_sdesc_sw128(sb + k * B_KADV, B_LBO, B_SBO);
+            if (ElemTraits<T>::TF32) umma_tf32(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            else umma_f16(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);   // stage reusable once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) tc_commit(&acc_full[as]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int row_in_tile = q * 32 + lane;
+    bool ok = true;
+    int it = 0;
+    for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      const int b = (int)(t / tiles_per_batch);
+      long long r = t % tiles_per_batch;
+      const int split = (int)(r / ((long long)m_blocks * n_blocks));
+      r %= (long long)m_blocks * n_blocks;
+      const int mb = (int)(r / n_blocks), nb = (int)(r % n_blocks);
+      const int kb0 = split * kb_per_split;
+      const bool has_k = kb0 < min(kb0 + kb_per_split, num_kb);
+      const int as = it & 1;
+      const uint32_t aphase = (it >> 1) & 1;
+      if (!mbar_wait(&acc_full[as], aphase, p.status, ST_TIMEOUT_ACC_FULL)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int row = mb * BM + row_in_tile;
+      const bool row_ok = row < p.M;
+      const long long crow = (long long)b * p.strideC + (long long)row * p.ldc;
+      const long long rrow = (long long)b * p.strideR + (long long)row * p.ldr;
+      const bool first_split = (split == 0);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_x32(tmem_base + (uint32_t(q * 32) << 16) + as * BN + c * 32, v);
+        tmem_ld_wait();
+        const int col0 = nb * BN + c * 32;
+        if (!row_ok || col0 >= p.N) continue;
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = has_k ? __uint_as_float(v[j]) * p.alpha : 0.f;
+        const bool full = (col0 + 32 <= p.N);
+        if (p.bias && first_split) {
+          if (p.bias_f32) {
+            const float* bp = reinterpret_cast<const float*>(p.bias) + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (full || col0 + j < p.N) f[j] += __ldg(bp + j);
+          } else {
+            const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (full || col0 + j < p.N) f[j] += __bfloat162float(bp[j]);
+          }
+        }
+        const bool vec_ok = full && p.vec_ok;
+        if (p.aux_out) {
+          __nv_bfloat16* ap = reinterpret_cast<__nv_bfloat16*>(p.aux_out) + crow + col0;
+          if (vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 o = make_uint4(pack_bf16x2(f[j], f[j + 1]), pack_bf16x2(f[j + 2], f[j + 3]),
+                                   pack_bf16x2(f[j + 4], f[j + 5]), pack_bf16x2(f[j + 6], f[j + 7]));
+              *reinterpret_cast<uint4*>(ap + j) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (col0 + j < p.N) ap[j] = __float2bfloat16(f[j]);
+          }
+        }
+        if (p.act != ACT_NONE) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = act_fwd(f[j], p.act);
+        }
+        if (p.aux_in) {
+          const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + crow + col0;
+          if (vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 u = *reinterpret_cast<const uint4*>(ap + j);
+              float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y), a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
+              f[j] *= act_bwd(a0.x, p.dact); f[j + 1] *= act_bwd(a0.y, p.dact);
+              f[j + 2] *= act_bwd(a1.x, p.dact); f[j + 3] *= act_bwd(a1.y, p.dact);
+              f[j + 4] *= act_bwd(a2.x, p.dact); f[j + 5] *= act_bwd(a2.y, p.dact);
+              f[j + 6] *= act_bwd(a3.x, p.dact); f[j + 7] *= act_bwd(a3.y, p.dact);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (col0 + j < p.N) f[j] *= act_bwd(__bfloat162float(ap[j]), p.dact);
+          }
+        }
+        if (p.residual && first_split) {
+          const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(p.residual) + rrow + col0;
+          if (full && p.res_vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 u = *reinterpret_cast<const uint4*>(rp + j);
+              float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y), a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
+              f[j] += a0.x; f[j + 1] += a0.y; f[j + 2] += a1.x; f[j + 3] += a1.y;
+              f[j + 4] += a2.x; f[j + 5] += a2.y; f[j + 6] += a3.x; f[j + 7] += a3.y;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (col0 + j < p.N) f[j] += __bfloat162float(rp[j]);
+          }
+        }
+        if (p.out_mode == OUT_BF16) {
+          __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + crow + col0;
+          if (vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 o = make_uint4(pack_bf16x2(f[j], f[j + 1]), pack_bf16x2(f[j + 2], f[j + 3]),
+                                   pack_bf16x2(f[j + 4], f[j + 5]), pack_bf16x2(f[j + 6], f[j + 7]));
+              *reinterpret_cast<uint4*>(cp + j) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (col0 + j < p.N) cp[j] = __float2bfloat16(f[j]);
+          }
+        } else if (p.out_mode == OUT_F32) {
+          float* cp = reinterpret_cast<float*>(p.C) + crow + col0;
+          if (vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<float4*>(cp + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (col0 + j < p.N) cp[j] = f[j];
+          }
+        } else {  // OUT_F32_ATOMIC
+          float* cp = reinterpret_cast<float*>(p.C) + crow + col0;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) if (col0 + j < p.N) atomicAdd(cp + j, f[j]);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[as]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------- host side
+template <typename T> struct DT;
+template <> struct DT<__nv_bfloat16> { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; };
+template <> struct DT<float> { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; };
+
+template <typename T, int BN, bool A_MN, bool B_MN>
+static int launch_one(const GemmArgs& a, cudaStream_t stream, int num_sms) {
+  using S = GemmSmem<T, BN, A_MN, B_MN>;
+  constexpr int BK = S::BK;
+  constexpr int ATOM = TILE_K_BYTES / sizeof(T);
+  CUtensorMap tmA, tmB;
+  int rc;
+  // K-major: view [batch][rows][K], box {BK, rows_per_tile}. MN-major: view [batch][K][rows], box {ATOM, BK}.
+  if (!A_MN) rc = make_tmap_3d(&tmA, a.A, DT<T>::v, sizeof(T), a.K, a.M, a.batch, a.lda * sizeof(T), a.strideA * sizeof(T), BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  else       rc = make_tmap_3d(&tmA, a.A, DT<T>::v, sizeof(T), a.M, a.K, a.batch, a.lda * sizeof(T), a.strideA * sizeof(T), ATOM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return 100 + rc;
+  if (!B_MN) rc = make_tmap_3d(&tmB, a.B, DT<T>::v, sizeof(T), a.K, a.N, a.batch, a.ldb * sizeof(T), a.strideB * sizeof(T), BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+  else       rc = make_tmap_3d(&tmB, a.B, DT<T>::v, sizeof(T), a.N, a.K, a.batch, a.ldb * sizeof(T), a.strideB * sizeof(T), ATOM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return 200 + rc;
+
+  static bool attr_set = false;
+  auto kfn = gemm_kernel<T, BN, A_MN, B_MN>;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) return 300 + (int)e;
+    attr_set = true;
+  }
+  GemmParams p = a.p;
+  const long long m_blocks = (p.M + BM - 1) / BM, n_blocks = (p.N + BN - 1) / BN;
+  const long long tiles = m_blocks * n_blocks * p.splits * p.batch;
+  int grid = (int)(tiles < num_sms ? tiles : num_sms);
+  if (grid < 1) grid = 1;
+  kfn<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+template <typename T, int BN>
+static int launch_major(const GemmArgs& a, cudaStream_t s, int sms) {
+  if (!a.a_mn && !a.b_mn) return launch_one<T, BN, false, false>(a, s, sms);
+  if (!a.a_mn && a.b_mn) return launch_one<T, BN, false, true>(a, s, sms);
+  if (a.a_mn && !a.b_mn) return launch_one<T, BN, true, false>(a, s, sms);
+  return launch_one<T, BN, true, true>(a, s, sms);
+}
+
+}  // namespace b200
+
+extern "C" int b200_gemm_launch(const b200::GemmArgs* args, int bn, int num_sms, cudaStream_t stream) {
+  using namespace b200;
+  const GemmArgs& a = *args;
+  if (a.p.M <= 0 || a.p.N <= 0 || a.p.batch <= 0) return 0;
+  if (a.is_f32) {
+    return launch_major<float, 128>(a, stream, num_sms);
+  }
+  switch (bn) {
+    case 64: return launch_major<__nv_bfloat16, 64>(a, stream, num_sms);
+    case 128: return launch_major<__nv_bfloat16, 128>(a, stream, num_sms);
+    case 256: return launch_major<__nv_bfloat16, 256>(a, stream, num_sms);
+    default: return -2;
+  }
+}

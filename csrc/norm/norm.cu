@@ -1,0 +1,223 @@
+// N1 LayerNorm forward/backward (last axis, eps inside the sqrt, biased variance) and
+// N2 BatchNorm1D forward/backward with the full gradient and running statistics.
+// Math restates rust-nn src/tensor.rs:1013-1062 (forward), 1904-2001 (backward) and
+// src/nn.rs:342-388 (batch statistics, biased variance, eps 1e-5).
+//
+// LayerNorm: one warp per row, rows in a grid-stride loop; x is read once from HBM (the second
+// pass hits L1), statistics are fp32, gamma/beta are fp32. dgamma/dbeta are reduced in shared
+// memory per block and flushed with one fp32 atomic per column per block.
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+
+namespace b200 {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
+
+__device__ __forceinline__ float wsum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// two elements per lane per step -> 128-byte (bf16) / 256-byte (f32) warp transactions
+template <typename T> struct Pair;
+template <> struct Pair<float> { using V = float2;
+  static __device__ __forceinline__ float2 ld(const float* p) { return *reinterpret_cast<const float2*>(p); }
+  static __device__ __forceinline__ void st(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); } };
+template <> struct Pair<__nv_bfloat16> { using V = __nv_bfloat162;
+  static __device__ __forceinline__ float2 ld(const __nv_bfloat16* p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); }
+  static __device__ __forceinline__ void st(__nv_bfloat16* p, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b); } };
+
+template <typename T>
+__global__ void layernorm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
+                                     const float* __restrict__ beta, T* __restrict__ y, float* __restrict__ mean_out,
+                                     float* __restrict__ rstd_out, long long rows, int d, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  long long row = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const long long row_stride = (long long)gridDim.x * warps_per_block;
+  const bool even = (d % 2 == 0);
+  for (; row < rows; row += row_stride) {
+    const T* xr = x + row * d;
+    float s = 0.f;
+    if (even) { for (int c = 2 * lane; c < d; c += 64) { float2 v = Pair<T>::ld(xr + c); s += v.x + v.y; } }
+    else { for (int c = lane; c < d; c += 32) s += ldf(xr + c); }
+    const float mean = wsum(s) / d;
+    float q = 0.f;
+    if (even) { for (int c = 2 * lane; c < d; c += 64) { float2 v = Pair<T>::ld(xr + c); float a = v.x - mean, b = v.y - mean; q += a * a + b * b; } }
+    else { for (int c = lane; c < d; c += 32) { float a = ldf(xr + c) - mean; q += a * a; } }
+    const float rstd = rsqrtf(wsum(q) / d + eps);
+    T* yr = y + row * d;
+    if (even) {
+      for (int c = 2 * lane; c < d; c += 64) {
+        float2 v = Pair<T>::ld(xr + c);
+        float2 g = *reinterpret_cast<const float2*>(gamma + c);
+        float2 b = *reinterpret_cast<const float2*>(beta + c);
+        Pair<T>::st(yr + c, (v.x - mean) * rstd * g.x + b.x, (v.y - mean) * rstd * g.y + b.y);
+      }
+    } else {
+      for (int c = lane; c < d; c += 32) stf(yr + c, (ldf(xr + c) - mean) * rstd * gamma[c] + beta[c]);
+    }
+    if (lane == 0) { if (mean_out) mean_out[row] = mean; if (rstd_out) rstd_out[row] = rstd; }
+  }
+}
+
+template <typename T>
+__global__ void layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
+                                     const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                                     T* __restrict__ dx, float* __restrict__ dgamma, float* __restrict__ dbeta,
+                                     long long rows, int d) {
+  extern __shared__ float sh[];   // [2*d]: dgamma partial, dbeta partial
+  float* s_dg = sh; float* s_db = sh + d;
+  for (int c = threadIdx.x; c < 2 * d; c += blockDim.x) sh[c] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  long long row = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const long long row_stride = (long long)gridDim.x * warps_per_block;
+  for (; row < rows; row += row_stride) {
+    const T* xr = x + row * d; const T* gr = dy + row * d;
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float s1 = 0.f, s2 = 0.f;
+    for (int c = lane; c < d; c += 32) {
+      float xh = (ldf(xr + c) - mean) * rstd;
+      float g = ldf(gr + c);
+      float gg = g * gamma[c];
+      s1 += gg; s2 += gg * xh;
+      atomicAdd(&s_dg[c], g * xh);
+      atomicAdd(&s_db[c], g);
+    }
+    s1 = wsum(s1) / d; s2 = wsum(s2) / d;
+    T* dxr = dx + row * d;
+    for (int c = lane; c < d; c += 32) {
+      float xh = (ldf(xr + c) - mean) * rstd;
+      float gg = ldf(gr + c) * gamma[c];
+      stf(dxr + c, rstd * (gg - s1 - xh * s2));
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    atomicAdd(dgamma + c, s_dg[c]);
+    atomicAdd(dbeta + c, s_db[c]);
+  }
+}
+
+// ------------------------------------------------------------------ BatchNorm1D  x:[batch, n]
+// one thread per feature column; coalesced across threads for every row
+template <typename T>
+__global__ void batchnorm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
+                                     const float* __restrict__ beta, T* __restrict__ y, float* __restrict__ mean_out,
+                                     float* __restrict__ rstd_out, float* __restrict__ run_mean,
+                                     float* __restrict__ run_var, int batch, int n, float eps, float momentum,
+                                     int training) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= n) return;
+  float mean, rstd;
+  if (training) {
+    float s = 0.f;
+    for (int r = 0; r < batch; ++r) s += ldf(x + (long long)r * n + c);
+    mean = s / batch;
+    float q = 0.f;
+    for (int r = 0; r < batch; ++r) { float a = ldf(x + (long long)r * n + c) - mean; q += a * a; }
+    float var = q / batch;
+    rstd = rsqrtf(var + eps);
+    if (run_mean) {
+      run_mean[c] = (1.f - momentum) * run_mean[c] + momentum * mean;
+      float unb = batch > 1 ? var * batch / (batch - 1) : var;
+      run_var[c] = (1.f - momentum) * run_var[c] + momentum * unb;
+    }
+  } else {
+    mean = run_mean[c]; rstd = rsqrtf(run_var[c] + eps);
+  }
+  if (mean_out) { mean_out[c] = mean; rstd_out[c] = rstd; }
+  const float g = gamma[c], b = beta[c];
+  for (int r = 0; r < batch; ++r) {
+    long long i = (long long)r * n + c;
+    stf(y + i, (ldf(x + i) - mean) * rstd * g + b);
+  }
+}
+
+template <typename T>
+__global__ void batchnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
+                                     const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                                     T* __restrict__ dx, float* __restrict__ dgamma, float* __restrict__ dbeta,
+                                     int batch, int n, int training) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= n) return;
+  const float mean = mean_in[c], rstd = rstd_in[c], g = gamma[c];
+  float sg = 0.f, sgx = 0.f;
+  for (int r = 0; r < batch; ++r) {
+    long long i = (long long)r * n + c;
+    float gy = ldf(dy + i); float xh = (ldf(x + i) - mean) * rstd;
+    sg += gy; sgx += gy * xh;
+  }
+  dgamma[c] += sgx; dbeta[c] += sg;
+  for (int r = 0; r < batch; ++r) {
+    long long i = (long long)r * n + c;
+    float gy = ldf(dy + i); float xh = (ldf(x + i) - mean) * rstd;
+    float v = training ? g * rstd * (gy - sg / batch - xh * sgx / batch) : g * rstd * gy;
+    stf(dx + i, v);
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_layernorm_fwd(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd,
+                       long long rows, int d, float eps, int is_bf16, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  const int block = 256, wpb = block / 32;
+  long long g = (rows + wpb - 1) / wpb; if (g > 148 * 8) g = 148 * 8;
+  if (is_bf16) layernorm_fwd_kernel<__nv_bfloat16><<<(int)g, block, 0, st>>>((const __nv_bfloat16*)x, gamma, beta, (__nv_bfloat16*)y, mean, rstd, rows, d, eps);
+  else layernorm_fwd_kernel<float><<<(int)g, block, 0, st>>>((const float*)x, gamma, beta, (float*)y, mean, rstd, rows, d, eps);
+  return (int)cudaGetLastError();
+}
+
+// dgamma / dbeta are accumulated into (caller zero-initialises for a fresh gradient)
+int b200_layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
+                       void* dx, float* dgamma, float* dbeta, long long rows, int d, int is_bf16, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  const int block = 256, wpb = block / 32;
+  long long g = (rows + wpb - 1) / wpb; if (g > 148 * 2) g = 148 * 2;
+  size_t smem = 2 * (size_t)d * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e;
+    if (is_bf16) e = cudaFuncSetAttribute(layernorm_bwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    else e = cudaFuncSetAttribute(layernorm_bwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  if (is_bf16) layernorm_bwd_kernel<__nv_bfloat16><<<(int)g, block, smem, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, gamma, mean, rstd, (__nv_bfloat16*)dx, dgamma, dbeta, rows, d);
+  else layernorm_bwd_kernel<float><<<(int)g, block, smem, st>>>((const float*)dy, (const float*)x, gamma, mean, rstd, (float*)dx, dgamma, dbeta, rows, d);
+  return (int)cudaGetLastError();
+}
+
+int b200_batchnorm_fwd(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd,
+                       float* run_mean, float* run_var, int batch, int n, float eps, float momentum, int training,
+                       int is_bf16, cudaStream_t st) {
+  if (n <= 0 || batch <= 0) return 0;
+  int grid = (n + 127) / 128;
+  if (is_bf16) batchnorm_fwd_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, gamma, beta, (__nv_bfloat16*)y, mean, rstd, run_mean, run_var, batch, n, eps, momentum, training);
+  else batchnorm_fwd_kernel<float><<<grid, 128, 0, st>>>((const float*)x, gamma, beta, (float*)y, mean, rstd, run_mean, run_var, batch, n, eps, momentum, training);
+  return (int)cudaGetLastError();
+}
+
+int b200_batchnorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
+                       void* dx, float* dgamma, float* dbeta, int batch, int n, int training, int is_bf16,
+                       cudaStream_t st) {
+  if (n <= 0 || batch <= 0) return 0;
+  int grid = (n + 127) / 128;
+  if (is_bf16) batchnorm_bwd_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, gamma, mean, rstd, (__nv_bfloat16*)dx, dgamma, dbeta, batch, n, training);
+  else batchnorm_bwd_kernel<float><<<grid, 128, 0, st>>>((const float*)dy, (const float*)x, gamma, mean, rstd, (float*)dx, dgamma, dbeta, batch, n, training);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

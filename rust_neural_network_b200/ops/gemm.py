@@ -1,0 +1,217 @@
+"""GEMM front-end: the replacement for rust-nn's `blas::sgemm` (src/blas.rs:104-186).
+
+``gemm(a, b, ...)`` computes ``act(alpha * A @ B^T + bias) [* act'(aux_in)] [+ residual]`` where
+``A`` is logically ``[M, K]`` and ``B`` is logically ``[N, K]``. ``a_mn`` / ``b_mn`` say that the
+operand is *stored* transposed (``[K, M]`` / ``[K, N]``); no transposed copy is ever made - the
+layout goes into the TMA descriptor and the tensor-core matrix descriptor.
+
+On CUDA tensors this always launches the hand-written tcgen05 kernel (csrc/gemm/gemm_sm100.cu).
+On CPU tensors it evaluates the same expression with PyTorch in fp32 (the oracle).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from .. import _native as nv
+
+ACT = {"none": 0, "relu": 1, "gelu": 2, "silu": 3, "sigmoid": 4, "tanh": 5}
+OUT_BF16, OUT_F32, OUT_F32_ATOMIC = 0, 1, 2
+_NUM_SMS = {}
+
+
+def _num_sms(device) -> int:
+    idx = torch.device(device).index or 0
+    if idx not in _NUM_SMS:
+        _NUM_SMS[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _NUM_SMS[idx]
+
+
+def act_ref(x: torch.Tensor, act: str) -> torch.Tensor:
+    if act == "relu":
+        return torch.relu(x)
+    if act == "gelu":
+        return torch.nn.functional.gelu(x, approximate="tanh")
+    if act == "silu":
+        return torch.nn.functional.silu(x)
+    if act == "sigmoid":
+        return torch.sigmoid(x)
+    if act == "tanh":
+        return torch.tanh(x)
+    return x
+
+
+def dact_ref(saved: torch.Tensor, act: str) -> torch.Tensor:
+    """Derivative of `act` given the saved tensor (pre-activation for gelu/silu, output otherwise)."""
+    s = saved.float()
+    if act == "relu":
+        return (s > 0).float()
+    if act == "gelu":
+        k0, k1 = 0.7978845608028654, 0.044715
+        t = torch.tanh(k0 * (s + k1 * s ** 3))
+        return 0.5 * (1 + t) + 0.5 * s * (1 - t * t) * k0 * (1 + 3 * k1 * s * s)
+    if act == "silu":
+        sg = torch.sigmoid(s)
+        return sg * (1 + s * (1 - sg))
+    if act == "sigmoid":
+        return s * (1 - s)
+    if act == "tanh":
+        return 1 - s * s
+    return torch.ones_like(s)
+
+
+def gemm_ref(a, b, *, a_mn=False, b_mn=False, bias=None, act="none", residual=None, aux_in=None, dact="none",
+             alpha=1.0, out_dtype=None, accumulate_into=None, want_aux=False):
+    """fp32 PyTorch evaluation of the same expression (used on CPU and as the test oracle)."""
+    A = a.float().transpose(-1, -2) if a_mn else a.float()
+    B = b.float().transpose(-1, -2) if b_mn else b.float()
+    v = alpha * (A @ B.transpose(-1, -2))
+    if bias is not None:
+        v = v + bias.float()
+    pre = v
+    v = act_ref(v, act)
+    if aux_in is not None:
+        v = v * dact_ref(aux_in, dact)
+    if residual is not None:
+        v = v + residual.float()
+    if accumulate_into is not None:
+        accumulate_into.add_(v.to(accumulate_into.dtype))
+        v = accumulate_into
+    else:
+        v = v.to(out_dtype or a.dtype)
+    if want_aux:
+        return v, pre.to(a.dtype)
+    return v
+
+
+def _as3d(t: torch.Tensor):
+    if t.dim() == 2:
+        return t.unsqueeze(0)
+    if t.dim() == 3:
+        return t
+    raise ValueError("gemm operands must be 2-D or 3-D")
+
+
+def _tma_ready(t: torch.Tensor) -> torch.Tensor:
+    """Return `t` (3-D view) or a padded copy such that TMA constraints hold:
+    innermost stride 1, other strides multiples of 16 bytes, base 16-byte aligned."""
+    es = t.element_size()
+    q = 16 // es
+    ok = t.stride(-1) == 1 and t.stride(-2) % q == 0 and t.data_ptr() % 16 == 0 and t.stride(-2) >= t.shape[-1]
+    if ok and t.shape[0] > 1:
+        ok = t.stride(0) % q == 0
+    if ok:
+        return t
+    inner = (t.shape[-1] + q - 1) // q * q
+    buf = torch.zeros(t.shape[0], t.shape[1], inner, dtype=t.dtype, device=t.device)
+    buf[..., : t.shape[-1]].copy_(t)
+    return buf[..., : t.shape[-1]]
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias=None, act: str = "none",
+         residual=None, aux_in=None, dact: str = "none", want_aux: bool = False, alpha: float = 1.0,
+         out_dtype=None, accumulate_into=None, splits: int = 0, bn: int = 0):
+    """See module docstring. Returns C (and the bf16 pre-activation when ``want_aux``)."""
+    if not a.is_cuda:
+        return gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, act=act, residual=residual, aux_in=aux_in, dact=dact,
+                        alpha=alpha, out_dtype=out_dtype, accumulate_into=accumulate_into, want_aux=want_aux)
+    lib = nv.cuda()
+    if a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError(f"gemm operands must both be bf16 or both fp32 (got {a.dtype}, {b.dtype})")
+    is_f32 = a.dtype == torch.float32
+    squeeze = a.dim() == 2
+    a3, b3 = _tma_ready(_as3d(a)), _tma_ready(_as3d(b))
+    batch = a3.shape[0]
+    if b3.shape[0] != batch:
+        raise ValueError("batch mismatch")
+    M, K = (a3.shape[2], a3.shape[1]) if a_mn else (a3.shape[1], a3.shape[2])
+    N, Kb = (b3.shape[2], b3.shape[1]) if b_mn else (b3.shape[1], b3.shape[2])
+    if K != Kb:
+        raise ValueError(f"gemm K mismatch: {K} vs {Kb}")
+    dev = a.device
+    if accumulate_into is not None:
+        out = accumulate_into
+        if out.dtype != torch.float32 or not out.is_contiguous():
+            raise ValueError("accumulate_into must be a contiguous fp32 tensor")
+        out_mode = OUT_F32_ATOMIC
+    else:
+        odt = out_dtype or (torch.float32 if is_f32 else torch.bfloat16)
+        out_mode = OUT_F32 if odt == torch.float32 else OUT_BF16
+        out = None
+    # tile width and split-K
+    sms = _num_sms(dev)
+    if is_f32:
+        bn = 128
+    elif bn == 0:
+        if N <= 64:
+            bn = 64
+        elif N <= 128:
+            bn = 128
+        else:
+            t256 = math.ceil(M / 128) * math.ceil(N / 256) * batch
+            bn = 256 if t256 >= sms else 128
+    bk = 32 if is_f32 else 64
+    num_kb = max(1, math.ceil(K / bk))
+    tiles = math.ceil(M / 128) * math.ceil(N / bn) * batch
+    if splits == 0:
+        splits = 1
+        if out_mode != OUT_BF16 and tiles < sms // 2 and num_kb >= 16 and act == "none" and aux_in is None and not want_aux:
+            splits = max(1, min(sms // tiles, num_kb // 8))
+    if splits > 1:
+        per = math.ceil(num_kb / splits)
+        splits = math.ceil(num_kb / per)
+    if splits > 1:
+        if out_mode == OUT_BF16 or act != "none" or aux_in is not None or want_aux:
+            raise ValueError("split-K needs an fp32 output and a linear epilogue")
+        out_mode = OUT_F32_ATOMIC
+    if out is None:
+        shape = (batch, M, N)
+        odt = torch.float32 if out_mode != OUT_BF16 else torch.bfloat16
+        out = torch.zeros(shape, dtype=odt, device=dev) if out_mode == OUT_F32_ATOMIC else torch.empty(shape, dtype=odt, device=dev)
+    out3 = out if out.dim() == 3 else out.view(1, M, N) if batch == 1 else out.view(batch, M, N)
+    ldc = out3.stride(1)
+    aux = torch.empty((batch, M, N), dtype=torch.bfloat16, device=dev) if want_aux else None
+    if aux_in is not None:
+        aux_in = aux_in.contiguous().view(batch, M, N)
+        if aux_in.dtype != torch.bfloat16:
+            raise TypeError("aux_in must be bf16")
+    if residual is not None:
+        residual = residual.reshape(batch, M, N)
+        if residual.dtype != torch.bfloat16:
+            residual = residual.to(torch.bfloat16)
+        if residual.stride(-1) != 1:
+            residual = residual.contiguous()
+    if bias is not None and bias.dtype not in (torch.float32, torch.bfloat16):
+        raise TypeError("bias must be fp32 or bf16")
+
+    args = nv.GemmArgs()
+    p = args.p
+    p.M, p.N, p.K, p.batch, p.splits = M, N, K, batch, splits
+    p.C, p.ldc, p.strideC = out3.data_ptr(), ldc, out3.stride(0) if batch > 1 else M * ldc
+    p.bias = nv.ptr(bias); p.bias_f32 = 1 if (bias is not None and bias.dtype == torch.float32) else 0
+    p.residual = nv.ptr(residual)
+    p.ldr = residual.stride(1) if residual is not None else 0
+    p.strideR = residual.stride(0) if residual is not None else 0
+    p.aux_out = nv.ptr(aux); p.aux_in = nv.ptr(aux_in)
+    p.alpha = float(alpha); p.act = ACT[act]; p.dact = ACT[dact]; p.out_mode = out_mode
+    es_out = 4 if out_mode != OUT_BF16 else 2
+    aux_ok = (aux is None and aux_in is None) or (ldc == N and N % 8 == 0)
+    p.vec_ok = 1 if (ldc * es_out % 16 == 0 and out3.data_ptr() % 16 == 0 and (batch == 1 or p.strideC * es_out % 16 == 0) and aux_ok) else 0
+    if (aux is not None or aux_in is not None) and ldc != N:
+        raise ValueError("aux tensors need a dense output (ldc == N)")
+    p.res_vec_ok = 1 if (residual is not None and residual.stride(1) % 8 == 0 and residual.data_ptr() % 16 == 0 and (batch == 1 or residual.stride(0) % 8 == 0)) else 0
+    p.status = nv.status_word(dev).data_ptr()
+    args.A, args.lda, args.strideA, args.a_mn = a3.data_ptr(), a3.stride(1), a3.stride(0), int(a_mn)
+    args.B, args.ldb, args.strideB, args.b_mn = b3.data_ptr(), b3.stride(1), b3.stride(0), int(b_mn)
+    args.M, args.N, args.K, args.batch, args.is_f32 = M, N, K, batch, int(is_f32)
+    rc = lib.b200_gemm_launch(C.byref(args), bn, sms, nv.stream_ptr())
+    nv.check(rc, "b200_gemm_launch")
+    nv.count_launch()
+    res = out3[0] if (squeeze and out.dim() == 3) else out
+    if accumulate_into is not None:
+        res = accumulate_into
+    if want_aux:
+        return res, (aux[0] if squeeze else aux)
+    return res

@@ -1,0 +1,491 @@
+"""Raw (non-autograd) launchers for the elementwise / norm / loss / optimizer / attention kernels.
+
+Every function takes torch tensors, launches the sm_100a kernel on the current stream when the
+tensors live on a GPU, and otherwise evaluates a plain PyTorch fp32 reference of the same op
+(these references are also the oracles of the numerics tests).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from .. import _native as nv
+
+# op codes of csrc/elementwise/elementwise.cu
+OPS = {
+    "add": 0, "sub": 1, "mul": 2, "div": 3,
+    "relu": 10, "gelu": 11, "silu": 12, "sigmoid": 13, "tanh": 14, "softplus": 15,
+    "scale": 16, "exp": 17, "abs": 18, "square": 19, "clamp": 20, "round": 21, "add_scalar": 22,
+    "relu_bwd": 30, "gelu_bwd": 31, "silu_bwd": 32, "sigmoid_bwd": 33, "tanh_bwd": 34, "softplus_bwd": 35,
+    "mul_silu": 40,
+}
+
+
+def _isbf(t):
+    if t.dtype == torch.bfloat16:
+        return 1
+    if t.dtype == torch.float32:
+        return 0
+    raise TypeError(f"unsupported dtype {t.dtype}: kernels take bf16 or fp32")
+
+
+# ----------------------------------------------------------------------------- references
+def unary_ref(x, op, s0=0.0, s1=0.0):
+    f = x.float()
+    F = torch.nn.functional
+    r = {
+        "relu": lambda: torch.relu(f), "gelu": lambda: F.gelu(f, approximate="tanh"), "silu": lambda: F.silu(f),
+        "sigmoid": lambda: torch.sigmoid(f), "tanh": lambda: torch.tanh(f), "softplus": lambda: F.softplus(f, threshold=20.0),
+        "scale": lambda: f * s0, "exp": lambda: torch.exp(f), "abs": lambda: f.abs(), "square": lambda: f * f,
+        "clamp": lambda: f.clamp(s0, s1), "round": lambda: torch.round(f), "add_scalar": lambda: f + s0,
+    }[op]()
+    return r.to(x.dtype)
+
+
+def binary_ref(a, b, op):
+    from .gemm import dact_ref
+    fa, fb = a.float(), b.float()
+    if op == "add": r = fa + fb
+    elif op == "sub": r = fa - fb
+    elif op == "mul": r = fa * fb
+    elif op == "div": r = fa / fb
+    elif op == "relu_bwd": r = fa * (fb > 0)
+    elif op == "gelu_bwd": r = fa * dact_ref(fb, "gelu")
+    elif op == "silu_bwd": r = fa * dact_ref(fb, "silu")
+    elif op == "sigmoid_bwd": s = torch.sigmoid(fb); r = fa * s * (1 - s)
+    elif op == "tanh_bwd": t = torch.tanh(fb); r = fa * (1 - t * t)
+    elif op == "softplus_bwd": r = fa * torch.sigmoid(fb)
+    elif op == "mul_silu": r = fa * torch.nn.functional.silu(fb)
+    else: raise ValueError(op)
+    return r.to(a.dtype)
+
+
+# ----------------------------------------------------------------------------- elementwise
+def unary(x, op, s0=0.0, s1=0.0, out=None):
+    if not x.is_cuda:
+        return unary_ref(x, op, s0, s1)
+    x = x.contiguous()
+    y = torch.empty_like(x) if out is None else out
+    nv.check(nv.cuda().b200_unary(x.data_ptr(), y.data_ptr(), x.numel(), OPS[op], float(s0), float(s1), _isbf(x), nv.stream_ptr()), "unary")
+    nv.count_launch()
+    return y
+
+
+def binary(a, b, op, out=None):
+    """a (op) b; `b` may be a trailing-dims broadcast of `a` (e.g. a bias row)."""
+    if not a.is_cuda:
+        return binary_ref(a, b, op)
+    a = a.contiguous()
+    b = b.contiguous().to(a.dtype)
+    period = 0
+    if b.numel() != a.numel():
+        if a.numel() % max(b.numel(), 1) != 0 or tuple(a.shape[a.dim() - b.dim():]) != tuple(b.shape):
+            raise ValueError(f"cannot broadcast {tuple(b.shape)} onto {tuple(a.shape)} along trailing dims")
+        period = b.numel()
+    y = torch.empty_like(a) if out is None else out
+    nv.check(nv.cuda().b200_binary(a.data_ptr(), b.data_ptr(), y.data_ptr(), a.numel(), OPS[op], period, _isbf(a), nv.stream_ptr()), "binary")
+    nv.count_launch()
+    return y
+
+
+def cast(x, dtype, scale=1.0):
+    if x.dtype == dtype and scale == 1.0:
+        return x
+    if not x.is_cuda or {x.dtype, dtype} != {torch.float32, torch.bfloat16}:
+        return (x.float() * scale).to(dtype)
+    x = x.contiguous()
+    y = torch.empty(x.shape, dtype=dtype, device=x.device)
+    d = 0 if x.dtype == torch.float32 else 1
+    nv.check(nv.cuda().b200_cast(x.data_ptr(), y.data_ptr(), x.numel(), float(scale), d, nv.stream_ptr()), "cast")
+    nv.count_launch()
+    return y
+
+
+def colsum(x2d, out=None):
+    """fp32 column sums of a 2-D tensor (the bias gradient)."""
+    rows, cols = x2d.shape
+    if not x2d.is_cuda:
+        r = x2d.float().sum(0)
+        if out is not None:
+            out.add_(r); return out
+        return r
+    if x2d.stride(1) != 1:
+        x2d = x2d.contiguous()
+    if out is None:
+        out = torch.zeros(cols, dtype=torch.float32, device=x2d.device)
+    nv.check(nv.cuda().b200_colsum(x2d.data_ptr(), out.data_ptr(), rows, cols, x2d.stride(0), _isbf(x2d), nv.stream_ptr()), "colsum")
+    nv.count_launch()
+    return out
+
+
+def reduce_all(x, what="sum", out=None):
+    """Full reduction to a 0-d fp32 tensor: sum | sumsq | max | min."""
+    code = {"sum": 0, "sumsq": 1, "max": 2, "min": 3}[what]
+    if not x.is_cuda:
+        f = x.float()
+        return {"sum": f.sum, "sumsq": lambda: (f * f).sum(), "max": f.max, "min": f.min}[what]()
+    x = x.contiguous()
+    if out is None:
+        init = {0: 0.0, 1: 0.0, 2: -math.inf, 3: math.inf}[code]
+        out = torch.full((1,), init, dtype=torch.float32, device=x.device)
+    nv.check(nv.cuda().b200_reduce(x.data_ptr(), out.data_ptr(), x.numel(), code, _isbf(x), nv.stream_ptr()), "reduce")
+    nv.count_launch()
+    return out.view(())
+
+
+def dropout_mask_apply(x, p, seed):
+    if not x.is_cuda:
+        g = torch.Generator().manual_seed(int(seed) & 0x7FFFFFFF)
+        keep = (torch.rand(x.shape, generator=g) >= p).to(x.dtype)
+        return x * keep / max(1.0 - p, 1e-12) if p < 1 else torch.zeros_like(x)
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    nv.check(nv.cuda().b200_dropout(x.data_ptr(), y.data_ptr(), x.numel(), float(p), int(seed) & 0xFFFFFFFFFFFFFFFF, _isbf(x), nv.stream_ptr()), "dropout")
+    nv.count_launch()
+    return y
+
+
+def fake_quant(x, scale, qmin, qmax):
+    if not x.is_cuda:
+        return (torch.clamp(torch.round(x.float() / scale), qmin, qmax) * scale).to(x.dtype)
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    nv.check(nv.cuda().b200_fake_quant(x.data_ptr(), y.data_ptr(), x.numel(), float(scale), float(qmin), float(qmax), _isbf(x), nv.stream_ptr()), "fake_quant")
+    nv.count_launch()
+    return y
+
+
+def embedding_fwd(table, ids):
+    if not table.is_cuda:
+        return table[ids]
+    ids_c = ids.contiguous().view(-1).to(torch.int64)
+    out = torch.empty(ids_c.numel(), table.shape[1], dtype=table.dtype, device=table.device)
+    nv.check(nv.cuda().b200_embedding_fwd(table.data_ptr(), ids_c.data_ptr(), out.data_ptr(), ids_c.numel(), table.shape[1], table.shape[0], _isbf(table), nv.stream_ptr()), "embedding_fwd")
+    nv.count_launch()
+    return out.view(*ids.shape, table.shape[1])
+
+
+def embedding_bwd(grad_out, ids, vocab):
+    dim = grad_out.shape[-1]
+    g2 = grad_out.reshape(-1, dim)
+    if not grad_out.is_cuda:
+        gt = torch.zeros(vocab, dim, dtype=torch.float32)
+        gt.index_add_(0, ids.reshape(-1), g2.float())
+        return gt
+    g2 = g2.contiguous()
+    ids_c = ids.contiguous().view(-1).to(torch.int64)
+    gt = torch.zeros(vocab, dim, dtype=torch.float32, device=grad_out.device)
+    nv.check(nv.cuda().b200_embedding_bwd(g2.data_ptr(), ids_c.data_ptr(), gt.data_ptr(), ids_c.numel(), dim, vocab, _isbf(g2), nv.stream_ptr()), "embedding_bwd")
+    nv.count_launch()
+    return gt
+
+
+# ----------------------------------------------------------------------------- normalisation
+def layernorm_fwd(x2d, gamma, beta, eps):
+    rows, d = x2d.shape
+    if not x2d.is_cuda:
+        f = x2d.float()
+        mean = f.mean(1)
+        var = f.var(1, unbiased=False)
+        rstd = torch.rsqrt(var + eps)
+        y = (f - mean[:, None]) * rstd[:, None] * gamma.float() + beta.float()
+        return y.to(x2d.dtype), mean, rstd
+    x2d = x2d.contiguous()
+    y = torch.empty_like(x2d)
+    mean = torch.empty(rows, dtype=torch.float32, device=x2d.device)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x2d.device)
+    nv.check(nv.cuda().b200_layernorm_fwd(x2d.data_ptr(), gamma.data_ptr(), beta.data_ptr(), y.data_ptr(), mean.data_ptr(), rstd.data_ptr(), rows, d, float(eps), _isbf(x2d), nv.stream_ptr()), "layernorm_fwd")
+    nv.count_launch()
+    return y, mean, rstd
+
+
+def layernorm_bwd(dy2d, x2d, gamma, mean, rstd):
+    rows, d = x2d.shape
+    if not x2d.is_cuda:
+        xh = (x2d.float() - mean[:, None]) * rstd[:, None]
+        g = dy2d.float()
+        gg = g * gamma.float()
+        s1 = gg.mean(1, keepdim=True)
+        s2 = (gg * xh).mean(1, keepdim=True)
+        dx = rstd[:, None] * (gg - s1 - xh * s2)
+        return dx.to(x2d.dtype), (g * xh).sum(0), g.sum(0)
+    dy2d = dy2d.contiguous()
+    dx = torch.empty_like(x2d)
+    dgamma = torch.zeros(d, dtype=torch.float32, device=x2d.device)
+    dbeta = torch.zeros(d, dtype=torch.float32, device=x2d.device)
+    nv.check(nv.cuda().b200_layernorm_bwd(dy2d.data_ptr(), x2d.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), rows, d, _isbf(x2d), nv.stream_ptr()), "layernorm_bwd")
+    nv.count_launch()
+    return dx, dgamma, dbeta
+
+
+def batchnorm_fwd(x2d, gamma, beta, run_mean, run_var, eps, momentum, training):
+    batch, n = x2d.shape
+    if not x2d.is_cuda:
+        f = x2d.float()
+        if training:
+            mean = f.mean(0); var = f.var(0, unbiased=False)
+            if run_mean is not None:
+                run_mean.mul_(1 - momentum).add_(momentum * mean)
+                unb = var * batch / (batch - 1) if batch > 1 else var
+                run_var.mul_(1 - momentum).add_(momentum * unb)
+        else:
+            mean, var = run_mean, run_var
+        rstd = torch.rsqrt(var + eps)
+        return ((f - mean) * rstd * gamma + beta).to(x2d.dtype), mean, rstd
+    x2d = x2d.contiguous()
+    y = torch.empty_like(x2d)
+    mean = torch.empty(n, dtype=torch.float32, device=x2d.device)
+    rstd = torch.empty(n, dtype=torch.float32, device=x2d.device)
+    nv.check(nv.cuda().b200_batchnorm_fwd(x2d.data_ptr(), gamma.data_ptr(), beta.data_ptr(), y.data_ptr(), mean.data_ptr(), rstd.data_ptr(), nv.ptr(run_mean), nv.ptr(run_var), batch, n, float(eps), float(momentum), int(training), _isbf(x2d), nv.stream_ptr()), "batchnorm_fwd")
+    nv.count_launch()
+    return y, mean, rstd
+
+
+def batchnorm_bwd(dy2d, x2d, gamma, mean, rstd, training):
+    batch, n = x2d.shape
+    if not x2d.is_cuda:
+        g = dy2d.float(); xh = (x2d.float() - mean) * rstd
+        dgamma = (g * xh).sum(0); dbeta = g.sum(0)
+        if training:
+            dx = gamma * rstd * (g - dbeta / batch - xh * dgamma / batch)
+        else:
+            dx = gamma * rstd * g
+        return dx.to(x2d.dtype), dgamma, dbeta
+    dy2d = dy2d.contiguous()
+    dx = torch.empty_like(x2d)
+    dgamma = torch.zeros(n, dtype=torch.float32, device=x2d.device)
+    dbeta = torch.zeros(n, dtype=torch.float32, device=x2d.device)
+    nv.check(nv.cuda().b200_batchnorm_bwd(dy2d.data_ptr(), x2d.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), batch, n, int(training), _isbf(x2d), nv.stream_ptr()), "batchnorm_bwd")
+    nv.count_launch()
+    return dx, dgamma, dbeta
+
+
+# ----------------------------------------------------------------------------- losses
+def ce_label(logits2d, labels, want_grad=True):
+    """Mean cross-entropy over rows with integer labels; returns (loss 0-d fp32, dlogits or None).
+    dlogits already carries the 1/rows factor."""
+    rows, V = logits2d.shape
+    if not logits2d.is_cuda:
+        f = logits2d.float()
+        lse = torch.logsumexp(f, 1)
+        valid = (labels >= 0) & (labels < V)
+        safe = labels.clamp(0, V - 1)
+        l = (lse - f.gather(1, safe[:, None])[:, 0]) * valid
+        grad = None
+        if want_grad:
+            grad = torch.softmax(f, 1)
+            grad[torch.arange(rows), safe] -= 1
+            grad = (grad * valid[:, None] / rows).to(logits2d.dtype)
+        return l.sum() / rows, grad
+    if logits2d.stride(1) != 1:
+        logits2d = logits2d.contiguous()
+    labels = labels.contiguous().to(torch.int64)
+    grad = torch.empty((rows, V), dtype=logits2d.dtype, device=logits2d.device) if want_grad else None
+    if grad is not None and logits2d.stride(0) != V:
+        logits2d = logits2d.contiguous()
+    loss = torch.zeros(1, dtype=torch.float32, device=logits2d.device)
+    nv.check(nv.cuda().b200_ce_label(logits2d.data_ptr(), labels.data_ptr(), nv.ptr(grad), 0, loss.data_ptr(), rows, V, logits2d.stride(0), 1.0 / rows, 1.0 / rows, _isbf(logits2d), nv.stream_ptr()), "ce_label")
+    nv.count_launch()
+    return loss.view(()), grad
+
+
+def ce_dense(logits2d, target2d, want_grad=True):
+    rows, V = logits2d.shape
+    if not logits2d.is_cuda:
+        f, t = logits2d.float(), target2d.float()
+        p = torch.softmax(f, 1)
+        l = -(t * torch.log(p.clamp_min(1e-12))).sum() / rows
+        grad = ((p * t.sum(1, keepdim=True) - t) / rows).to(logits2d.dtype) if want_grad else None
+        return l, grad
+    logits2d = logits2d.contiguous(); target2d = target2d.contiguous().to(logits2d.dtype)
+    grad = torch.empty_like(logits2d) if want_grad else None
+    loss = torch.zeros(1, dtype=torch.float32, device=logits2d.device)
+    nv.check(nv.cuda().b200_ce_dense(logits2d.data_ptr(), target2d.data_ptr(), nv.ptr(grad), loss.data_ptr(), rows, V, 1.0 / rows, 1.0 / rows, _isbf(logits2d), nv.stream_ptr()), "ce_dense")
+    nv.count_launch()
+    return loss.view(()), grad
+
+
+LOSS_KIND = {"mse": 0, "l1": 1, "huber": 2, "bce": 3, "bce_logits": 4}
+
+
+def pointwise_loss(pred, target, kind, delta=1.0, reduction="mean", want_grad=True):
+    n = pred.numel()
+    scale = 1.0 / n if reduction == "mean" else 1.0
+    if not pred.is_cuda:
+        p, t = pred.float(), target.float()
+        d = p - t
+        if kind == "mse": l = d * d; g = 2 * d
+        elif kind == "l1": l = d.abs(); g = torch.sign(d)
+        elif kind == "huber":
+            small = d.abs() <= delta
+            l = torch.where(small, 0.5 * d * d, delta * (d.abs() - 0.5 * delta)); g = torch.where(small, d, delta * torch.sign(d))
+        elif kind == "bce":
+            pc = p.clamp(1e-12, 1 - 1e-12); l = -(t * torch.log(pc) + (1 - t) * torch.log(1 - pc)); g = (pc - t) / (pc * (1 - pc))
+        else:
+            l = torch.clamp(p, min=0) - p * t + torch.log1p(torch.exp(-p.abs())); g = torch.sigmoid(p) - t
+        return l.sum() * scale, ((g * scale).to(pred.dtype) if want_grad else None)
+    pred = pred.contiguous(); target = target.contiguous().to(pred.dtype)
+    grad = torch.empty_like(pred) if want_grad else None
+    loss = torch.zeros(1, dtype=torch.float32, device=pred.device)
+    nv.check(nv.cuda().b200_pointwise_loss(pred.data_ptr(), target.data_ptr(), nv.ptr(grad), loss.data_ptr(), n, LOSS_KIND[kind], float(delta), scale, scale, _isbf(pred), nv.stream_ptr()), "pointwise_loss")
+    nv.count_launch()
+    return loss.view(()), grad
+
+
+# ----------------------------------------------------------------------------- attention
+def _attn_tensor(t):
+    # t: [B, S, H, hd] view with unit stride on hd
+    a = nv.AttnTensor()
+    a.ptr, a.sb, a.ss, a.sh = t.data_ptr(), t.stride(0), t.stride(1), t.stride(2)
+    return a
+
+
+def _attn_ok(t):
+    return t.stride(3) == 1 and all(s % 8 == 0 for s in (t.stride(0), t.stride(1), t.stride(2))) and t.data_ptr() % 16 == 0
+
+
+def attention_ref(q, k, v, scale, causal):
+    """Dense fp32 softmax attention on [B, S, H, hd] tensors."""
+    qf, kf, vf = (t.float().permute(0, 2, 1, 3) for t in (q, k, v))
+    s = qf @ kf.transpose(-1, -2) * scale
+    if causal:
+        Sq, Sk = s.shape[-2:]
+        mask = torch.ones(Sq, Sk, dtype=torch.bool, device=s.device).tril()
+        s = s.masked_fill(~mask, float("-inf"))
+    p = torch.softmax(s, -1)
+    return (p @ vf).permute(0, 2, 1, 3)
+
+
+def flash_fwd(q, k, v, scale, causal):
+    """q,k,v: [B, S, H, hd] bf16 views (hd contiguous). Returns (o [B,S,H,hd] bf16, lse [B,H,S] fp32)."""
+    B, Sq, H, hd = q.shape
+    Skv = k.shape[1]
+    if not q.is_cuda:
+        o = attention_ref(q, k, v, scale, causal)
+        return o.to(q.dtype), None
+    if q.dtype != torch.bfloat16:
+        raise TypeError("flash attention kernels take bf16")
+    q, k, v = (t if _attn_ok(t) else t.contiguous() for t in (q, k, v))
+    o = torch.empty((B, Sq, H, hd), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
+    a = nv.FlashArgs()
+    a.q, a.k, a.v, a.o = _attn_tensor(q), _attn_tensor(k), _attn_tensor(v), _attn_tensor(o)
+    a.lse = lse.data_ptr()
+    a.B, a.H, a.Sq, a.Skv, a.hd = B, H, Sq, Skv, hd
+    a.scale, a.causal = float(scale), int(causal)
+    a.status = nv.status_word(q.device).data_ptr()
+    nv.check(nv.cuda().b200_flash_fwd(C.byref(a), nv.stream_ptr()), "flash_fwd")
+    nv.count_launch()
+    return o, lse
+
+
+def flash_bwd(dout, q, k, v, o, lse, scale, causal, dq=None, dk=None, dv=None):
+    """Gradients of flash_fwd. dq/dk/dv may be preallocated strided views (e.g. slices of a fused dQKV)."""
+    B, Sq, H, hd = q.shape
+    Skv = k.shape[1]
+    dev = q.device
+    dout = dout if _attn_ok(dout) else dout.contiguous()
+    if dq is None: dq = torch.empty((B, Sq, H, hd), dtype=torch.bfloat16, device=dev)
+    if dk is None: dk = torch.empty((B, Skv, H, hd), dtype=torch.bfloat16, device=dev)
+    if dv is None: dv = torch.empty((B, Skv, H, hd), dtype=torch.bfloat16, device=dev)
+    delta = torch.empty((B, H, Sq), dtype=torch.float32, device=dev)
+    dq_accum = torch.empty((B, Sq, H, hd), dtype=torch.float32, device=dev)
+    a = nv.FlashArgs()
+    a.q, a.k, a.v, a.o = _attn_tensor(q), _attn_tensor(k), _attn_tensor(v), _attn_tensor(o)
+    a.dout, a.dq, a.dk, a.dv = _attn_tensor(dout), _attn_tensor(dq), _attn_tensor(dk), _attn_tensor(dv)
+    a.lse, a.delta, a.dq_accum = lse.data_ptr(), delta.data_ptr(), dq_accum.data_ptr()
+    a.B, a.H, a.Sq, a.Skv, a.hd = B, H, Sq, Skv, hd
+    a.scale, a.causal = float(scale), int(causal)
+    a.status = nv.status_word(dev).data_ptr()
+    nv.check(nv.cuda().b200_flash_bwd(C.byref(a), nv.stream_ptr()), "flash_bwd")
+    nv.count_launch(4)
+    return dq, dk, dv
+
+
+# ----------------------------------------------------------------------------- optimizers (flat buffers)
+def adam_step(p, g, m, v, shadow, lr, b1, b2, eps, weight_decay, torch_form, step_t, grad_scale=None):
+    """One fused Adam step over flat fp32 buffers; `step_t` is a 1-element fp32 device tensor holding
+    the number of steps taken so far (incremented here)."""
+    if not p.is_cuda:
+        t = float(step_t.item()) + 1.0
+        gs = float(grad_scale.item()) if grad_scale is not None else 1.0
+        gg = g * gs
+        if weight_decay:
+            p.mul_(1 - lr * weight_decay)
+        m.mul_(b1).add_(gg, alpha=1 - b1)
+        v.mul_(b2).addcmul_(gg, gg, value=1 - b2)
+        bc1, bc2 = 1 - b1 ** t, 1 - b2 ** t
+        if torch_form:
+            p.addcdiv_(m, (v.sqrt() / math.sqrt(bc2)).add_(eps), value=-lr / bc1)
+        else:
+            p.addcdiv_(m, v.sqrt().add_(eps), value=-lr * math.sqrt(bc2) / bc1)
+        if shadow is not None:
+            shadow.copy_(p)
+        step_t.add_(1.0)
+        return
+    lib = nv.cuda()
+    nv.check(lib.b200_adam(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), nv.ptr(shadow), p.numel(), lr, b1, b2, eps, weight_decay, int(torch_form), step_t.data_ptr(), nv.ptr(grad_scale), nv.stream_ptr()), "adam")
+    nv.check(lib.b200_incr_step(step_t.data_ptr(), nv.stream_ptr()), "incr_step")
+    nv.count_launch(2)
+
+
+def sgd_step(p, g, buf, shadow, lr, momentum, step_t, grad_scale=None):
+    if not p.is_cuda:
+        gs = float(grad_scale.item()) if grad_scale is not None else 1.0
+        gg = g * gs
+        if buf is not None and momentum != 0.0:
+            if float(step_t.item()) == 0.0: buf.copy_(gg)
+            else: buf.mul_(momentum).add_(gg)
+            gg = buf
+        p.add_(gg, alpha=-lr)
+        if shadow is not None: shadow.copy_(p)
+        step_t.add_(1.0)
+        return
+    lib = nv.cuda()
+    nv.check(lib.b200_sgd(p.data_ptr(), g.data_ptr(), nv.ptr(buf), nv.ptr(shadow), p.numel(), lr, momentum, step_t.data_ptr(), nv.ptr(grad_scale), nv.stream_ptr()), "sgd")
+    nv.check(lib.b200_incr_step(step_t.data_ptr(), nv.stream_ptr()), "incr_step")
+    nv.count_launch(2)
+
+
+def rmsprop_step(p, g, v, shadow, lr, alpha, eps, grad_scale=None):
+    if not p.is_cuda:
+        gs = float(grad_scale.item()) if grad_scale is not None else 1.0
+        gg = g * gs
+        v.mul_(alpha).addcmul_(gg, gg, value=1 - alpha)
+        p.addcdiv_(gg, v.sqrt().add_(eps), value=-lr)
+        if shadow is not None: shadow.copy_(p)
+        return
+    nv.check(nv.cuda().b200_rmsprop(p.data_ptr(), g.data_ptr(), v.data_ptr(), nv.ptr(shadow), p.numel(), lr, alpha, eps, nv.ptr(grad_scale), nv.stream_ptr()), "rmsprop")
+    nv.count_launch()
+
+
+def muon_rms_step(p, g, buf, shadow, seg_off, lr, momentum, eps=1e-8, scratch=None):
+    """Reference-variant Muon: per-tensor RMS-normalised gradient then momentum SGD. `seg_off` is an
+    int64 tensor of nseg+1 offsets delimiting the tensors inside the flat buffers."""
+    nseg = seg_off.numel() - 1
+    if not p.is_cuda:
+        offs = seg_off.tolist()
+        for s in range(nseg):
+            a, b = offs[s], offs[s + 1]
+            gg = g[a:b]
+            rms = max(float((gg * gg).mean().sqrt()), eps) if b > a else 1.0
+            buf[a:b].mul_(momentum).add_(gg / rms)
+            p[a:b].add_(buf[a:b], alpha=-lr)
+        if shadow is not None: shadow.copy_(p)
+        return
+    if scratch is None:
+        scratch = torch.empty(nseg, dtype=torch.float32, device=p.device)
+    nv.check(nv.cuda().b200_muon_rms(p.data_ptr(), g.data_ptr(), buf.data_ptr(), nv.ptr(shadow), seg_off.data_ptr(), nseg, scratch.data_ptr(), lr, momentum, eps, nv.stream_ptr()), "muon_rms")
+    nv.count_launch(3)
+
+
+def clip_coef(scalars, max_norm):
+    """scalars[0] = sum of squared grads -> scalars[1] = min(1, max_norm/(norm+1e-6)), scalars[2] = norm."""
+    if not scalars.is_cuda:
+        norm = float(scalars[0].sqrt())
+        scalars[1] = min(1.0, max_norm / (norm + 1e-6)); scalars[2] = norm
+        return
+    nv.check(nv.cuda().b200_clip_coef(scalars.data_ptr(), float(max_norm), nv.stream_ptr()), "clip_coef")
+    nv.count_launch()

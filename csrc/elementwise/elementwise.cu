@@ -41,6 +41,7 @@ enum : int {
   // backward of a unary op: out = g * f'(saved); saved is the INPUT of the forward op
   OP_RELU_BWD = 30, OP_GELU_BWD = 31, OP_SILU_BWD = 32, OP_SIGMOID_BWD = 33, OP_TANH_BWD = 34, OP_SOFTPLUS_BWD = 35,
   // fused: out = a * silu(b)  (Mamba gate) and its two gradients
+  OP_SIGMOID_BWD_OUT = 36, OP_TANH_BWD_OUT = 37,
   OP_MUL_SILU = 40,
 };
 
@@ -74,6 +75,8 @@ __device__ __forceinline__ float binary_apply(float a, float b, int op) {
     case OP_SIGMOID_BWD: { float sg = 1.f / (1.f + __expf(-b)); return a * sg * (1.f - sg); }
     case OP_TANH_BWD: { float t = tanhf(b); return a * (1.f - t * t); }
     case OP_SOFTPLUS_BWD: return a / (1.f + __expf(-b));
+    case OP_SIGMOID_BWD_OUT: return a * b * (1.f - b);
+    case OP_TANH_BWD_OUT: return a * (1.f - b * b);
     case OP_MUL_SILU: return a * b / (1.f + __expf(-b));
     default: return a;
   }
@@ -114,6 +117,14 @@ __global__ void binary_kernel(const T* __restrict__ a, const T* __restrict__ b, 
     }
     long long tail = nv * N + i;
     if (tail < n) y[tail] = from_f<T>(binary_apply(to_f(a[tail]), to_f(b[tail]), op));
+  } else if (b_period % N == 0 && n % N == 0) {
+    long long nv = n / N;
+    for (long long k = i; k < nv; k += stride) {
+      P pa = reinterpret_cast<const P*>(a)[k], pb = reinterpret_cast<const P*>(b)[(k * N % b_period) / N], out;
+#pragma unroll
+      for (int j = 0; j < N; ++j) out.v[j] = from_f<T>(binary_apply(to_f(pa.v[j]), to_f(pb.v[j]), op));
+      reinterpret_cast<P*>(y)[k] = out;
+    }
   } else {
     for (long long k = i; k < n; k += stride)
       y[k] = from_f<T>(binary_apply(to_f(a[k]), to_f(b[k % b_period]), op));
@@ -237,6 +248,25 @@ __global__ void embedding_bwd_kernel(const T* __restrict__ g, const long long* _
   }
 }
 
+// out[c, r] = in[r, c] for a batch of row-major matrices (32x32 tiles through shared memory)
+template <typename T>
+__global__ void transpose_kernel(const T* __restrict__ in, T* __restrict__ out, int rows, int cols, long long ld_in,
+                                 long long ld_out, long long bs_in, long long bs_out) {
+  __shared__ T tile[32][33];
+  const T* src = in + blockIdx.z * bs_in; T* dst = out + blockIdx.z * bs_out;
+  int c = blockIdx.x * 32 + threadIdx.x;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    int r = blockIdx.y * 32 + j;
+    if (r < rows && c < cols) tile[j][threadIdx.x] = src[(long long)r * ld_in + c];
+  }
+  __syncthreads();
+  int r2 = blockIdx.y * 32 + threadIdx.x;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    int c2 = blockIdx.x * 32 + j;
+    if (r2 < rows && c2 < cols) dst[(long long)c2 * ld_out + r2] = tile[threadIdx.x][j];
+  }
+}
+
 static inline int grid_for(long long work, int block, int max_blocks = 148 * 16) {
   long long g = (work + block - 1) / block;
   if (g < 1) g = 1;
@@ -260,7 +290,8 @@ int b200_unary(const void* x, void* y, long long n, int op, float s0, float s1, 
 int b200_binary(const void* a, const void* b, void* y, long long n, int op, long long b_period, int is_bf16,
                 cudaStream_t st) {
   if (n <= 0) return 0;
-  long long work = b_period ? n : n / (is_bf16 ? 8 : 4) + 1;
+  const int vw = is_bf16 ? 8 : 4;
+  long long work = (b_period && (b_period % vw || n % vw)) ? n : n / vw + 1;
   if (is_bf16) binary_kernel<__nv_bfloat16><<<grid_for(work, 256), 256, 0, st>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, n, op, b_period);
   else binary_kernel<float><<<grid_for(work, 256), 256, 0, st>>>((const float*)a, (const float*)b, (float*)y, n, op, b_period);
   return (int)cudaGetLastError();
@@ -305,6 +336,15 @@ int b200_fake_quant(const void* x, void* y, long long n, float scale, float qmin
   if (n <= 0) return 0;
   if (is_bf16) fake_quant_kernel<__nv_bfloat16><<<grid_for(n, 256), 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, n, scale, qmin, qmax);
   else fake_quant_kernel<float><<<grid_for(n, 256), 256, 0, st>>>((const float*)x, (float*)y, n, scale, qmin, qmax);
+  return (int)cudaGetLastError();
+}
+
+int b200_transpose(const void* in, void* out, int rows, int cols, long long ld_in, long long ld_out, long long bs_in,
+                   long long bs_out, int batch, int is_bf16, cudaStream_t st) {
+  if (rows <= 0 || cols <= 0 || batch <= 0) return 0;
+  dim3 grid((cols + 31) / 32, (rows + 31) / 32, batch), block(32, 8);
+  if (is_bf16) transpose_kernel<__nv_bfloat16><<<grid, block, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, rows, cols, ld_in, ld_out, bs_in, bs_out);
+  else transpose_kernel<float><<<grid, block, 0, st>>>((const float*)in, (float*)out, rows, cols, ld_in, ld_out, bs_in, bs_out);
   return (int)cudaGetLastError();
 }
 

@@ -401,7 +401,10 @@ extern "C" int b200_gemm_launch(const b200::GemmArgs* args, int bn, int num_sms,
   const GemmArgs& a = *args;
   if (a.p.M <= 0 || a.p.N <= 0 || a.p.batch <= 0) return 0;
   if (a.is_f32) {
-    return launch_major<float, 128>(a, stream, num_sms);
+    // TF32 runs K-major only: MN-major 32-bit operands need a different swizzle atom, so the
+    // front-end hands this path explicitly transposed operands (b200_transpose below).
+    if (a.a_mn || a.b_mn) return -4;
+    return launch_one<float, 128, false, false>(a, stream, num_sms);
   }
   switch (bn) {
     case 64: return launch_major<__nv_bfloat16, 64>(a, stream, num_sms);

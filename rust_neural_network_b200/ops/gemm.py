@@ -121,6 +121,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float32):
         raise TypeError(f"gemm operands must both be bf16 or both fp32 (got {a.dtype}, {b.dtype})")
     is_f32 = a.dtype == torch.float32
+    if is_f32 and (a_mn or b_mn):
+        # TF32 tiles are K-major only; 32-bit MN-major operands are transposed by a kernel first
+        from .kernels import transpose_last2
+        if a_mn:
+            a, a_mn = transpose_last2(a), False
+        if b_mn:
+            b, b_mn = transpose_last2(b), False
     squeeze = a.dim() == 2
     a3, b3 = _tma_ready(_as3d(a)), _tma_ready(_as3d(b))
     batch = a3.shape[0]

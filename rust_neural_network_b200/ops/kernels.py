@@ -19,7 +19,7 @@ OPS = {
     "relu": 10, "gelu": 11, "silu": 12, "sigmoid": 13, "tanh": 14, "softplus": 15,
     "scale": 16, "exp": 17, "abs": 18, "square": 19, "clamp": 20, "round": 21, "add_scalar": 22,
     "relu_bwd": 30, "gelu_bwd": 31, "silu_bwd": 32, "sigmoid_bwd": 33, "tanh_bwd": 34, "softplus_bwd": 35,
-    "mul_silu": 40,
+    "sigmoid_bwd_out": 36, "tanh_bwd_out": 37, "mul_silu": 40,
 }
 
 
@@ -57,6 +57,8 @@ def binary_ref(a, b, op):
     elif op == "sigmoid_bwd": s = torch.sigmoid(fb); r = fa * s * (1 - s)
     elif op == "tanh_bwd": t = torch.tanh(fb); r = fa * (1 - t * t)
     elif op == "softplus_bwd": r = fa * torch.sigmoid(fb)
+    elif op == "sigmoid_bwd_out": r = fa * fb * (1 - fb)
+    elif op == "tanh_bwd_out": r = fa * (1 - fb * fb)
     elif op == "mul_silu": r = fa * torch.nn.functional.silu(fb)
     else: raise ValueError(op)
     return r.to(a.dtype)
@@ -101,6 +103,20 @@ def cast(x, dtype, scale=1.0):
     nv.check(nv.cuda().b200_cast(x.data_ptr(), y.data_ptr(), x.numel(), float(scale), d, nv.stream_ptr()), "cast")
     nv.count_launch()
     return y
+
+
+def transpose_last2(x):
+    """Materialised transpose of the last two dims of a 2-D / 3-D tensor (row-major result)."""
+    if not x.is_cuda:
+        return x.transpose(-1, -2).contiguous()
+    x3 = x if x.dim() == 3 else x.unsqueeze(0)
+    if x3.stride(-1) != 1:
+        x3 = x3.contiguous()
+    b, r, c = x3.shape
+    out = torch.empty((b, c, r), dtype=x.dtype, device=x.device)
+    nv.check(nv.cuda().b200_transpose(x3.data_ptr(), out.data_ptr(), r, c, x3.stride(1), r, x3.stride(0), c * r, b, _isbf(x), nv.stream_ptr()), "transpose")
+    nv.count_launch()
+    return out if x.dim() == 3 else out[0]
 
 
 def colsum(x2d, out=None):

@@ -213,6 +213,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const float alpha = p.alpha_ptr ? p.alpha * __ldg(p.alpha_ptr) : p.alpha;
     const int row_in_tile = q * 32 + lane;
     bool ok = true;
     int it = 0;
@@ -242,7 +243,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (!row_ok || col0 >= p.N) continue;
         float f[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) f[j] = has_k ? __uint_as_float(v[j]) * p.alpha : 0.f;
+        for (int j = 0; j < 32; ++j) f[j] = has_k ? __uint_as_float(v[j]) * alpha : 0.f;
         const bool full = (col0 + 32 <= p.N);
         if (p.bias && first_split) {
           if (p.bias_f32) {

@@ -18,6 +18,7 @@ struct GemmParams {
   void* aux_out;           // bf16 copy of the pre-activation value (layout of C)
   const void* aux_in;      // bf16 saved value; result is multiplied by act'(aux_in) (layout of C)
   float alpha;
+  const float* alpha_ptr;   // optional device scalar multiplied into alpha (e.g. an upstream loss gradient)
   int act, dact, out_mode;
   int vec_ok, res_vec_ok;  // 16-byte vector access is legal for C/aux and for residual
   uint32_t* status;        // device word, receives a non-zero code on a bounded-wait expiry

@@ -39,6 +39,8 @@ __global__ void ce_label_kernel(const T* __restrict__ logits, const long long* _
   const long long row = blockIdx.x;
   const T* xr = logits + row * ld;
   const long long label = labels[row];
+  // read before any gradient is written: dlogits may alias logits (in-place use by the fused LM head)
+  const float x_label = (threadIdx.x == 0 && label >= 0 && label < V) ? lf(xr + label) : 0.f;
   float m = -INFINITY, s = 0.f;
   const bool vec = (ld % N == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0);
   const int nv = vec ? V / N : 0;
@@ -75,7 +77,7 @@ __global__ void ce_label_kernel(const T* __restrict__ logits, const long long* _
   const float lse = m + logf(s);
   const bool valid = label >= 0 && label < V;
   if (threadIdx.x == 0) {
-    float l = valid ? lse - lf(xr + label) : 0.f;
+    float l = valid ? lse - x_label : 0.f;
     if (loss_rows) loss_rows[row] = l;
     if (loss_sum && valid) atomicAdd(loss_sum, l * loss_scale);
   }

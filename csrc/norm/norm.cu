@@ -72,7 +72,7 @@ template <typename T>
 __global__ void layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
                                      const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                                      T* __restrict__ dx, float* __restrict__ dgamma, float* __restrict__ dbeta,
-                                     long long rows, int d) {
+                                     const T* __restrict__ dres, long long rows, int d) {
   extern __shared__ float sh[];   // [2*d]: dgamma partial, dbeta partial
   float* s_dg = sh; float* s_db = sh + d;
   for (int c = threadIdx.x; c < 2 * d; c += blockDim.x) sh[c] = 0.f;
@@ -98,7 +98,9 @@ __global__ void layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restri
     for (int c = lane; c < d; c += 32) {
       float xh = (ldf(xr + c) - mean) * rstd;
       float gg = ldf(gr + c) * gamma[c];
-      stf(dxr + c, rstd * (gg - s1 - xh * s2));
+      float out = rstd * (gg - s1 - xh * s2);
+      if (dres) out += ldf(dres + row * d + c);   // gradient arriving through the residual branch
+      stf(dxr + c, out);
     }
   }
   __syncthreads();
@@ -184,7 +186,8 @@ int b200_layernorm_fwd(const void* x, const float* gamma, const float* beta, voi
 
 // dgamma / dbeta are accumulated into (caller zero-initialises for a fresh gradient)
 int b200_layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
-                       void* dx, float* dgamma, float* dbeta, long long rows, int d, int is_bf16, cudaStream_t st) {
+                       void* dx, float* dgamma, float* dbeta, const void* dres, long long rows, int d, int is_bf16,
+                       cudaStream_t st) {
   if (rows <= 0) return 0;
   const int block = 256, wpb = block / 32;
   long long g = (rows + wpb - 1) / wpb; if (g > 148 * 2) g = 148 * 2;
@@ -195,8 +198,8 @@ int b200_layernorm_bwd(const void* dy, const void* x, const float* gamma, const 
     else e = cudaFuncSetAttribute(layernorm_bwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  if (is_bf16) layernorm_bwd_kernel<__nv_bfloat16><<<(int)g, block, smem, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, gamma, mean, rstd, (__nv_bfloat16*)dx, dgamma, dbeta, rows, d);
-  else layernorm_bwd_kernel<float><<<(int)g, block, smem, st>>>((const float*)dy, (const float*)x, gamma, mean, rstd, (float*)dx, dgamma, dbeta, rows, d);
+  if (is_bf16) layernorm_bwd_kernel<__nv_bfloat16><<<(int)g, block, smem, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, gamma, mean, rstd, (__nv_bfloat16*)dx, dgamma, dbeta, (const __nv_bfloat16*)dres, rows, d);
+  else layernorm_bwd_kernel<float><<<(int)g, block, smem, st>>>((const float*)dy, (const float*)x, gamma, mean, rstd, (float*)dx, dgamma, dbeta, (const float*)dres, rows, d);
   return (int)cudaGetLastError();
 }
 

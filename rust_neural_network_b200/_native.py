@@ -24,7 +24,7 @@ class GemmParams(C.Structure):
         ("bias", c_void_p), ("bias_f32", c_int),
         ("residual", c_void_p), ("ldr", c_ll), ("strideR", c_ll),
         ("aux_out", c_void_p), ("aux_in", c_void_p),
-        ("alpha", c_float), ("act", c_int), ("dact", c_int), ("out_mode", c_int),
+        ("alpha", c_float), ("alpha_ptr", c_void_p), ("act", c_int), ("dact", c_int), ("out_mode", c_int),
         ("vec_ok", c_int), ("res_vec_ok", c_int),
         ("status", c_void_p),
     ]
@@ -69,7 +69,7 @@ _SIGS = {
     "b200_embedding_fwd": [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_ll, c_int, c_void_p],
     "b200_embedding_bwd": [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_ll, c_int, c_void_p],
     "b200_layernorm_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_float, c_int, c_void_p],
-    "b200_layernorm_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p],
+    "b200_layernorm_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p],
     "b200_batchnorm_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p],
     "b200_batchnorm_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "b200_ce_label": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_ll, c_float, c_float, c_int, c_void_p],

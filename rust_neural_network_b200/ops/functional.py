@@ -39,13 +39,14 @@ def compute_weight(w: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
     return lp(w) if like.dtype == torch.bfloat16 else w.detach()
 
 
-def _wgrad(g2, x2, w):
-    """dW = g^T x. If the parameter carries a pre-set fp32 `.grad` owned by a flat optimizer buffer
-    (`_fused_grad`), accumulate straight into it and return None so autograd adds nothing."""
+def _wgrad(g2, x2, w, alpha_t=None):
+    """dW = g^T x (times the optional device scalar `alpha_t`). If the parameter carries a pre-set
+    fp32 `.grad` owned by a flat optimizer buffer (`_fused_grad`), accumulate straight into it and
+    return None so autograd adds nothing."""
     if getattr(w, "_fused_grad", False) and w.grad is not None:
-        gemm(g2, x2, a_mn=True, b_mn=True, accumulate_into=w.grad)
+        gemm(g2, x2, a_mn=True, b_mn=True, accumulate_into=w.grad, alpha_t=alpha_t)
         return None
-    return gemm(g2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32)
+    return gemm(g2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32, alpha_t=alpha_t)
 
 
 def _bgrad(g2, b):

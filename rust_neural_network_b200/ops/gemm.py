@@ -112,9 +112,11 @@ def _tma_ready(t: torch.Tensor) -> torch.Tensor:
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias=None, act: str = "none",
          residual=None, aux_in=None, dact: str = "none", want_aux: bool = False, alpha: float = 1.0,
-         out_dtype=None, accumulate_into=None, splits: int = 0, bn: int = 0):
+         out_dtype=None, accumulate_into=None, splits: int = 0, bn: int = 0, alpha_t=None):
     """See module docstring. Returns C (and the bf16 pre-activation when ``want_aux``)."""
     if not a.is_cuda:
+        if alpha_t is not None:
+            alpha = alpha * float(alpha_t)
         return gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, act=act, residual=residual, aux_in=aux_in, dact=dact,
                         alpha=alpha, out_dtype=out_dtype, accumulate_into=accumulate_into, want_aux=want_aux)
     lib = nv.cuda()
@@ -202,7 +204,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     p.ldr = residual.stride(1) if residual is not None else 0
     p.strideR = residual.stride(0) if residual is not None else 0
     p.aux_out = nv.ptr(aux); p.aux_in = nv.ptr(aux_in)
-    p.alpha = float(alpha); p.act = ACT[act]; p.dact = ACT[dact]; p.out_mode = out_mode
+    p.alpha = float(alpha); p.alpha_ptr = nv.ptr(alpha_t.float() if alpha_t is not None and alpha_t.dtype != torch.float32 else alpha_t); p.act = ACT[act]; p.dact = ACT[dact]; p.out_mode = out_mode
     es_out = 4 if out_mode != OUT_BF16 else 2
     aux_ok = (aux is None and aux_in is None) or (ldc == N and N % 8 == 0)
     p.vec_ok = 1 if (ldc * es_out % 16 == 0 and out3.data_ptr() % 16 == 0 and (batch == 1 or p.strideC * es_out % 16 == 0) and aux_ok) else 0

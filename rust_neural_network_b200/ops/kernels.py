@@ -217,7 +217,10 @@ def layernorm_fwd(x2d, gamma, beta, eps):
     return y, mean, rstd
 
 
-def layernorm_bwd(dy2d, x2d, gamma, mean, rstd):
+def layernorm_bwd(dy2d, x2d, gamma, mean, rstd, dres=None, dgamma=None, dbeta=None):
+    """Returns (dx [+ dres], dgamma, dbeta). `dres` is an optional gradient of the same shape that is
+    added to dx in the same pass (the residual branch); dgamma/dbeta may be existing fp32
+    accumulators."""
     rows, d = x2d.shape
     if not x2d.is_cuda:
         xh = (x2d.float() - mean[:, None]) * rstd[:, None]
@@ -226,12 +229,20 @@ def layernorm_bwd(dy2d, x2d, gamma, mean, rstd):
         s1 = gg.mean(1, keepdim=True)
         s2 = (gg * xh).mean(1, keepdim=True)
         dx = rstd[:, None] * (gg - s1 - xh * s2)
-        return dx.to(x2d.dtype), (g * xh).sum(0), g.sum(0)
+        if dres is not None:
+            dx = dx + dres.float()
+        dg, db = (g * xh).sum(0), g.sum(0)
+        if dgamma is not None:
+            dgamma.add_(dg); dbeta.add_(db); dg, db = dgamma, dbeta
+        return dx.to(x2d.dtype), dg, db
     dy2d = dy2d.contiguous()
     dx = torch.empty_like(x2d)
-    dgamma = torch.zeros(d, dtype=torch.float32, device=x2d.device)
-    dbeta = torch.zeros(d, dtype=torch.float32, device=x2d.device)
-    nv.check(nv.cuda().b200_layernorm_bwd(dy2d.data_ptr(), x2d.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), rows, d, _isbf(x2d), nv.stream_ptr()), "layernorm_bwd")
+    if dgamma is None:
+        dgamma = torch.zeros(d, dtype=torch.float32, device=x2d.device)
+        dbeta = torch.zeros(d, dtype=torch.float32, device=x2d.device)
+    if dres is not None:
+        dres = dres.contiguous()
+    nv.check(nv.cuda().b200_layernorm_bwd(dy2d.data_ptr(), x2d.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), nv.ptr(dres), rows, d, _isbf(x2d), nv.stream_ptr()), "layernorm_bwd")
     nv.count_launch()
     return dx, dgamma, dbeta
 

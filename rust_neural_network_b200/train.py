@@ -1,0 +1,112 @@
+"""Training loop (rust-nn src/train.rs): `SimpleDataLoader` and `Trainer`.
+
+`Trainer.train_epoch(loader)` = for each batch: zero_grad -> forward -> loss -> backward -> step,
+returning the mean batch loss (src/train.rs:117-144). Batches are staged through pinned host
+memory and copied to the model's device asynchronously; the per-batch losses stay on the device and
+are read back once per epoch. `train_step` is the single-step entry point (host tensors in, loss
+out) and can replay the whole step as one captured CUDA graph.
+"""
+from __future__ import annotations
+
+from typing import Iterator, Optional, Tuple
+
+import torch
+
+from . import _native as nv
+
+
+class SimpleDataLoader:
+    """Splits `inputs` / `targets` along dim 0 into batches of `batch_size`; no shuffle; the last
+    batch may be short (src/train.rs:21-107)."""
+
+    def __init__(self, inputs: torch.Tensor, targets: torch.Tensor, batch_size: int):
+        if inputs.shape[0] != targets.shape[0]:
+            raise ValueError("inputs and targets must have the same number of rows")
+        self.inputs, self.targets, self.batch_size = inputs, targets, max(1, int(batch_size))
+        if torch.cuda.is_available() and not inputs.is_cuda:
+            self.inputs = inputs.pin_memory()
+            self.targets = targets.pin_memory()
+
+    def __len__(self):
+        return (self.inputs.shape[0] + self.batch_size - 1) // self.batch_size
+
+    def __iter__(self) -> Iterator[Tuple[torch.Tensor, torch.Tensor]]:
+        n = self.inputs.shape[0]
+        for i in range(0, n, self.batch_size):
+            yield self.inputs[i:i + self.batch_size], self.targets[i:i + self.batch_size]
+
+
+class Trainer:
+    """`Trainer(model, optimizer, loss_fn)`; if `loss_fn` is None the model must expose
+    `loss(inputs, targets)` (the fused LM head + cross-entropy path)."""
+
+    def __init__(self, model, optimizer, loss_fn=None, use_cuda_graph: bool = False, grad_clip: Optional[float] = None):
+        self.model, self.optimizer, self.loss_fn = model, optimizer, loss_fn
+        self.use_cuda_graph = use_cuda_graph
+        self.grad_clip = grad_clip
+        self._graph = None
+        self._static = None
+        self.steps = 0
+
+    # -- one optimisation step on device tensors
+    def _step_device(self, x, y):
+        self.optimizer.zero_grad()
+        if self.loss_fn is None:
+            loss = self.model.loss(x, y)
+        else:
+            loss = self.loss_fn(self.model(x), y)
+        loss.backward()
+        if self.grad_clip is not None:
+            self.optimizer.clip_grad_norm(self.grad_clip)
+        self.optimizer.step()
+        return loss.detach()
+
+    def _to_device(self, t, like_dtype=None):
+        dev = self.model.device
+        if t.device != dev:
+            t = t.to(dev, non_blocking=True)
+        if like_dtype is not None and t.is_floating_point() and t.dtype != like_dtype:
+            t = t.to(like_dtype)
+        return t
+
+    def capture(self, x, y):
+        """Capture zero_grad + forward + backward + optimizer step for inputs of this shape."""
+        dev = self.model.device
+        self._static = (torch.empty_like(x, device=dev), torch.empty_like(y, device=dev))
+        self._static[0].copy_(x); self._static[1].copy_(y)
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(2):                       # warm-up on a side stream (allocator, lazy init)
+                self._step_device(*self._static)
+        torch.cuda.current_stream().wait_stream(s)
+        nv.check_status()
+        self._graph = torch.cuda.CUDAGraph()
+        before = nv.launch_count()
+        with torch.cuda.graph(self._graph):
+            self._static_loss = self._step_device(*self._static)
+        self.launches_per_step = nv.launch_count() - before
+
+    def train_step(self, inputs: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """One step. Host tensors (ideally pinned) are copied to the device here. Returns the loss
+        as a 0-d device tensor (call `.item()` / `float()` to read it back)."""
+        cd = getattr(self.model, "compute_dtype", None)
+        if self.use_cuda_graph and self.model.device.type == "cuda":
+            if self._graph is None:
+                self.capture(self._to_device(inputs, cd), self._to_device(targets))
+            self._static[0].copy_(inputs, non_blocking=True)
+            self._static[1].copy_(targets, non_blocking=True)
+            self._graph.replay()
+            self.steps += 1
+            return self._static_loss
+        loss = self._step_device(self._to_device(inputs, cd), self._to_device(targets))
+        self.steps += 1
+        return loss
+
+    def train_epoch(self, loader) -> float:
+        losses = []
+        for x, y in loader:
+            losses.append(self.train_step(x, y).clone())
+        if not losses:
+            return 0.0
+        return float(torch.stack([l.float() for l in losses]).mean())

@@ -310,6 +310,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }
 
 template <int HD, bool CAUSAL>
+static int bwd_set_attr() {
+  static bool done = false;
+  if (done) return 0;
+  constexpr int STAGES = (HD == 64) ? 2 : 1;
+  constexpr int SMEM = 2 * 128 * HD * 2 + 2 * STAGES * 128 * HD * 2 + 2 * 128 * 128 * 2 + 128;
+  (void)cudaGetLastError();
+  if (cudaFuncSetAttribute(flash_bwd_kernel<HD, CAUSAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return 1;
+  done = true;
+  return 0;
+}
+
+template <int HD, bool CAUSAL>
 static int launch_bwd(const FlashArgs& a, cudaStream_t st) {
   CUtensorMap tmQ, tmK, tmV, tmdO;
   const auto BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -321,11 +333,7 @@ static int launch_bwd(const FlashArgs& a, cudaStream_t st) {
   constexpr int STAGES = (HD == 64) ? 2 : 1;
   constexpr int SMEM = 2 * 128 * HD * 2 + 2 * STAGES * 128 * HD * 2 + 2 * 128 * 128 * 2 + 128;
   auto kfn = flash_bwd_kernel<HD, CAUSAL>;
-  static bool attr = false;
-  if (!attr) {
-    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return 105;
-    attr = true;
-  }
+  if (bwd_set_attr<HD, CAUSAL>()) return 105;
   const long long rows = (long long)a.B * a.H * a.Sq;
   flash_delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>(
       (const __nv_bfloat16*)a.o.ptr, a.o.sb, a.o.ss, a.o.sh, (const __nv_bfloat16*)a.dout.ptr, a.dout.sb, a.dout.ss,
@@ -348,6 +356,11 @@ static int launch_bwd(const FlashArgs& a, cudaStream_t st) {
 }
 
 }  // namespace b200
+
+extern "C" int b200_flash_bwd_init() {
+  using namespace b200;
+  return bwd_set_attr<64, true>() | bwd_set_attr<64, false>() | bwd_set_attr<128, true>() | bwd_set_attr<128, false>();
+}
 
 extern "C" int b200_flash_bwd(const b200::FlashArgs* a, cudaStream_t st) {
   using namespace b200;

@@ -246,6 +246,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }
 
 template <int HD, int BN, bool CAUSAL>
+static int fwd_set_attr() {
+  static bool done = false;
+  if (done) return 0;
+  constexpr int SMEM = 128 * HD * 2 + 4 * BN * HD * 2 + 128 * BN * 2 + 128;
+  (void)cudaGetLastError();
+  if (cudaFuncSetAttribute(flash_fwd_kernel<HD, BN, CAUSAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return 1;
+  done = true;
+  return 0;
+}
+
+template <int HD, int BN, bool CAUSAL>
 static int launch_fwd(const FlashArgs& a, cudaStream_t st) {
   CUtensorMap tmQ, tmK, tmV;
   const auto BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -254,11 +265,7 @@ static int launch_fwd(const FlashArgs& a, cudaStream_t st) {
   if (make_tmap_attn(&tmV, a.v.ptr, BF, 2, a.hd, a.H, a.Skv, a.B, a.v.sh, a.v.ss, a.v.sb, 64, BN, CU_TENSOR_MAP_SWIZZLE_128B)) return 103;
   constexpr int SMEM = 128 * HD * 2 + 4 * BN * HD * 2 + 128 * BN * 2 + 128;
   auto kfn = flash_fwd_kernel<HD, BN, CAUSAL>;
-  static bool attr = false;
-  if (!attr) {
-    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return 104;
-    attr = true;
-  }
+  if (fwd_set_attr<HD, BN, CAUSAL>()) return 104;
   FwdParams p;
   p.o = (__nv_bfloat16*)a.o.ptr; p.o_sb = a.o.sb; p.o_ss = a.o.ss; p.o_sh = a.o.sh;
   p.lse = a.lse; p.B = a.B; p.H = a.H; p.Sq = a.Sq; p.Skv = a.Skv;
@@ -271,6 +278,11 @@ static int launch_fwd(const FlashArgs& a, cudaStream_t st) {
 }
 
 }  // namespace b200
+
+extern "C" int b200_flash_fwd_init() {
+  using namespace b200;
+  return fwd_set_attr<64, 128, true>() | fwd_set_attr<64, 128, false>() | fwd_set_attr<128, 64, true>() | fwd_set_attr<128, 64, false>();
+}
 
 extern "C" int b200_flash_fwd(const b200::FlashArgs* a, cudaStream_t st) {
   using namespace b200;

@@ -29,6 +29,18 @@ inline PFN_encodeTiled get_encode_fn() {
   return fn;
 }
 
+// cuTensorMapEncodeTiled is a driver call and needs a current context on the calling thread. A fresh
+// thread (e.g. an autograd worker) that has made no runtime call yet has none, so bind the primary
+// context of the runtime's current device once per thread.
+inline void ensure_context() {
+  thread_local bool bound = false;
+  if (!bound) {
+    int d = 0;
+    if (cudaGetDevice(&d) == cudaSuccess) cudaSetDevice(d);
+    bound = true;
+  }
+}
+
 // 3-D map over a row-major [batch][rows][cols] view. `row_stride_bytes` and `batch_stride_bytes`
 // must be multiples of 16; `base` must be 16-byte aligned. Box = {box_cols, box_rows, 1}.
 // Returns 0 on success, a CUresult-like non-zero code otherwise.
@@ -36,6 +48,7 @@ inline int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType 
                         uint64_t cols, uint64_t rows, uint64_t batch, uint64_t row_stride_bytes,
                         uint64_t batch_stride_bytes, uint32_t box_cols, uint32_t box_rows,
                         CUtensorMapSwizzle swz) {
+  ensure_context();
   PFN_encodeTiled fn = get_encode_fn();
   if (!fn) return -1;
   cuuint64_t gdim[3] = {cols, rows, batch};
@@ -56,6 +69,7 @@ inline int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType 
 inline int make_tmap_attn(CUtensorMap* out, const void* base, CUtensorMapDataType dt, uint32_t elem_bytes,
                           uint64_t hd, uint64_t H, uint64_t S, uint64_t B, uint64_t sh, uint64_t ss, uint64_t sb,
                           uint32_t box_e, uint32_t box_s, CUtensorMapSwizzle swz) {
+  ensure_context();
   PFN_encodeTiled fn = get_encode_fn();
   if (!fn) return -1;
   cuuint64_t gdim[4] = {hd, H, S, B};

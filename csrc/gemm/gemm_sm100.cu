@@ -355,6 +355,19 @@ template <typename T> struct DT;
 template <> struct DT<__nv_bfloat16> { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; };
 template <> struct DT<float> { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; };
 
+// Opt in to the large dynamic shared-memory carve-out (once per instantiation).
+template <typename T, int BN, bool A_MN, bool B_MN>
+static int gemm_set_attr() {
+  static bool done = false;
+  if (done) return 0;
+  (void)cudaGetLastError();   // do not inherit a stale error from an unrelated earlier call
+  cudaError_t e = cudaFuncSetAttribute(gemm_kernel<T, BN, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       GemmSmem<T, BN, A_MN, B_MN>::TOTAL);
+  if (e != cudaSuccess) return (int)e;
+  done = true;
+  return 0;
+}
+
 template <typename T, int BN, bool A_MN, bool B_MN>
 static int launch_one(const GemmArgs& a, cudaStream_t stream, int num_sms) {
   using S = GemmSmem<T, BN, A_MN, B_MN>;
@@ -370,13 +383,8 @@ static int launch_one(const GemmArgs& a, cudaStream_t stream, int num_sms) {
   else       rc = make_tmap_3d(&tmB, a.B, DT<T>::v, sizeof(T), a.N, a.K, a.batch, a.ldb * sizeof(T), a.strideB * sizeof(T), ATOM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return 200 + rc;
 
-  static bool attr_set = false;
   auto kfn = gemm_kernel<T, BN, A_MN, B_MN>;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-    if (e != cudaSuccess) return 300 + (int)e;
-    attr_set = true;
-  }
+  { int e = gemm_set_attr<T, BN, A_MN, B_MN>(); if (e) return 300 + e; }
   GemmParams p = a.p;
   const long long m_blocks = (p.M + BM - 1) / BM, n_blocks = (p.N + BN - 1) / BN;
   const long long tiles = m_blocks * n_blocks * p.splits * p.batch;
@@ -396,6 +404,19 @@ static int launch_major(const GemmArgs& a, cudaStream_t s, int sms) {
 }
 
 }  // namespace b200
+
+// Loads every GEMM variant and sets its attributes up front (called once after the library is loaded).
+extern "C" int b200_gemm_init() {
+  using namespace b200;
+  int e = 0;
+#define B200_INIT_BN(BN) \
+  e |= gemm_set_attr<__nv_bfloat16, BN, false, false>(); e |= gemm_set_attr<__nv_bfloat16, BN, false, true>(); \
+  e |= gemm_set_attr<__nv_bfloat16, BN, true, false>(); e |= gemm_set_attr<__nv_bfloat16, BN, true, true>();
+  B200_INIT_BN(64) B200_INIT_BN(128) B200_INIT_BN(256)
+#undef B200_INIT_BN
+  e |= gemm_set_attr<float, 128, false, false>();
+  return e;
+}
 
 extern "C" int b200_gemm_launch(const b200::GemmArgs* args, int bn, int num_sms, cudaStream_t stream) {
   using namespace b200;

@@ -86,7 +86,9 @@ def build_all(verbose: bool = False, jobs: int | None = None) -> dict[str, Path]
         cpp_objs = [f.result() for f in cpp_futs]
     out = {}
     cuda_lib = LIBDIR / "libb200nn_cuda.so"
-    cmd = [_nvcc(), "-shared", "-o", str(cuda_lib)] + [str(o) for o in cu_objs] + ["-lcudart", "-Xcompiler", "-fPIC"]
+    # one CUDA runtime per process: link the shared cudart so the kernels use the same runtime instance
+    # (current device, streams, lazily loaded modules) as PyTorch, which has it loaded already
+    cmd = [_nvcc(), "-shared", "--cudart", "shared", "-o", str(cuda_lib)] + [str(o) for o in cu_objs] + ["-Xcompiler", "-fPIC"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed\n{r.stdout}\n{r.stderr}")

@@ -114,6 +114,16 @@ def cuda():
         _cuda_lib = C.CDLL(str(path), mode=C.RTLD_GLOBAL)
         _declare(_cuda_lib, _SIGS)
         _declare(_cuda_lib, _EXTRA_SIGS)
+        if torch.cuda.is_available():
+            torch.cuda.init()
+            # load every tensor-core kernel variant and opt in to its shared-memory carve-out now,
+            # from the importing thread, instead of lazily from an autograd worker thread
+            for name in ("b200_gemm_init", "b200_flash_fwd_init", "b200_flash_bwd_init"):
+                fn = getattr(_cuda_lib, name)
+                fn.argtypes, fn.restype = [], c_int
+                rc = fn()
+                if rc != 0:
+                    raise RuntimeError(f"{name} failed with CUDA error {rc}")
     return _cuda_lib
 
 

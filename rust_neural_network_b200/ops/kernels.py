@@ -82,7 +82,9 @@ def binary(a, b, op, out=None):
     a = a.contiguous()
     b = b.contiguous().to(a.dtype)
     period = 0
-    if b.numel() != a.numel():
+    if b.numel() == 1 and a.numel() != 1:
+        period = 1
+    elif b.numel() != a.numel():
         if a.numel() % max(b.numel(), 1) != 0 or tuple(a.shape[a.dim() - b.dim():]) != tuple(b.shape):
             raise ValueError(f"cannot broadcast {tuple(b.shape)} onto {tuple(a.shape)} along trailing dims")
         period = b.numel()

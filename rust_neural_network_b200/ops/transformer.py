@@ -22,20 +22,28 @@ from .functional import _bgrad, _scale_by, _wgrad, lp
 from .gemm import gemm
 
 
-def _fused_qkv(wq, wk, wv, getter):
-    """[3d, d] matrix holding q, k, v weights (zero-copy when they are adjacent in memory)."""
-    a, b, c = getter(wq), getter(wk), getter(wv)
+def _adjacent(a, b, c):
+    """True when a, b, c are contiguous tensors laid out back to back inside ONE storage."""
     es = a.element_size()
-    if (a.is_contiguous() and b.is_contiguous() and c.is_contiguous()
-            and b.data_ptr() == a.data_ptr() + a.numel() * es and c.data_ptr() == b.data_ptr() + b.numel() * es):
+    sa = a.untyped_storage()
+    if not (a.is_contiguous() and b.is_contiguous() and c.is_contiguous()):
+        return False
+    if b.untyped_storage().data_ptr() != sa.data_ptr() or c.untyped_storage().data_ptr() != sa.data_ptr():
+        return False
+    return b.data_ptr() == a.data_ptr() + a.numel() * es and c.data_ptr() == b.data_ptr() + b.numel() * es
+
+
+def _fused_qkv(wq, wk, wv, getter):
+    """[3d, d] matrix holding q, k, v weights (zero-copy when they are adjacent in one storage)."""
+    a, b, c = getter(wq), getter(wk), getter(wv)
+    if _adjacent(a, b, c):
         return torch.as_strided(a, (a.shape[0] * 3, a.shape[1]), (a.shape[1], 1))
     return torch.cat([a, b, c], 0)
 
 
 def _fused_vec(bq, bk, bv, getter):
     a, b, c = getter(bq), getter(bk), getter(bv)
-    es = a.element_size()
-    if b.data_ptr() == a.data_ptr() + a.numel() * es and c.data_ptr() == b.data_ptr() + b.numel() * es:
+    if _adjacent(a, b, c):
         return torch.as_strided(a, (a.numel() * 3,), (1,))
     return torch.cat([a, b, c], 0)
 

@@ -21,6 +21,20 @@ def rel_err(a, b):
     return float((a - b).norm() / (b.norm() + 1e-12))
 
 
+def grads_close(got, ref, rel=5e-2, floor=2e-2):
+    """Per-parameter gradient check that tolerates parameters whose true gradient is ~0 (e.g. the key
+    bias of softmax attention): error <= rel*|ref| + floor*(global rms of all reference grads)*sqrt(n)."""
+    allref = torch.cat([r.float().reshape(-1).cpu() for r in ref])
+    rms = float(allref.pow(2).mean().sqrt())
+    bad = []
+    for i, (g, r) in enumerate(zip(got, ref)):
+        g, r = g.float().cpu(), r.float().cpu()
+        err = float((g - r).norm())
+        if err > rel * float(r.norm()) + floor * rms * (r.numel() ** 0.5):
+            bad.append((i, tuple(r.shape), err, float(r.norm())))
+    return bad
+
+
 def _clone_to(module, device, dtype):
     m = copy.deepcopy(module)
     return m.to_device(device, dtype)
@@ -43,9 +57,8 @@ def test_fused_block_matches_fp32_reference(causal):
     (yg.float() * w.cuda()).sum().backward()
     assert rel_err(yg, yr) < 2e-2
     assert rel_err(xg.grad, xr.grad) < 4e-2
-    for pg, pr in zip(g.parameters(), ref_blk.parameters()):
-        assert pg.grad is not None
-        assert rel_err(pg.grad, pr.grad) < 5e-2, (pg.shape,)
+    assert all(p.grad is not None for p in g.parameters())
+    assert grads_close([p.grad for p in g.parameters()], [p.grad for p in ref_blk.parameters()]) == []
 
 
 def test_lm_loss_matches_reference_and_learns():
@@ -57,8 +70,7 @@ def test_lm_loss_matches_reference_and_learns():
     lc = cpu.loss(ids, labels); lg = gpu.loss(ids.cuda(), labels.cuda())
     assert abs(float(lc) - float(lg)) < 0.05
     lc.backward(); lg.backward()
-    for pg, pc in zip(gpu.parameters(), cpu.parameters()):
-        assert rel_err(pg.grad, pc.grad) < 0.12, tuple(pg.shape)
+    assert grads_close([p.grad for p in gpu.parameters()], [p.grad for p in cpu.parameters()], rel=0.12, floor=0.05) == []
     opt = Adam(gpu.parameters(), lr=2e-3)
     tr = Trainer(gpu, opt)
     first = float(tr.train_step(ids, labels))

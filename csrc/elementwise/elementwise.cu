@@ -267,6 +267,28 @@ __global__ void transpose_kernel(const T* __restrict__ in, T* __restrict__ out, 
   }
 }
 
+// P1 rotary embedding, rotate-half convention with duplicated-half tables [seq, dim]
+// (rust-nn src/tensor.rs:1077-1124): out[i] = x[i] cos[i] - x[h+i] sin[i]; out[h+i] = x[h+i] cos[h+i] + x[i] sin[h+i].
+// `sign` = -1 applies the inverse rotation, which is the backward pass (src/tensor.rs:2002-2013).
+template <typename T>
+__global__ void rope_kernel(const T* __restrict__ x, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                            T* __restrict__ y, long long leading, int seq, int dim, float sign) {
+  const int half = dim / 2;
+  const long long total = leading * seq * half;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const int j = (int)(i % half); long long r = i / half;
+    const int s = (int)(r % seq);
+    const long long base = r * dim;
+    const float xi = to_f(x[base + j]), xj = to_f(x[base + half + j]);
+    const float c0 = cos_t[s * dim + j], c1 = cos_t[s * dim + half + j];
+    const float s0 = sign * sin_t[s * dim + j], s1 = sign * sin_t[s * dim + half + j];
+    y[base + j] = from_f<T>(xi * c0 - xj * s0);
+    y[base + half + j] = from_f<T>(xj * c1 + xi * s1);
+  }
+}
+
 static inline int grid_for(long long work, int block, int max_blocks = 148 * 16) {
   long long g = (work + block - 1) / block;
   if (g < 1) g = 1;
@@ -345,6 +367,15 @@ int b200_transpose(const void* in, void* out, int rows, int cols, long long ld_i
   dim3 grid((cols + 31) / 32, (rows + 31) / 32, batch), block(32, 8);
   if (is_bf16) transpose_kernel<__nv_bfloat16><<<grid, block, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, rows, cols, ld_in, ld_out, bs_in, bs_out);
   else transpose_kernel<float><<<grid, block, 0, st>>>((const float*)in, (float*)out, rows, cols, ld_in, ld_out, bs_in, bs_out);
+  return (int)cudaGetLastError();
+}
+
+int b200_rope(const void* x, const float* cos_t, const float* sin_t, void* y, long long leading, int seq, int dim,
+              float sign, int is_bf16, cudaStream_t st) {
+  if (leading <= 0 || seq <= 0 || dim <= 0) return 0;
+  long long total = leading * seq * (dim / 2);
+  if (is_bf16) rope_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, st>>>((const __nv_bfloat16*)x, cos_t, sin_t, (__nv_bfloat16*)y, leading, seq, dim, sign);
+  else rope_kernel<float><<<grid_for(total, 256), 256, 0, st>>>((const float*)x, cos_t, sin_t, (float*)y, leading, seq, dim, sign);
   return (int)cudaGetLastError();
 }
 

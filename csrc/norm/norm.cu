@@ -110,6 +110,74 @@ __global__ void layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restri
   }
 }
 
+// Register-accumulating variant for even d <= 64*J: lane l owns the column pairs {2l + 64j}, so the
+// per-column dgamma/dbeta partial sums of every row a warp processes stay in that lane's registers;
+// x and dy are read exactly once. Warps of a block are combined through shared memory, blocks with
+// one fp32 atomic per column.
+template <typename T, int J>
+__global__ void __launch_bounds__(256)
+layernorm_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
+                         const float* __restrict__ mean_in, const float* __restrict__ rstd_in, T* __restrict__ dx,
+                         float* __restrict__ dgamma, float* __restrict__ dbeta, const T* __restrict__ dres,
+                         long long rows, int d) {
+  extern __shared__ float sh[];   // [warps][2][d]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps_per_block = blockDim.x >> 5;
+  float2 gam[J], adg[J], adb[J];
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int c = 2 * lane + 64 * j;
+    gam[j] = c < d ? *reinterpret_cast<const float2*>(gamma + c) : make_float2(0.f, 0.f);
+    adg[j] = make_float2(0.f, 0.f); adb[j] = make_float2(0.f, 0.f);
+  }
+  const float inv_d = 1.f / d;
+  long long row = (long long)blockIdx.x * warps_per_block + warp;
+  const long long row_stride = (long long)gridDim.x * warps_per_block;
+  for (; row < rows; row += row_stride) {
+    const T* xr = x + row * d; const T* gr = dy + row * d;
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float2 xh[J], g[J];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int c = 2 * lane + 64 * j;
+      if (c < d) {
+        const float2 xv = Pair<T>::ld(xr + c);
+        g[j] = Pair<T>::ld(gr + c);
+        xh[j] = make_float2((xv.x - mean) * rstd, (xv.y - mean) * rstd);
+      } else { g[j] = make_float2(0.f, 0.f); xh[j] = make_float2(0.f, 0.f); }
+      const float g0 = g[j].x * gam[j].x, g1 = g[j].y * gam[j].y;
+      s1 += g0 + g1; s2 += g0 * xh[j].x + g1 * xh[j].y;
+      adg[j].x += g[j].x * xh[j].x; adg[j].y += g[j].y * xh[j].y;
+      adb[j].x += g[j].x; adb[j].y += g[j].y;
+    }
+    s1 = wsum(s1) * inv_d; s2 = wsum(s2) * inv_d;
+    T* dxr = dx + row * d;
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int c = 2 * lane + 64 * j;
+      if (c < d) {
+        float o0 = rstd * (g[j].x * gam[j].x - s1 - xh[j].x * s2);
+        float o1 = rstd * (g[j].y * gam[j].y - s1 - xh[j].y * s2);
+        if (dres) { const float2 rr = Pair<T>::ld(dres + row * d + c); o0 += rr.x; o1 += rr.y; }
+        Pair<T>::st(dxr + c, o0, o1);
+      }
+    }
+  }
+  float* my = sh + (size_t)warp * 2 * d;
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int c = 2 * lane + 64 * j;
+    if (c < d) { my[c] = adg[j].x; my[c + 1] = adg[j].y; my[d + c] = adb[j].x; my[d + c + 1] = adb[j].y; }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 2 * d; c += blockDim.x) {
+    float acc = 0.f;
+    for (int w = 0; w < warps_per_block; ++w) acc += sh[(size_t)w * 2 * d + c];
+    atomicAdd(c < d ? dgamma + c : dbeta + (c - d), acc);
+  }
+}
+
 // ------------------------------------------------------------------ BatchNorm1D  x:[batch, n]
 // one thread per feature column; coalesced across threads for every row
 template <typename T>
@@ -191,6 +259,16 @@ int b200_layernorm_bwd(const void* dy, const void* x, const float* gamma, const 
   if (rows <= 0) return 0;
   const int block = 256, wpb = block / 32;
   long long g = (rows + wpb - 1) / wpb; if (g > 148 * 2) g = 148 * 2;
+  if (d % 2 == 0 && d <= 1024) {
+    const size_t sm = (size_t)wpb * 2 * d * sizeof(float);   // <= 64 KB
+#define B200_LNB(TT, JJ) { auto k = layernorm_bwd_reg_kernel<TT, JJ>; \
+      if (sm > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); if (e != cudaSuccess) return (int)e; } \
+      k<<<(int)g, block, sm, st>>>((const TT*)dy, (const TT*)x, gamma, mean, rstd, (TT*)dx, dgamma, dbeta, (const TT*)dres, rows, d); }
+    if (is_bf16) { if (d <= 256) B200_LNB(__nv_bfloat16, 4) else if (d <= 512) B200_LNB(__nv_bfloat16, 8) else B200_LNB(__nv_bfloat16, 16) }
+    else { if (d <= 256) B200_LNB(float, 4) else if (d <= 512) B200_LNB(float, 8) else B200_LNB(float, 16) }
+#undef B200_LNB
+    return (int)cudaGetLastError();
+  }
   size_t smem = 2 * (size_t)d * sizeof(float);
   if (smem > 48 * 1024) {
     cudaError_t e;

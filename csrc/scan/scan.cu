@@ -1,0 +1,443 @@
+// S1/S2: Mamba (S6) selective scan forward / backward, S3: depthwise causal conv1d (+SiLU) forward / backward.
+//
+// Recurrence (rust-nn src/tensor.rs:833-896, backward 1710-1819):
+//   h_t[d,n] = exp(delta_t[d] * A[d,n]) * h_{t-1}[d,n] + delta_t[d] * B_t[n] * u_t[d]
+//   y_t[d]   = sum_n C_t[n] * h_t[d,n]   (+ Dskip[d] * u_t[d])   (* silu(z_t[d]) when a gate is given)
+// with delta = softplus(delta_raw + delta_bias) when `delta_softplus` is set.
+//
+// A is diagonal per (channel, state), so this is not a tensor-core contraction: the kernels keep the
+// fp32 state in registers, one thread per (batch, channel) with all N <= 16 states, stream u/delta/z
+// through coalesced loads and B_t/C_t through shared memory, and use exp2 with log2(e) folded into A.
+// The forward stores the state every CK steps; the backward walks those checkpoints in reverse,
+// recomputes the CK intermediate states into shared memory and runs the adjoint recurrence -
+// it never stores seq x d x n states as the reference's backward does (src/tensor.rs:1750-1802).
+// dB_t / dC_t are reduced across the 32 channels of a warp with a transpose-reduce (31 shuffles for
+// 32 values) and then added atomically.
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+
+namespace b200 {
+
+constexpr int SCAN_N = 16;       // max states per channel
+constexpr int SCAN_CK = 8;       // checkpoint interval (steps)
+constexpr int SCAN_THREADS = 128;
+
+template <typename T> __device__ __forceinline__ float s_ld(const T* p);
+template <> __device__ __forceinline__ float s_ld<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float s_ld<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void s_st(T* p, float v);
+template <> __device__ __forceinline__ void s_st<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void s_st<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
+
+__device__ __forceinline__ float softplus20(float v) { return v > 20.f ? v : log1pf(__expf(v)); }
+__device__ __forceinline__ float sigmoidf_(float v) { return 1.f / (1.f + __expf(-v)); }
+
+struct ScanArgs {
+  const void* u; long long u_ld;            // [B, S, D] rows of stride u_ld
+  const void* delta; long long delta_ld;    // [B, S, D]
+  const void* z; long long z_ld;            // optional gate [B, S, D]
+  const void* Bm; long long b_ld;           // [B, S, N]
+  const void* Cm; long long c_ld;           // [B, S, N]
+  const float* A;                           // [D, N] (negative)
+  const float* Dskip;                       // optional [D]
+  const float* delta_bias;                  // optional [D]
+  void* y; long long y_ld;                  // [B, S, D]
+  float* hck;                               // checkpoints [B, ceil(S/CK), D, N] (state BEFORE step c*CK)
+  int B, S, D, N;
+  int delta_softplus;
+  // backward
+  const void* dy; long long dy_ld;
+  void* du; long long du_ld;
+  void* ddelta; long long ddelta_ld;
+  void* dz; long long dz_ld;
+  float* dB; float* dC;                     // [B, S, N] fp32, zero-initialised by the caller
+  float* dA; float* dDskip; float* ddelta_bias;   // fp32 accumulators [D,N], [D], [D]
+};
+
+template <typename T>
+__global__ void __launch_bounds__(SCAN_THREADS)
+selective_scan_fwd_kernel(ScanArgs a) {
+  const int b = blockIdx.y;
+  const int d = blockIdx.x * SCAN_THREADS + threadIdx.x;
+  const bool active = d < a.D;
+  const int N = a.N;
+  __shared__ float sB[SCAN_CK][SCAN_N], sC[SCAN_CK][SCAN_N];
+  float A2[SCAN_N], h[SCAN_N];
+#pragma unroll
+  for (int n = 0; n < SCAN_N; ++n) {
+    A2[n] = (active && n < N) ? a.A[(long long)d * N + n] * 1.4426950408889634f : 0.f;
+    h[n] = 0.f;
+  }
+  const float dsk = (active && a.Dskip) ? a.Dskip[d] : 0.f;
+  const float dbias = (active && a.delta_bias) ? a.delta_bias[d] : 0.f;
+  const T* up = (const T*)a.u + (long long)b * a.S * a.u_ld + d;
+  const T* dp = (const T*)a.delta + (long long)b * a.S * a.delta_ld + d;
+  const T* zp = a.z ? (const T*)a.z + (long long)b * a.S * a.z_ld + d : nullptr;
+  T* yp = (T*)a.y + (long long)b * a.S * a.y_ld + d;
+  const T* Bp = (const T*)a.Bm + (long long)b * a.S * a.b_ld;
+  const T* Cp = (const T*)a.Cm + (long long)b * a.S * a.c_ld;
+  const int n_ck = (a.S + SCAN_CK - 1) / SCAN_CK;
+  for (int c = 0; c < n_ck; ++c) {
+    const int t0 = c * SCAN_CK;
+    __syncthreads();
+    for (int i = threadIdx.x; i < SCAN_CK * SCAN_N; i += SCAN_THREADS) {
+      const int tt = i / SCAN_N, n = i % SCAN_N;
+      const bool ok = (t0 + tt < a.S) && n < N;
+      sB[tt][n] = ok ? s_ld(Bp + (long long)(t0 + tt) * a.b_ld + n) : 0.f;
+      sC[tt][n] = ok ? s_ld(Cp + (long long)(t0 + tt) * a.c_ld + n) : 0.f;
+    }
+    __syncthreads();
+    if (!active) continue;
+    if (a.hck) {
+      float* ck = a.hck + (((long long)b * n_ck + c) * a.D + d) * N;
+#pragma unroll
+      for (int n = 0; n < SCAN_N; ++n) if (n < N) ck[n] = h[n];
+    }
+    float uu[SCAN_CK], dd[SCAN_CK], zz[SCAN_CK];
+#pragma unroll
+    for (int tt = 0; tt < SCAN_CK; ++tt) {
+      const bool ok = t0 + tt < a.S;
+      uu[tt] = ok ? s_ld(up + (long long)(t0 + tt) * a.u_ld) : 0.f;
+      dd[tt] = ok ? s_ld(dp + (long long)(t0 + tt) * a.delta_ld) : 0.f;
+      zz[tt] = (ok && zp) ? s_ld(zp + (long long)(t0 + tt) * a.z_ld) : 0.f;
+    }
+#pragma unroll
+    for (int tt = 0; tt < SCAN_CK; ++tt) {
+      if (t0 + tt >= a.S) break;
+      float dl = dd[tt] + dbias;
+      if (a.delta_softplus) dl = softplus20(dl);
+      const float du = dl * uu[tt];
+      float y = dsk * uu[tt];
+#pragma unroll
+      for (int n = 0; n < SCAN_N; ++n) {
+        h[n] = exp2f(dl * A2[n]) * h[n] + du * sB[tt][n];
+        y += sC[tt][n] * h[n];
+      }
+      if (zp) y *= zz[tt] * sigmoidf_(zz[tt]);
+      s_st(yp + (long long)(t0 + tt) * a.y_ld, y);
+    }
+  }
+}
+
+// Sum 32 per-lane arrays of 32 values across the warp; afterwards lane i holds the total of value i.
+__device__ __forceinline__ float warp_transpose_reduce32(float (&v)[32], int lane) {
+#pragma unroll
+  for (int step = 0; step < 5; ++step) {
+    const int half = 16 >> step;           // number of values kept after this step
+    const int lane_bit = 16 >> step;
+    const bool upper = (lane & lane_bit) != 0;
+#pragma unroll
+    for (int i = 0; i < half; ++i) {
+      // lanes with the bit set keep the upper half of the remaining values, the others the lower half
+      const float send = upper ? v[i] : v[i + half];
+      const float keep = upper ? v[i + half] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, lane_bit);
+    }
+  }
+  return v[0];
+}
+// index of the value that ends up in `lane` after warp_transpose_reduce32
+__device__ __forceinline__ int transpose_reduce_owner(int lane) { return lane; }
+
+template <typename T>
+__global__ void __launch_bounds__(SCAN_THREADS)
+selective_scan_bwd_kernel(ScanArgs a) {
+  extern __shared__ float smem[];
+  float* sH = smem;                                         // [CK+1][N][THREADS] states h_{t0-1} .. h_{t0+CK-1}
+  float* sB = sH + (SCAN_CK + 1) * SCAN_N * SCAN_THREADS;   // [CK][N]
+  float* sC = sB + SCAN_CK * SCAN_N;                        // [CK][N]
+  const int b = blockIdx.y;
+  const int d = blockIdx.x * SCAN_THREADS + threadIdx.x;
+  const int lane = threadIdx.x & 31;
+  const bool active = d < a.D;
+  const int N = a.N;
+  float A2[SCAN_N], Araw[SCAN_N], dh[SCAN_N], dAacc[SCAN_N];
+#pragma unroll
+  for (int n = 0; n < SCAN_N; ++n) {
+    Araw[n] = (active && n < N) ? a.A[(long long)d * N + n] : 0.f;
+    A2[n] = Araw[n] * 1.4426950408889634f;
+    dh[n] = 0.f; dAacc[n] = 0.f;
+  }
+  const float dsk = (active && a.Dskip) ? a.Dskip[d] : 0.f;
+  const float dbias = (active && a.delta_bias) ? a.delta_bias[d] : 0.f;
+  float dDacc = 0.f, ddbias_acc = 0.f;
+  const long long rb = (long long)b * a.S;
+  const T* up = (const T*)a.u + rb * a.u_ld + d;
+  const T* dp = (const T*)a.delta + rb * a.delta_ld + d;
+  const T* zp = a.z ? (const T*)a.z + rb * a.z_ld + d : nullptr;
+  const T* gyp = (const T*)a.dy + rb * a.dy_ld + d;
+  T* dup = (T*)a.du + rb * a.du_ld + d;
+  T* ddp = (T*)a.ddelta + rb * a.ddelta_ld + d;
+  T* dzp = a.dz ? (T*)a.dz + rb * a.dz_ld + d : nullptr;
+  const T* Bp = (const T*)a.Bm + rb * a.b_ld;
+  const T* Cp = (const T*)a.Cm + rb * a.c_ld;
+  const int n_ck = (a.S + SCAN_CK - 1) / SCAN_CK;
+#define SH(t, n) sH[((t) * SCAN_N + (n)) * SCAN_THREADS + threadIdx.x]
+  for (int c = n_ck - 1; c >= 0; --c) {
+    const int t0 = c * SCAN_CK;
+    __syncthreads();
+    for (int i = threadIdx.x; i < SCAN_CK * SCAN_N; i += SCAN_THREADS) {
+      const int tt = i / SCAN_N, n = i % SCAN_N;
+      const bool ok = (t0 + tt < a.S) && n < N;
+      sB[i] = ok ? s_ld(Bp + (long long)(t0 + tt) * a.b_ld + n) : 0.f;
+      sC[i] = ok ? s_ld(Cp + (long long)(t0 + tt) * a.c_ld + n) : 0.f;
+    }
+    __syncthreads();
+    float uu[SCAN_CK], dl[SCAN_CK], draw[SCAN_CK], zz[SCAN_CK], gy[SCAN_CK], yraw[SCAN_CK];
+#pragma unroll
+    for (int tt = 0; tt < SCAN_CK; ++tt) {
+      const bool ok = active && (t0 + tt < a.S);
+      uu[tt] = ok ? s_ld(up + (long long)(t0 + tt) * a.u_ld) : 0.f;
+      draw[tt] = ok ? s_ld(dp + (long long)(t0 + tt) * a.delta_ld) + dbias : 0.f;
+      dl[tt] = a.delta_softplus ? softplus20(draw[tt]) : draw[tt];
+      if (!ok) dl[tt] = 0.f;
+      zz[tt] = (ok && zp) ? s_ld(zp + (long long)(t0 + tt) * a.z_ld) : 0.f;
+      gy[tt] = ok ? s_ld(gyp + (long long)(t0 + tt) * a.dy_ld) : 0.f;
+    }
+    // recompute the states of this chunk from its checkpoint
+    if (active) {
+      const float* ck = a.hck + (((long long)b * n_ck + c) * a.D + d) * N;
+#pragma unroll
+      for (int n = 0; n < SCAN_N; ++n) SH(0, n) = n < N ? ck[n] : 0.f;
+#pragma unroll
+      for (int tt = 0; tt < SCAN_CK; ++tt) {
+        const float du = dl[tt] * uu[tt];
+        float y = dsk * uu[tt];
+#pragma unroll
+        for (int n = 0; n < SCAN_N; ++n) {
+          const float hn = exp2f(dl[tt] * A2[n]) * SH(tt, n) + du * sB[tt * SCAN_N + n];
+          SH(tt + 1, n) = hn;
+          y += sC[tt * SCAN_N + n] * hn;
+        }
+        yraw[tt] = y;
+      }
+    }
+    // adjoint recurrence, reverse in time
+#pragma unroll
+    for (int tt = SCAN_CK - 1; tt >= 0; --tt) {
+      const int t = t0 + tt;
+      const bool step_ok = t < a.S;          // block-uniform
+      if (!step_ok) continue;
+      float g = gy[tt];
+      if (zp) {
+        const float sg = sigmoidf_(zz[tt]);
+        const float sz = zz[tt] * sg;
+        if (active && dzp) s_st(dzp + (long long)t * a.dz_ld, g * yraw[tt] * sg * (1.f + zz[tt] * (1.f - sg)));
+        g *= sz;
+      }
+      dDacc += g * uu[tt];
+      float du_t = g * dsk;
+      float ddl = 0.f;
+      float red[32];
+#pragma unroll
+      for (int n = 0; n < SCAN_N; ++n) {
+        const float hprev = SH(tt, n), hcur = SH(tt + 1, n);
+        const float Bn = sB[tt * SCAN_N + n], Cn = sC[tt * SCAN_N + n];
+        red[SCAN_N + n] = g * hcur;                         // dC_t[n] contribution of this channel
+        const float dhn = dh[n] + g * Cn;
+        const float da = exp2f(dl[tt] * A2[n]);
+        const float dda = dhn * hprev;
+        ddl += dda * da * Araw[n] + dhn * Bn * uu[tt];
+        dAacc[n] += dda * da * dl[tt];
+        red[n] = dhn * dl[tt] * uu[tt];                      // dB_t[n] contribution
+        du_t += dhn * dl[tt] * Bn;
+        dh[n] = dhn * da;
+      }
+      if (!active) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) red[i] = 0.f;
+      }
+      const float total = warp_transpose_reduce32(red, lane);
+      // lane i now holds the warp total of value i: i < 16 -> dB[n = i], else dC[n = i - 16]
+      {
+        const int n = lane & 15;
+        if (n < N) {
+          float* dst = (lane < 16 ? a.dB : a.dC) + (rb + t) * N + n;
+          atomicAdd(dst, total);
+        }
+      }
+      if (active) {
+        float ddraw = ddl;
+        if (a.delta_softplus) ddraw *= sigmoidf_(draw[tt]);
+        ddbias_acc += ddraw;
+        s_st(dup + (long long)t * a.du_ld, du_t);
+        s_st(ddp + (long long)t * a.ddelta_ld, ddraw);
+      }
+    }
+  }
+#undef SH
+  if (active) {
+#pragma unroll
+    for (int n = 0; n < SCAN_N; ++n) if (n < N) atomicAdd(a.dA + (long long)d * N + n, dAacc[n]);
+    if (a.dDskip) atomicAdd(a.dDskip + d, dDacc);
+    if (a.ddelta_bias) atomicAdd(a.ddelta_bias + d, ddbias_acc);
+  }
+}
+
+// ---------------------------------------------------------------------------- causal depthwise conv1d
+// y[b,t,c] = act( bias[c] + sum_k w[c,k] * x[b, t-(K-1)+k, c] ), K <= 8, act in {none, silu}
+// (rust-nn src/tensor.rs:903-944; its MambaBlock applies SiLU right after, src/mamba.rs:95-98)
+constexpr int CONV_MAXK = 8;
+constexpr int CONV_TCHUNK = 64;
+
+template <typename T, int K>
+__global__ void conv1d_fwd_kernel(const T* __restrict__ x, long long x_ld, const float* __restrict__ w,
+                                  const float* __restrict__ bias, T* __restrict__ y, long long y_ld, int B, int S, int C,
+                                  int act) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.z;
+  const int t0 = blockIdx.y * CONV_TCHUNK;
+  if (c >= C) return;
+  float wk[K], win[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) wk[k] = w[c * K + k];
+  const float bs = bias ? bias[c] : 0.f;
+  const T* xp = x + (long long)b * S * x_ld + c;
+  T* yp = y + (long long)b * S * y_ld + c;
+  // win[k] holds x[t-(K-1)+k]
+#pragma unroll
+  for (int k = 0; k < K - 1; ++k) {
+    const int t = t0 - (K - 1) + k;
+    win[k] = t >= 0 ? s_ld(xp + (long long)t * x_ld) : 0.f;
+  }
+  const int t1 = min(t0 + CONV_TCHUNK, S);
+  for (int t = t0; t < t1; ++t) {
+    win[K - 1] = s_ld(xp + (long long)t * x_ld);
+    float acc = bs;
+#pragma unroll
+    for (int k = 0; k < K; ++k) acc += wk[k] * win[k];
+    if (act) acc = acc * sigmoidf_(acc);
+    s_st(yp + (long long)t * y_ld, acc);
+#pragma unroll
+    for (int k = 0; k < K - 1; ++k) win[k] = win[k + 1];
+  }
+}
+
+// dx[b,t,c] = sum_k w[c,k] * dpre[b, t+(K-1)-k, c];  dw[c,k] += sum dpre[t] x[t-(K-1)+k];  dbias[c] += sum dpre[t]
+// with dpre = dy * act'(pre), pre recomputed from x.
+template <typename T, int K>
+__global__ void conv1d_bwd_kernel(const T* __restrict__ x, long long x_ld, const float* __restrict__ w,
+                                  const float* __restrict__ bias, const T* __restrict__ dy, long long dy_ld,
+                                  T* __restrict__ dx, long long dx_ld, float* __restrict__ dw, float* __restrict__ dbias,
+                                  int B, int S, int C, int act) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.z;
+  const int t0 = blockIdx.y * CONV_TCHUNK;
+  if (c >= C) return;
+  float wk[K], dwk[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) { wk[k] = w[c * K + k]; dwk[k] = 0.f; }
+  const float bs = bias ? bias[c] : 0.f;
+  const T* xp = x + (long long)b * S * x_ld + c;
+  const T* gp = dy + (long long)b * S * dy_ld + c;
+  T* dxp = dx + (long long)b * S * dx_ld + c;
+  const int t1 = min(t0 + CONV_TCHUNK, S);
+  float dbacc = 0.f;
+  // dpre at time t (0 outside [0,S)); recomputes the convolution at t
+  auto dpre_at = [&](int t) -> float {
+    if (t < 0 || t >= S) return 0.f;
+    float g = s_ld(gp + (long long)t * dy_ld);
+    if (!act) return g;
+    float pre = bs;
+#pragma unroll
+    for (int k = 0; k < K; ++k) { const int tx = t - (K - 1) + k; if (tx >= 0) pre += wk[k] * s_ld(xp + (long long)tx * x_ld); }
+    const float sg = sigmoidf_(pre);
+    return g * sg * (1.f + pre * (1.f - sg));
+  };
+  // sliding window dwin[i] = dpre[t + i], i in [0, K)
+  float dwin[K];
+#pragma unroll
+  for (int k = 0; k < K - 1; ++k) dwin[k] = dpre_at(t0 + k);
+  for (int t = t0; t < t1; ++t) {
+    dwin[K - 1] = dpre_at(t + K - 1);
+    float acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) acc += wk[k] * dwin[K - 1 - k];
+    s_st(dxp + (long long)t * dx_ld, acc);
+    // weight / bias gradients use dpre[t] (= dwin[0]) against x[t-(K-1)+k]
+    const float dp = dwin[0];
+    dbacc += dp;
+#pragma unroll
+    for (int k = 0; k < K; ++k) { const int tx = t - (K - 1) + k; if (tx >= 0) dwk[k] += dp * s_ld(xp + (long long)tx * x_ld); }
+#pragma unroll
+    for (int k = 0; k < K - 1; ++k) dwin[k] = dwin[k + 1];
+  }
+#pragma unroll
+  for (int k = 0; k < K; ++k) atomicAdd(dw + c * K + k, dwk[k]);
+  if (dbias) atomicAdd(dbias + c, dbacc);
+}
+
+template <typename T, int K>
+static void conv_fwd_launch(const void* x, long long x_ld, const float* w, const float* bias, void* y, long long y_ld,
+                            int B, int S, int C, int act, cudaStream_t st) {
+  dim3 grid((C + 127) / 128, (S + CONV_TCHUNK - 1) / CONV_TCHUNK, B);
+  conv1d_fwd_kernel<T, K><<<grid, 128, 0, st>>>((const T*)x, x_ld, w, bias, (T*)y, y_ld, B, S, C, act);
+}
+template <typename T, int K>
+static void conv_bwd_launch(const void* x, long long x_ld, const float* w, const float* bias, const void* dy,
+                            long long dy_ld, void* dx, long long dx_ld, float* dw, float* dbias, int B, int S, int C,
+                            int act, cudaStream_t st) {
+  dim3 grid((C + 127) / 128, (S + CONV_TCHUNK - 1) / CONV_TCHUNK, B);
+  conv1d_bwd_kernel<T, K><<<grid, 128, 0, st>>>((const T*)x, x_ld, w, bias, (const T*)dy, dy_ld, (T*)dx, dx_ld, dw, dbias, B, S, C, act);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_scan_ck() { return SCAN_CK; }
+
+int b200_selective_scan_fwd(const ScanArgs* a, int is_bf16, cudaStream_t st) {
+  if (a->B <= 0 || a->S <= 0 || a->D <= 0) return 0;
+  if (a->N < 1 || a->N > SCAN_N) return -1;
+  dim3 grid((a->D + SCAN_THREADS - 1) / SCAN_THREADS, a->B);
+  if (is_bf16) selective_scan_fwd_kernel<__nv_bfloat16><<<grid, SCAN_THREADS, 0, st>>>(*a);
+  else selective_scan_fwd_kernel<float><<<grid, SCAN_THREADS, 0, st>>>(*a);
+  return (int)cudaGetLastError();
+}
+
+int b200_selective_scan_bwd(const ScanArgs* a, int is_bf16, cudaStream_t st) {
+  if (a->B <= 0 || a->S <= 0 || a->D <= 0) return 0;
+  if (a->N < 1 || a->N > SCAN_N || !a->hck) return -1;
+  dim3 grid((a->D + SCAN_THREADS - 1) / SCAN_THREADS, a->B);
+  const int smem = ((SCAN_CK + 1) * SCAN_N * SCAN_THREADS + 2 * SCAN_CK * SCAN_N) * sizeof(float);
+  static bool attr = false;
+  if (!attr) {
+    (void)cudaGetLastError();
+    if (cudaFuncSetAttribute(selective_scan_bwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -2;
+    if (cudaFuncSetAttribute(selective_scan_bwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -2;
+    attr = true;
+  }
+  if (is_bf16) selective_scan_bwd_kernel<__nv_bfloat16><<<grid, SCAN_THREADS, smem, st>>>(*a);
+  else selective_scan_bwd_kernel<float><<<grid, SCAN_THREADS, smem, st>>>(*a);
+  return (int)cudaGetLastError();
+}
+
+#define B200_CONV_SWITCH(FN, T, ...) \
+  switch (K) { case 1: FN<T, 1>(__VA_ARGS__); break; case 2: FN<T, 2>(__VA_ARGS__); break; case 3: FN<T, 3>(__VA_ARGS__); break; \
+    case 4: FN<T, 4>(__VA_ARGS__); break; case 5: FN<T, 5>(__VA_ARGS__); break; case 6: FN<T, 6>(__VA_ARGS__); break; \
+    case 7: FN<T, 7>(__VA_ARGS__); break; default: FN<T, 8>(__VA_ARGS__); break; }
+
+int b200_conv1d_fwd(const void* x, long long x_ld, const float* w, const float* bias, void* y, long long y_ld, int B,
+                    int S, int C, int K, int act, int is_bf16, cudaStream_t st) {
+  if (B <= 0 || S <= 0 || C <= 0) return 0;
+  if (K < 1 || K > CONV_MAXK) return -1;
+  if (is_bf16) { B200_CONV_SWITCH(conv_fwd_launch, __nv_bfloat16, x, x_ld, w, bias, y, y_ld, B, S, C, act, st) }
+  else { B200_CONV_SWITCH(conv_fwd_launch, float, x, x_ld, w, bias, y, y_ld, B, S, C, act, st) }
+  return (int)cudaGetLastError();
+}
+
+int b200_conv1d_bwd(const void* x, long long x_ld, const float* w, const float* bias, const void* dy, long long dy_ld,
+                    void* dx, long long dx_ld, float* dw, float* dbias, int B, int S, int C, int K, int act, int is_bf16,
+                    cudaStream_t st) {
+  if (B <= 0 || S <= 0 || C <= 0) return 0;
+  if (K < 1 || K > CONV_MAXK) return -1;
+  if (is_bf16) { B200_CONV_SWITCH(conv_bwd_launch, __nv_bfloat16, x, x_ld, w, bias, dy, dy_ld, dx, dx_ld, dw, dbias, B, S, C, act, st) }
+  else { B200_CONV_SWITCH(conv_bwd_launch, float, x, x_ld, w, bias, dy, dy_ld, dx, dx_ld, dw, dbias, B, S, C, act, st) }
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

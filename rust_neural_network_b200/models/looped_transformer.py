@@ -161,8 +161,12 @@ class LoopedTransformer(nn.Module):
 
     def time_conditioning(self, device, dtype) -> torch.Tensor:
         """[num_loops, d] time embeddings through time_proj (one pair of small GEMMs per step)."""
-        emb = torch.cat([sinusoidal_embedding(t, self.d_model, device) for t in range(self.num_loops)], 0)
-        return self.time_proj(emb.to(dtype))
+        cache = getattr(self, "_time_emb", None)
+        if cache is None or cache.device != device or cache.dtype != dtype or cache.shape[0] != self.num_loops:
+            emb = torch.cat([sinusoidal_embedding(t, self.d_model) for t in range(self.num_loops)], 0)
+            cache = emb.to(device=device, dtype=dtype)
+            self._time_emb = cache          # constant table: built once, not per step
+        return self.time_proj(cache)
 
     def trunk(self, h):
         """Apply the looped block to already-embedded activations; returns (h, loops_run)."""

@@ -1,0 +1,73 @@
+"""Selective scan / causal conv1d kernels against the sequential fp32 PyTorch reference
+(forward values and every gradient), including odd sizes (rust-nn tests/selective_scan.rs uses
+finite differences on tiny shapes; here the oracle is autograd through the fp32 recurrence)."""
+import pytest
+import torch
+
+from rust_neural_network_b200.ops import scan as SC
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return float((a - b).norm() / (b.norm() + 1e-9))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,S,D,N,full", [(2, 64, 128, 16, True), (1, 37, 70, 8, True), (2, 130, 256, 16, False), (1, 8, 33, 4, True)])
+def test_selective_scan_fwd_bwd(B, S, D, N, full, dtype):
+    torch.manual_seed(0)
+    dev = "cuda"
+    u = torch.randn(B, S, D, device=dev); delta = torch.randn(B, S, D, device=dev) * 0.5
+    A = -(torch.rand(D, N, device=dev) * 2 + 0.2)
+    Bm = torch.randn(B, S, N, device=dev); Cm = torch.randn(B, S, N, device=dev)
+    Dskip = torch.randn(D, device=dev) if full else None
+    z = torch.randn(B, S, D, device=dev) if full else None
+    dbias = torch.randn(D, device=dev) * 0.3 if full else None
+    softplus = full
+    if not full:
+        delta = delta.abs() + 0.05
+    cast = lambda t: t.to(dtype) if t is not None else None
+    ins_k = [cast(u), cast(delta), A.clone(), cast(Bm), cast(Cm), Dskip.clone() if full else None, cast(z), dbias.clone() if full else None]
+    ins_r = [t.float().clone() if t is not None else None for t in ins_k]
+    for t in ins_k + ins_r:
+        if t is not None:
+            t.requires_grad_(True)
+    y = SC.selective_scan(*ins_k, softplus)
+    yr = SC.selective_scan_ref(*ins_r, softplus)
+    tol = 3e-2 if dtype == torch.bfloat16 else 2e-4
+    assert rel_err(y, yr) < tol
+    w = torch.randn_like(yr)
+    (y.float() * w).sum().backward()
+    (yr * w).sum().backward()
+    names = ["u", "delta", "A", "B", "C", "D", "z", "dbias"]
+    gtol = 6e-2 if dtype == torch.bfloat16 else 2e-3
+    for nm, a, b in zip(names, ins_k, ins_r):
+        if a is None:
+            continue
+        assert a.grad is not None, nm
+        assert rel_err(a.grad, b.grad) < gtol, nm
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,S,C,K,act,bias", [(2, 100, 192, 4, "silu", True), (1, 33, 70, 3, "none", False), (2, 64, 128, 2, "silu", False), (1, 200, 64, 4, "none", True)])
+def test_causal_conv1d(B, S, C, K, act, bias, dtype):
+    torch.manual_seed(1)
+    dev = "cuda"
+    x = torch.randn(B, S, C, device=dev).to(dtype).requires_grad_(True)
+    w = (torch.randn(C, K, device=dev) * 0.5).requires_grad_(True)
+    b = (torch.randn(C, device=dev) * 0.2).requires_grad_(True) if bias else None
+    y = SC.causal_conv1d(x, w, b, act)
+    xr = x.detach().float().requires_grad_(True); wr = w.detach().clone().requires_grad_(True)
+    br = b.detach().clone().requires_grad_(True) if bias else None
+    yr = SC.causal_conv1d_ref(xr, wr, br, act)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    assert rel_err(y, yr) < tol
+    g = torch.randn_like(yr)
+    (y.float() * g).sum().backward(); (yr * g).sum().backward()
+    gtol = 3e-2 if dtype == torch.bfloat16 else 1e-4
+    assert rel_err(x.grad, xr.grad) < gtol
+    assert rel_err(w.grad, wr.grad) < gtol
+    if bias:
+        assert rel_err(b.grad, br.grad) < gtol

@@ -8,13 +8,17 @@
 // GEMM, which folds transposes into packing (rust-nn src/blas.rs:104-186, 273-339), and it is the
 // one routine behind Linear forward (NT), dX (NN) and dW (TN) (src/tensor.rs:767-781, 1649-1687).
 //
-// Structure per CTA (192 threads, one CTA per SM, persistent over output tiles):
+// Structure per CTA (320 threads, one CTA per SM, persistent over output tiles):
 //   warp 0    : TMA producer  - cp.async.bulk.tensor into a ring of 128B-swizzled stages
 //   warp 1    : MMA issuer    - one elected thread issues tcgen05.mma (128 x BN x 16), accumulators
 //                               live in TMEM, double-buffered so the epilogue overlaps the next tile
-//   warps 2-5 : epilogue      - tcgen05.ld TMEM -> registers, fused bias / activation / activation
-//                               gradient / residual, direct global stores (bf16, fp32 or fp32 atomic add
-//                               for split-K and gradient accumulation)
+//   warps 2-9 : epilogue      - two warps per TMEM lane quarter, each draining half of the tile's
+//                               columns: tcgen05.ld TMEM -> registers (one row per thread), fused bias /
+//                               activation / activation gradient / residual, then a transpose through
+//                               a per-warp swizzled shared-memory panel so that global stores (and the
+//                               residual / saved-activation loads) move whole 128-byte row segments.
+//                               fp32 outputs and fp32 atomic accumulation (split-K, gradient
+//                               accumulation) are written straight from registers.
 // All waits are bounded; on expiry a code lands in the status word and the CTA unwinds.
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
@@ -23,9 +27,11 @@
 namespace b200 {
 
 constexpr int BM = 128;
-constexpr int GEMM_THREADS = 192;
+constexpr int EPI_WARPS = 8;
+constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;   // TMA warp + MMA warp + epilogue warps
 constexpr int TILE_K_BYTES = 128;  // one swizzle row
 constexpr int UMMA_K_BYTES = 32;
+constexpr int EPI_PANEL_BYTES = 32 * 128;   // per-warp staging panel: 32 rows x 128 bytes
 
 template <typename T> struct ElemTraits;
 template <> struct ElemTraits<__nv_bfloat16> {
@@ -39,17 +45,23 @@ template <> struct ElemTraits<float> {
   static constexpr bool TF32 = true;
 };
 
+// hardware tanh (MUFU.TANH): relative error ~2^-11, far below bf16 output precision
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float act_fwd(float v, int act) {
   switch (act) {
     case ACT_RELU: return v > 0.f ? v : 0.f;
     case ACT_GELU: {
       const float k0 = 0.7978845608028654f, k1 = 0.044715f;
       float u = k0 * (v + k1 * v * v * v);
-      return 0.5f * v * (1.f + tanhf(u));
+      return 0.5f * v * (1.f + tanh_fast(u));
     }
     case ACT_SILU: return v / (1.f + __expf(-v));
     case ACT_SIGMOID: return 1.f / (1.f + __expf(-v));
-    case ACT_TANH: return tanhf(v);
+    case ACT_TANH: return tanh_fast(v);
     default: return v;
   }
 }
@@ -61,7 +73,7 @@ __device__ __forceinline__ float act_bwd(float s, int act) {
     case ACT_GELU: {
       const float k0 = 0.7978845608028654f, k1 = 0.044715f;
       float u = k0 * (s + k1 * s * s * s);
-      float t = tanhf(u);
+      float t = tanh_fast(u);
       float du = k0 * (1.f + 3.f * k1 * s * s);
       return 0.5f * (1.f + t) + 0.5f * s * (1.f - t * t) * du;
     }
@@ -81,12 +93,71 @@ struct GemmSmem {
   static constexpr int A_BYTES = BM * TILE_K_BYTES;   // 16 KB
   static constexpr int B_BYTES = BN * TILE_K_BYTES;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BUDGET = 200 * 1024;
-  static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int EPI_BYTES = EPI_WARPS * EPI_PANEL_BYTES;   // 32 KB
   static constexpr int BAR_BYTES = 256;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment
+  static constexpr int LIMIT = 227 * 1024;
+  static constexpr int STAGES_RAW = (LIMIT - EPI_BYTES - BAR_BYTES - 1024) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment
 };
+
+// ---------------------------------------------------------------------------- epilogue panel helpers
+// A "panel" is the 32 rows x PW columns (bf16) a warp holds with one row per thread. It is moved
+// through a per-warp shared-memory buffer (rows of PW*2 bytes, 16-byte chunks XOR-swizzled so both
+// the row-owner accesses and the coalesced accesses are bank-conflict free) so that every global
+// load / store instruction of the warp touches RPI complete row segments of PW*2 bytes.
+template <int PW>
+struct Panel {
+  static constexpr int CPR = PW / 8;          // 16-byte chunks per row
+  static constexpr int RPI = 32 / CPR;        // rows per warp-wide instruction
+  static constexpr int NI = 32 / RPI;         // instructions per panel
+  static constexpr int ROW_BYTES = PW * 2;
+  __device__ static __forceinline__ uint32_t off(int row, int chunk) {
+    const int sw = (PW == 64) ? (row & 7) : ((row >> 1) & 3);
+    return row * ROW_BYTES + ((chunk ^ sw) << 4);
+  }
+};
+
+// registers (row owner: this lane = row `lane`, PW fp32 values) -> bf16 -> global, coalesced
+template <int PW>
+__device__ __forceinline__ void panel_store(uint8_t* sbuf, int lane, const float (&f)[PW], __nv_bfloat16* gpanel,
+                                            long long ld, int rows_valid, int chunks_valid) {
+  using P = Panel<PW>;
+  __syncwarp();
+#pragma unroll
+  for (int c = 0; c < P::CPR; ++c) {
+    uint4 o = make_uint4(pack_bf16x2(f[8 * c], f[8 * c + 1]), pack_bf16x2(f[8 * c + 2], f[8 * c + 3]),
+                         pack_bf16x2(f[8 * c + 4], f[8 * c + 5]), pack_bf16x2(f[8 * c + 6], f[8 * c + 7]));
+    *reinterpret_cast<uint4*>(sbuf + P::off(lane, c)) = o;
+  }
+  __syncwarp();
+  const int c = lane % P::CPR, r0 = lane / P::CPR;
+#pragma unroll
+  for (int i = 0; i < P::NI; ++i) {
+    const int row = i * P::RPI + r0;
+    const uint4 v = *reinterpret_cast<const uint4*>(sbuf + P::off(row, c));
+    if (row < rows_valid && c < chunks_valid) *reinterpret_cast<uint4*>(gpanel + (long long)row * ld + c * 8) = v;
+  }
+}
+
+// global (bf16, coalesced) -> row-owner registers: out[c] = 8 bf16 of this lane's row, chunk c
+template <int PW>
+__device__ __forceinline__ void panel_load(uint8_t* sbuf, int lane, const __nv_bfloat16* gpanel, long long ld,
+                                           int rows_valid, int chunks_valid, uint4 (&out)[PW / 8]) {
+  using P = Panel<PW>;
+  __syncwarp();
+  const int c = lane % P::CPR, r0 = lane / P::CPR;
+#pragma unroll
+  for (int i = 0; i < P::NI; ++i) {
+    const int row = i * P::RPI + r0;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < rows_valid && c < chunks_valid) v = *reinterpret_cast<const uint4*>(gpanel + (long long)row * ld + c * 8);
+    *reinterpret_cast<uint4*>(sbuf + P::off(row, c)) = v;
+  }
+  __syncwarp();
+#pragma unroll
+  for (int cc = 0; cc < P::CPR; ++cc) out[cc] = *reinterpret_cast<const uint4*>(sbuf + P::off(lane, cc));
+}
 
 template <typename T, int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -101,7 +172,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+  uint8_t* epi_smem = smem + STAGES * S::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + S::EPI_BYTES);
   uint64_t* full_bar = bars;                 // [STAGES]
   uint64_t* empty_bar = bars + STAGES;       // [STAGES]
   uint64_t* acc_full = bars + 2 * STAGES;    // [2]
@@ -120,7 +192,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], EPI_WARPS); }
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
@@ -211,10 +283,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    const int ew = warp - 2;
+    const int q = warp & 3;                      // TMEM lane quarter this warp may read
+    const int chalf = ew >> 2;                   // which half of the tile's columns this warp drains
+    constexpr int CPW = BN / 2;                  // columns per warp (32, 64 or 128)
+    constexpr int PW = CPW >= 64 ? 64 : 32;      // panel width
+    constexpr int NPANEL = CPW / PW;
+    uint8_t* sbuf = epi_smem + ew * EPI_PANEL_BYTES;
     const float alpha = p.alpha_ptr ? p.alpha * __ldg(p.alpha_ptr) : p.alpha;
-    const int row_in_tile = q * 32 + lane;
+    const bool staged = (p.out_mode == OUT_BF16) && p.vec_ok;       // coalesced bf16 path
     bool ok = true;
     int it = 0;
     for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
@@ -229,111 +307,124 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const uint32_t aphase = (it >> 1) & 1;
       if (!mbar_wait(&acc_full[as], aphase, p.status, ST_TIMEOUT_ACC_FULL)) { ok = false; break; }
       tc_fence_after_sync();
-      const int row = mb * BM + row_in_tile;
+      const int row0 = mb * BM + q * 32;          // first row of this warp's panel
+      const int row = row0 + lane;
       const bool row_ok = row < p.M;
-      const long long crow = (long long)b * p.strideC + (long long)row * p.ldc;
-      const long long rrow = (long long)b * p.strideR + (long long)row * p.ldr;
+      const int rows_valid = min(32, p.M - row0);  // may be <= 0
+      const long long cbase = (long long)b * p.strideC + (long long)row0 * p.ldc;   // element offset of (row0, 0)
+      const long long rbase = (long long)b * p.strideR + (long long)row0 * p.ldr;
       const bool first_split = (split == 0);
+      const uint32_t tbase = tmem_base + (uint32_t(q * 32) << 16) + as * BN + chalf * CPW;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_x32(tmem_base + (uint32_t(q * 32) << 16) + as * BN + c * 32, v);
-        tmem_ld_wait();
-        const int col0 = nb * BN + c * 32;
-        if (!row_ok || col0 >= p.N) continue;
-        float f[32];
+      for (int pn = 0; pn < NPANEL; ++pn) {
+        const int col0 = nb * BN + chalf * CPW + pn * PW;
+        uint32_t v[PW];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) f[j] = has_k ? __uint_as_float(v[j]) * alpha : 0.f;
-        const bool full = (col0 + 32 <= p.N);
+        for (int c = 0; c < PW / 32; ++c) tmem_ld_x32(tbase + pn * PW + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+        tmem_ld_wait();
+        if (rows_valid <= 0 || col0 >= p.N) continue;
+        const int cols_valid = min(PW, p.N - col0);
+        const int chunks_valid = cols_valid / 8;       // staged path has N % 8 == 0
+        const bool full = cols_valid == PW;
+        float f[PW];
+#pragma unroll
+        for (int j = 0; j < PW; ++j) f[j] = has_k ? __uint_as_float(v[j]) * alpha : 0.f;
         if (p.bias && first_split) {
-          if (p.bias_f32) {
+          if (p.bias_f32 && full && p.bias_vec_ok) {
+            const float4* bp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + col0);
+#pragma unroll
+            for (int j = 0; j < PW / 4; ++j) {
+              const float4 bb = __ldg(bp + j);
+              f[4 * j] += bb.x; f[4 * j + 1] += bb.y; f[4 * j + 2] += bb.z; f[4 * j + 3] += bb.w;
+            }
+          } else if (p.bias_f32) {
             const float* bp = reinterpret_cast<const float*>(p.bias) + col0;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) if (full || col0 + j < p.N) f[j] += __ldg(bp + j);
+            for (int j = 0; j < PW; ++j) if (j < cols_valid) f[j] += __ldg(bp + j);
           } else {
             const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) if (full || col0 + j < p.N) f[j] += __bfloat162float(bp[j]);
+            for (int j = 0; j < PW; ++j) if (j < cols_valid) f[j] += __bfloat162float(bp[j]);
           }
         }
-        const bool vec_ok = full && p.vec_ok;
-        if (p.aux_out) {
-          __nv_bfloat16* ap = reinterpret_cast<__nv_bfloat16*>(p.aux_out) + crow + col0;
-          if (vec_ok) {
+        if (p.aux_out) {          // bf16 copy of the pre-activation (dense layout of C)
+          __nv_bfloat16* ap = reinterpret_cast<__nv_bfloat16*>(p.aux_out) + cbase + col0;
+          if (staged) panel_store<PW>(sbuf, lane, f, ap, p.ldc, rows_valid, chunks_valid);
+          else if (row_ok) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 o = make_uint4(pack_bf16x2(f[j], f[j + 1]), pack_bf16x2(f[j + 2], f[j + 3]),
-                                   pack_bf16x2(f[j + 4], f[j + 5]), pack_bf16x2(f[j + 6], f[j + 7]));
-              *reinterpret_cast<uint4*>(ap + j) = o;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) if (col0 + j < p.N) ap[j] = __float2bfloat16(f[j]);
+            for (int j = 0; j < PW; ++j) if (j < cols_valid) ap[(long long)lane * p.ldc + j] = __float2bfloat16(f[j]);
           }
         }
-        if (p.act != ACT_NONE) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) f[j] = act_fwd(f[j], p.act);
+        // the activation switch sits OUTSIDE the element loops: one straight-line loop per case keeps
+        // the unrolled epilogue small enough for the instruction cache
+        switch (p.act) {
+#define B200_ACT_CASE(A) case A: { _Pragma("unroll") for (int j = 0; j < PW; ++j) f[j] = act_fwd(f[j], A); } break;
+          B200_ACT_CASE(ACT_RELU) B200_ACT_CASE(ACT_GELU) B200_ACT_CASE(ACT_SILU) B200_ACT_CASE(ACT_SIGMOID) B200_ACT_CASE(ACT_TANH)
+#undef B200_ACT_CASE
+          default: break;
         }
-        if (p.aux_in) {
-          const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + crow + col0;
-          if (vec_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 u = *reinterpret_cast<const uint4*>(ap + j);
-              float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y), a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
-              f[j] *= act_bwd(a0.x, p.dact); f[j + 1] *= act_bwd(a0.y, p.dact);
-              f[j + 2] *= act_bwd(a1.x, p.dact); f[j + 3] *= act_bwd(a1.y, p.dact);
-              f[j + 4] *= act_bwd(a2.x, p.dact); f[j + 5] *= act_bwd(a2.y, p.dact);
-              f[j + 6] *= act_bwd(a3.x, p.dact); f[j + 7] *= act_bwd(a3.y, p.dact);
+        if (p.aux_in) {           // multiply by act'(saved)
+          const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + cbase + col0;
+          if (staged) {
+            uint4 u[PW / 8];
+            panel_load<PW>(sbuf, lane, ap, p.ldc, rows_valid, chunks_valid, u);
+            switch (p.dact) {
+#define B200_DACT_CASE(A) case A: { _Pragma("unroll") for (int j = 0; j < PW / 8; ++j) { \
+                const float2 a0 = unpack_bf16x2(u[j].x), a1 = unpack_bf16x2(u[j].y), a2 = unpack_bf16x2(u[j].z), a3 = unpack_bf16x2(u[j].w); \
+                f[8 * j] *= act_bwd(a0.x, A); f[8 * j + 1] *= act_bwd(a0.y, A); f[8 * j + 2] *= act_bwd(a1.x, A); f[8 * j + 3] *= act_bwd(a1.y, A); \
+                f[8 * j + 4] *= act_bwd(a2.x, A); f[8 * j + 5] *= act_bwd(a2.y, A); f[8 * j + 6] *= act_bwd(a3.x, A); f[8 * j + 7] *= act_bwd(a3.y, A); } } break;
+              B200_DACT_CASE(ACT_RELU) B200_DACT_CASE(ACT_GELU) B200_DACT_CASE(ACT_SILU) B200_DACT_CASE(ACT_SIGMOID) B200_DACT_CASE(ACT_TANH)
+#undef B200_DACT_CASE
+              default: break;
             }
-          } else {
+          } else if (row_ok) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) if (col0 + j < p.N) f[j] *= act_bwd(__bfloat162float(ap[j]), p.dact);
+            for (int j = 0; j < PW; ++j) if (j < cols_valid) f[j] *= act_bwd(__bfloat162float(ap[(long long)lane * p.ldc + j]), p.dact);
           }
         }
         if (p.residual && first_split) {
-          const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(p.residual) + rrow + col0;
-          if (full && p.res_vec_ok) {
+          const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(p.residual) + rbase + col0;
+          if (staged && p.res_vec_ok) {
+            uint4 u[PW / 8];
+            panel_load<PW>(sbuf, lane, rp, p.ldr, rows_valid, chunks_valid, u);
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 u = *reinterpret_cast<const uint4*>(rp + j);
-              float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y), a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
-              f[j] += a0.x; f[j + 1] += a0.y; f[j + 2] += a1.x; f[j + 3] += a1.y;
-              f[j + 4] += a2.x; f[j + 5] += a2.y; f[j + 6] += a3.x; f[j + 7] += a3.y;
+            for (int j = 0; j < PW / 8; ++j) {
+              const float2 a0 = unpack_bf16x2(u[j].x), a1 = unpack_bf16x2(u[j].y), a2 = unpack_bf16x2(u[j].z), a3 = unpack_bf16x2(u[j].w);
+              f[8 * j] += a0.x; f[8 * j + 1] += a0.y; f[8 * j + 2] += a1.x; f[8 * j + 3] += a1.y;
+              f[8 * j + 4] += a2.x; f[8 * j + 5] += a2.y; f[8 * j + 6] += a3.x; f[8 * j + 7] += a3.y;
             }
-          } else {
+          } else if (row_ok) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) if (col0 + j < p.N) f[j] += __bfloat162float(rp[j]);
+            for (int j = 0; j < PW; ++j) if (j < cols_valid) f[j] += __bfloat162float(rp[(long long)lane * p.ldr + j]);
           }
         }
         if (p.out_mode == OUT_BF16) {
-          __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + crow + col0;
-          if (vec_ok) {
+          __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + cbase + col0;
+          if (staged) panel_store<PW>(sbuf, lane, f, cp, p.ldc, rows_valid, chunks_valid);
+          else if (row_ok) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 o = make_uint4(pack_bf16x2(f[j], f[j + 1]), pack_bf16x2(f[j + 2], f[j + 3]),
-                                   pack_bf16x2(f[j + 4], f[j + 5]), pack_bf16x2(f[j + 6], f[j + 7]));
-              *reinterpret_cast<uint4*>(cp + j) = o;
+            for (int j = 0; j < PW; ++j) if (j < cols_valid) cp[(long long)lane * p.ldc + j] = __float2bfloat16(f[j]);
+          }
+        } else if (row_ok) {
+          float* cp = reinterpret_cast<float*>(p.C) + cbase + (long long)lane * p.ldc + col0;
+          const bool vec = full && p.vec_ok;
+          if (p.out_mode == OUT_F32) {
+            if (vec) {
+#pragma unroll
+              for (int j = 0; j < PW; j += 4) *reinterpret_cast<float4*>(cp + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < PW; ++j) if (j < cols_valid) cp[j] = f[j];
             }
-          } else {
+          } else {  // OUT_F32_ATOMIC
+            if (vec) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) if (col0 + j < p.N) cp[j] = __float2bfloat16(f[j]);
+              for (int j = 0; j < PW; j += 4) atomicAdd(reinterpret_cast<float4*>(cp + j), make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]));
+            } else {
+#pragma unroll
+              for (int j = 0; j < PW; ++j) if (j < cols_valid) atomicAdd(cp + j, f[j]);
+            }
           }
-        } else if (p.out_mode == OUT_F32) {
-          float* cp = reinterpret_cast<float*>(p.C) + crow + col0;
-          if (vec_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              *reinterpret_cast<float4*>(cp + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) if (col0 + j < p.N) cp[j] = f[j];
-          }
-        } else {  // OUT_F32_ATOMIC
-          float* cp = reinterpret_cast<float*>(p.C) + crow + col0;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) if (col0 + j < p.N) atomicAdd(cp + j, f[j]);
         }
       }
       tc_fence_before_sync();
@@ -424,7 +515,7 @@ extern "C" int b200_gemm_launch(const b200::GemmArgs* args, int bn, int num_sms,
   if (a.p.M <= 0 || a.p.N <= 0 || a.p.batch <= 0) return 0;
   if (a.is_f32) {
     // TF32 runs K-major only: MN-major 32-bit operands need a different swizzle atom, so the
-    // front-end hands this path explicitly transposed operands (b200_transpose below).
+    // front-end hands this path explicitly transposed operands (b200_transpose).
     if (a.a_mn || a.b_mn) return -4;
     return launch_one<float, 128, false, false>(a, stream, num_sms);
   }

@@ -92,7 +92,7 @@ __global__ void rmsprop_kernel(float* __restrict__ p, const float* __restrict__ 
 __global__ void muon_sumsq_kernel(const float* __restrict__ g, const long long* __restrict__ seg_off, int nseg,
                                   float* __restrict__ seg_sumsq) {
   int s = blockIdx.y;
-  long long a = seg_off[s], b = seg_off[s + 1];
+  long long a = seg_off[2 * s], b = seg_off[2 * s + 1];
   float acc = 0.f;
   for (long long i = a + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < b; i += (long long)gridDim.x * blockDim.x)
     acc += g[i] * g[i];
@@ -110,7 +110,7 @@ __global__ void muon_rms_kernel(float* __restrict__ p, const float* __restrict__
                                 __nv_bfloat16* __restrict__ shadow, const long long* __restrict__ seg_off, int nseg,
                                 const float* __restrict__ seg_sumsq, float lr, float momentum, float eps) {
   int s = blockIdx.y;
-  long long a = seg_off[s], b = seg_off[s + 1];
+  long long a = seg_off[2 * s], b = seg_off[2 * s + 1];
   float rms = fmaxf(sqrtf(seg_sumsq[s] / (float)(b - a > 0 ? b - a : 1)), eps);
   for (long long i = a + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < b; i += (long long)gridDim.x * blockDim.x) {
     float gn = g[i] / rms;
@@ -158,7 +158,7 @@ int b200_rmsprop(float* p, const float* g, float* v, void* shadow_bf16, long lon
   rmsprop_kernel<<<ogrid(n, 1), 256, 0, st>>>(p, g, v, (__nv_bfloat16*)shadow_bf16, n, lr, alpha, eps, grad_scale_ptr);
   return (int)cudaGetLastError();
 }
-// seg_off: device array of nseg+1 offsets into the flat buffers; seg_sumsq: device scratch of nseg floats
+// seg_off: device array of nseg [begin, end) pairs into the flat buffers; seg_sumsq: device scratch of nseg floats
 int b200_muon_rms(float* p, const float* g, float* buf, void* shadow_bf16, const long long* seg_off, int nseg,
                   float* seg_sumsq, float lr, float momentum, float eps, cudaStream_t st) {
   if (nseg <= 0) return 0;

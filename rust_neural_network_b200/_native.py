@@ -21,7 +21,7 @@ class GemmParams(C.Structure):
     _fields_ = [
         ("M", c_int), ("N", c_int), ("K", c_int), ("batch", c_int), ("splits", c_int),
         ("C", c_void_p), ("ldc", c_ll), ("strideC", c_ll),
-        ("bias", c_void_p), ("bias_f32", c_int),
+        ("bias", c_void_p), ("bias_f32", c_int), ("bias_vec_ok", c_int),
         ("residual", c_void_p), ("ldr", c_ll), ("strideR", c_ll),
         ("aux_out", c_void_p), ("aux_in", c_void_p),
         ("alpha", c_float), ("alpha_ptr", c_void_p), ("act", c_int), ("dact", c_int), ("out_mode", c_int),

@@ -200,6 +200,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     p.M, p.N, p.K, p.batch, p.splits = M, N, K, batch, splits
     p.C, p.ldc, p.strideC = out3.data_ptr(), ldc, out3.stride(0) if batch > 1 else M * ldc
     p.bias = nv.ptr(bias); p.bias_f32 = 1 if (bias is not None and bias.dtype == torch.float32) else 0
+    p.bias_vec_ok = 1 if (bias is not None and bias.data_ptr() % 16 == 0 and bias.is_contiguous()) else 0
     p.residual = nv.ptr(residual)
     p.ldr = residual.stride(1) if residual is not None else 0
     p.strideR = residual.stride(0) if residual is not None else 0

@@ -492,12 +492,13 @@ def rmsprop_step(p, g, v, shadow, lr, alpha, eps, grad_scale=None):
 
 def muon_rms_step(p, g, buf, shadow, seg_off, lr, momentum, eps=1e-8, scratch=None):
     """Reference-variant Muon: per-tensor RMS-normalised gradient then momentum SGD. `seg_off` is an
-    int64 tensor of nseg+1 offsets delimiting the tensors inside the flat buffers."""
-    nseg = seg_off.numel() - 1
+    int64 [nseg, 2] table of [begin, end) ranges of the tensors inside the flat buffers."""
+    seg_off = seg_off.reshape(-1, 2)
+    nseg = seg_off.shape[0]
     if not p.is_cuda:
         offs = seg_off.tolist()
         for s in range(nseg):
-            a, b = offs[s], offs[s + 1]
+            a, b = offs[s]
             gg = g[a:b]
             rms = max(float((gg * gg).mean().sqrt()), eps) if b > a else 1.0
             buf[a:b].mul_(momentum).add_(gg / rms)

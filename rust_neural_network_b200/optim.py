@@ -85,8 +85,9 @@ class FlatParams:
                 self.shadow.copy_(self.master)
 
     def segments(self) -> torch.Tensor:
-        """int64 offsets [nseg+1] of the parameters in layout order (padding belongs to the previous segment)."""
-        offs = [self.offsets[id(p)] for p in self.order] + [self.numel]
+        """int64 [nseg, 2] table of [begin, end) element ranges of the parameters in layout order
+        (alignment padding between parameters belongs to no segment)."""
+        offs = [[self.offsets[id(p)], self.offsets[id(p)] + p.numel()] for p in self.order]
         return torch.tensor(offs, dtype=torch.int64, device=self.device)
 
     def refresh_views(self):
@@ -221,7 +222,7 @@ class Muon(Optimizer):
         self.momentum, self.mode, self.ns_steps = float(momentum), mode, ns_steps
         self.buf = torch.zeros_like(self.flat.master)
         self.seg = self.flat.segments()
-        self._scratch = torch.zeros(self.seg.numel() - 1, dtype=torch.float32, device=self.flat.device)
+        self._scratch = torch.zeros(self.seg.shape[0], dtype=torch.float32, device=self.flat.device)
 
     def step(self):
         if self.mode == "rms":

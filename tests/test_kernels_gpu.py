@@ -265,7 +265,7 @@ def test_sgd_rmsprop_muon():
         pd = p0.to(DEV).clone(); pc = p0.clone()
         sd = torch.zeros(n, device=DEV); sc = torch.zeros(n)
         std = torch.zeros(1, device=DEV); stc = torch.zeros(1)
-        seg = torch.tensor([0, 1000, 1000, n], dtype=torch.int64)
+        seg = torch.tensor([[0, 1000], [1000, 1000], [1000, n]], dtype=torch.int64)
         for gi in (g1, g2):
             if name == "sgd":
                 K.sgd_step(pd, gi.to(DEV), sd, None, 0.1, 0.9, std); K.sgd_step(pc, gi, sc, None, 0.1, 0.9, stc)

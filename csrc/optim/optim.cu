@@ -178,3 +178,69 @@ int b200_incr_step(float* step, cudaStream_t st) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of b200_muon_rms (declared in optim_noalloc.h).
+//
+// b200_muon_rms needs one float of scratch per parameter segment (the per-tensor sum of squared
+// gradients) and takes that scratch from its caller. Some callers have no way to provide it: code
+// that runs where the device allocator must not be touched - inside a region that a framework has
+// frozen (a captured or replayed stream, a memory pool that is closed for the duration of a step), in
+// a signal-safe or real-time section, or in a host program that was handed device pointers by
+// another runtime and owns no allocator of its own. For them the scratch lives in a fixed array
+// inside this library: every GPU that loads the library holds B200_NOALLOC_MAX_SEGMENTS floats
+// (16 KiB) until the process exits, and this entry point calls no cudaMalloc / cudaFree and no
+// allocating library routine.
+//
+// Contract:
+//   * at most B200_NOALLOC_MAX_SEGMENTS segments; more is rejected with B200_NOALLOC_TOO_MANY_SEGMENTS
+//     (and a message on stderr) before anything is launched;
+//   * the first call on a device looks up the device address of the array (cudaGetSymbolAddress, with
+//     that device current) and remembers it; make that first call outside any stream capture;
+//   * all calls share the one array, which keeps the previous call's sums: the entry point clears
+//     the part it uses on the caller's stream before accumulating into it, and two calls that
+//     overlap on the GPU (different streams, no ordering between them) race on it - serialise them.
+#include "optim_noalloc.h"
+#include <cstdio>
+
+namespace b200 {
+
+static __device__ __align__(256) float g_noalloc_seg_sumsq[B200_NOALLOC_MAX_SEGMENTS];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+// Device address of g_noalloc_seg_sumsq per device ordinal. In host code the array's NAME is only a
+// stand-in for the symbol, not a device address, so it must never be passed to a kernel directly.
+static float* g_noalloc_scratch_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+
+}  // namespace b200
+
+extern "C" int b200_muon_rms_noalloc(float* p, const float* g, float* buf, void* shadow_bf16, const long long* seg_off,
+                                     int nseg, float lr, float momentum, float eps, cudaStream_t st) {
+  using namespace b200;
+  if (nseg <= 0) return 0;
+  if (nseg > B200_NOALLOC_MAX_SEGMENTS) {
+    fprintf(stderr, "b200_muon_rms_noalloc: %d segments exceed the built-in scratch of %d segments; "
+                    "use b200_muon_rms with caller-provided scratch\n", nseg, B200_NOALLOC_MAX_SEGMENTS);
+    return B200_NOALLOC_TOO_MANY_SEGMENTS;
+  }
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return B200_NOALLOC_BAD_DEVICE;
+  float* scratch = g_noalloc_scratch_ptr[dev];
+  if (scratch == nullptr) {
+    // one-time set-up for this device (it is the current device here)
+    void* sym = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&sym, g_noalloc_seg_sumsq);
+    if (e != cudaSuccess || sym == nullptr) {
+      fprintf(stderr, "b200_muon_rms_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+      return B200_NOALLOC_SYMBOL_LOOKUP_FAILED;
+    }
+    scratch = static_cast<float*>(sym);
+    g_noalloc_scratch_ptr[dev] = scratch;
+  }
+  // the array still holds the sums of the previous call: clear the part this call accumulates into
+  if (cudaMemsetAsync(scratch, 0, sizeof(float) * nseg, st) != cudaSuccess) return (int)cudaGetLastError();
+  dim3 grid(32, nseg);
+  muon_sumsq_kernel<<<grid, 256, 0, st>>>(g, seg_off, nseg, scratch);
+  muon_rms_kernel<<<grid, 256, 0, st>>>(p, g, buf, (__nv_bfloat16*)shadow_bf16, seg_off, nseg, scratch, lr, momentum, eps);
+  return (int)cudaGetLastError();
+}

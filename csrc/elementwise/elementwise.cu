@@ -38,10 +38,14 @@ enum : int {
   OP_ADD = 0, OP_SUB = 1, OP_MUL = 2, OP_DIV = 3,
   OP_RELU = 10, OP_GELU = 11, OP_SILU = 12, OP_SIGMOID = 13, OP_TANH = 14, OP_SOFTPLUS = 15,
   OP_SCALE = 16, OP_EXP = 17, OP_ABS = 18, OP_SQUARE = 19, OP_CLAMP = 20, OP_ROUND = 21, OP_ADD_SCALAR = 22,
+  // linear-attention feature maps of (s0 * x): elu(x)+1 and relu(x)^2 (rust-nn src/linear_attention.rs:42-94)
+  OP_ELU1 = 23, OP_RELU2 = 24,
   // backward of a unary op: out = g * f'(saved); saved is the INPUT of the forward op
   OP_RELU_BWD = 30, OP_GELU_BWD = 31, OP_SILU_BWD = 32, OP_SIGMOID_BWD = 33, OP_TANH_BWD = 34, OP_SOFTPLUS_BWD = 35,
   // fused: out = a * silu(b)  (Mamba gate) and its two gradients
   OP_SIGMOID_BWD_OUT = 36, OP_TANH_BWD_OUT = 37,
+  OP_DIV_BWD_B = 38,   // -a * b
+  OP_ELU1_BWD = 41, OP_RELU2_BWD = 42,   // saved = the (already scaled) input of the feature map
   OP_MUL_SILU = 40,
 };
 
@@ -60,6 +64,8 @@ __device__ __forceinline__ float unary_apply(float x, int op, float s0, float s1
     case OP_SQUARE: return x * x;
     case OP_CLAMP: return fminf(fmaxf(x, s0), s1);
     case OP_ROUND: return rintf(x);
+    case OP_ELU1: { float v = x * s0; return v > 0.f ? v + 1.f : __expf(v); }
+    case OP_RELU2: { float v = x * s0; return v > 0.f ? v * v : 0.f; }
     default: return x;
   }
 }
@@ -77,6 +83,9 @@ __device__ __forceinline__ float binary_apply(float a, float b, int op) {
     case OP_SOFTPLUS_BWD: return a / (1.f + __expf(-b));
     case OP_SIGMOID_BWD_OUT: return a * b * (1.f - b);
     case OP_TANH_BWD_OUT: return a * (1.f - b * b);
+    case OP_DIV_BWD_B: return -a * b;
+    case OP_ELU1_BWD: return b > 0.f ? a : a * __expf(b);
+    case OP_RELU2_BWD: return b > 0.f ? 2.f * a * b : 0.f;
     case OP_MUL_SILU: return a * b / (1.f + __expf(-b));
     default: return a;
   }

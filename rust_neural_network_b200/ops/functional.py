@@ -108,18 +108,40 @@ def linear(x, w, b=None, act="none", residual=None):
 
 
 # ----------------------------------------------------------------------------- matmul (2-D or batched)
+def _mm(a, b, out_dtype=None):
+    """a [.., M, K] @ b [.., K, N] where either operand may be a transposed VIEW: the view's layout
+    becomes the kernel's K-major / MN-major flag, so no transposed copy is made."""
+    if a.stride(-1) == 1:
+        A, a_mn = a, False
+    elif a.stride(-2) == 1:
+        A, a_mn = a.transpose(-1, -2), True            # stored [K, M]
+    else:
+        A, a_mn = a.contiguous(), False
+    if b.stride(-1) == 1:
+        Bm, b_mn = b, True                             # stored [K, N]
+    elif b.stride(-2) == 1:
+        Bm, b_mn = b.transpose(-1, -2), False          # stored [N, K]
+    else:
+        Bm, b_mn = b.contiguous(), True
+    if A.dtype != Bm.dtype:
+        Bm = Bm.to(A.dtype)
+    return gemm(A, Bm, a_mn=a_mn, b_mn=b_mn, out_dtype=out_dtype)
+
+
 class MatmulFn(Function):
     @staticmethod
     def forward(ctx, a, b):
         ctx.save_for_backward(a, b)
-        return gemm(a.contiguous(), b.contiguous(), b_mn=True)
+        return _mm(a, b)
 
     @staticmethod
     def backward(ctx, g):
         a, b = ctx.saved_tensors
-        g = g.contiguous()
-        da = gemm(g, b.contiguous()) if ctx.needs_input_grad[0] else None            # g @ b^T
-        db = gemm(a.contiguous(), g, a_mn=True, b_mn=True) if ctx.needs_input_grad[1] else None   # a^T @ g
+        if g.stride(-1) != 1 and g.stride(-2) != 1:
+            g = g.contiguous()
+        g = g.to(a.dtype) if g.dtype != a.dtype else g
+        da = _mm(g, b.transpose(-1, -2)) if ctx.needs_input_grad[0] else None       # g @ b^T
+        db = _mm(a.transpose(-1, -2), g) if ctx.needs_input_grad[1] else None       # a^T @ g
         return da, db
 
 

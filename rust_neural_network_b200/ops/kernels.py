@@ -17,9 +17,9 @@ from .. import _native as nv
 OPS = {
     "add": 0, "sub": 1, "mul": 2, "div": 3,
     "relu": 10, "gelu": 11, "silu": 12, "sigmoid": 13, "tanh": 14, "softplus": 15,
-    "scale": 16, "exp": 17, "abs": 18, "square": 19, "clamp": 20, "round": 21, "add_scalar": 22,
+    "scale": 16, "exp": 17, "abs": 18, "square": 19, "clamp": 20, "round": 21, "add_scalar": 22, "elu1": 23, "relu2": 24,
     "relu_bwd": 30, "gelu_bwd": 31, "silu_bwd": 32, "sigmoid_bwd": 33, "tanh_bwd": 34, "softplus_bwd": 35,
-    "sigmoid_bwd_out": 36, "tanh_bwd_out": 37, "mul_silu": 40,
+    "sigmoid_bwd_out": 36, "tanh_bwd_out": 37, "div_bwd_b": 38, "mul_silu": 40, "elu1_bwd": 41, "relu2_bwd": 42,
 }
 
 
@@ -40,6 +40,7 @@ def unary_ref(x, op, s0=0.0, s1=0.0):
         "sigmoid": lambda: torch.sigmoid(f), "tanh": lambda: torch.tanh(f), "softplus": lambda: F.softplus(f, threshold=20.0),
         "scale": lambda: f * s0, "exp": lambda: torch.exp(f), "abs": lambda: f.abs(), "square": lambda: f * f,
         "clamp": lambda: f.clamp(s0, s1), "round": lambda: torch.round(f), "add_scalar": lambda: f + s0,
+        "elu1": lambda: torch.where(f * s0 > 0, f * s0 + 1, torch.exp(f * s0)), "relu2": lambda: torch.relu(f * s0) ** 2,
     }[op]()
     return r.to(x.dtype)
 
@@ -57,6 +58,9 @@ def binary_ref(a, b, op):
     elif op == "sigmoid_bwd": s = torch.sigmoid(fb); r = fa * s * (1 - s)
     elif op == "tanh_bwd": t = torch.tanh(fb); r = fa * (1 - t * t)
     elif op == "softplus_bwd": r = fa * torch.sigmoid(fb)
+    elif op == "elu1_bwd": r = torch.where(fb > 0, fa, fa * torch.exp(fb))
+    elif op == "relu2_bwd": r = torch.where(fb > 0, 2 * fa * fb, torch.zeros_like(fa))
+    elif op == "div_bwd_b": r = -fa * fb
     elif op == "sigmoid_bwd_out": r = fa * fb * (1 - fb)
     elif op == "tanh_bwd_out": r = fa * (1 - fb * fb)
     elif op == "mul_silu": r = fa * torch.nn.functional.silu(fb)

@@ -161,6 +161,19 @@ __global__ void colsum_kernel(const T* __restrict__ x, float* __restrict__ out, 
   atomicAdd(out + c, acc);
 }
 
+// batched column sum: out[z, c] += sum_r x[z, r, c]  (per-expert bias gradients)
+template <typename T>
+__global__ void colsum_batched_kernel(const T* __restrict__ x, float* __restrict__ out, long long rows, int cols,
+                                      long long ld, long long bs) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  const T* xp = x + blockIdx.z * bs;
+  long long r0 = (long long)blockIdx.y * 256, r1 = r0 + 256; if (r1 > rows) r1 = rows;
+  float acc = 0.f;
+  for (long long r = r0; r < r1; ++r) acc += to_f(xp[r * ld + c]);
+  atomicAdd(out + (long long)blockIdx.z * cols + c, acc);
+}
+
 // full reduction sum / sum of squares / max / min into fp32 scalar slots (out[0..3])
 template <typename T>
 __global__ void reduce_kernel(const T* __restrict__ x, float* __restrict__ out, long long n, int what) {
@@ -343,6 +356,15 @@ int b200_colsum(const void* x, float* out, long long rows, int cols, long long l
   dim3 grid((cols + 127) / 128, (unsigned)((rows + rpb - 1) / rpb));
   if (is_bf16) colsum_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, out, rows, cols, ld, rpb);
   else colsum_kernel<float><<<grid, 128, 0, st>>>((const float*)x, out, rows, cols, ld, rpb);
+  return (int)cudaGetLastError();
+}
+
+int b200_colsum_batched(const void* x, float* out, int batch, long long rows, int cols, long long ld, long long bs,
+                        int is_bf16, cudaStream_t st) {
+  if (rows <= 0 || cols <= 0 || batch <= 0) return 0;
+  dim3 grid((cols + 127) / 128, (unsigned)((rows + 255) / 256), batch);
+  if (is_bf16) colsum_batched_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, out, rows, cols, ld, bs);
+  else colsum_batched_kernel<float><<<grid, 128, 0, st>>>((const float*)x, out, rows, cols, ld, bs);
   return (int)cudaGetLastError();
 }
 

@@ -331,18 +331,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         for (int j = 0; j < PW; ++j) f[j] = has_k ? __uint_as_float(v[j]) * alpha : 0.f;
         if (p.bias && first_split) {
           if (p.bias_f32 && full && p.bias_vec_ok) {
-            const float4* bp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + col0);
+            const float4* bp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + b * p.strideBias + col0);
 #pragma unroll
             for (int j = 0; j < PW / 4; ++j) {
               const float4 bb = __ldg(bp + j);
               f[4 * j] += bb.x; f[4 * j + 1] += bb.y; f[4 * j + 2] += bb.z; f[4 * j + 3] += bb.w;
             }
           } else if (p.bias_f32) {
-            const float* bp = reinterpret_cast<const float*>(p.bias) + col0;
+            const float* bp = reinterpret_cast<const float*>(p.bias) + b * p.strideBias + col0;
 #pragma unroll
             for (int j = 0; j < PW; ++j) if (j < cols_valid) f[j] += __ldg(bp + j);
           } else {
-            const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
+            const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(p.bias) + b * p.strideBias + col0;
 #pragma unroll
             for (int j = 0; j < PW; ++j) if (j < cols_valid) f[j] += __bfloat162float(bp[j]);
           }

@@ -14,6 +14,7 @@ struct GemmParams {
   int splits;              // split-K factor; >1 requires OUT_F32_ATOMIC
   void* C; long long ldc, strideC;
   const void* bias; int bias_f32; int bias_vec_ok;   // bias_vec_ok: fp32 bias is 16-byte aligned
+  long long strideBias;    // elements between the bias vectors of consecutive batches (0: shared)
   const void* residual; long long ldr, strideR;   // bf16, added after the activation
   void* aux_out;           // bf16 copy of the pre-activation value (layout of C)
   const void* aux_in;      // bf16 saved value; result is multiplied by act'(aux_in) (layout of C)

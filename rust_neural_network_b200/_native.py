@@ -21,7 +21,7 @@ class GemmParams(C.Structure):
     _fields_ = [
         ("M", c_int), ("N", c_int), ("K", c_int), ("batch", c_int), ("splits", c_int),
         ("C", c_void_p), ("ldc", c_ll), ("strideC", c_ll),
-        ("bias", c_void_p), ("bias_f32", c_int), ("bias_vec_ok", c_int),
+        ("bias", c_void_p), ("bias_f32", c_int), ("bias_vec_ok", c_int), ("strideBias", c_ll),
         ("residual", c_void_p), ("ldr", c_ll), ("strideR", c_ll),
         ("aux_out", c_void_p), ("aux_in", c_void_p),
         ("alpha", c_float), ("alpha_ptr", c_void_p), ("act", c_int), ("dact", c_int), ("out_mode", c_int),
@@ -63,6 +63,7 @@ _SIGS = {
     "b200_cast": [c_void_p, c_void_p, c_ll, c_float, c_int, c_void_p],
     "b200_transpose": [c_void_p, c_void_p, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_int, c_int, c_void_p],
     "b200_colsum": [c_void_p, c_void_p, c_ll, c_int, c_ll, c_int, c_void_p],
+    "b200_colsum_batched": [c_void_p, c_void_p, c_int, c_ll, c_int, c_ll, c_ll, c_int, c_void_p],
     "b200_reduce": [c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p],
     "b200_dropout": [c_void_p, c_void_p, c_ll, c_float, c_ull, c_int, c_void_p],
     "b200_fake_quant": [c_void_p, c_void_p, c_ll, c_float, c_float, c_float, c_int, c_void_p],

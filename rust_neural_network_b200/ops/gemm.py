@@ -69,7 +69,7 @@ def gemm_ref(a, b, *, a_mn=False, b_mn=False, bias=None, act="none", residual=No
     B = b.float().transpose(-1, -2) if b_mn else b.float()
     v = alpha * (A @ B.transpose(-1, -2))
     if bias is not None:
-        v = v + bias.float()
+        v = v + (bias.float()[:, None, :] if bias.dim() == 2 else bias.float())   # [batch, N]: one vector per batch
     pre = v
     v = act_ref(v, act)
     if aux_in is not None:
@@ -200,7 +200,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     p.M, p.N, p.K, p.batch, p.splits = M, N, K, batch, splits
     p.C, p.ldc, p.strideC = out3.data_ptr(), ldc, out3.stride(0) if batch > 1 else M * ldc
     p.bias = nv.ptr(bias); p.bias_f32 = 1 if (bias is not None and bias.dtype == torch.float32) else 0
-    p.bias_vec_ok = 1 if (bias is not None and bias.data_ptr() % 16 == 0 and bias.is_contiguous()) else 0
+    p.bias_vec_ok = 1 if (bias is not None and bias.data_ptr() % 16 == 0 and bias.is_contiguous() and N % 4 == 0) else 0
+    p.strideBias = N if (bias is not None and bias.dim() == 2) else 0      # [batch, N] bias: one vector per batch
     p.residual = nv.ptr(residual)
     p.ldr = residual.stride(1) if residual is not None else 0
     p.strideR = residual.stride(0) if residual is not None else 0

@@ -1,0 +1,102 @@
+"""MoE kernels: router forward/backward against torch softmax/top-k autograd, routed experts
+(dispatch -> batched expert GEMMs -> combine) against the dense per-token fp32 loop, incl. gradients;
+linear attention on the GPU against the O(S^2) reference."""
+import pytest
+import torch
+
+from rust_neural_network_b200.models import moe as M
+from rust_neural_network_b200.ops.linear_attention import linear_attention, linear_attention_ref
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(a, b):
+    a, b = a.float().cpu(), b.float().cpu()
+    return float((a - b).norm() / (b.norm() + 1e-9))
+
+
+@pytest.mark.parametrize("T,E,k,renorm", [(100, 8, 2, True), (257, 64, 6, True), (64, 40, 3, False), (33, 200, 8, True)])
+def test_router_forward_backward(T, E, k, renorm):
+    torch.manual_seed(0)
+    logits = (torch.randn(T, E, device="cuda") * 2).requires_grad_(True)
+    idx, w, counts, aux = M.RouterFn.apply(logits, k, renorm, 0.01)
+    lr = logits.detach().clone().requires_grad_(True)
+    p = torch.softmax(lr, -1)
+    wr, ir = torch.topk(p, k, dim=-1)
+    if renorm:
+        wr = wr / wr.sum(-1, keepdim=True)
+    assert torch.equal(idx.long(), ir)
+    assert torch.allclose(w, wr, atol=1e-5)
+    assert torch.equal(counts.long(), torch.bincount(ir.reshape(-1), minlength=E))
+    f = counts.float() / (T * k)
+    auxr = E * (f * p.mean(0)).sum()
+    assert torch.allclose(aux, auxr, atol=1e-5)
+    g = torch.randn_like(w)
+    ((w * g).sum() + 3.0 * aux).backward()
+    ((wr * g).sum() + 3.0 * auxr).backward()
+    assert rel_err(logits.grad, lr.grad) < 1e-3
+
+
+@pytest.mark.parametrize("act", ["relu", "silu"])
+def test_routed_experts_match_dense_loop(act):
+    torch.manual_seed(1)
+    T, d, hid, E, k = 300, 64, 128, 8, 2
+    dev = "cuda"
+    x = (torch.randn(T, d, device=dev) * 0.5).bfloat16().requires_grad_(True)
+    W1 = torch.nn.Parameter(torch.randn(E, hid, d, device=dev) * 0.1); b1 = torch.nn.Parameter(torch.randn(E, hid, device=dev) * 0.1)
+    W2 = torch.nn.Parameter(torch.randn(E, d, hid, device=dev) * 0.1); b2 = torch.nn.Parameter(torch.randn(E, d, device=dev) * 0.1)
+    logits = torch.randn(T, E, device=dev)
+    idx, w, _, _ = M.RouterFn.apply(logits, k, True, 0.0)
+    w = w.detach().requires_grad_(True)
+    out = M.MoEExpertsFn.apply(x, idx, w, W1, b1, W2, b2, act, 384, None)       # capacity large enough: nothing dropped
+    xr = x.detach().float().requires_grad_(True); wr = w.detach().clone().requires_grad_(True)
+    ps = [t.detach().clone().requires_grad_(True) for t in (W1, b1, W2, b2)]
+    ref = M._experts_dense_autograd(xr, idx, wr, *ps, act)
+    assert rel_err(out, ref) < 2e-2
+    g = torch.randn_like(ref)
+    (out.float() * g).sum().backward(); (ref * g).sum().backward()
+    assert rel_err(x.grad, xr.grad) < 3e-2
+    assert rel_err(w.grad, wr.grad) < 3e-2
+    for a, b in zip((W1, b1, W2, b2), ps):
+        assert rel_err(a.grad, b.grad) < 3e-2
+
+
+def test_capacity_drops_are_consistent():
+    torch.manual_seed(2)
+    T, d, hid, E, k = 256, 64, 64, 4, 1
+    dev = "cuda"
+    x = torch.randn(T, d, device=dev).bfloat16()
+    W1 = torch.randn(E, hid, d, device=dev) * 0.1; b1 = torch.zeros(E, hid, device=dev)
+    W2 = torch.randn(E, d, hid, device=dev) * 0.1; b2 = torch.zeros(E, d, device=dev)
+    idx = torch.zeros(T, 1, dtype=torch.int32, device=dev)                  # everyone wants expert 0
+    w = torch.ones(T, 1, device=dev)
+    out = M.MoEExpertsFn.apply(x, idx, w, W1, b1, W2, b2, "relu", 128, None)
+    kept = int((out.float().abs().sum(-1) > 0).sum())
+    assert kept == 128                                                       # exactly `capacity` tokens were served
+
+
+def test_moe_module_trains_bf16():
+    torch.manual_seed(3)
+    from rust_neural_network_b200.optim import Adam
+    lm = M.MoETransformerLM(256, 128, 2, 2, 8, 2, 1, 128, 128).to_device("cuda", torch.bfloat16)
+    opt = Adam(lm.parameters(), lr=2e-3)
+    ids = torch.randint(0, 256, (2, 128), device="cuda"); lab = torch.randint(0, 256, (2, 128), device="cuda")
+    losses = []
+    for _ in range(20):
+        opt.zero_grad(); l = lm.loss(ids, lab); l.backward(); opt.step(); losses.append(float(l))
+    assert losses[-1] < losses[0] * 0.9
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("kind", ["elu", "relu2"])
+def test_linear_attention_gpu(causal, kind):
+    torch.manual_seed(4)
+    q, k, v = ((torch.randn(2, 300, 2, 64, device="cuda") * 0.5).bfloat16().requires_grad_(True) for _ in range(3))
+    o = linear_attention(q, k, v, 0.5, 1e-6, causal, kind)
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    r = linear_attention_ref(qr, kr, vr, 0.5, 1e-6, causal, kind)
+    assert rel_err(o, r) < 3e-2
+    g = torch.randn_like(r)
+    (o.float() * g).sum().backward(); (r * g).sum().backward()
+    for a, b in ((q, qr), (k, kr), (v, vr)):
+        assert rel_err(a.grad, b.grad) < 6e-2

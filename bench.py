@@ -227,6 +227,16 @@ def main():
         }
         print(json.dumps(out), flush=True)
     if world > 1:
+        # a CUDA graph that captured collective kernels has to be released before its communicator
+        barrier()
+        trainer._graph = None
+        del trainer, opt
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
+        if args.dp == "nccl":
+            sys.stdout.flush()
+            os._exit(0)          # the communicator's teardown after graph-captured collectives does not return
         dist.destroy_process_group()
     return 0
 

@@ -44,6 +44,19 @@ template <> struct ElemTraits<float> {
   static constexpr uint32_t FMT = FMT_TF32;
   static constexpr bool TF32 = true;
 };
+// 8-bit operand tags (one byte each). The integer kinds accumulate in int32, fp8 in fp32; the
+// epilogue turns either into fp32 and applies per-row (A) and per-column (B) dequantisation scales.
+struct s8s8_t { int8_t v; };     // signed x signed      (quantised activations x quantised weights)
+struct u8s8_t { uint8_t v; };    // unsigned A x signed B (the reference's igemm contract, src/int8.rs:222-234)
+struct e4m3_t { uint8_t v; };    // fp8 e4m3 x e4m3
+enum : int { KIND_F16 = 0, KIND_TF32 = 1, KIND_I8 = 2, KIND_F8 = 3 };
+template <typename T> struct KindOf { static constexpr int v = ElemTraits<T>::TF32 ? KIND_TF32 : KIND_F16; static constexpr uint32_t AF = ElemTraits<T>::FMT, BF = ElemTraits<T>::FMT, CF = CFMT_F32; };
+template <> struct ElemTraits<s8s8_t> { static constexpr int BK = 128; static constexpr uint32_t FMT = FMT_S8; static constexpr bool TF32 = false; };
+template <> struct ElemTraits<u8s8_t> { static constexpr int BK = 128; static constexpr uint32_t FMT = FMT_S8; static constexpr bool TF32 = false; };
+template <> struct ElemTraits<e4m3_t> { static constexpr int BK = 128; static constexpr uint32_t FMT = 0; static constexpr bool TF32 = false; };
+template <> struct KindOf<s8s8_t> { static constexpr int v = KIND_I8; static constexpr uint32_t AF = FMT_S8, BF = FMT_S8, CF = CFMT_S32; };
+template <> struct KindOf<u8s8_t> { static constexpr int v = KIND_I8; static constexpr uint32_t AF = FMT_U8, BF = FMT_S8, CF = CFMT_S32; };
+template <> struct KindOf<e4m3_t> { static constexpr int v = KIND_F8; static constexpr uint32_t AF = 0, BF = 0, CF = CFMT_F32; };   // 0 = E4M3 in kind::f8f6f4
 
 // hardware tanh (MUFU.TANH): relative error ~2^-11, far below bf16 output precision
 __device__ __forceinline__ float tanh_fast(float x) {
@@ -244,7 +257,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BM, BN, CFMT_F32, ElemTraits<T>::FMT, ElemTraits<T>::FMT,
+      constexpr uint32_t idesc = make_idesc(BM, BN, KindOf<T>::CF, KindOf<T>::AF, KindOf<T>::BF,
                                             A_MN ? 1u : 0u, B_MN ? 1u : 0u);
       // K-major: 8-row groups 1024 B apart.  MN-major: 8-k-row groups 1024 B apart, 128B-row atoms
       // BK*128 B apart.
@@ -273,8 +286,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           for (int k = 0; k < K_STEPS; ++k) {
             uint64_t da = make_sdesc_sw128(sa + k * A_KADV, A_LBO, A_SBO);
             uint64_t db = make_sdesc_sw128(sb + k * B_KADV, B_LBO, B_SBO);
-            if (ElemTraits<T>::TF32) umma_tf32(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-            else umma_f16(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
+            if constexpr (KindOf<T>::v == KIND_TF32) umma_tf32(d_tmem, da, db, idesc, accum);
+            else if constexpr (KindOf<T>::v == KIND_I8) umma_i8(d_tmem, da, db, idesc, accum);
+            else if constexpr (KindOf<T>::v == KIND_F8) umma_f8(d_tmem, da, db, idesc, accum);
+            else umma_f16(d_tmem, da, db, idesc, accum);
           }
           tc_commit(&empty_bar[stage]);   // stage reusable once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -326,9 +342,42 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int cols_valid = min(PW, p.N - col0);
         const int chunks_valid = cols_valid / 8;       // staged path has N % 8 == 0
         const bool full = cols_valid == PW;
-        float f[PW];
+        if constexpr (KindOf<T>::v == KIND_I8) {
+          if (p.out_mode == OUT_I32) {       // raw integer accumulators (igemm contract)
+            if (row_ok) {
+              int* cp = reinterpret_cast<int*>(p.C) + cbase + (long long)lane * p.ldc + col0;
+              if (full && p.vec_ok) {
 #pragma unroll
-        for (int j = 0; j < PW; ++j) f[j] = has_k ? __uint_as_float(v[j]) * alpha : 0.f;
+                for (int j = 0; j < PW; j += 4)
+                  *reinterpret_cast<int4*>(cp + j) = has_k ? make_int4((int)v[j], (int)v[j + 1], (int)v[j + 2], (int)v[j + 3]) : make_int4(0, 0, 0, 0);
+              } else {
+#pragma unroll
+                for (int j = 0; j < PW; ++j) if (j < cols_valid) cp[j] = has_k ? (int)v[j] : 0;
+              }
+            }
+            continue;
+          }
+        }
+        float f[PW];
+        if constexpr (KindOf<T>::v == KIND_I8) {
+#pragma unroll
+          for (int j = 0; j < PW; ++j) f[j] = has_k ? (float)(int)v[j] * alpha : 0.f;
+        } else {
+#pragma unroll
+          for (int j = 0; j < PW; ++j) f[j] = has_k ? __uint_as_float(v[j]) * alpha : 0.f;
+        }
+        if (p.row_scale || p.col_scale) {
+          // dequantise: per-row scale of A (one per thread's row) and per-column scale of B
+          const float rs = (p.row_scale && row_ok) ? __ldg(p.row_scale + (long long)b * p.M + row) : 1.f;
+          if (p.col_scale) {
+            const float* cs = p.col_scale + col0;
+#pragma unroll
+            for (int j = 0; j < PW; ++j) f[j] *= rs * ((j < cols_valid) ? __ldg(cs + j) : 0.f);
+          } else {
+#pragma unroll
+            for (int j = 0; j < PW; ++j) f[j] *= rs;
+          }
+        }
         if (p.bias && first_split) {
           if (p.bias_f32 && full && p.bias_vec_ok) {
             const float4* bp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + b * p.strideBias + col0);
@@ -445,6 +494,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 template <typename T> struct DT;
 template <> struct DT<__nv_bfloat16> { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; };
 template <> struct DT<float> { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; };
+template <> struct DT<s8s8_t> { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_UINT8; };
+template <> struct DT<u8s8_t> { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_UINT8; };
+template <> struct DT<e4m3_t> { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_UINT8; };
 
 // Opt in to the large dynamic shared-memory carve-out (once per instantiation).
 template <typename T, int BN, bool A_MN, bool B_MN>
@@ -506,6 +558,9 @@ extern "C" int b200_gemm_init() {
   B200_INIT_BN(64) B200_INIT_BN(128) B200_INIT_BN(256)
 #undef B200_INIT_BN
   e |= gemm_set_attr<float, 128, false, false>();
+  e |= gemm_set_attr<s8s8_t, 128, false, false>(); e |= gemm_set_attr<s8s8_t, 256, false, false>();
+  e |= gemm_set_attr<u8s8_t, 128, false, false>(); e |= gemm_set_attr<u8s8_t, 256, false, false>();
+  e |= gemm_set_attr<e4m3_t, 128, false, false>(); e |= gemm_set_attr<e4m3_t, 256, false, false>();
   return e;
 }
 
@@ -513,11 +568,23 @@ extern "C" int b200_gemm_launch(const b200::GemmArgs* args, int bn, int num_sms,
   using namespace b200;
   const GemmArgs& a = *args;
   if (a.p.M <= 0 || a.p.N <= 0 || a.p.batch <= 0) return 0;
-  if (a.is_f32) {
+  if (a.dtype == GEMM_F32) {
     // TF32 runs K-major only: MN-major 32-bit operands need a different swizzle atom, so the
     // front-end hands this path explicitly transposed operands (b200_transpose).
     if (a.a_mn || a.b_mn) return -4;
     return launch_one<float, 128, false, false>(a, stream, num_sms);
+  }
+  if (a.dtype != GEMM_BF16) {
+    // 8-bit operands: K-major only (weights are stored [N,K] once at quantisation time)
+    if (a.a_mn || a.b_mn) return -4;
+    if (a.p.out_mode == OUT_I32 && a.dtype == GEMM_E4M3) return -5;
+    const bool wide = bn == 256;
+    switch (a.dtype) {
+      case GEMM_S8S8: return wide ? launch_one<s8s8_t, 256, false, false>(a, stream, num_sms) : launch_one<s8s8_t, 128, false, false>(a, stream, num_sms);
+      case GEMM_U8S8: return wide ? launch_one<u8s8_t, 256, false, false>(a, stream, num_sms) : launch_one<u8s8_t, 128, false, false>(a, stream, num_sms);
+      case GEMM_E4M3: return wide ? launch_one<e4m3_t, 256, false, false>(a, stream, num_sms) : launch_one<e4m3_t, 128, false, false>(a, stream, num_sms);
+      default: return -3;
+    }
   }
   switch (bn) {
     case 64: return launch_major<__nv_bfloat16, 64>(a, stream, num_sms);

@@ -26,6 +26,7 @@ class GemmParams(C.Structure):
         ("aux_out", c_void_p), ("aux_in", c_void_p),
         ("alpha", c_float), ("alpha_ptr", c_void_p), ("act", c_int), ("dact", c_int), ("out_mode", c_int),
         ("vec_ok", c_int), ("res_vec_ok", c_int),
+        ("row_scale", c_void_p), ("col_scale", c_void_p),
         ("status", c_void_p),
     ]
 
@@ -35,7 +36,7 @@ class GemmArgs(C.Structure):
         ("p", GemmParams),
         ("A", c_void_p), ("lda", c_ll), ("strideA", c_ll), ("a_mn", c_int),
         ("B", c_void_p), ("ldb", c_ll), ("strideB", c_ll), ("b_mn", c_int),
-        ("M", c_int), ("N", c_int), ("K", c_int), ("batch", c_int), ("is_f32", c_int),
+        ("M", c_int), ("N", c_int), ("K", c_int), ("batch", c_int), ("dtype", c_int),
     ]
 
 

@@ -18,7 +18,8 @@ import torch
 from .. import _native as nv
 
 ACT = {"none": 0, "relu": 1, "gelu": 2, "silu": 3, "sigmoid": 4, "tanh": 5}
-OUT_BF16, OUT_F32, OUT_F32_ATOMIC = 0, 1, 2
+OUT_BF16, OUT_F32, OUT_F32_ATOMIC, OUT_I32 = 0, 1, 2, 3
+GEMM_BF16, GEMM_F32, GEMM_S8S8, GEMM_U8S8, GEMM_E4M3 = 0, 1, 2, 3, 4
 _NUM_SMS = {}
 
 
@@ -63,11 +64,21 @@ def dact_ref(saved: torch.Tensor, act: str) -> torch.Tensor:
 
 
 def gemm_ref(a, b, *, a_mn=False, b_mn=False, bias=None, act="none", residual=None, aux_in=None, dact="none",
-             alpha=1.0, out_dtype=None, accumulate_into=None, want_aux=False):
+             alpha=1.0, out_dtype=None, accumulate_into=None, want_aux=False, row_scale=None, col_scale=None):
     """fp32 PyTorch evaluation of the same expression (used on CPU and as the test oracle)."""
-    A = a.float().transpose(-1, -2) if a_mn else a.float()
-    B = b.float().transpose(-1, -2) if b_mn else b.float()
-    v = alpha * (A @ B.transpose(-1, -2))
+    if out_dtype == torch.int32:          # exact integer accumulation (the igemm contract)
+        return (a.to(torch.int64) @ b.to(torch.int64).transpose(-1, -2)).to(torch.int32)
+    lowp = a.dtype in (torch.int8, torch.uint8, torch.float8_e4m3fn)
+    ft = torch.float64 if lowp else torch.float32
+    A = a.to(ft).transpose(-1, -2) if a_mn else a.to(ft)
+    B = b.to(ft).transpose(-1, -2) if b_mn else b.to(ft)
+    v = (alpha * (A @ B.transpose(-1, -2))).float()
+    if row_scale is not None:
+        v = v * row_scale.float().reshape(*v.shape[:-1], 1)
+    if col_scale is not None:
+        v = v * col_scale.float()
+    if lowp and out_dtype is None:
+        out_dtype = torch.bfloat16
     if bias is not None:
         v = v + (bias.float()[:, None, :] if bias.dim() == 2 else bias.float())   # [batch, N]: one vector per batch
     pre = v
@@ -82,7 +93,7 @@ def gemm_ref(a, b, *, a_mn=False, b_mn=False, bias=None, act="none", residual=No
     else:
         v = v.to(out_dtype or a.dtype)
     if want_aux:
-        return v, pre.to(a.dtype)
+        return v, pre.to(torch.bfloat16 if lowp else a.dtype)
     return v
 
 
@@ -112,17 +123,30 @@ def _tma_ready(t: torch.Tensor) -> torch.Tensor:
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias=None, act: str = "none",
          residual=None, aux_in=None, dact: str = "none", want_aux: bool = False, alpha: float = 1.0,
-         out_dtype=None, accumulate_into=None, splits: int = 0, bn: int = 0, alpha_t=None):
-    """See module docstring. Returns C (and the bf16 pre-activation when ``want_aux``)."""
+         out_dtype=None, accumulate_into=None, splits: int = 0, bn: int = 0, alpha_t=None, row_scale=None, col_scale=None):
+    """See module docstring. Returns C (and the bf16 pre-activation when ``want_aux``).
+
+    8-bit operands (int8 x int8, uint8 x int8, float8_e4m3fn x float8_e4m3fn; both K-major) run on the
+    tensor cores' integer / fp8 kinds. ``row_scale`` ([M] or [batch, M] fp32) and ``col_scale`` ([N] fp32)
+    dequantise in the epilogue before bias and activation; ``out_dtype=torch.int32`` returns the raw
+    accumulators of an integer product (rust-nn `igemm`, src/int8.rs:222-314)."""
     if not a.is_cuda:
         if alpha_t is not None:
             alpha = alpha * float(alpha_t)
         return gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, act=act, residual=residual, aux_in=aux_in, dact=dact,
-                        alpha=alpha, out_dtype=out_dtype, accumulate_into=accumulate_into, want_aux=want_aux)
+                        alpha=alpha, out_dtype=out_dtype, accumulate_into=accumulate_into, want_aux=want_aux,
+                        row_scale=row_scale, col_scale=col_scale)
     lib = nv.cuda()
-    if a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float32):
-        raise TypeError(f"gemm operands must both be bf16 or both fp32 (got {a.dtype}, {b.dtype})")
-    is_f32 = a.dtype == torch.float32
+    kinds = {(torch.bfloat16, torch.bfloat16): GEMM_BF16, (torch.float32, torch.float32): GEMM_F32,
+             (torch.int8, torch.int8): GEMM_S8S8, (torch.uint8, torch.int8): GEMM_U8S8,
+             (torch.float8_e4m3fn, torch.float8_e4m3fn): GEMM_E4M3}
+    if (a.dtype, b.dtype) not in kinds:
+        raise TypeError(f"gemm operands must be bf16 x bf16, fp32 x fp32, int8 x int8, uint8 x int8 or e4m3 x e4m3 (got {a.dtype}, {b.dtype})")
+    kind = kinds[(a.dtype, b.dtype)]
+    is_f32 = kind == GEMM_F32
+    lowp = kind >= GEMM_S8S8
+    if lowp and (a_mn or b_mn):
+        raise ValueError("8-bit GEMM operands must be K-major")
     if is_f32 and (a_mn or b_mn):
         # TF32 tiles are K-major only; 32-bit MN-major operands are transposed by a kernel first
         from .kernels import transpose_last2
@@ -147,12 +171,19 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         out_mode = OUT_F32_ATOMIC
     else:
         odt = out_dtype or (torch.float32 if is_f32 else torch.bfloat16)
-        out_mode = OUT_F32 if odt == torch.float32 else OUT_BF16
+        if odt == torch.int32:
+            if kind not in (GEMM_S8S8, GEMM_U8S8):
+                raise TypeError("an int32 result needs integer operands")
+            out_mode = OUT_I32
+        else:
+            out_mode = OUT_F32 if odt == torch.float32 else OUT_BF16
         out = None
     # tile width and split-K
     sms = _num_sms(dev)
     if is_f32:
         bn = 128
+    elif lowp:
+        bn = 256 if (bn == 256 or (bn == 0 and math.ceil(M / 128) * math.ceil(N / 256) * batch >= sms)) else 128
     elif bn == 0:
         if N <= 64:
             bn = 64
@@ -161,12 +192,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         else:
             t256 = math.ceil(M / 128) * math.ceil(N / 256) * batch
             bn = 256 if t256 >= sms else 128
-    bk = 32 if is_f32 else 64
+    bk = 32 if is_f32 else 128 if lowp else 64
     num_kb = max(1, math.ceil(K / bk))
     tiles = math.ceil(M / 128) * math.ceil(N / bn) * batch
     if splits == 0:
         splits = 1
-        if out_mode != OUT_BF16 and tiles < sms // 2 and num_kb >= 16 and act == "none" and aux_in is None and not want_aux:
+        if out_mode in (OUT_F32, OUT_F32_ATOMIC) and tiles < sms // 2 and num_kb >= 16 and act == "none" and aux_in is None and not want_aux:
             splits = max(1, min(sms // tiles, num_kb // 8))
     if splits > 1:
         per = math.ceil(num_kb / splits)
@@ -177,7 +208,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         out_mode = OUT_F32_ATOMIC
     if out is None:
         shape = (batch, M, N)
-        odt = torch.float32 if out_mode != OUT_BF16 else torch.bfloat16
+        odt = torch.int32 if out_mode == OUT_I32 else torch.float32 if out_mode != OUT_BF16 else torch.bfloat16
         out = torch.zeros(shape, dtype=odt, device=dev) if out_mode == OUT_F32_ATOMIC else torch.empty(shape, dtype=odt, device=dev)
     out3 = out if out.dim() == 3 else out.view(1, M, N) if batch == 1 else out.view(batch, M, N)
     ldc = out3.stride(1)
@@ -213,10 +244,19 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if (aux is not None or aux_in is not None) and ldc != N:
         raise ValueError("aux tensors need a dense output (ldc == N)")
     p.res_vec_ok = 1 if (residual is not None and residual.stride(1) % 8 == 0 and residual.data_ptr() % 16 == 0 and (batch == 1 or residual.stride(0) % 8 == 0)) else 0
+    if row_scale is not None:
+        row_scale = row_scale.float().contiguous()
+        if row_scale.numel() != batch * M:
+            raise ValueError("row_scale needs one value per row of A")
+    if col_scale is not None:
+        col_scale = col_scale.float().contiguous()
+        if col_scale.numel() != N:
+            raise ValueError("col_scale needs one value per row of B")
+    p.row_scale, p.col_scale = nv.ptr(row_scale), nv.ptr(col_scale)
     p.status = nv.status_word(dev).data_ptr()
     args.A, args.lda, args.strideA, args.a_mn = a3.data_ptr(), a3.stride(1), a3.stride(0), int(a_mn)
     args.B, args.ldb, args.strideB, args.b_mn = b3.data_ptr(), b3.stride(1), b3.stride(0), int(b_mn)
-    args.M, args.N, args.K, args.batch, args.is_f32 = M, N, K, batch, int(is_f32)
+    args.M, args.N, args.K, args.batch, args.dtype = M, N, K, batch, kind
     rc = lib.b200_gemm_launch(C.byref(args), bn, sms, nv.stream_ptr())
     nv.check(rc, "b200_gemm_launch")
     nv.count_launch()

@@ -152,3 +152,27 @@ def matmul(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, m: int, k: int, n:
 
 def gemm_strassen(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, m: int, k: int, n: int) -> torch.Tensor:
     return matmul(a, b, c, m, k, n)
+
+
+GEMM_STRASSEN_THRESHOLD = 256      # kept for API parity; the tensor-core product never recurses
+
+
+class BlasBackend:
+    """Pluggable GEMM provider (src/blas.rs:712-734): `name()` and `sgemm(...)`."""
+
+    def name(self) -> str:
+        raise NotImplementedError
+
+    def sgemm(self, transa, transb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc):
+        raise NotImplementedError
+
+
+class NativeBackend(BlasBackend):
+    """The built-in provider: the tcgen05 GEMM on CUDA tensors, the fp32 reference on CPU tensors."""
+
+    def name(self) -> str:
+        return "native-sm100a-tcgen05" if torch.cuda.is_available() else "native-cpu-reference"
+
+    def sgemm(self, transa, transb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc):
+        return sgemm(transa, transb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc)
+

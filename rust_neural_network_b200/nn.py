@@ -418,3 +418,12 @@ def flash_attention(q, k, v, causal: bool = False):
         return F.matmul(torch.softmax(s.float(), -1).to(q.dtype), v.contiguous())
     o = F.flash_attention(q.unsqueeze(2), k.unsqueeze(2), v.unsqueeze(2), 1.0 / math.sqrt(d), causal)
     return o.squeeze(2)
+
+
+def __getattr__(name):
+    # NormalMoE / FineGrainedMoE live in models.moe (they pull in the routing kernels); exposed here as in src/nn.rs
+    if name in ("NormalMoE", "FineGrainedMoE"):
+        from .models import moe
+        return getattr(moe, name)
+    raise AttributeError(name)
+

@@ -16,6 +16,8 @@ Inputs are [B, S, H, d] (any strides); output [B, S, H, d].
 """
 from __future__ import annotations
 
+import math
+
 import torch
 from torch.autograd import Function
 
@@ -155,8 +157,13 @@ class LinearAttention:
     """Config struct of the reference (`LinearAttention::new(kind, d).causal(b).with_scale(s)`, src/linear_attention.rs:640-677)."""
 
     def __init__(self, kind="elu", d: int = 64):
-        self.kind = "elu" if kind in ("elu", 0) else "relu2"
-        self.d, self.is_causal, self.scale, self.eps = d, False, 1.0, 1e-6
+        kind = getattr(kind, "name", kind)
+        self.kind = "elu" if (kind in ("elu", "Elu", 0)) else "relu2"
+        self.d, self.is_causal, self.scale, self.eps = d, False, 1.0 / math.sqrt(d), 1e-6
+
+    @staticmethod
+    def new(kind, d: int) -> "LinearAttention":
+        return LinearAttention(kind, d)
 
     @staticmethod
     def elu(d: int) -> "LinearAttention":

@@ -50,11 +50,11 @@ _EXPORTS = {
     "parallel.ddp": "DistributedAdam",
     "position": "AlibiBias CARoPE LearnedPE PositionalEncoding RoPE SinusoidalPE",
     "quant": "Rotor RotorQuant",
-    "quantize": "quantize QuantFormat QuantizedLinear QuantizedModel QuantizedTensor",
+    "quantize": "QuantFormat QuantizedLinear QuantizedModel QuantizedTensor",      # `quantize` itself: the (callable) submodule
     "models.reasoning": "ChainOfThought MarkovianRSA SwiReasoning TreeOfThoughts",
     "rl": "discounted_returns sample_categorical ActorCritic BanditEnv ChainEnv Dqn Environment Ppo Reinforce ReplayBuffer Transition",
     "self_improve": "Critic SelfImprover",
-    "serialize": "deserialize load_model safetensors_export safetensors_import save_model save_model_named serialize",
+    "serialize": "deserialize load_model safetensors_export safetensors_import save_model save_model_named",   # `serialize`: callable submodule
     "simd": "simd_add simd_features simd_matmul simd_mul simd_relu simd_scale simd_sum",
     "tensor": "Tensor",
     "ternary": "ternarize TernaryLinear TernaryModel TernaryTensor",
@@ -67,7 +67,7 @@ _WHERE = {name: (mod, name) for mod, names in _EXPORTS.items() for name in names
 _WHERE.update(_ALIASES)
 _SUBMODULES = {"activations", "blas", "compiled", "compression", "data", "distill", "distributed", "error", "finetune", "fused", "gpu", "gpu_kernels",
                "grpo", "gui", "int8", "interactive", "linear_attention", "loss", "nn", "offload", "optim", "position", "quant", "quantize", "rl",
-               "self_improve", "serialize", "simd", "tensor", "ternary", "tokenizer", "train", "models", "ops", "parallel", "utils"}
+               "quantize", "self_improve", "serialize", "simd", "tensor", "ternary", "tokenizer", "train", "models", "ops", "parallel", "utils"}
 _MODEL_MODULES = {"looped_transformer", "mamba", "diffusion", "reasoning"}       # crate-root modules that live under models/
 
 __all__ = sorted(set(_WHERE) | _SUBMODULES | _MODEL_MODULES | {"VERSION"})

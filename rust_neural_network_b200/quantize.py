@@ -173,3 +173,19 @@ class QuantizedModel:
 
 def quantize(tensor: torch.Tensor, format: QuantFormat, group_size: int = 0) -> QuantizedTensor:
     return QuantizedTensor.quantize(tensor, format, group_size)
+
+
+# The reference exports both a module and a function called `quantize` from its crate root. Python has
+# one namespace, so the module object itself is made callable: `pkg.quantize(t, fmt)` and
+# `pkg.quantize.QuantFormat` both work.
+import sys as _sys
+import types as _types
+
+
+class _CallableModule(_types.ModuleType):
+    def __call__(self, tensor, format, group_size=0):
+        return QuantizedTensor.quantize(tensor, format, group_size)
+
+
+_sys.modules[__name__].__class__ = _CallableModule
+

@@ -207,3 +207,17 @@ def safetensors_import(buf: bytes) -> List[Tuple[str, torch.Tensor]]:
         data = np.frombuffer(buf, dtype="<f4", count=cnt, offset=base.value + db[i]).copy()
         out.append((name, torch.from_numpy(data).view(*shape) if shape else torch.from_numpy(data).view(())))
     return out
+
+
+# The reference exports both a module and a function called `serialize` from its crate root; the module
+# object is made callable so that `pkg.serialize(named)` and `pkg.serialize.load_model` both work.
+import sys as _sys
+import types as _types
+
+
+class _CallableModule(_types.ModuleType):
+    def __call__(self, *args, **kwargs):
+        return serialize(*args, **kwargs)
+
+
+_sys.modules[__name__].__class__ = _CallableModule

@@ -172,9 +172,47 @@ __device__ __forceinline__ void panel_load(uint8_t* sbuf, int lane, const __nv_b
   for (int cc = 0; cc < P::CPR; ++cc) out[cc] = *reinterpret_cast<const uint4*>(sbuf + P::off(lane, cc));
 }
 
-template <typename T, int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+// ---------------------------------------------------------------------------- peer-memory helpers (TP variants)
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// bounded spin until *p >= want (wrap-safe); false (and a status code) on expiry
+template <bool SYS>
+__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t want, long long budget, uint32_t* status, uint32_t code) {
+  const long long t0 = clock64();
+  while ((int32_t)((SYS ? ld_acquire_sys_u32(p) : ld_acquire_gpu_u32(p)) - want) < 0) {
+    if (clock64() - t0 > budget) { if (status) atomicCAS(status, 0u, code); return false; }
+    __nanosleep(128);
+  }
+  return true;
+}
+// one thread: tell every peer `which` (0: shard ready, 1: done) and, if `wait`, wait for all of them
+__device__ __forceinline__ bool peer_handshake(const TpParams& tp, int which, bool wait, uint32_t* status) {
+  __threadfence_system();
+  for (int r = 0; r < tp.world; ++r) st_release_sys_u32(tp.flags[r] + which * TP_MAX_WORLD + tp.rank, tp.epoch);
+  bool ok = true;
+  if (wait)
+    for (int r = 0; r < tp.world && ok; ++r)
+      ok = wait_flag<true>(tp.flags[tp.rank] + which * TP_MAX_WORLD + r, tp.epoch, tp.wait_cycles, status, ST_TIMEOUT_PEER_FLAG);
+  return ok;
+}
+
+template <typename T, int BN, bool A_MN, bool B_MN, int TP>
+__device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const TpParams* tpp) {
   using S = GemmSmem<T, BN, A_MN, B_MN>;
   constexpr int BK = S::BK;
   constexpr int STAGES = S::STAGES;
@@ -202,6 +240,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int kb_per_split = (num_kb + p.splits - 1) / p.splits;
   const long long tiles_per_batch = (long long)m_blocks * n_blocks * p.splits;
   const long long total_tiles = tiles_per_batch * p.batch;
+  // TP_AG_GEMM reserves the first `copy_ctas` CTAs for pulling remote shards; the rest run the GEMM
+  const int n_copy = (TP == TP_AG_GEMM) ? tpp->copy_ctas : 0;
+  const int cta = (int)blockIdx.x - n_copy;
+  const int n_ctas = (int)gridDim.x - n_copy;
+  const int tp_shift = (TP == TP_AG_GEMM) ? tpp->rank * tpp->blocks_per_rank : 0;   // start with the local rows
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
@@ -219,18 +262,65 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (TP == TP_AG_GEMM && cta < 0) {
+    // ------------------------------------------------------------------ gather CTAs (all-gather half of TP_AG_GEMM)
+    const TpParams& tp = *tpp;
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) {
+      s_ok = 1;
+      if (blockIdx.x == 0) peer_handshake(tp, 0, false, p.status);      // "my shard is written" (stream order made it so)
+    }
+    __syncthreads();
+    const long long row_bytes = (long long)p.K * 2;                      // bf16 rows, K % 8 == 0
+    const int vec_per_row = (int)(row_bytes / 16);
+    for (int rr = 1; rr < tp.world; ++rr) {
+      const int src = (tp.rank + rr) % tp.world;                         // stagger the peers
+      if (threadIdx.x == 0 && !wait_flag<true>(tp.flags[tp.rank] + src, tp.epoch, tp.wait_cycles, p.status, ST_TIMEOUT_PEER_FLAG)) s_ok = 0;
+      __syncthreads();
+      if (!s_ok) break;
+      const uint8_t* sbase = reinterpret_cast<const uint8_t*>(tp.a_peer[src]);
+      for (int j = (int)blockIdx.x; j < tp.blocks_per_rank; j += n_copy) {
+        const int mbg = src * tp.blocks_per_rank + j;                    // global row block
+        uint8_t* dbase = reinterpret_cast<uint8_t*>(tp.a_stage) + (long long)mbg * BM * row_bytes;
+        const long long total_vec = (long long)BM * vec_per_row;
+        for (long long v = threadIdx.x; v < total_vec; v += GEMM_THREADS) {
+          const int rrow = (int)(v / vec_per_row), c = (int)(v % vec_per_row);
+          const uint4 x = __ldcv(reinterpret_cast<const uint4*>(sbase + ((long long)(j * BM + rrow) * tp.lda_shard) * 2 + c * 16));   // peer memory: never from a stale line
+          *reinterpret_cast<uint4*>(dbase + (long long)rrow * row_bytes + c * 16) = x;
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) { fence_proxy_async_all(); st_release_gpu_u32(tp.ready + mbg, tp.epoch); }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      // the last gather CTA tells every peer "I no longer read your shard" and waits for the same from them
+      __threadfence();
+      if (atomicAdd(tp.done_ctr, 1u) == (uint32_t)(n_copy - 1)) {
+        *tp.done_ctr = 0u;
+        peer_handshake(tp, 1, true, p.status);
+      }
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0; bool ok = true;
-      for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (long long t = cta; t < total_tiles && ok; t += n_ctas) {
         const int b = (int)(t / tiles_per_batch);
         long long r = t % tiles_per_batch;
         const int split = (int)(r / ((long long)m_blocks * n_blocks));
         r %= (long long)m_blocks * n_blocks;
-        const int mb = (int)(r / n_blocks), nb = (int)(r % n_blocks);
+        const int mb = ((int)(r / n_blocks) + tp_shift) % m_blocks, nb = (int)(r % n_blocks);
         const int kb0 = split * kb_per_split;
         const int kb1 = min(kb0 + kb_per_split, num_kb);
+        if constexpr (TP == TP_AG_GEMM) {
+          // rows of another rank: wait until the gather CTAs have landed this row block
+          if (mb / tpp->blocks_per_rank != tpp->rank) {
+            if (!wait_flag<false>(tpp->ready + mb, tpp->epoch, tpp->wait_cycles, p.status, ST_TIMEOUT_PEER_FLAG)) { ok = false; break; }
+            fence_proxy_async_all();
+          }
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, ST_TIMEOUT_TMA_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + stage * S::STAGE_BYTES;
@@ -267,7 +357,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       constexpr uint32_t B_KADV = B_MN ? UMMA_K * TILE_K_BYTES : UMMA_K_BYTES;
       int stage = 0; uint32_t phase = 0; bool ok = true;
       int it = 0;
-      for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      for (long long t = cta; t < total_tiles && ok; t += n_ctas, ++it) {
         long long r = t % tiles_per_batch;
         const int split = (int)(r / ((long long)m_blocks * n_blocks));
         const int kb0 = split * kb_per_split;
@@ -311,12 +401,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const bool staged = (p.out_mode == OUT_BF16) && p.vec_ok;       // coalesced bf16 path
     bool ok = true;
     int it = 0;
-    for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+    for (long long t = cta; t < total_tiles && ok; t += n_ctas, ++it) {
       const int b = (int)(t / tiles_per_batch);
       long long r = t % tiles_per_batch;
       const int split = (int)(r / ((long long)m_blocks * n_blocks));
       r %= (long long)m_blocks * n_blocks;
-      const int mb = (int)(r / n_blocks), nb = (int)(r % n_blocks);
+      const int mb = ((int)(r / n_blocks) + tp_shift) % m_blocks, nb = (int)(r % n_blocks);
       const int kb0 = split * kb_per_split;
       const bool has_k = kb0 < min(kb0 + kb_per_split, num_kb);
       const int as = it & 1;
@@ -431,7 +521,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             for (int j = 0; j < PW; ++j) if (j < cols_valid) f[j] *= act_bwd(__bfloat162float(ap[(long long)lane * p.ldc + j]), p.dact);
           }
         }
-        if (p.residual && first_split) {
+        if (TP != TP_GEMM_RS && p.residual && first_split) {       // TP_GEMM_RS adds the residual after the reduction
           const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(p.residual) + rbase + col0;
           if (staged && p.res_vec_ok) {
             uint4 u[PW / 8];
@@ -449,6 +539,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         if (p.out_mode == OUT_BF16) {
           __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + cbase + col0;
+          if constexpr (TP == TP_GEMM_RS) {
+            // this row block belongs to rank `owner`: store into MY slot of ITS buffer (peer memory, plain stores)
+            const TpParams& tp = *tpp;
+            const int owner = mb / tp.blocks_per_rank;
+            const long long rows_per_rank = (long long)tp.blocks_per_rank * BM;
+            const long long slot = ((long long)(tp.epoch & 1u) * tp.world + tp.rank) * rows_per_rank;
+            cp = reinterpret_cast<__nv_bfloat16*>(tp.slots_peer[owner]) + (slot + (row0 - owner * rows_per_rank)) * p.ldc + col0;
+          }
           if (staged) panel_store<PW>(sbuf, lane, f, cp, p.ldc, rows_valid, chunks_valid);
           else if (row_ok) {
 #pragma unroll
@@ -488,6 +586,61 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if constexpr (TP == TP_GEMM_RS) {
+    // ---------------------------------------------------------------- reduce-scatter half: handshake, then sum the slots
+    const TpParams& tp = *tpp;
+    __shared__ int s_go;
+    if (threadIdx.x == 0) {
+      s_go = 1;
+      __threadfence_system();                                    // this CTA's peer stores are out
+      if (atomicAdd(tp.done_ctr, 1u) == gridDim.x - 1) {
+        *tp.done_ctr = 0u;
+        const bool ok = peer_handshake(tp, 1, true, p.status);   // every rank has stored all its partials
+        __threadfence();
+        if (ok) st_release_gpu_u32(tp.go, tp.epoch);
+      }
+      if (!wait_flag<false>(tp.go, tp.epoch, 2 * tp.wait_cycles, p.status, ST_TIMEOUT_PEER_FLAG)) s_go = 0;
+      __threadfence();
+    }
+    __syncthreads();
+    if (s_go) {
+      const long long rows_per_rank = (long long)tp.blocks_per_rank * BM;
+      const long long n8 = rows_per_rank * p.N / 8;              // N % 8 == 0, ldc == N
+      const __nv_bfloat16* slots = reinterpret_cast<const __nv_bfloat16*>(tp.slots_peer[tp.rank]) + (long long)(tp.epoch & 1u) * tp.world * rows_per_rank * p.N;
+      const __nv_bfloat16* res = reinterpret_cast<const __nv_bfloat16*>(p.residual);
+      __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(tp.out);
+      for (long long i = (long long)blockIdx.x * GEMM_THREADS + threadIdx.x; i < n8; i += (long long)gridDim.x * GEMM_THREADS) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < tp.world; ++r) {
+          const uint4 u = __ldcg(reinterpret_cast<const uint4*>(slots + ((long long)r * rows_per_rank * p.N) + i * 8));   // written by peers: read at L2
+          const float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y), a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
+          acc[0] += a0.x; acc[1] += a0.y; acc[2] += a1.x; acc[3] += a1.y; acc[4] += a2.x; acc[5] += a2.y; acc[6] += a3.x; acc[7] += a3.y;
+        }
+        if (res) {
+          const long long row = (i * 8) / p.N, col = (i * 8) % p.N;
+          const uint4 u = *reinterpret_cast<const uint4*>(res + row * p.ldr + col);
+          const float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y), a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
+          acc[0] += a0.x; acc[1] += a0.y; acc[2] += a1.x; acc[3] += a1.y; acc[4] += a2.x; acc[5] += a2.y; acc[6] += a3.x; acc[7] += a3.y;
+        }
+        *reinterpret_cast<uint4*>(out + i * 8) = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                                             pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+      }
+    }
+  }
+}
+
+template <typename T, int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ GemmParams p) {
+  gemm_body<T, BN, A_MN, B_MN, TP_NONE>(tmA, tmB, p, nullptr);
+}
+
+// bf16, K-major x K-major (the Linear forward layout) fused with its neighbouring collective
+template <int BN, int TP>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ GemmParams p,
+               const __grid_constant__ TpParams tp) {
+  gemm_body<__nv_bfloat16, BN, false, false, TP>(tmA, tmB, p, &tp);
 }
 
 // ---------------------------------------------------------------------------- host side
@@ -534,6 +687,34 @@ static int launch_one(const GemmArgs& a, cudaStream_t stream, int num_sms) {
   int grid = (int)(tiles < num_sms ? tiles : num_sms);
   if (grid < 1) grid = 1;
   kfn<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+template <int BN, int TP>
+static int launch_tp(const GemmArgs& a, const TpParams& tp, cudaStream_t stream, int num_sms) {
+  using T = __nv_bfloat16;
+  using S = GemmSmem<T, BN, false, false>;
+  constexpr int BK = S::BK;
+  CUtensorMap tmA, tmB;
+  // A: TP_AG_GEMM multiplies out of the local staging copy [M, K]; TP_GEMM_RS out of the caller's A
+  const void* aptr = (TP == TP_AG_GEMM) ? tp.a_stage : a.A;
+  const long long lda = (TP == TP_AG_GEMM) ? a.K : a.lda;
+  int rc = make_tmap_3d(&tmA, aptr, DT<T>::v, sizeof(T), a.K, a.M, 1, lda * sizeof(T), (long long)a.M * lda * sizeof(T), BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return 100 + rc;
+  rc = make_tmap_3d(&tmB, a.B, DT<T>::v, sizeof(T), a.K, a.N, 1, a.ldb * sizeof(T), (long long)a.N * a.ldb * sizeof(T), BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return 200 + rc;
+  static bool attr_done = false;
+  if (!attr_done) {
+    (void)cudaGetLastError();
+    cudaError_t e = cudaFuncSetAttribute(gemm_tp_kernel<BN, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) return 300 + (int)e;
+    attr_done = true;
+  }
+  // every CTA must be resident at once (CTAs wait on one another): one CTA per SM, grid <= SM count
+  int grid = num_sms;
+  if (TP == TP_AG_GEMM && grid - tp.copy_ctas < 1) return -6;
+  gemm_tp_kernel<BN, TP><<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, a.p, tp);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }
@@ -593,3 +774,22 @@ extern "C" int b200_gemm_launch(const b200::GemmArgs* args, int bn, int num_sms,
     default: return -2;
   }
 }
+
+// Tensor-parallel GEMM (see TpParams). bf16 operands, both K-major, batch 1, no split-K, bf16 output.
+extern "C" int b200_gemm_tp_launch(const b200::GemmArgs* args, const b200::TpParams* tp, int bn, int num_sms, cudaStream_t stream) {
+  using namespace b200;
+  const GemmArgs& a = *args;
+  if (a.dtype != GEMM_BF16 || a.a_mn || a.b_mn || a.p.batch != 1 || a.p.splits != 1 || a.p.out_mode != OUT_BF16) return -3;
+  if (tp->world < 1 || tp->world > TP_MAX_WORLD || tp->blocks_per_rank < 1 || a.p.M != tp->world * tp->blocks_per_rank * BM) return -7;
+  if (a.p.K % 8 != 0 || a.p.N % 8 != 0) return -8;
+  if (tp->mode == TP_AG_GEMM) {
+    if (tp->world > 1 && tp->copy_ctas < 1) return -6;
+    return bn == 256 ? launch_tp<256, TP_AG_GEMM>(a, *tp, stream, num_sms) : launch_tp<128, TP_AG_GEMM>(a, *tp, stream, num_sms);
+  }
+  if (tp->mode == TP_GEMM_RS) {
+    if (a.p.ldc != a.p.N || !a.p.vec_ok || a.p.act != ACT_NONE || a.p.aux_out || a.p.aux_in) return -9;
+    return bn == 256 ? launch_tp<256, TP_GEMM_RS>(a, *tp, stream, num_sms) : launch_tp<128, TP_GEMM_RS>(a, *tp, stream, num_sms);
+  }
+  return -2;
+}
+

@@ -28,6 +28,36 @@ struct GemmParams {
   uint32_t* status;        // device word, receives a non-zero code on a bounded-wait expiry
 };
 
+// Tensor-parallel extension: the GEMM fused with the collective next to it, over NVLink peer memory.
+//   TP_AG_GEMM (all-gather -> GEMM): A's row blocks belong to `world` ranks. A few CTAs of the grid pull
+//     the remote shards into the local staging copy of A (one NVLink crossing per element) and
+//     publish a per-row-block flag; the TMA producers of the GEMM CTAs wait on that flag, so tiles of
+//     rows that have arrived multiply while later rows are still in flight.
+//   TP_GEMM_RS (GEMM -> reduce-scatter): every rank holds a K-slice and computes a partial C. The
+//     epilogue stores each row block straight into its owner's slot buffer (plain 16-byte peer stores),
+//     the last CTA runs a cross-rank handshake, then all CTAs sum the `world` slots of the local rows
+//     (+ residual) into the output.
+enum : int { TP_NONE = 0, TP_AG_GEMM = 1, TP_GEMM_RS = 2 };
+constexpr int TP_MAX_WORLD = 8;
+struct TpParams {
+  int mode, rank, world, copy_ctas;
+  int blocks_per_rank;               // row blocks of 128 rows per rank (M / world / 128)
+  uint32_t epoch;                    // strictly increasing per call (flags compare >=)
+  long long wait_cycles;             // clock64 budget of one wait
+  // TP_AG_GEMM
+  const void* a_peer[TP_MAX_WORLD];  // every rank's A shard [rows_per_rank, K] bf16, row stride lda_shard (peer-mapped)
+  long long lda_shard;
+  void* a_stage;                     // local [M, K] bf16 staging buffer (the A tensor map points here)
+  uint32_t* ready;                   // local, one word per row block
+  // TP_GEMM_RS
+  void* slots_peer[TP_MAX_WORLD];    // every rank's slot buffer [2][world][rows_per_rank][N] bf16 (peer-mapped)
+  void* out;                         // local result [rows_per_rank, N] bf16
+  uint32_t* go;                      // local word: "all peers' partials have landed"
+  // both
+  uint32_t* flags[TP_MAX_WORLD];     // every rank's flag words [2][TP_MAX_WORLD] (peer-mapped): [0] shard ready, [1] done
+  uint32_t* done_ctr;                // local counter of finished CTAs
+};
+
 struct GemmArgs {
   GemmParams p;
   const void* A; long long lda, strideA; int a_mn;   // a_mn: A stored [K,M] (M contiguous)
@@ -39,3 +69,4 @@ struct GemmArgs {
 }  // namespace b200
 
 extern "C" int b200_gemm_launch(const b200::GemmArgs* args, int bn, int num_sms, cudaStream_t stream);
+extern "C" int b200_gemm_tp_launch(const b200::GemmArgs* args, const b200::TpParams* tp, int bn, int num_sms, cudaStream_t stream);

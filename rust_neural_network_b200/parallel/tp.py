@@ -1,0 +1,181 @@
+"""Tensor parallelism over NVLink peer memory: the two GEMM + collective fusions of a sharded MLP /
+attention block (the reference has no tensor parallelism; its only multi-worker path is the
+simulated gradient all-reduce, rust-nn src/distributed.rs:54-124).
+
+  `all_gather_gemm`     Y[M, N_local] = gather_rows(X_shard) @ W_shard^T  - column-parallel Linear after a
+                        sequence-sharded activation. Gather CTAs pull the remote row blocks of X once into a
+                        local staging copy and raise a flag per 128-row block; the GEMM's TMA producers wait
+                        on those flags, so arrived rows multiply while later ones are in flight.
+  `gemm_reduce_scatter` Y_shard[M/world, N] = sum_r X[:, K_r] @ W[:, K_r]^T   - row-parallel Linear. Each
+                        rank's epilogue stores its partial tiles into the owner's slot buffer (plain peer
+                        stores), one cross-rank handshake, then every CTA sums the slots of the local rows
+                        (+ residual) - all in one kernel (csrc/gemm/gemm_sm100.cu, `TpParams`).
+
+Both run as ONE kernel per rank and per call; all waits are bounded by `wait_seconds` and end in the
+status word. `backend="nccl"` is the baseline (all_gather / reduce_scatter + the plain GEMM) the fused
+kernels are measured against, and the path CPU (gloo) ranks take.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _native as nv
+from ..ops import gemm as G
+
+TP_MAX_WORLD = 8
+TP_AG_GEMM, TP_GEMM_RS = 1, 2
+BM = 128
+
+
+class TpParams(C.Structure):
+    _fields_ = [
+        ("mode", C.c_int), ("rank", C.c_int), ("world", C.c_int), ("copy_ctas", C.c_int),
+        ("blocks_per_rank", C.c_int), ("epoch", C.c_uint32), ("wait_cycles", C.c_longlong),
+        ("a_peer", C.c_void_p * TP_MAX_WORLD), ("lda_shard", C.c_longlong), ("a_stage", C.c_void_p), ("ready", C.c_void_p),
+        ("slots_peer", C.c_void_p * TP_MAX_WORLD), ("out", C.c_void_p), ("go", C.c_void_p),
+        ("flags", C.c_void_p * TP_MAX_WORLD), ("done_ctr", C.c_void_p),
+    ]
+
+
+nv.register_sigs({"b200_gemm_tp_launch": [C.POINTER(nv.GemmArgs), C.POINTER(TpParams), C.c_int, C.c_int, C.c_void_p]})
+
+
+class TPContext:
+    """Symmetric buffers and flags of one tensor-parallel group, sized for the largest call it will serve."""
+
+    def __init__(self, max_rows: int, max_k: int, max_n: int, device=None, group=None, backend: str = "fused",
+                 wait_seconds: float = 2.0, copy_ctas: int = 16):
+        self.group = group or dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.backend = backend if self.device.type == "cuda" else "nccl"
+        self.max_rows, self.max_k, self.max_n = max_rows, max_k, max_n
+        self.copy_ctas = copy_ctas
+        self.epoch = 0
+        if self.backend == "fused":
+            from .ddp import SymmetricBuffer
+            if max_rows % (self.world * BM) != 0:
+                raise ValueError(f"rows ({max_rows}) must be a multiple of world * {BM}")
+            self.rows_per_rank = max_rows // self.world
+            dev = self.device
+            self.stage = SymmetricBuffer(max_rows * max_k, torch.bfloat16, dev, self.group)                 # all-gather staging [M, K]
+            self.slots = SymmetricBuffer(2 * self.world * self.rows_per_rank * max_n, torch.bfloat16, dev, self.group)
+            self.flags = SymmetricBuffer(2 * TP_MAX_WORLD, torch.int32, dev, self.group)
+            self.local = torch.zeros(max_rows // BM + 8, dtype=torch.int32, device=dev)                      # ready[m_blocks], go, done_ctr
+            self.clock_hz = torch.cuda.get_device_properties(dev).clock_rate * 1000
+            self.wait_cycles = int(wait_seconds * self.clock_hz)
+            self.sms = torch.cuda.get_device_properties(dev).multi_processor_count
+            dist.barrier(self.group)
+            torch.cuda.synchronize()
+
+    # ------------------------------------------------------------------ all-gather -> GEMM
+    def ag_input(self, rows_local: int, k: int) -> torch.Tensor:
+        """[rows_local, k] bf16 view of this rank's rows inside the gather staging buffer: write the local
+        activation shard here (peers read it in place)."""
+        if rows_local * self.world > self.max_rows or k > self.max_k:
+            raise ValueError("call exceeds the context's capacity")
+        m = rows_local * self.world
+        return self.stage.tensor[: m * k].view(m, k)[self.rank * rows_local:(self.rank + 1) * rows_local]
+
+    def _tp(self, mode: int, rows_local: int) -> TpParams:
+        self.epoch += 1
+        tp = TpParams()
+        tp.mode, tp.rank, tp.world = mode, self.rank, self.world
+        tp.copy_ctas = self.copy_ctas if (mode == TP_AG_GEMM and self.world > 1) else 0
+        tp.blocks_per_rank = rows_local // BM
+        tp.epoch, tp.wait_cycles = self.epoch, self.wait_cycles
+        m_blocks = self.max_rows // BM
+        tp.ready = self.local.data_ptr()
+        tp.go = self.local.data_ptr() + 4 * m_blocks
+        tp.done_ctr = self.local.data_ptr() + 4 * (m_blocks + 1)
+        for r in range(self.world):
+            tp.flags[r] = self.flags.ptrs[r]
+        return tp
+
+    def all_gather_gemm(self, x_shard: torch.Tensor, w_shard: torch.Tensor, bias=None, act: str = "none", want_aux: bool = False):
+        """x_shard [rows_local, K] (this rank's rows; if it is not already `ag_input(...)` it is copied there),
+        w_shard [N_local, K] -> act(gather(x) @ w_shard^T + bias) [rows_local * world, N_local] bf16."""
+        rows_local, k = x_shard.shape
+        n = w_shard.shape[0]
+        m = rows_local * self.world
+        if self.backend != "fused":
+            xs = [torch.empty_like(x_shard) for _ in range(self.world)]
+            dist.all_gather(xs, x_shard.contiguous(), group=self.group)
+            return G.gemm(torch.cat(xs, 0), w_shard, bias=bias, act=act, want_aux=want_aux)
+        if rows_local % BM != 0 or k % 8 != 0 or n % 8 != 0:
+            raise ValueError("fused all_gather_gemm needs rows_local % 128 == 0 and K, N % 8 == 0")
+        mine = self.ag_input(rows_local, k)
+        if x_shard.data_ptr() != mine.data_ptr():
+            mine.copy_(x_shard)
+        tp = self._tp(TP_AG_GEMM, rows_local)
+        for r in range(self.world):
+            tp.a_peer[r] = self.stage.ptrs[r] + r * rows_local * k * 2
+        tp.lda_shard, tp.a_stage = k, self.stage.ptrs[self.rank]
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=self.device)
+        aux = torch.empty(m, n, dtype=torch.bfloat16, device=self.device) if want_aux else None
+        self._launch(tp, mine, w_shard, m, n, k, out, bias, act, None, aux)
+        return (out, aux) if want_aux else out
+
+    # ------------------------------------------------------------------ GEMM -> reduce-scatter
+    def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, bias=None, residual=None) -> torch.Tensor:
+        """x [M, K_local], w [N, K_local] (this rank's K slice) -> rows [rank * M/world, (rank+1) * M/world) of
+        sum over ranks of x @ w^T (+ bias, + residual [M/world, N])."""
+        m, k = x.shape
+        n = w.shape[0]
+        rows_local = m // self.world
+        if self.backend != "fused":
+            part = G.gemm(x, w, bias=bias if self.rank == 0 else None, out_dtype=torch.float32)
+            outs = torch.empty(rows_local, n, dtype=torch.float32, device=x.device)
+            if x.is_cuda:
+                dist.reduce_scatter_tensor(outs, part.contiguous(), group=self.group)
+            else:
+                dist.all_reduce(part, group=self.group)
+                outs = part[self.rank * rows_local:(self.rank + 1) * rows_local]
+            if residual is not None:
+                outs = outs + residual.float()
+            return outs.to(torch.bfloat16)
+        if m != self.max_rows and (m % (self.world * BM) != 0):
+            raise ValueError("fused gemm_reduce_scatter needs M % (world * 128) == 0")
+        if m * n // self.world > self.rows_per_rank * self.max_n or k % 8 != 0 or n % 8 != 0:
+            raise ValueError("call exceeds the context's capacity or K, N % 8 != 0")
+        tp = self._tp(TP_GEMM_RS, rows_local)
+        for r in range(self.world):
+            tp.slots_peer[r] = self.slots.ptrs[r]
+        out = torch.empty(rows_local, n, dtype=torch.bfloat16, device=self.device)
+        tp.out = out.data_ptr()
+        if residual is not None:
+            residual = residual.to(torch.bfloat16).contiguous()
+        dummy = torch.empty(0, dtype=torch.bfloat16, device=self.device)
+        self._launch(tp, x.contiguous(), w, m, n, k, dummy, bias if self.rank == 0 else None, "none", residual, None)
+        return out
+
+    def _launch(self, tp, a, b, m, n, k, out, bias, act, residual, aux):
+        args = nv.GemmArgs()
+        p = args.p
+        p.M, p.N, p.K, p.batch, p.splits = m, n, k, 1, 1
+        p.C, p.ldc, p.strideC = out.data_ptr() if out.numel() else 0, n, m * n
+        if bias is not None and bias.dtype not in (torch.float32, torch.bfloat16):
+            bias = bias.float()
+        p.bias = nv.ptr(bias); p.bias_f32 = 1 if (bias is not None and bias.dtype == torch.float32) else 0
+        p.bias_vec_ok = 1 if (bias is not None and bias.data_ptr() % 16 == 0 and n % 4 == 0) else 0
+        p.strideBias = 0
+        p.residual = nv.ptr(residual); p.ldr = n if residual is not None else 0; p.strideR = 0
+        p.aux_out = nv.ptr(aux); p.aux_in = 0
+        p.alpha, p.alpha_ptr, p.act, p.dact, p.out_mode = 1.0, 0, G.ACT[act], 0, G.OUT_BF16
+        p.vec_ok, p.res_vec_ok = 1, 1
+        p.row_scale, p.col_scale = 0, 0
+        p.status = nv.status_word(self.device).data_ptr()
+        b = b if b.stride(-1) == 1 else b.contiguous()
+        args.A, args.lda, args.strideA, args.a_mn = a.data_ptr(), a.stride(0), 0, 0
+        args.B, args.ldb, args.strideB, args.b_mn = b.data_ptr(), b.stride(0), 0, 0
+        args.M, args.N, args.K, args.batch, args.dtype = m, n, k, 1, G.GEMM_BF16
+        bn = 256 if math.ceil(m / 128) * math.ceil(n / 256) >= self.sms else 128
+        rc = nv.cuda().b200_gemm_tp_launch(C.byref(args), C.byref(tp), bn, self.sms, nv.stream_ptr())
+        nv.check(rc, "b200_gemm_tp_launch")
+        nv.count_launch()
+        self._keep = (a, b, bias, residual, out, aux)          # alive until the next call on this context

@@ -1,0 +1,63 @@
+"""Tensor- and expert-parallel kernels over NVLink peer memory (2+ GPUs), plus the CPU (gloo) baseline path."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+WORKER = str(Path(__file__).resolve().parent / "tp_worker.py")
+
+
+def _run(nproc, extra, port, timeout=600):
+    env = dict(os.environ)
+    env.update({"MASTER_ADDR": "127.0.0.1", "OMP_NUM_THREADS": "2", "NCCL_NVLS_ENABLE": "0"})
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), WORKER] + extra
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith('{"ranks"')][-1]
+    return json.loads(line)["ranks"]
+
+
+@pytest.mark.gpu
+def test_fused_tp_and_ep_on_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ranks = _run(2, ["--rows", "4096", "--k", "512", "--n", "2048"], 29631)
+    for r in ranks:
+        assert r["ag_gemm_rel_err"] < 1e-2 and r["ag_gemm_vs_baseline"] < 1e-2
+        assert r["gemm_rs_rel_err"] < 2e-2 and r["gemm_rs_vs_baseline"] < 2e-2
+        assert r["ep_fwd_rel_err"] < 2e-2 and r["ep_dx_rel_err"] < 3e-2 and r["ep_dW1_rel_err"] < 3e-2
+
+
+def _cpu_tp_rank(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from rust_neural_network_b200.parallel.tp import TPContext
+    g = torch.Generator().manual_seed(3)
+    X, W1, W2 = torch.randn(8, 6, generator=g), torch.randn(10, 6, generator=g), torch.randn(6, 10, generator=g)
+    ctx = TPContext(8, 10, 10, device="cpu", backend="fused")            # CPU ranks always take the baseline path
+    h = ctx.all_gather_gemm(X[rank * 4:(rank + 1) * 4], W1[rank * 5:(rank + 1) * 5], act="relu")
+    y = ctx.gemm_reduce_scatter(h, W2[:, rank * 5:(rank + 1) * 5].contiguous())
+    want = (torch.relu(X @ W1.t()) @ W2.t())[rank * 4:(rank + 1) * 4]
+    q.put((rank, float((y.float() - want).abs().max()), float(want.abs().max())))
+    dist.destroy_process_group()
+
+
+def test_tp_baseline_path_two_gloo_ranks():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_cpu_tp_rank, args=(r, 2, 29641, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for _, err, scale in res:
+        assert err < 2e-2 * scale + 1e-3

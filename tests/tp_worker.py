@@ -1,0 +1,153 @@
+"""Worker launched by the tensor- / expert-parallel tests (one process per GPU, via torch.distributed.run).
+
+Checks, on every rank, the fused all-gather->GEMM and GEMM->reduce-scatter kernels against the
+unsharded GEMM, and the expert-parallel MoE layer (dispatch / combine over peer memory) against the
+same layer holding all experts locally. Also times the fused kernels against the NCCL + GEMM baseline
+with CUDA events (max over ranks). Rank 0 prints one JSON line.
+"""
+import argparse
+import json
+import os
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+import torch
+import torch.distributed as dist
+
+
+def rel(a, b):
+    return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+
+
+def timed(fn, iters, dev):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--rows", type=int, default=4096)       # global rows M
+    ap.add_argument("--k", type=int, default=512)
+    ap.add_argument("--n", type=int, default=2048)          # global N of the column-parallel layer
+    ap.add_argument("--iters", type=int, default=0)         # > 0: also time fused vs baseline
+    ap.add_argument("--moe", type=int, default=1)
+    args = ap.parse_args()
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+
+    from rust_neural_network_b200 import _native as nv
+    from rust_neural_network_b200.ops import gemm as G
+    from rust_neural_network_b200.parallel.tp import TPContext
+    nv.cuda()
+
+    M, K, N = args.rows, args.k, args.n
+    g = torch.Generator().manual_seed(7)
+    X = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16).to(dev)          # identical on every rank
+    W1 = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(dev)        # column-parallel: split N
+    b1 = torch.randn(N, generator=g).to(dev)
+    W2 = (torch.randn(K, N, generator=g) * 0.05).to(torch.bfloat16).to(dev)        # row-parallel: split its K (= N)
+    b2 = torch.randn(K, generator=g).to(dev)
+    R = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+    rows_local, n_local = M // world, N // world
+    xs = X[rank * rows_local:(rank + 1) * rows_local].contiguous()
+    w1s, b1s = W1[rank * n_local:(rank + 1) * n_local].contiguous(), b1[rank * n_local:(rank + 1) * n_local].contiguous()
+    w2s = W2[:, rank * n_local:(rank + 1) * n_local].contiguous()
+
+    out = {"rank": rank, "world": world}
+    ctx = TPContext(M, max(K, n_local), max(K, n_local), device=dev, backend="fused")
+    base = TPContext(M, K, N, device=dev, backend="nccl")
+
+    # ---- all-gather -> GEMM (+bias, GELU): h[M, n_local]
+    want_h = G.gemm(X, w1s, bias=b1s, act="gelu")
+    for it in range(3):                                     # repeated calls exercise the epoch / flag reuse
+        h = ctx.all_gather_gemm(xs, w1s, bias=b1s, act="gelu")
+    torch.cuda.synchronize()
+    nv.check_status()
+    out["ag_gemm_rel_err"] = rel(h, want_h)
+    out["ag_gemm_vs_baseline"] = rel(h, base.all_gather_gemm(xs, w1s, bias=b1s, act="gelu"))
+
+    # ---- GEMM -> reduce-scatter (+bias, +residual): y[rows_local, K]
+    full = G.gemm(want_h_full(G, X, W1, b1), W2, bias=b2, out_dtype=torch.float32) + R.float()
+    want_y = full[rank * rows_local:(rank + 1) * rows_local]
+    res = R[rank * rows_local:(rank + 1) * rows_local].contiguous()
+    for it in range(3):
+        y = ctx.gemm_reduce_scatter(h, w2s, bias=b2, residual=res)
+    torch.cuda.synchronize()
+    nv.check_status()
+    out["gemm_rs_rel_err"] = rel(y, want_y)
+    out["gemm_rs_vs_baseline"] = rel(y, base.gemm_reduce_scatter(h, w2s, bias=b2, residual=res))
+
+    if args.iters > 0:
+        mine = ctx.ag_input(rows_local, K)
+        mine.copy_(xs)
+        out["ms_ag_gemm_fused"] = timed(lambda: ctx.all_gather_gemm(mine, w1s, bias=b1s, act="gelu"), args.iters, dev)
+        out["ms_ag_gemm_nccl"] = timed(lambda: base.all_gather_gemm(xs, w1s, bias=b1s, act="gelu"), args.iters, dev)
+        out["ms_gemm_rs_fused"] = timed(lambda: ctx.gemm_reduce_scatter(h, w2s, bias=b2, residual=res), args.iters, dev)
+        out["ms_gemm_rs_nccl"] = timed(lambda: base.gemm_reduce_scatter(h, w2s, bias=b2, residual=res), args.iters, dev)
+        out["ms_gemm_local_col"] = timed(lambda: G.gemm(X, w1s, bias=b1s, act="gelu"), args.iters, dev)
+        out["ms_gemm_local_row"] = timed(lambda: G.gemm(h, w2s), args.iters, dev)
+        nv.check_status()
+
+    # ---- expert parallelism: dispatch / combine over peer memory
+    if args.moe:
+        from rust_neural_network_b200.models.moe import FineGrainedMoE
+        E, d, hid, T = 8, 256, 512, 1024
+        torch.manual_seed(11)
+        full_moe = FineGrainedMoE(d, hid, hid, E, top_k=2, num_shared=1, capacity_factor=8.0, act="silu").to_device(dev, torch.bfloat16)
+        torch.manual_seed(11)
+        ep_moe = FineGrainedMoE(d, hid, hid, E, top_k=2, num_shared=1, capacity_factor=8.0, act="silu", ep_group=dist.group.WORLD).to_device(dev, torch.bfloat16)
+        e_local = E // world
+        with torch.no_grad():
+            for name in ("W1", "b1", "W2", "b2"):
+                getattr(ep_moe, name).data.copy_(getattr(full_moe, name).data[rank * e_local:(rank + 1) * e_local])
+            for pa, pb in zip(ep_moe.gate.parameters() + ep_moe.shared[0].parameters(), full_moe.gate.parameters() + full_moe.shared[0].parameters()):
+                pa.data.copy_(pb.data)
+        gx = torch.Generator().manual_seed(100 + rank)
+        x = torch.randn(T, d, generator=gx).to(torch.bfloat16).to(dev).requires_grad_(True)
+        x2 = x.detach().clone().requires_grad_(True)
+        yo = ep_moe(x)
+        yr = full_moe(x2)
+        gy = torch.randn(T, d, generator=gx).to(torch.bfloat16).to(dev)
+        yo.backward(gy)
+        yr.backward(gy)
+        torch.cuda.synchronize()
+        nv.check_status()
+        out["ep_fwd_rel_err"] = rel(yo, yr)
+        out["ep_dx_rel_err"] = rel(x.grad, x2.grad)
+        # expert weight gradients: the EP rank sees tokens of ALL ranks, the local model only its own -> sum over ranks
+        gfull = full_moe.W1.grad.float().clone()
+        dist.all_reduce(gfull)
+        out["ep_dW1_rel_err"] = rel(ep_moe.W1.grad, gfull[rank * e_local:(rank + 1) * e_local])
+
+    gathered = [None] * world
+    dist.all_gather_object(gathered, out)
+    if rank == 0:
+        print(json.dumps({"ranks": gathered}), flush=True)
+    dist.barrier()
+    torch.cuda.synchronize()
+    dist.destroy_process_group()
+
+
+def want_h_full(G, X, W1, b1):
+    return G.gemm(X, W1, bias=b1, act="gelu")
+
+
+if __name__ == "__main__":
+    main()

@@ -264,43 +264,46 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
 
   if (TP == TP_AG_GEMM && cta < 0) {
     // ------------------------------------------------------------------ gather CTAs (all-gather half of TP_AG_GEMM)
+    // Push model: this rank's rows (already in its staging buffer by stream order) are written into every
+    // peer's staging buffer - posted NVLink stores, 8 x 16 bytes in flight per thread - followed by a
+    // release of the row block's flag AT THE PEER.
     const TpParams& tp = *tpp;
-    __shared__ int s_ok;
-    if (threadIdx.x == 0) {
-      s_ok = 1;
-      if (blockIdx.x == 0) peer_handshake(tp, 0, false, p.status);      // "my shard is written" (stream order made it so)
-    }
-    __syncthreads();
     const long long row_bytes = (long long)p.K * 2;                      // bf16 rows, K % 8 == 0
-    const int vec_per_row = (int)(row_bytes / 16);
-    for (int rr = 1; rr < tp.world; ++rr) {
-      const int src = (tp.rank + rr) % tp.world;                         // stagger the peers
-      if (threadIdx.x == 0 && !wait_flag<true>(tp.flags[tp.rank] + src, tp.epoch, tp.wait_cycles, p.status, ST_TIMEOUT_PEER_FLAG)) s_ok = 0;
-      __syncthreads();
-      if (!s_ok) break;
-      const uint8_t* sbase = reinterpret_cast<const uint8_t*>(tp.a_peer[src]);
-      for (int j = (int)blockIdx.x; j < tp.blocks_per_rank; j += n_copy) {
-        const int mbg = src * tp.blocks_per_rank + j;                    // global row block
-        uint8_t* dbase = reinterpret_cast<uint8_t*>(tp.a_stage) + (long long)mbg * BM * row_bytes;
-        const long long total_vec = (long long)BM * vec_per_row;
-        for (long long v = threadIdx.x; v < total_vec; v += GEMM_THREADS) {
-          const int rrow = (int)(v / vec_per_row), c = (int)(v % vec_per_row);
-          const uint4 x = __ldcv(reinterpret_cast<const uint4*>(sbase + ((long long)(j * BM + rrow) * tp.lda_shard) * 2 + c * 16));   // peer memory: never from a stale line
-          *reinterpret_cast<uint4*>(dbase + (long long)rrow * row_bytes + c * 16) = x;
+    const long long blk_vec = (long long)BM * row_bytes / 16;            // 16-byte vectors per row block
+    constexpr int UNROLL = 8;
+    // a system-scope fence drains every outstanding NVLink store, so it is paid once per GROUP row blocks
+    constexpr int GROUP = 4;
+    const int n_groups = (tp.blocks_per_rank + GROUP - 1) / GROUP;
+    for (int jg = (int)blockIdx.x; jg < n_groups; jg += n_copy) {
+      const int j0 = jg * GROUP;
+      const int nblk = min(GROUP, tp.blocks_per_rank - j0);
+      const int mbg = tp.rank * tp.blocks_per_rank + j0;                 // first global row block of the group
+      const long long boff = (long long)mbg * BM * row_bytes;
+      const long long grp_vec = blk_vec * nblk;
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(tp.stage_peer[tp.rank]) + boff);
+      for (long long v0 = threadIdx.x; v0 < grp_vec; v0 += (long long)GEMM_THREADS * UNROLL) {
+        uint4 x[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const long long v = v0 + (long long)u * GEMM_THREADS;
+          if (v < grp_vec) x[u] = src[v];
         }
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) { fence_proxy_async_all(); st_release_gpu_u32(tp.ready + mbg, tp.epoch); }
+        for (int rr = 1; rr < tp.world; ++rr) {
+          const int peer = (tp.rank + rr) % tp.world;                    // stagger the peers
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(tp.stage_peer[peer]) + boff);
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            const long long v = v0 + (long long)u * GEMM_THREADS;
+            if (v < grp_vec) dst[v] = x[u];
+          }
+        }
       }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      // the last gather CTA tells every peer "I no longer read your shard" and waits for the same from them
-      __threadfence();
-      if (atomicAdd(tp.done_ctr, 1u) == (uint32_t)(n_copy - 1)) {
-        *tp.done_ctr = 0u;
-        peer_handshake(tp, 1, true, p.status);
-      }
+      __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x == 0)
+        for (int rr = 1; rr < tp.world; ++rr)
+          for (int q = 0; q < nblk; ++q) st_release_sys_u32(tp.ready_peer[(tp.rank + rr) % tp.world] + mbg + q, tp.epoch);
+      __syncthreads();
     }
   } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -317,7 +320,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         if constexpr (TP == TP_AG_GEMM) {
           // rows of another rank: wait until the gather CTAs have landed this row block
           if (mb / tpp->blocks_per_rank != tpp->rank) {
-            if (!wait_flag<false>(tpp->ready + mb, tpp->epoch, tpp->wait_cycles, p.status, ST_TIMEOUT_PEER_FLAG)) { ok = false; break; }
+            if (!wait_flag<true>(tpp->ready_peer[tpp->rank] + mb, tpp->epoch, tpp->wait_cycles, p.status, ST_TIMEOUT_PEER_FLAG)) { ok = false; break; }
             fence_proxy_async_all();
           }
         }
@@ -586,6 +589,17 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if constexpr (TP == TP_AG_GEMM) {
+    // The last CTA of the grid tells every peer "my GEMM no longer reads my staging buffer" and waits for the
+    // same from them: when this kernel ends, the next call may push into any peer's staging buffer.
+    if (threadIdx.x == 0) {
+      __threadfence();
+      if (atomicAdd(tpp->done_ctr, 1u) == gridDim.x - 1) {
+        *tpp->done_ctr = 0u;
+        peer_handshake(*tpp, 1, true, p.status);
+      }
+    }
+  }
   if constexpr (TP == TP_GEMM_RS) {
     // ---------------------------------------------------------------- reduce-scatter half: handshake, then sum the slots
     const TpParams& tp = *tpp;
@@ -698,7 +712,7 @@ static int launch_tp(const GemmArgs& a, const TpParams& tp, cudaStream_t stream,
   constexpr int BK = S::BK;
   CUtensorMap tmA, tmB;
   // A: TP_AG_GEMM multiplies out of the local staging copy [M, K]; TP_GEMM_RS out of the caller's A
-  const void* aptr = (TP == TP_AG_GEMM) ? tp.a_stage : a.A;
+  const void* aptr = (TP == TP_AG_GEMM) ? tp.stage_peer[tp.rank] : a.A;
   const long long lda = (TP == TP_AG_GEMM) ? a.K : a.lda;
   int rc = make_tmap_3d(&tmA, aptr, DT<T>::v, sizeof(T), a.K, a.M, 1, lda * sizeof(T), (long long)a.M * lda * sizeof(T), BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return 100 + rc;

@@ -29,10 +29,10 @@ struct GemmParams {
 };
 
 // Tensor-parallel extension: the GEMM fused with the collective next to it, over NVLink peer memory.
-//   TP_AG_GEMM (all-gather -> GEMM): A's row blocks belong to `world` ranks. A few CTAs of the grid pull
-//     the remote shards into the local staging copy of A (one NVLink crossing per element) and
-//     publish a per-row-block flag; the TMA producers of the GEMM CTAs wait on that flag, so tiles of
-//     rows that have arrived multiply while later rows are still in flight.
+//   TP_AG_GEMM (all-gather -> GEMM): A's row blocks belong to `world` ranks. A few CTAs of the grid push
+//     this rank's rows into every peer's staging copy of A (one NVLink crossing per element and peer) and
+//     release a per-row-block flag at the peer; the TMA producers of the GEMM CTAs wait on their local
+//     flags, so tiles of rows that have arrived multiply while later rows are still in flight.
 //   TP_GEMM_RS (GEMM -> reduce-scatter): every rank holds a K-slice and computes a partial C. The
 //     epilogue stores each row block straight into its owner's slot buffer (plain 16-byte peer stores),
 //     the last CTA runs a cross-rank handshake, then all CTAs sum the `world` slots of the local rows
@@ -45,10 +45,9 @@ struct TpParams {
   uint32_t epoch;                    // strictly increasing per call (flags compare >=)
   long long wait_cycles;             // clock64 budget of one wait
   // TP_AG_GEMM
-  const void* a_peer[TP_MAX_WORLD];  // every rank's A shard [rows_per_rank, K] bf16, row stride lda_shard (peer-mapped)
-  long long lda_shard;
-  void* a_stage;                     // local [M, K] bf16 staging buffer (the A tensor map points here)
-  uint32_t* ready;                   // local, one word per row block
+  void* stage_peer[TP_MAX_WORLD];    // every rank's staging buffer [M, K] bf16 (peer-mapped); rank r fills rows r*M/world.. of
+                                     // its own copy before the call, the gather CTAs push them into all the others
+  uint32_t* ready_peer[TP_MAX_WORLD];// every rank's per-row-block flags (peer-mapped): written by the pushing rank
   // TP_GEMM_RS
   void* slots_peer[TP_MAX_WORLD];    // every rank's slot buffer [2][world][rows_per_rank][N] bf16 (peer-mapped)
   void* out;                         // local result [rows_per_rank, N] bf16

@@ -3,9 +3,9 @@ attention block (the reference has no tensor parallelism; its only multi-worker 
 simulated gradient all-reduce, rust-nn src/distributed.rs:54-124).
 
   `all_gather_gemm`     Y[M, N_local] = gather_rows(X_shard) @ W_shard^T  - column-parallel Linear after a
-                        sequence-sharded activation. Gather CTAs pull the remote row blocks of X once into a
-                        local staging copy and raise a flag per 128-row block; the GEMM's TMA producers wait
-                        on those flags, so arrived rows multiply while later ones are in flight.
+                        sequence-sharded activation. Gather CTAs push this rank's row blocks of X into every
+                        peer's staging copy and raise a flag per 128-row block there; the GEMM's TMA producers
+                        wait on their local flags, so arrived rows multiply while later ones are in flight.
   `gemm_reduce_scatter` Y_shard[M/world, N] = sum_r X[:, K_r] @ W[:, K_r]^T   - row-parallel Linear. Each
                         rank's epilogue stores its partial tiles into the owner's slot buffer (plain peer
                         stores), one cross-rank handshake, then every CTA sums the slots of the local rows
@@ -36,7 +36,7 @@ class TpParams(C.Structure):
     _fields_ = [
         ("mode", C.c_int), ("rank", C.c_int), ("world", C.c_int), ("copy_ctas", C.c_int),
         ("blocks_per_rank", C.c_int), ("epoch", C.c_uint32), ("wait_cycles", C.c_longlong),
-        ("a_peer", C.c_void_p * TP_MAX_WORLD), ("lda_shard", C.c_longlong), ("a_stage", C.c_void_p), ("ready", C.c_void_p),
+        ("stage_peer", C.c_void_p * TP_MAX_WORLD), ("ready_peer", C.c_void_p * TP_MAX_WORLD),
         ("slots_peer", C.c_void_p * TP_MAX_WORLD), ("out", C.c_void_p), ("go", C.c_void_p),
         ("flags", C.c_void_p * TP_MAX_WORLD), ("done_ctr", C.c_void_p),
     ]
@@ -65,8 +65,8 @@ class TPContext:
             dev = self.device
             self.stage = SymmetricBuffer(max_rows * max_k, torch.bfloat16, dev, self.group)                 # all-gather staging [M, K]
             self.slots = SymmetricBuffer(2 * self.world * self.rows_per_rank * max_n, torch.bfloat16, dev, self.group)
-            self.flags = SymmetricBuffer(2 * TP_MAX_WORLD, torch.int32, dev, self.group)
-            self.local = torch.zeros(max_rows // BM + 8, dtype=torch.int32, device=dev)                      # ready[m_blocks], go, done_ctr
+            self.flags = SymmetricBuffer(2 * TP_MAX_WORLD + max_rows // BM, torch.int32, dev, self.group)   # handshake words, then ready[m_blocks]
+            self.local = torch.zeros(8, dtype=torch.int32, device=dev)                                       # go, done_ctr
             self.clock_hz = torch.cuda.get_device_properties(dev).clock_rate * 1000
             self.wait_cycles = int(wait_seconds * self.clock_hz)
             self.sms = torch.cuda.get_device_properties(dev).multi_processor_count
@@ -89,12 +89,11 @@ class TPContext:
         tp.copy_ctas = self.copy_ctas if (mode == TP_AG_GEMM and self.world > 1) else 0
         tp.blocks_per_rank = rows_local // BM
         tp.epoch, tp.wait_cycles = self.epoch, self.wait_cycles
-        m_blocks = self.max_rows // BM
-        tp.ready = self.local.data_ptr()
-        tp.go = self.local.data_ptr() + 4 * m_blocks
-        tp.done_ctr = self.local.data_ptr() + 4 * (m_blocks + 1)
+        tp.go = self.local.data_ptr()
+        tp.done_ctr = self.local.data_ptr() + 4
         for r in range(self.world):
             tp.flags[r] = self.flags.ptrs[r]
+            tp.ready_peer[r] = self.flags.ptrs[r] + 4 * 2 * TP_MAX_WORLD
         return tp
 
     def all_gather_gemm(self, x_shard: torch.Tensor, w_shard: torch.Tensor, bias=None, act: str = "none", want_aux: bool = False):
@@ -114,8 +113,7 @@ class TPContext:
             mine.copy_(x_shard)
         tp = self._tp(TP_AG_GEMM, rows_local)
         for r in range(self.world):
-            tp.a_peer[r] = self.stage.ptrs[r] + r * rows_local * k * 2
-        tp.lda_shard, tp.a_stage = k, self.stage.ptrs[self.rank]
+            tp.stage_peer[r] = self.stage.ptrs[r]
         out = torch.empty(m, n, dtype=torch.bfloat16, device=self.device)
         aux = torch.empty(m, n, dtype=torch.bfloat16, device=self.device) if want_aux else None
         self._launch(tp, mine, w_shard, m, n, k, out, bias, act, None, aux)

@@ -26,7 +26,7 @@ def _run(nproc, extra, port, timeout=600):
 def test_fused_tp_and_ep_on_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    ranks = _run(2, ["--rows", "4096", "--k", "512", "--n", "2048"], 29631)
+    ranks = _run(2, ["--rows", "4096", "--kdim", "512", "--ncols", "2048"], 29631)
     for r in ranks:
         assert r["ag_gemm_rel_err"] < 1e-2 and r["ag_gemm_vs_baseline"] < 1e-2
         assert r["gemm_rs_rel_err"] < 2e-2 and r["gemm_rs_vs_baseline"] < 2e-2

@@ -40,10 +40,11 @@ def timed(fn, iters, dev):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--rows", type=int, default=4096)       # global rows M
-    ap.add_argument("--k", type=int, default=512)
-    ap.add_argument("--n", type=int, default=2048)          # global N of the column-parallel layer
+    ap.add_argument("--kdim", type=int, default=512)
+    ap.add_argument("--ncols", type=int, default=2048)          # global N of the column-parallel layer
     ap.add_argument("--iters", type=int, default=0)         # > 0: also time fused vs baseline
     ap.add_argument("--moe", type=int, default=1)
+    ap.add_argument("--copy-ctas", type=int, default=16)
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -57,7 +58,7 @@ def main():
     from rust_neural_network_b200.parallel.tp import TPContext
     nv.cuda()
 
-    M, K, N = args.rows, args.k, args.n
+    M, K, N = args.rows, args.kdim, args.ncols
     g = torch.Generator().manual_seed(7)
     X = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16).to(dev)          # identical on every rank
     W1 = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(dev)        # column-parallel: split N
@@ -71,7 +72,7 @@ def main():
     w2s = W2[:, rank * n_local:(rank + 1) * n_local].contiguous()
 
     out = {"rank": rank, "world": world}
-    ctx = TPContext(M, max(K, n_local), max(K, n_local), device=dev, backend="fused")
+    ctx = TPContext(M, max(K, n_local), max(K, n_local), device=dev, backend="fused", copy_ctas=args.copy_ctas)
     base = TPContext(M, K, N, device=dev, backend="nccl")
 
     # ---- all-gather -> GEMM (+bias, GELU): h[M, n_local]

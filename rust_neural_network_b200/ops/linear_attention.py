@@ -87,7 +87,9 @@ def _heads_first(t):
     return t.permute(0, 2, 1, 3).reshape(B * H, S, d)
 
 
-def linear_attention(q, k, v, scale: float = 1.0, eps: float = 1e-6, causal: bool = False, kind: str = "elu", chunk: int = CHUNK):
+def linear_attention(q, k, v, scale: float = 1.0, eps: float = 1e-6, causal: bool = False, kind: str = "elu", chunk: int = CHUNK, sp=None):
+    """[B, S, H, d] tensors. `sp`: a `parallel.sp.SPContext` when S is this rank's contiguous slice of a longer
+    sequence - the KV states of the other ranks then enter through one state exchange."""
     B, S, H, d = q.shape
     dtype = q.dtype
     pq = _heads_first(phi(q, scale, kind))                  # [BH, S, d]
@@ -100,6 +102,8 @@ def linear_attention(q, k, v, scale: float = 1.0, eps: float = 1e-6, causal: boo
     v1 = torch.cat([vh, ones], -1)                           # [BH, S, d+8]
     if not causal:
         state = matmul(pk.transpose(1, 2), v1)               # [BH, d, d+8]   (TN GEMM, K = S)
+        if sp is not None:
+            state = sp.all_sum(state.float()).to(dtype)      # every rank's tokens attend to every rank's state
         nd = matmul(pq, state)                               # [BH, S, d+8]
     else:
         C = min(chunk, S)
@@ -117,7 +121,10 @@ def linear_attention(q, k, v, scale: float = 1.0, eps: float = 1e-6, causal: boo
         intra = matmul(a, v1c)                               # [BHn, C, d+8]
         # between chunks: exclusive prefix sum of the chunk states (fp32)
         st = matmul(pkc.transpose(1, 2), v1c).reshape(BH, n, d, d + 8).float()
-        prefix = (torch.cumsum(st, 1) - st).to(dtype).reshape(BH * n, d, d + 8)
+        prefix = torch.cumsum(st, 1) - st
+        if sp is not None:
+            prefix = prefix + sp.exclusive_prefix(st.sum(1))[:, None]      # states of the tokens on lower ranks
+        prefix = prefix.to(dtype).reshape(BH * n, d, d + 8)
         inter = matmul(pqc, prefix)                          # [BHn, C, d+8]
         nd = (intra.float() + inter.float()).reshape(BH, Sp, d + 8)[:, :S]
     nd = nd.float()

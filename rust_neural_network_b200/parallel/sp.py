@@ -1,0 +1,94 @@
+"""Sequence (context) parallelism for linear attention: every rank owns a contiguous slice of the
+sequence and the ranks exchange only the [d x (d_v + 8)] KV states - O(d^2) per head instead of the
+O(S d) keys and values a softmax-attention ring would move. The reference scales sequence length only
+algorithmically (rust-nn src/linear_attention.rs:110-300) and has no multi-worker attention.
+
+`SPContext.exclusive_prefix(total)` returns, on rank r, the sum of `total` over ranks < r (differentiable:
+the backward is the mirror-image suffix exchange); `all_sum(total)` the sum over all ranks. Both are one
+kernel (csrc/comm/state_exchange.cu): publish into peer-mapped memory, flag handshake, peer loads, second
+handshake. CPU (gloo) ranks and `backend="nccl"` use an all-gather of the states instead.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+from torch.autograd import Function
+
+from .. import _native as nv
+
+SX_MAX_WORLD, SX_MAX_CTAS = 8, 64
+
+
+class StateExchangeArgs(C.Structure):
+    _fields_ = [("slot", C.c_void_p * SX_MAX_WORLD), ("flags", C.c_void_p * SX_MAX_WORLD), ("inp", C.c_void_p), ("out", C.c_void_p),
+                ("numel", C.c_longlong), ("rank", C.c_int), ("world", C.c_int), ("mode", C.c_int), ("epoch", C.c_uint32),
+                ("wait_cycles", C.c_longlong), ("status", C.c_void_p)]
+
+
+nv.register_sigs({"b200_state_exchange": [C.POINTER(StateExchangeArgs), C.c_int, C.c_void_p], "b200_state_exchange_flag_words": []})
+
+LOWER, HIGHER, ALL = 0, 1, 2
+
+
+class _ExchangeFn(Function):
+    @staticmethod
+    def forward(ctx, total, sp, mode):
+        ctx.sp, ctx.mode = sp, mode
+        return sp._exchange(total, mode)
+
+    @staticmethod
+    def backward(ctx, g):
+        back = {LOWER: HIGHER, HIGHER: LOWER, ALL: ALL}[ctx.mode]
+        return ctx.sp._exchange(g.contiguous(), back), None, None
+
+
+class SPContext:
+    def __init__(self, max_numel: int, device=None, group=None, backend: str = "fused", wait_seconds: float = 2.0, grid: int = 32):
+        self.group = group or dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.backend = backend if self.device.type == "cuda" else "nccl"
+        self.max_numel = (max_numel + 3) // 4 * 4
+        self.epoch = 0
+        self.grid = min(grid, SX_MAX_CTAS)
+        if self.backend == "fused":
+            from .ddp import SymmetricBuffer
+            self.slot = SymmetricBuffer(self.max_numel, torch.float32, self.device, self.group)
+            self.flags = SymmetricBuffer(2 * SX_MAX_WORLD * SX_MAX_CTAS, torch.int32, self.device, self.group)
+            self.wait_cycles = int(wait_seconds * torch.cuda.get_device_properties(self.device).clock_rate * 1000)
+            dist.barrier(self.group)
+            torch.cuda.synchronize()
+
+    def _exchange(self, total: torch.Tensor, mode: int) -> torch.Tensor:
+        if self.backend != "fused":
+            parts = [torch.empty_like(total) for _ in range(self.world)]
+            dist.all_gather(parts, total.contiguous(), group=self.group)
+            take = [r for r in range(self.world) if mode == ALL or (mode == LOWER and r < self.rank) or (mode == HIGHER and r > self.rank)]
+            out = torch.zeros_like(total)
+            for r in take:
+                out = out + parts[r]
+            return out
+        t = total.float().contiguous()
+        n = t.numel()
+        if n > self.max_numel or n % 4 != 0:
+            raise ValueError(f"state of {n} elements does not fit this context ({self.max_numel}) or is not a multiple of 4")
+        out = torch.empty_like(t)
+        self.epoch += 1
+        a = StateExchangeArgs()
+        for r in range(self.world):
+            a.slot[r], a.flags[r] = self.slot.ptrs[r], self.flags.ptrs[r]
+        a.inp, a.out, a.numel = t.data_ptr(), out.data_ptr(), n
+        a.rank, a.world, a.mode, a.epoch, a.wait_cycles = self.rank, self.world, mode, self.epoch, self.wait_cycles
+        a.status = nv.status_word(self.device).data_ptr()
+        nv.check(nv.cuda().b200_state_exchange(C.byref(a), self.grid, nv.stream_ptr()), "state_exchange")
+        nv.count_launch()
+        self._keep = (t, out)
+        return out.to(total.dtype).view(total.shape)
+
+    def exclusive_prefix(self, total: torch.Tensor) -> torch.Tensor:
+        return _ExchangeFn.apply(total, self, LOWER)
+
+    def all_sum(self, total: torch.Tensor) -> torch.Tensor:
+        return _ExchangeFn.apply(total, self, ALL)

@@ -31,6 +31,9 @@ def test_fused_tp_and_ep_on_two_gpus():
         assert r["ag_gemm_rel_err"] < 1e-2 and r["ag_gemm_vs_baseline"] < 1e-2
         assert r["gemm_rs_rel_err"] < 2e-2 and r["gemm_rs_vs_baseline"] < 2e-2
         assert r["ep_fwd_rel_err"] < 2e-2 and r["ep_dx_rel_err"] < 3e-2 and r["ep_dW1_rel_err"] < 3e-2
+        for tag in ("causal", "full"):
+            assert r[f"sp_{tag}_fwd_rel_err"] < 2e-2
+            assert max(r[f"sp_{tag}_dq_rel_err"], r[f"sp_{tag}_dk_rel_err"], r[f"sp_{tag}_dv_rel_err"]) < 4e-2
 
 
 def _cpu_tp_rank(rank, world, port, q):
@@ -46,6 +49,45 @@ def _cpu_tp_rank(rank, world, port, q):
     want = (torch.relu(X @ W1.t()) @ W2.t())[rank * 4:(rank + 1) * 4]
     q.put((rank, float((y.float() - want).abs().max()), float(want.abs().max())))
     dist.destroy_process_group()
+
+
+def _cpu_sp_rank(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from rust_neural_network_b200.ops.linear_attention import linear_attention
+    from rust_neural_network_b200.parallel.sp import SPContext
+    g = torch.Generator().manual_seed(9)
+    full = [torch.randn(1, 32 * world, 2, 8, generator=g) for _ in range(3)]
+    gy = torch.randn(1, 32 * world, 2, 8, generator=g)
+    sp = SPContext(2 * 8 * 16, device="cpu")
+    errs = []
+    for causal in (True, False):
+        ref_in = [t.clone().requires_grad_(True) for t in full]
+        ref = linear_attention(*ref_in, scale=0.3, causal=causal, chunk=16)
+        ref.backward(gy)
+        sl = slice(rank * 32, (rank + 1) * 32)
+        loc = [t[:, sl].clone().requires_grad_(True) for t in full]
+        got = linear_attention(*loc, scale=0.3, causal=causal, chunk=16, sp=sp)
+        got.backward(gy[:, sl])
+        errs.append(float((got - ref[:, sl]).abs().max()))
+        errs += [float((a.grad - b.grad[:, sl]).abs().max()) for a, b in zip(loc, ref_in)]
+    q.put((rank, max(errs)))
+    dist.destroy_process_group()
+
+
+def test_sequence_parallel_linear_attention_three_gloo_ranks():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_cpu_sp_rank, args=(r, 3, 29651, q)) for r in range(3)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(err < 1e-3 for _, err in res), res
 
 
 def test_tp_baseline_path_two_gloo_ranks():

@@ -137,6 +137,31 @@ def main():
         dist.all_reduce(gfull)
         out["ep_dW1_rel_err"] = rel(ep_moe.W1.grad, gfull[rank * e_local:(rank + 1) * e_local])
 
+    # ---- sequence-parallel linear attention: only the KV states cross ranks
+    if args.moe:
+        from rust_neural_network_b200.ops.linear_attention import linear_attention
+        from rust_neural_network_b200.parallel.sp import SPContext
+        B, S_loc, H, d = 2, 512, 4, 64
+        gq = torch.Generator().manual_seed(5)
+        full = [(torch.randn(B, S_loc * world, H, d, generator=gq) * 0.5).to(torch.bfloat16).to(dev) for _ in range(3)]
+        gfull = (torch.randn(B, S_loc * world, H, d, generator=gq)).to(torch.bfloat16).to(dev)
+        sp = SPContext(B * H * d * (d + 8), device=dev, backend="fused")
+        for causal in (True, False):
+            ref_in = [t.clone().requires_grad_(True) for t in full]
+            ref = linear_attention(*ref_in, scale=0.125, causal=causal)
+            ref.backward(gfull)
+            sl = slice(rank * S_loc, (rank + 1) * S_loc)
+            loc_in = [t[:, sl].clone().requires_grad_(True) for t in full]
+            got = linear_attention(*loc_in, scale=0.125, causal=causal, sp=sp)
+            got.backward(gfull[:, sl])
+            torch.cuda.synchronize()
+            nv.check_status()
+            tag = "causal" if causal else "full"
+            out[f"sp_{tag}_fwd_rel_err"] = rel(got, ref[:, sl])
+            out[f"sp_{tag}_dq_rel_err"] = rel(loc_in[0].grad, ref_in[0].grad[:, sl])
+            out[f"sp_{tag}_dk_rel_err"] = rel(loc_in[1].grad, ref_in[1].grad[:, sl])
+            out[f"sp_{tag}_dv_rel_err"] = rel(loc_in[2].grad, ref_in[2].grad[:, sl])
+
     gathered = [None] * world
     dist.all_gather_object(gathered, out)
     if rank == 0:

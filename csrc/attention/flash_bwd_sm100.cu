@@ -12,6 +12,7 @@
 //   dQ  = dS K                                             (K-major x MN-major)       -> TMEM -> fp32 atomics
 // dK / dV stay resident in TMEM for the whole loop. Warp w reads TMEM lanes 32*(w%4).. (its rows) and
 // the column half w/4. Every wait is bounded.
+#include <type_traits>
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
 #include "flash_sm100.h"
@@ -28,25 +29,30 @@ struct BwdParams {
   uint32_t* status;
 };
 
-// delta[b,h,s] = sum_e dO[b,s,h,e] * O[b,s,h,e]; one warp per row
+// delta[b,h,s] = sum_e dO[b,s,h,e] * O[b,s,h,e]; hd/8 lanes per row, one 16-byte load of each operand per lane
 __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, long long o_sb, long long o_ss, long long o_sh,
                                    const __nv_bfloat16* __restrict__ d, long long d_sb, long long d_ss, long long d_sh,
                                    float* __restrict__ delta, int B, int H, int S, int hd) {
-  long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+  const int lpr = hd / 8;                                   // lanes per row: 8 (hd 64) or 16 (hd 128)
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long w = t / lpr;
+  const int sub = (int)(t % lpr);
   const long long total = (long long)B * H * S;
-  if (w >= total) return;
-  const int s = (int)(w % S); long long r = w / S; const int h = (int)(r % H); const int b = (int)(r / H);
-  const __nv_bfloat16* op = o + b * o_sb + s * o_ss + h * o_sh;
-  const __nv_bfloat16* dp = d + b * d_sb + s * d_ss + h * d_sh;
   float acc = 0.f;
-  for (int e = 2 * lane; e < hd; e += 64) {
-    float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(op + e));
-    float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dp + e));
-    acc += a.x * c.x + a.y * c.y;
+  if (w < total) {
+    // rows are enumerated [b][s][h] so that neighbouring lanes read neighbouring memory
+    const int h = (int)(w % H); long long r = w / H; const int s = (int)(r % S); const int b = (int)(r / S);
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(o + b * o_sb + s * o_ss + h * o_sh + sub * 8));
+    const uint4 c = __ldg(reinterpret_cast<const uint4*>(d + b * d_sb + s * d_ss + h * d_sh + sub * 8));
+    const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
+    const float2 c0 = unpack_bf16x2(c.x), c1 = unpack_bf16x2(c.y), c2 = unpack_bf16x2(c.z), c3 = unpack_bf16x2(c.w);
+    acc = a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y + a2.x * c2.x + a2.y * c2.y + a3.x * c3.x + a3.y * c3.y;
   }
-  acc = warp_sum(acc);
-  if (lane == 0) delta[w] = acc;
+  for (int o2 = lpr >> 1; o2; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
+  if (w < total && sub == 0) {
+    const int h = (int)(w % H); long long r = w / H; const int s = (int)(r % S); const int b = (int)(r / S);
+    delta[((long long)b * H + h) * S + s] = acc;
+  }
 }
 
 // dq[b,s,h,:] (bf16, strided) = dq_accum[b,s,h,:] (fp32, contiguous)
@@ -72,11 +78,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, BwdParams p) {
   constexpr int BLK = 128;
   constexpr int KA = HD / 64;
-  constexpr int STAGES = (HD == 64) ? 2 : 1;
+  // head_dim 64 leaves room in TMEM for a double-buffered dQ and in shared memory for three Q/dO stages: the
+  // tensor cores then run dV/dK/dQ of block i and S/dP of block i+1 back to back while the CTA retires dQ of
+  // block i-1. head_dim 128 fills TMEM (dK, dV 128 columns each), dQ aliases S there and the steps serialise.
+  constexpr bool PIPE = (HD == 64);
+  constexpr int STAGES = PIPE ? 3 : 1;
   constexpr int TILE_BYTES = BLK * HD * 2;       // one Q / dO / K / V tile
   constexpr int PS_BYTES = BLK * BLK * 2;        // P or dS tile
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DK = 256, COL_DV = 256 + HD;
+  constexpr uint32_t COL_DQ = PIPE ? 384 : COL_S;   // PIPE: two buffers at 384 and 448
 
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sK = smem;
@@ -87,10 +98,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* sdS = sP + PS_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + PS_BYTES);
   uint64_t* kv_bar = bars;            // 1
-  uint64_t* q_bar = bars + 1;         // STAGES (Q and dO of one query block arrive together)
-  uint64_t* sdp_bar = bars + 3;       // 1
-  uint64_t* dq_bar = bars + 4;        // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  uint64_t* q_bar = bars + 1;         // up to 3 (Q and dO of one query block arrive together)
+  uint64_t* sdp_bar = bars + 4;       // 1
+  uint64_t* dq_bar = bars + 5;        // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int quarter = warp & 3, chalf = warp >> 2;
@@ -154,11 +165,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     tc_commit(sdp_bar);
   };
-  auto issue_grads = [&](int it) {
+  auto issue_grads = [&](int it, bool commit) {
     const int st = it % STAGES;
     const uint32_t aQ = smem_u32(sQ + st * TILE_BYTES), adO = smem_u32(sdO + st * TILE_BYTES);
     const uint32_t aK = smem_u32(sK), aP = smem_u32(sP), adS = smem_u32(sdS);
     const uint32_t acc = it > 0 ? 1u : 0u;
+    const uint32_t dq_col = PIPE ? COL_DQ + (uint32_t)(it & 1) * 64u : COL_DQ;
 #pragma unroll
     for (int k = 0; k < BLK / 16; ++k) {   // dV += P^T dO   (K dimension = query rows)
       umma_f16(tmem_base + COL_DV, make_sdesc_sw128(aP + k * 2048, BLK * 128, 1024),
@@ -172,39 +184,35 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
     for (int k = 0; k < BLK / 16; ++k) {   // dQ = dS K      (K dimension = key rows)
       const int atom = k >> 2, kk = k & 3;
-      umma_f16(tmem_base + COL_S, make_sdesc_sw128(adS + atom * (BLK * 128) + kk * 32, 0, 1024),
+      umma_f16(tmem_base + dq_col, make_sdesc_sw128(adS + atom * (BLK * 128) + kk * 32, 0, 1024),
                make_sdesc_sw128(aK + k * 2048, BLK * 128, 1024), idesc_km, k > 0 ? 1u : 0u);
     }
-    tc_commit(dq_bar);
+    if (commit) tc_commit(dq_bar);
   };
-
-  bool ok = true;
-  if (tid == 0 && n_iter > 0) {
-    mbar_expect_tx(kv_bar, 2 * TILE_BYTES);
+  // dQ rows of query block `it` -> fp32 atomics (scaled). The block's MMAs must be known complete.
+  auto retire_dq = [&](int it) {
+    const int q_row = (i_start + it) * BLK + row;
+    const uint32_t dq_col = PIPE ? COL_DQ + (uint32_t)(it & 1) * 64u : COL_DQ;
+    float* dst = p.dq_accum + ((((long long)b * p.Sq + q_row) * p.H + h) * HD);
 #pragma unroll
-    for (int a = 0; a < KA; ++a) {
-      tma_load_4d(sK + a * (BLK * 128), &tmK, kv_bar, a * 64, h, kv0, b);
-      tma_load_4d(sV + a * (BLK * 128), &tmV, kv_bar, a * 64, h, kv0, b);
+    for (int c = 0; c < HD / 64; ++c) {
+      const int colbase = chalf * (HD / 2) + c * 32;
+      uint32_t v[32];
+      tmem_ld_x32(tmem_row + dq_col + colbase, v);
+      tmem_ld_wait();
+      if (q_row < p.Sq) {
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          float4 a = make_float4(__uint_as_float(v[e]) * p.scale, __uint_as_float(v[e + 1]) * p.scale,
+                                 __uint_as_float(v[e + 2]) * p.scale, __uint_as_float(v[e + 3]) * p.scale);
+          atomicAdd(reinterpret_cast<float4*>(dst + colbase + e), a);
+        }
+      }
     }
-    load_q(0);
-    if (STAGES > 1 && n_iter > 1) load_q(1);
-    ok = mbar_wait(kv_bar, 0, p.status, ST_TIMEOUT_TMA_FULL) && mbar_wait(&q_bar[0], 0, p.status, ST_TIMEOUT_TMA_FULL);
-    if (ok) { tc_fence_after_sync(); issue_s_dp(0); }
-  }
-
-  const float log2e = 1.4426950408889634f;
-  for (int it = 0; it < n_iter; ++it) {
-    const int i = i_start + it;
-    const int q0 = i * BLK;
-    const int q_row = q0 + row;
-    const bool row_ok = q_row < p.Sq;
-    const long long stat_idx = ((long long)b * p.H + h) * p.Sq + q_row;
-    const float lse2 = row_ok ? p.lse[stat_idx] * log2e : 0.f;
-    const float dlt = row_ok ? p.delta[stat_idx] : 0.f;
-    if (!mbar_wait(sdp_bar, it & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
-    if (__syncthreads_or(!ok)) { ok = false; break; }
-    tc_fence_after_sync();
-    const bool need_mask = CAUSAL && (kv0 + BLK - 1 > q0);
+  };
+  // P = exp2(S c - lse), dS = P (dP - delta) for this thread's row and column half -> bf16 tiles in shared memory
+  auto softmax_block = [&](auto masked, int q_row, bool row_ok, float lse2, float dlt) {
+    constexpr bool MASK = decltype(masked)::value;
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
       const int colbase = chalf * 64 + c * 32;
@@ -215,8 +223,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       float pp[32], ds[32];
 #pragma unroll
       for (int e = 0; e < 32; ++e) {
-        float pr = exp2f(__uint_as_float(sv[e]) * p.scale_log2 - lse2);
-        if (!row_ok || (need_mask && (kv0 + colbase + e > q_row))) pr = 0.f;
+        float pr = ex2_approx(fmaf(__uint_as_float(sv[e]), p.scale_log2, -lse2));
+        if (MASK) { if (!row_ok || (CAUSAL && (kv0 + colbase + e > q_row))) pr = 0.f; }
         pp[e] = pr;
         ds[e] = pr * (__uint_as_float(dv[e]) - dlt);
       }
@@ -231,39 +239,85 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                                                           pack_bf16x2(ds[g * 8 + 4], ds[g * 8 + 5]), pack_bf16x2(ds[g * 8 + 6], ds[g * 8 + 7]));
       }
     }
+  };
+
+  bool ok = true;
+  if (tid == 0 && n_iter > 0) {
+    mbar_expect_tx(kv_bar, 2 * TILE_BYTES);
+#pragma unroll
+    for (int a = 0; a < KA; ++a) {
+      tma_load_4d(sK + a * (BLK * 128), &tmK, kv_bar, a * 64, h, kv0, b);
+      tma_load_4d(sV + a * (BLK * 128), &tmV, kv_bar, a * 64, h, kv0, b);
+    }
+    for (int s = 0; s < STAGES && s < n_iter; ++s) load_q(s);
+    ok = mbar_wait(kv_bar, 0, p.status, ST_TIMEOUT_TMA_FULL) && mbar_wait(&q_bar[0], 0, p.status, ST_TIMEOUT_TMA_FULL);
+    if (ok) { tc_fence_after_sync(); issue_s_dp(0); }
+  }
+
+  const float log2e = 1.4426950408889634f;
+  // per-row statistics of the next query block are fetched one iteration ahead (their latency hides behind the MMAs)
+  auto load_stats = [&](int it, float& lse2, float& dlt) {
+    const int q_row = (i_start + it) * BLK + row;
+    if (it < n_iter && q_row < p.Sq) {
+      const long long idx = ((long long)b * p.H + h) * p.Sq + q_row;
+      lse2 = __ldg(p.lse + idx) * log2e; dlt = __ldg(p.delta + idx);
+    } else { lse2 = 0.f; dlt = 0.f; }
+  };
+  float lse2_n, dlt_n;
+  load_stats(0, lse2_n, dlt_n);
+
+  for (int it = 0; it < n_iter; ++it) {
+    const int q0 = (i_start + it) * BLK;
+    const int q_row = q0 + row;
+    const bool row_ok = q_row < p.Sq;
+    const float lse2 = lse2_n, dlt = dlt_n;
+    load_stats(it + 1, lse2_n, dlt_n);
+    if (!mbar_wait(sdp_bar, it & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;      // S/dP of block it (and every MMA before) done
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    tc_fence_after_sync();
+    const bool need_mask = (CAUSAL && (kv0 + BLK - 1 > q0)) || (q0 + BLK > p.Sq);
+    if (need_mask) softmax_block(std::true_type{}, q_row, row_ok, lse2, dlt);
+    else softmax_block(std::false_type{}, q_row, row_ok, lse2, dlt);
     tc_fence_before_sync();
     fence_proxy_async_smem();
     __syncthreads();
-    if (tid == 0) { tc_fence_after_sync(); issue_grads(it); }
-    if (!mbar_wait(dq_bar, it & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
-    if (__syncthreads_or(!ok)) { ok = false; break; }
-    tc_fence_after_sync();
-    // the Q/dO stage of this iteration is free: prefetch a later query block into it
-    if (tid == 0 && it + STAGES < n_iter) load_q(it + STAGES);
-    // dQ rows -> fp32 atomics (scaled)
-    if (true) {
-      float* dst = p.dq_accum + ((((long long)b * p.Sq + q_row) * p.H + h) * HD);
-#pragma unroll
-      for (int c = 0; c < HD / 64; ++c) {
-        const int colbase = chalf * (HD / 2) + c * 32;
-        uint32_t v[32];
-        tmem_ld_x32(tmem_row + COL_S + colbase, v);
-        tmem_ld_wait();
-        if (row_ok) {
-#pragma unroll
-          for (int e = 0; e < 32; e += 4) {
-            float4 a = make_float4(__uint_as_float(v[e]) * p.scale, __uint_as_float(v[e + 1]) * p.scale,
-                                   __uint_as_float(v[e + 2]) * p.scale, __uint_as_float(v[e + 3]) * p.scale);
-            atomicAdd(reinterpret_cast<float4*>(dst + colbase + e), a);
-          }
+    if constexpr (PIPE) {
+      if (tid == 0) {
+        tc_fence_after_sync();
+        const bool last = (it + 1 == n_iter);
+        issue_grads(it, last);
+        if (!last) {
+          ok = mbar_wait(&q_bar[(it + 1) % STAGES], ((it + 1) / STAGES) & 1, p.status, ST_TIMEOUT_TMA_FULL);
+          if (ok) { tc_fence_after_sync(); issue_s_dp(it + 1); }
         }
       }
+      // while the tensor cores work: retire dQ of the previous block (complete since this iteration's sdp_bar)
+      if (it > 0) {
+        retire_dq(it - 1);
+        // Q/dO stage of block it-1 is free as well
+        if (tid == 0 && it - 1 + STAGES < n_iter) load_q(it - 1 + STAGES);
+      }
+      tc_fence_before_sync();
+    } else {
+      if (tid == 0) { tc_fence_after_sync(); issue_grads(it, true); }
+      if (!mbar_wait(dq_bar, it & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
+      if (__syncthreads_or(!ok)) { ok = false; break; }
+      tc_fence_after_sync();
+      if (tid == 0 && it + STAGES < n_iter) load_q(it + STAGES);
+      retire_dq(it);
+      tc_fence_before_sync();
+      __syncthreads();
+      if (tid == 0 && it + 1 < n_iter) {
+        ok = mbar_wait(&q_bar[(it + 1) % STAGES], ((it + 1) / STAGES) & 1, p.status, ST_TIMEOUT_TMA_FULL);
+        if (ok) { tc_fence_after_sync(); issue_s_dp(it + 1); }
+      }
     }
-    tc_fence_before_sync();
-    __syncthreads();
-    if (tid == 0 && it + 1 < n_iter) {
-      ok = mbar_wait(&q_bar[(it + 1) % STAGES], ((it + 1) / STAGES) & 1, p.status, ST_TIMEOUT_TMA_FULL);
-      if (ok) { tc_fence_after_sync(); issue_s_dp(it + 1); }
+  }
+  if constexpr (PIPE) {
+    if (n_iter > 0) {
+      if (ok && !mbar_wait(dq_bar, 0, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;      // the last block's dV / dK / dQ
+      if (__syncthreads_or(!ok)) ok = false;
+      if (ok) { tc_fence_after_sync(); retire_dq(n_iter - 1); }
     }
   }
 
@@ -313,7 +367,7 @@ template <int HD, bool CAUSAL>
 static int bwd_set_attr() {
   static bool done = false;
   if (done) return 0;
-  constexpr int STAGES = (HD == 64) ? 2 : 1;
+  constexpr int STAGES = (HD == 64) ? 3 : 1;
   constexpr int SMEM = 2 * 128 * HD * 2 + 2 * STAGES * 128 * HD * 2 + 2 * 128 * 128 * 2 + 128;
   (void)cudaGetLastError();
   if (cudaFuncSetAttribute(flash_bwd_kernel<HD, CAUSAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return 1;
@@ -330,12 +384,12 @@ static int launch_bwd(const FlashArgs& a, cudaStream_t st) {
   if (make_tmap_attn(&tmK, a.k.ptr, BF, 2, a.hd, a.H, a.Skv, a.B, a.k.sh, a.k.ss, a.k.sb, 64, 128, SW)) return 102;
   if (make_tmap_attn(&tmV, a.v.ptr, BF, 2, a.hd, a.H, a.Skv, a.B, a.v.sh, a.v.ss, a.v.sb, 64, 128, SW)) return 103;
   if (make_tmap_attn(&tmdO, a.dout.ptr, BF, 2, a.hd, a.H, a.Sq, a.B, a.dout.sh, a.dout.ss, a.dout.sb, 64, 128, SW)) return 104;
-  constexpr int STAGES = (HD == 64) ? 2 : 1;
+  constexpr int STAGES = (HD == 64) ? 3 : 1;
   constexpr int SMEM = 2 * 128 * HD * 2 + 2 * STAGES * 128 * HD * 2 + 2 * 128 * 128 * 2 + 128;
   auto kfn = flash_bwd_kernel<HD, CAUSAL>;
   if (bwd_set_attr<HD, CAUSAL>()) return 105;
   const long long rows = (long long)a.B * a.H * a.Sq;
-  flash_delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>(
+  flash_delta_kernel<<<(unsigned)((rows * (a.hd / 8) + 255) / 256), 256, 0, st>>>(
       (const __nv_bfloat16*)a.o.ptr, a.o.sb, a.o.ss, a.o.sh, (const __nv_bfloat16*)a.dout.ptr, a.dout.sb, a.dout.ss,
       a.dout.sh, a.delta, a.B, a.H, a.Sq, a.hd);
   cudaMemsetAsync(a.dq_accum, 0, sizeof(float) * (size_t)a.B * a.Sq * a.H * a.hd, st);

@@ -8,10 +8,10 @@
 //   S  = Q K_j^T     tcgen05.mma, both operands K-major 128B-swizzled tiles written by TMA   -> TMEM
 //   P  = exp2(S*c - m)  read back with tcgen05.ld (one row per thread: no shuffles), written to
 //                        shared memory as a bf16 K-major swizzled A operand
-//   PV = P V_j       tcgen05.mma, V consumed MN-major straight from its [kv][hd] layout      -> TMEM
-//   O  = O*alpha + PV   in registers (fp32)
-// K/V tiles are double-buffered by TMA; two CTAs share an SM (TMEM 2 x 256 columns) so one CTA's
-// exponentials overlap the other's MMAs. Every wait is bounded.
+//   O += P V_j       tcgen05.mma accumulating in TMEM, V consumed MN-major straight from its [kv][hd] layout;
+//                    O is rescaled (TMEM load / store) only when the running maximum grows by > 2^8
+// S_{j+1} is issued right behind P V_j, K/V tiles are double-buffered by TMA, and two CTAs share an SM
+// (TMEM 2 x 256 columns) so one CTA's exponentials overlap the other's MMAs. Every wait is bounded.
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
 #include "flash_sm100.h"
@@ -84,18 +84,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   constexpr uint32_t idesc_s = make_idesc(BMQ, BN, CFMT_F32, FMT_BF16, FMT_BF16, 0, 0);
   constexpr uint32_t idesc_pv = make_idesc(BMQ, HD, CFMT_F32, FMT_BF16, FMT_BF16, 0, 1);
 
-  auto load_kv = [&](int j) {
+  auto load_k = [&](int j) {
     const int st = j & 1;
+    mbar_expect_tx(&k_bar[st], KV_BYTES);
 #pragma unroll
-    for (int a = 0; a < KA; ++a) {
-      if (a == 0) mbar_expect_tx(&k_bar[st], KV_BYTES);
-      tma_load_4d(sK + st * KV_BYTES + a * (BN * 128), &tmK, &k_bar[st], a * 64, h, j * BN, b);
-    }
+    for (int a = 0; a < KA; ++a) tma_load_4d(sK + st * KV_BYTES + a * (BN * 128), &tmK, &k_bar[st], a * 64, h, j * BN, b);
+  };
+  auto load_v = [&](int j) {
+    const int st = j & 1;
+    mbar_expect_tx(&v_bar[st], KV_BYTES);
 #pragma unroll
-    for (int a = 0; a < KA; ++a) {
-      if (a == 0) mbar_expect_tx(&v_bar[st], KV_BYTES);
-      tma_load_4d(sV + st * KV_BYTES + a * (BN * 128), &tmV, &v_bar[st], a * 64, h, j * BN, b);
-    }
+    for (int a = 0; a < KA; ++a) tma_load_4d(sV + st * KV_BYTES + a * (BN * 128), &tmV, &v_bar[st], a * 64, h, j * BN, b);
   };
   auto issue_s = [&](int j) {   // S = Q K_j^T
     const int st = j & 1;
@@ -117,7 +116,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int atom = k >> 2, kk = k & 3;
       uint64_t da = make_sdesc_sw128(aP + atom * (BMQ * 128) + kk * 32, 0, 1024);
       uint64_t db = make_sdesc_sw128(aV + k * 2048, BN * 128, 1024);
-      umma_f16(tmem_base + PV_COL, da, db, idesc_pv, k > 0 ? 1u : 0u);
+      umma_f16(tmem_base + PV_COL, da, db, idesc_pv, (k > 0 || j > 0) ? 1u : 0u);
     }
     tc_commit(pv_bar);
   };
@@ -127,116 +126,120 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_expect_tx(q_bar, Q_BYTES);
 #pragma unroll
     for (int a = 0; a < KA; ++a) tma_load_4d(sQ + a * (BMQ * 128), &tmQ, q_bar, a * 64, h, q0, b);
-    load_kv(0);
-    if (n_blocks > 1) load_kv(1);
+    load_k(0); load_v(0);
+    if (n_blocks > 1) { load_k(1); load_v(1); }
     ok = mbar_wait(q_bar, 0, p.status, ST_TIMEOUT_TMA_FULL) && mbar_wait(&k_bar[0], 0, p.status, ST_TIMEOUT_TMA_FULL);
     if (ok) { tc_fence_after_sync(); issue_s(0); }
   }
 
-  float m_run = -INFINITY, l_run = 0.f;
-  float o_acc[HD];
-#pragma unroll
-  for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
+  // Online softmax with the output accumulator RESIDENT IN TMEM: P V_j accumulates onto O on the tensor
+  // cores and O is only touched by threads when the running maximum grows by more than 2^8 (lazy
+  // rescaling; P stays below 2^8, exact after the final division by l, which uses the same reference).
+  // m_used: the maximum the exponentials currently refer to (log2 domain); l_run: row sum in that scale.
+  float m_used = -INFINITY, l_run = 0.f;
   const int q_row = q0 + tid;
+  const float c = p.scale_log2;
 
   for (int j = 0; j < n_blocks; ++j) {
     const int st = j & 1;
-    const uint32_t ph_kv = (j >> 1) & 1;
-    if (!mbar_wait(s_bar, j & 1, p.status, ST_TIMEOUT_ACC_FULL)) { ok = false; }
+    if (!mbar_wait(s_bar, j & 1, p.status, ST_TIMEOUT_ACC_FULL)) { ok = false; }      // S_j done, and with it P V_{j-1}
     if (__syncthreads_or(!ok)) { ok = false; break; }
     tc_fence_after_sync();
+    // K_j has been consumed by S_j and V_{j-1} by P V_{j-1}: refill those buffers (K two blocks ahead, V one)
+    if (tid == 0) {
+      if (j + 2 < n_blocks) load_k(j + 2);
+      if (j >= 1 && j + 1 < n_blocks) load_v(j + 1);
+    }
     const int kv0 = j * BN;
     const bool need_mask = (kv0 + BN > p.Skv) || (CAUSAL && (kv0 + BN - 1 > q0));
-    // pass 1: row maximum
-    float mx = -INFINITY;
+    // the whole row of S in registers: one pass over TMEM
+    float s[BN];
 #pragma unroll
-    for (int c = 0; c < BN / 32; ++c) {
-      uint32_t v[32];
-      tmem_ld_x32(tmem_row + c * 32, v);
-      tmem_ld_wait();
+    for (int cc = 0; cc < BN / 32; ++cc) tmem_ld_x32(tmem_row + cc * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[cc * 32]));
+    tmem_ld_wait();
+    if (need_mask) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        float s = __uint_as_float(v[i]);
-        if (need_mask) {
-          const int col = kv0 + c * 32 + i;
-          if (col >= p.Skv || (CAUSAL && col > q_row)) s = -INFINITY;
-        }
-        mx = fmaxf(mx, s);
+      for (int i = 0; i < BN; ++i) {
+        const int col = kv0 + i;
+        if (col >= p.Skv || (CAUSAL && col > q_row)) s[i] = -INFINITY;
       }
     }
-    const float m_new = fmaxf(m_run, mx * p.scale_log2);
-    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-    const float alpha = exp2f(m_run - m_use);
-    // pass 2: exponentials, row sum, bf16 P tile into shared memory (K-major, 128B swizzle)
+    float mx = s[0];
+#pragma unroll
+    for (int i = 1; i < BN; ++i) mx = fmaxf(mx, s[i]);
+    const float m_new = fmaxf(m_used, mx * c);
+    const bool grow = m_new > m_used + 8.f;                     // also true on the first finite maximum (m_used = -inf)
+    if (__any_sync(0xffffffffu, grow)) {                        // TMEM accesses are warp-wide: the warp rescales together
+      const float alpha = (m_new == -INFINITY) ? 1.f : ex2_approx(m_used - m_new);
+      if (j > 0) {
+#pragma unroll
+        for (int cc = 0; cc < HD / 32; ++cc) {
+          uint32_t o[32];
+          tmem_ld_x32(tmem_row + PV_COL + cc * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_x32(tmem_row + PV_COL + cc * 32, o);
+        }
+        tmem_st_wait();
+      }
+      l_run *= alpha;
+      m_used = m_new;
+    }
+    const float m_ref = (m_used == -INFINITY) ? 0.f : m_used;
     float rs = 0.f;
 #pragma unroll
-    for (int c = 0; c < BN / 32; ++c) {
-      uint32_t v[32];
-      tmem_ld_x32(tmem_row + c * 32, v);
-      tmem_ld_wait();
-      float e[32];
+    for (int i = 0; i < BN; ++i) { s[i] = ex2_approx(fmaf(s[i], c, -m_ref)); rs += s[i]; }
+    l_run += rs;
+    // bf16 P tile into shared memory (K-major, 128B swizzle)
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        float s = __uint_as_float(v[i]);
-        if (need_mask) {
-          const int col = kv0 + c * 32 + i;
-          if (col >= p.Skv || (CAUSAL && col > q_row)) s = -INFINITY;
-        }
-        e[i] = exp2f(s * p.scale_log2 - m_use);
-        rs += e[i];
-      }
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        const int cc = c * 4 + g;                 // 16-byte chunk index along kv
-        const int atom = cc >> 3, chunk = cc & 7;
-        uint4 o = make_uint4(pack_bf16x2(e[g * 8 + 0], e[g * 8 + 1]), pack_bf16x2(e[g * 8 + 2], e[g * 8 + 3]),
-                             pack_bf16x2(e[g * 8 + 4], e[g * 8 + 5]), pack_bf16x2(e[g * 8 + 6], e[g * 8 + 7]));
-        *reinterpret_cast<uint4*>(sP + atom * (BMQ * 128) + sw128_offset(tid, chunk)) = o;
-      }
+    for (int g = 0; g < BN / 8; ++g) {
+      const int atom = g >> 3, chunk = g & 7;
+      uint4 o = make_uint4(pack_bf16x2(s[g * 8 + 0], s[g * 8 + 1]), pack_bf16x2(s[g * 8 + 2], s[g * 8 + 3]),
+                           pack_bf16x2(s[g * 8 + 4], s[g * 8 + 5]), pack_bf16x2(s[g * 8 + 6], s[g * 8 + 7]));
+      *reinterpret_cast<uint4*>(sP + atom * (BMQ * 128) + sw128_offset(tid, chunk)) = o;
     }
-    l_run = l_run * alpha + rs;
-    m_run = m_new;
     tc_fence_before_sync();
     fence_proxy_async_smem();
     __syncthreads();
     if (tid == 0) {
-      ok = mbar_wait(&v_bar[st], ph_kv, p.status, ST_TIMEOUT_TMA_FULL);
+      ok = mbar_wait(&v_bar[st], (j >> 1) & 1, p.status, ST_TIMEOUT_TMA_FULL);
       if (ok) {
         tc_fence_after_sync();
-        issue_pv(j);
+        issue_pv(j);                                              // O (+)= P V_j ; commits pv_bar
         if (j + 1 < n_blocks) {
           ok = mbar_wait(&k_bar[st ^ 1], ((j + 1) >> 1) & 1, p.status, ST_TIMEOUT_TMA_FULL);
           if (ok) issue_s(j + 1);
         }
       }
     }
-    if (!mbar_wait(pv_bar, j & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
-    if (__syncthreads_or(!ok)) { ok = false; break; }
-    tc_fence_after_sync();
-    // K_j / V_j buffers are free now: prefetch block j+2 into them
-    if (tid == 0 && j + 2 < n_blocks) load_kv(j + 2);
-#pragma unroll
-    for (int c = 0; c < HD / 32; ++c) {
-      uint32_t v[32];
-      tmem_ld_x32(tmem_row + PV_COL + c * 32, v);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha + __uint_as_float(v[i]);
-    }
-    tc_fence_before_sync();
   }
+  // the last P V: wait for its commit (pv_bar completes once per block; parity of the last one)
+  if (ok && !mbar_wait(pv_bar, (n_blocks - 1) & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
+  if (__syncthreads_or(!ok)) ok = false;
+  tc_fence_after_sync();
 
-  if (ok && q_row < p.Sq) {
+  if (ok) {
     const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
     __nv_bfloat16* op = p.o + (long long)b * p.o_sb + (long long)q_row * p.o_ss + (long long)h * p.o_sh;
 #pragma unroll
-    for (int i = 0; i < HD; i += 8) {
-      uint4 o = make_uint4(pack_bf16x2(o_acc[i] * inv_l, o_acc[i + 1] * inv_l), pack_bf16x2(o_acc[i + 2] * inv_l, o_acc[i + 3] * inv_l),
-                           pack_bf16x2(o_acc[i + 4] * inv_l, o_acc[i + 5] * inv_l), pack_bf16x2(o_acc[i + 6] * inv_l, o_acc[i + 7] * inv_l));
-      *reinterpret_cast<uint4*>(op + i) = o;
+    for (int cc = 0; cc < HD / 32; ++cc) {
+      uint32_t v[32];
+      tmem_ld_x32(tmem_row + PV_COL + cc * 32, v);
+      tmem_ld_wait();
+      if (q_row < p.Sq) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 o = make_uint4(pack_bf16x2(__uint_as_float(v[i]) * inv_l, __uint_as_float(v[i + 1]) * inv_l),
+                               pack_bf16x2(__uint_as_float(v[i + 2]) * inv_l, __uint_as_float(v[i + 3]) * inv_l),
+                               pack_bf16x2(__uint_as_float(v[i + 4]) * inv_l, __uint_as_float(v[i + 5]) * inv_l),
+                               pack_bf16x2(__uint_as_float(v[i + 6]) * inv_l, __uint_as_float(v[i + 7]) * inv_l));
+          *reinterpret_cast<uint4*>(op + cc * 32 + i) = o;
+        }
+      }
     }
-    if (p.lse) {
-      const float mu = (m_run == -INFINITY) ? 0.f : m_run;
+    if (p.lse && q_row < p.Sq) {
+      const float mu = (m_used == -INFINITY) ? 0.f : m_used;
       p.lse[((long long)b * p.H + h) * p.Sq + q_row] = (mu + log2f(fmaxf(l_run, 1e-37f))) * 0.6931471805599453f;
     }
   }

@@ -276,6 +276,12 @@ __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t chunk16)
 // ----------------------------------------------------------------------------
 // small numeric helpers
 // ----------------------------------------------------------------------------
+// 2^x on the special-function unit: one MUFU instruction, no denormal fix-up code around it
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

@@ -32,8 +32,9 @@ def test_fused_tp_and_ep_on_two_gpus():
         assert r["gemm_rs_rel_err"] < 2e-2 and r["gemm_rs_vs_baseline"] < 2e-2
         assert r["ep_fwd_rel_err"] < 2e-2 and r["ep_dx_rel_err"] < 3e-2 and r["ep_dW1_rel_err"] < 3e-2
         for tag in ("causal", "full"):
-            assert r[f"sp_{tag}_fwd_rel_err"] < 2e-2
-            assert max(r[f"sp_{tag}_dq_rel_err"], r[f"sp_{tag}_dk_rel_err"], r[f"sp_{tag}_dv_rel_err"]) < 4e-2
+            # against the fp32 oracle the sequence-sharded run is as accurate as the unsharded bf16 run
+            for nm in ("fwd", "dq", "dk", "dv"):
+                assert r[f"sp_{tag}_{nm}_rel_err"] < 1.5 * r[f"ref_{tag}_{nm}_rel_err"] + 1e-2, (tag, nm, r)
 
 
 def _cpu_tp_rank(rank, world, port, q):

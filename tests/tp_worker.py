@@ -157,10 +157,16 @@ def main():
             torch.cuda.synchronize()
             nv.check_status()
             tag = "causal" if causal else "full"
-            out[f"sp_{tag}_fwd_rel_err"] = rel(got, ref[:, sl])
-            out[f"sp_{tag}_dq_rel_err"] = rel(loc_in[0].grad, ref_in[0].grad[:, sl])
-            out[f"sp_{tag}_dk_rel_err"] = rel(loc_in[1].grad, ref_in[1].grad[:, sl])
-            out[f"sp_{tag}_dv_rel_err"] = rel(loc_in[2].grad, ref_in[2].grad[:, sl])
+            # fp32 O(S^2) oracle: the sharded run must be as close to it as the unsharded bf16 run is
+            from rust_neural_network_b200.ops.linear_attention import linear_attention_ref
+            orc_in = [t.float().clone().requires_grad_(True) for t in full]
+            orc = linear_attention_ref(*orc_in, scale=0.125, causal=causal)
+            orc.backward(gfull.float())
+            out[f"sp_{tag}_fwd_rel_err"] = rel(got, orc[:, sl])
+            out[f"ref_{tag}_fwd_rel_err"] = rel(ref[:, sl], orc[:, sl])
+            for i, nm in enumerate(("dq", "dk", "dv")):
+                out[f"sp_{tag}_{nm}_rel_err"] = rel(loc_in[i].grad, orc_in[i].grad[:, sl])
+                out[f"ref_{tag}_{nm}_rel_err"] = rel(ref_in[i].grad[:, sl], orc_in[i].grad[:, sl])
 
     gathered = [None] * world
     dist.all_gather_object(gathered, out)

@@ -41,20 +41,44 @@ class L2Flusher:
 
 
 def time_fn(fn, iters=10, warmup=3):
+    """Median device time of `fn` in ms. Each timed call follows an L2 flush; the sequence (flush, fn) x iters is
+    recorded into a CUDA graph and replayed, and a second graph with the flushes alone is subtracted, so neither
+    host launch latency nor the flush itself is in the number."""
     dev = torch.device("cuda")
     flush = L2Flusher(dev)
     for _ in range(max(3, warmup)):
         fn()
     torch.cuda.synchronize()
-    times = []
-    for _ in range(iters):
-        flush()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(); fn(); e1.record()
-        torch.cuda.synchronize()
-        times.append(e0.elapsed_time(e1))
-    times.sort()
-    return times[len(times) // 2]
+
+    def capture(with_fn):
+        g = torch.cuda.CUDAGraph()
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            flush()
+            if with_fn:
+                fn()
+        torch.cuda.current_stream().wait_stream(s)
+        with torch.cuda.graph(g):
+            for _ in range(iters):
+                flush()
+                if with_fn:
+                    fn()
+        return g
+
+    def replay_ms(g):
+        ts = []
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); g.replay(); e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    g_both, g_flush = capture(True), capture(False)
+    replay_ms(g_both); replay_ms(g_flush)
+    return max(replay_ms(g_both) - replay_ms(g_flush), 0.0) / iters
 
 
 def main(argv=None):
@@ -70,6 +94,7 @@ def main(argv=None):
     ap.add_argument("--a-mn", action="store_true")
     ap.add_argument("--b-mn", action="store_true")
     ap.add_argument("--f32-out", action="store_true")
+    ap.add_argument("--bn", type=int, default=0, help="GEMM tile width override (64 / 128 / 256)")
     args = ap.parse_args(argv)
 
     from rust_neural_network_b200 import _native as nv
@@ -88,7 +113,7 @@ def main(argv=None):
         bias = torch.randn(N, device=dev) if args.bias else None
         res = torch.randn(M, N, device=dev).bfloat16() if args.residual else None
         kw = dict(a_mn=args.a_mn, b_mn=args.b_mn, bias=bias, act=args.act, residual=res, want_aux=args.act in ("gelu", "silu"),
-                  out_dtype=torch.float32 if args.f32_out else None)
+                  out_dtype=torch.float32 if args.f32_out else None, bn=args.bn)
         ms = time_fn(lambda: G.gemm(a, b, **kw), args.iters)
         flops = 2.0 * M * N * Kd
         byts = 2.0 * (M * Kd + N * Kd) + (4.0 if args.f32_out else 2.0) * M * N * (2 if kw["want_aux"] else 1) + (2.0 * M * N if res is not None else 0)

@@ -4,7 +4,9 @@
 // rust-nn src/tensor.rs:1468-1554, assumes a uniform upstream gradient; the oracle here is autograd
 // through dense fp32 softmax attention.)
 //
-// One CTA = one (batch, head, 128-key block), 256 threads, looping over the query blocks that see it.
+// One CTA = one (batch, head, 128-key block), 512 threads (four warps per TMEM lane quarter, each owning a quarter
+// of the columns: 16 warps hide the TMEM / MUFU / shared-memory latencies of the softmax phase), looping over the
+// query blocks that see it.
 // Per query block, five tensor-core products, all operands fed from 128B-swizzled shared memory:
 //   S  = Q K^T            dP = dO V^T                      (K-major x K-major)        -> TMEM
 //   P  = exp2(S*c - lse)  dS = P * (dP - delta)            (tcgen05.ld, registers, bf16 tiles to smem)
@@ -73,7 +75,7 @@ __global__ void flash_dq_convert_kernel(const float* __restrict__ acc, __nv_bflo
 }
 
 template <int HD, bool CAUSAL>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(512, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, BwdParams p) {
   constexpr int BLK = 128;
@@ -104,7 +106,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int quarter = warp & 3, chalf = warp >> 2;
+  const int quarter = warp & 3, cq = warp >> 2;   // TMEM lane quarter (rows) and column quarter of this warp
+  constexpr int DQC = HD / 4;                     // dQ / dK / dV columns per thread: 16 or 32
   const int row = quarter * 32 + lane;          // row of the 128-row tile this thread owns
   const int n_kv_blocks = (p.Skv + BLK - 1) / BLK;
   const int m_blocks = (p.Sq + BLK - 1) / BLK;
@@ -147,45 +150,49 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tma_load_4d(sdO + st * TILE_BYTES + a * (BLK * 128), &tmdO, &q_bar[st], a * 64, h, i * BLK, b);
     }
   };
+  // MMA issue is a single thread's serial instruction stream on the critical path: descriptors are a base word
+  // plus an immediate, accumulate flags are compile-time.
   auto issue_s_dp = [&](int it) {
     const int st = it % STAGES;
-    const uint32_t aQ = smem_u32(sQ + st * TILE_BYTES), adO = smem_u32(sdO + st * TILE_BYTES);
-    const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
+    const uint32_t lQ = sdesc_lo(smem_u32(sQ + st * TILE_BYTES), 0), ldO = sdesc_lo(smem_u32(sdO + st * TILE_BYTES), 0);
+    const uint32_t lK = sdesc_lo(smem_u32(sK), 0), lV = sdesc_lo(smem_u32(sV), 0);
 #pragma unroll
     for (int k = 0; k < HD / 16; ++k) {
-      const int atom = k >> 2, kk = k & 3;
-      umma_f16(tmem_base + COL_S, make_sdesc_sw128(aQ + atom * (BLK * 128) + kk * 32, 0, 1024),
-               make_sdesc_sw128(aK + atom * (BLK * 128) + kk * 32, 0, 1024), idesc_kk, k > 0 ? 1u : 0u);
+      const uint32_t adv = (k >> 2) * (BLK * 128) + (k & 3) * 32;
+      if (k == 0) umma_f16_c<false>(tmem_base + COL_S, sdesc_at<1024>(lQ, adv), sdesc_at<1024>(lK, adv), idesc_kk);
+      else umma_f16_c<true>(tmem_base + COL_S, sdesc_at<1024>(lQ, adv), sdesc_at<1024>(lK, adv), idesc_kk);
     }
 #pragma unroll
     for (int k = 0; k < HD / 16; ++k) {
-      const int atom = k >> 2, kk = k & 3;
-      umma_f16(tmem_base + COL_DP, make_sdesc_sw128(adO + atom * (BLK * 128) + kk * 32, 0, 1024),
-               make_sdesc_sw128(aV + atom * (BLK * 128) + kk * 32, 0, 1024), idesc_kk, k > 0 ? 1u : 0u);
+      const uint32_t adv = (k >> 2) * (BLK * 128) + (k & 3) * 32;
+      if (k == 0) umma_f16_c<false>(tmem_base + COL_DP, sdesc_at<1024>(ldO, adv), sdesc_at<1024>(lV, adv), idesc_kk);
+      else umma_f16_c<true>(tmem_base + COL_DP, sdesc_at<1024>(ldO, adv), sdesc_at<1024>(lV, adv), idesc_kk);
     }
     tc_commit(sdp_bar);
   };
   auto issue_grads = [&](int it, bool commit) {
     const int st = it % STAGES;
-    const uint32_t aQ = smem_u32(sQ + st * TILE_BYTES), adO = smem_u32(sdO + st * TILE_BYTES);
-    const uint32_t aK = smem_u32(sK), aP = smem_u32(sP), adS = smem_u32(sdS);
-    const uint32_t acc = it > 0 ? 1u : 0u;
+    // MN-major views (dV, dK operands): atoms of 64 rows BLK*128 bytes apart
+    const uint32_t mQ = sdesc_lo(smem_u32(sQ + st * TILE_BYTES), BLK * 128), mdO = sdesc_lo(smem_u32(sdO + st * TILE_BYTES), BLK * 128);
+    const uint32_t mP = sdesc_lo(smem_u32(sP), BLK * 128), mdS = sdesc_lo(smem_u32(sdS), BLK * 128), mK = sdesc_lo(smem_u32(sK), BLK * 128);
+    const uint32_t kdS = sdesc_lo(smem_u32(sdS), 0);                       // K-major view of dS (dQ's A operand)
     const uint32_t dq_col = PIPE ? COL_DQ + (uint32_t)(it & 1) * 64u : COL_DQ;
+    const bool acc0 = it > 0;
 #pragma unroll
     for (int k = 0; k < BLK / 16; ++k) {   // dV += P^T dO   (K dimension = query rows)
-      umma_f16(tmem_base + COL_DV, make_sdesc_sw128(aP + k * 2048, BLK * 128, 1024),
-               make_sdesc_sw128(adO + k * 2048, BLK * 128, 1024), idesc_mm, (k > 0) ? 1u : acc);
+      if (k == 0 && !acc0) umma_f16_c<false>(tmem_base + COL_DV, sdesc_at<1024>(mP, 0), sdesc_at<1024>(mdO, 0), idesc_mm);
+      else umma_f16_c<true>(tmem_base + COL_DV, sdesc_at<1024>(mP, k * 2048), sdesc_at<1024>(mdO, k * 2048), idesc_mm);
     }
 #pragma unroll
     for (int k = 0; k < BLK / 16; ++k) {   // dK += dS^T Q
-      umma_f16(tmem_base + COL_DK, make_sdesc_sw128(adS + k * 2048, BLK * 128, 1024),
-               make_sdesc_sw128(aQ + k * 2048, BLK * 128, 1024), idesc_mm, (k > 0) ? 1u : acc);
+      if (k == 0 && !acc0) umma_f16_c<false>(tmem_base + COL_DK, sdesc_at<1024>(mdS, 0), sdesc_at<1024>(mQ, 0), idesc_mm);
+      else umma_f16_c<true>(tmem_base + COL_DK, sdesc_at<1024>(mdS, k * 2048), sdesc_at<1024>(mQ, k * 2048), idesc_mm);
     }
 #pragma unroll
     for (int k = 0; k < BLK / 16; ++k) {   // dQ = dS K      (K dimension = key rows)
-      const int atom = k >> 2, kk = k & 3;
-      umma_f16(tmem_base + dq_col, make_sdesc_sw128(adS + atom * (BLK * 128) + kk * 32, 0, 1024),
-               make_sdesc_sw128(aK + k * 2048, BLK * 128, 1024), idesc_km, k > 0 ? 1u : 0u);
+      const uint32_t adv = (k >> 2) * (BLK * 128) + (k & 3) * 32;
+      if (k == 0) umma_f16_c<false>(tmem_base + dq_col, sdesc_at<1024>(kdS, adv), sdesc_at<1024>(mK, k * 2048), idesc_km);
+      else umma_f16_c<true>(tmem_base + dq_col, sdesc_at<1024>(kdS, adv), sdesc_at<1024>(mK, k * 2048), idesc_km);
     }
     if (commit) tc_commit(dq_bar);
   };
@@ -193,51 +200,43 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   auto retire_dq = [&](int it) {
     const int q_row = (i_start + it) * BLK + row;
     const uint32_t dq_col = PIPE ? COL_DQ + (uint32_t)(it & 1) * 64u : COL_DQ;
-    float* dst = p.dq_accum + ((((long long)b * p.Sq + q_row) * p.H + h) * HD);
+    float* dst = p.dq_accum + ((((long long)b * p.Sq + q_row) * p.H + h) * HD) + cq * DQC;
+    uint32_t v[DQC];
+    if constexpr (DQC == 16) tmem_ld_x16(tmem_row + dq_col + cq * DQC, v); else tmem_ld_x32(tmem_row + dq_col + cq * DQC, v);
+    tmem_ld_wait();
+    if (q_row < p.Sq) {
 #pragma unroll
-    for (int c = 0; c < HD / 64; ++c) {
-      const int colbase = chalf * (HD / 2) + c * 32;
-      uint32_t v[32];
-      tmem_ld_x32(tmem_row + dq_col + colbase, v);
-      tmem_ld_wait();
-      if (q_row < p.Sq) {
-#pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          float4 a = make_float4(__uint_as_float(v[e]) * p.scale, __uint_as_float(v[e + 1]) * p.scale,
-                                 __uint_as_float(v[e + 2]) * p.scale, __uint_as_float(v[e + 3]) * p.scale);
-          atomicAdd(reinterpret_cast<float4*>(dst + colbase + e), a);
-        }
+      for (int e = 0; e < DQC; e += 4) {
+        float4 a = make_float4(__uint_as_float(v[e]) * p.scale, __uint_as_float(v[e + 1]) * p.scale,
+                               __uint_as_float(v[e + 2]) * p.scale, __uint_as_float(v[e + 3]) * p.scale);
+        atomicAdd(reinterpret_cast<float4*>(dst + e), a);
       }
     }
   };
   // P = exp2(S c - lse), dS = P (dP - delta) for this thread's row and column half -> bf16 tiles in shared memory
   auto softmax_block = [&](auto masked, int q_row, bool row_ok, float lse2, float dlt) {
     constexpr bool MASK = decltype(masked)::value;
+    const int colbase = cq * 32;                 // this thread's 32 key columns
+    uint32_t sv[32], dv[32];
+    tmem_ld_x32(tmem_row + COL_S + colbase, sv);
+    tmem_ld_x32(tmem_row + COL_DP + colbase, dv);
+    tmem_ld_wait();
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      const int colbase = chalf * 64 + c * 32;
-      uint32_t sv[32], dv[32];
-      tmem_ld_x32(tmem_row + COL_S + colbase, sv);
-      tmem_ld_x32(tmem_row + COL_DP + colbase, dv);
-      tmem_ld_wait();
-      float pp[32], ds[32];
+    for (int g = 0; g < 4; ++g) {
+      float pp[8], ds[8];
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
+      for (int u = 0; u < 8; ++u) {
+        const int e = g * 8 + u;
         float pr = ex2_approx(fmaf(__uint_as_float(sv[e]), p.scale_log2, -lse2));
         if (MASK) { if (!row_ok || (CAUSAL && (kv0 + colbase + e > q_row))) pr = 0.f; }
-        pp[e] = pr;
-        ds[e] = pr * (__uint_as_float(dv[e]) - dlt);
+        pp[u] = pr;
+        ds[u] = pr * (__uint_as_float(dv[e]) - dlt);
       }
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        const int cc = (colbase >> 3) + g;
-        const int atom = cc >> 3, chunk = cc & 7;
-        const uint32_t off = atom * (BLK * 128) + sw128_offset(row, chunk);
-        *reinterpret_cast<uint4*>(sP + off) = make_uint4(pack_bf16x2(pp[g * 8 + 0], pp[g * 8 + 1]), pack_bf16x2(pp[g * 8 + 2], pp[g * 8 + 3]),
-                                                         pack_bf16x2(pp[g * 8 + 4], pp[g * 8 + 5]), pack_bf16x2(pp[g * 8 + 6], pp[g * 8 + 7]));
-        *reinterpret_cast<uint4*>(sdS + off) = make_uint4(pack_bf16x2(ds[g * 8 + 0], ds[g * 8 + 1]), pack_bf16x2(ds[g * 8 + 2], ds[g * 8 + 3]),
-                                                          pack_bf16x2(ds[g * 8 + 4], ds[g * 8 + 5]), pack_bf16x2(ds[g * 8 + 6], ds[g * 8 + 7]));
-      }
+      const int cc = (colbase >> 3) + g;
+      const int atom = cc >> 3, chunk = cc & 7;
+      const uint32_t off = atom * (BLK * 128) + sw128_offset(row, chunk);
+      *reinterpret_cast<uint4*>(sP + off) = make_uint4(pack_bf16x2(pp[0], pp[1]), pack_bf16x2(pp[2], pp[3]), pack_bf16x2(pp[4], pp[5]), pack_bf16x2(pp[6], pp[7]));
+      *reinterpret_cast<uint4*>(sdS + off) = make_uint4(pack_bf16x2(ds[0], ds[1]), pack_bf16x2(ds[2], ds[3]), pack_bf16x2(ds[4], ds[5]), pack_bf16x2(ds[6], ds[7]));
     }
   };
 
@@ -321,38 +320,35 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   }
 
-  // dK / dV: TMEM -> bf16 global. Thread owns key row `row`, column half `chalf`.
+  // dK / dV: TMEM -> bf16 global. Thread owns key row `row`, column quarter `cq`.
   if (ok && n_iter > 0) {
     tc_fence_after_sync();
     const int kv_row = kv0 + row;
+    const int colbase = cq * DQC;
+    uint32_t vk[DQC], vv[DQC];
+    if constexpr (DQC == 16) { tmem_ld_x16(tmem_row + COL_DK + colbase, vk); tmem_ld_x16(tmem_row + COL_DV + colbase, vv); }
+    else { tmem_ld_x32(tmem_row + COL_DK + colbase, vk); tmem_ld_x32(tmem_row + COL_DV + colbase, vv); }
+    tmem_ld_wait();
+    if (kv_row < p.Skv) {
+      __nv_bfloat16* dkp = p.dk + (long long)b * p.dk_sb + (long long)kv_row * p.dk_ss + (long long)h * p.dk_sh + colbase;
+      __nv_bfloat16* dvp = p.dv + (long long)b * p.dv_sb + (long long)kv_row * p.dv_ss + (long long)h * p.dv_sh + colbase;
 #pragma unroll
-    for (int c = 0; c < HD / 64; ++c) {
-      const int colbase = chalf * (HD / 2) + c * 32;
-      uint32_t vk[32], vv[32];
-      tmem_ld_x32(tmem_row + COL_DK + colbase, vk);
-      tmem_ld_x32(tmem_row + COL_DV + colbase, vv);
-      tmem_ld_wait();
-      if (kv_row < p.Skv) {
-        __nv_bfloat16* dkp = p.dk + (long long)b * p.dk_sb + (long long)kv_row * p.dk_ss + (long long)h * p.dk_sh + colbase;
-        __nv_bfloat16* dvp = p.dv + (long long)b * p.dv_sb + (long long)kv_row * p.dv_ss + (long long)h * p.dv_sh + colbase;
-#pragma unroll
-        for (int e = 0; e < 32; e += 8) {
-          *reinterpret_cast<uint4*>(dkp + e) = make_uint4(
-              pack_bf16x2(__uint_as_float(vk[e]) * p.scale, __uint_as_float(vk[e + 1]) * p.scale),
-              pack_bf16x2(__uint_as_float(vk[e + 2]) * p.scale, __uint_as_float(vk[e + 3]) * p.scale),
-              pack_bf16x2(__uint_as_float(vk[e + 4]) * p.scale, __uint_as_float(vk[e + 5]) * p.scale),
-              pack_bf16x2(__uint_as_float(vk[e + 6]) * p.scale, __uint_as_float(vk[e + 7]) * p.scale));
-          *reinterpret_cast<uint4*>(dvp + e) = make_uint4(
-              pack_bf16x2(__uint_as_float(vv[e]), __uint_as_float(vv[e + 1])), pack_bf16x2(__uint_as_float(vv[e + 2]), __uint_as_float(vv[e + 3])),
-              pack_bf16x2(__uint_as_float(vv[e + 4]), __uint_as_float(vv[e + 5])), pack_bf16x2(__uint_as_float(vv[e + 6]), __uint_as_float(vv[e + 7])));
-        }
+      for (int e = 0; e < DQC; e += 8) {
+        *reinterpret_cast<uint4*>(dkp + e) = make_uint4(
+            pack_bf16x2(__uint_as_float(vk[e]) * p.scale, __uint_as_float(vk[e + 1]) * p.scale),
+            pack_bf16x2(__uint_as_float(vk[e + 2]) * p.scale, __uint_as_float(vk[e + 3]) * p.scale),
+            pack_bf16x2(__uint_as_float(vk[e + 4]) * p.scale, __uint_as_float(vk[e + 5]) * p.scale),
+            pack_bf16x2(__uint_as_float(vk[e + 6]) * p.scale, __uint_as_float(vk[e + 7]) * p.scale));
+        *reinterpret_cast<uint4*>(dvp + e) = make_uint4(
+            pack_bf16x2(__uint_as_float(vv[e]), __uint_as_float(vv[e + 1])), pack_bf16x2(__uint_as_float(vv[e + 2]), __uint_as_float(vv[e + 3])),
+            pack_bf16x2(__uint_as_float(vv[e + 4]), __uint_as_float(vv[e + 5])), pack_bf16x2(__uint_as_float(vv[e + 6]), __uint_as_float(vv[e + 7])));
       }
     }
   } else if (ok && n_iter <= 0) {
     // a key block no query attends to (cannot happen for causal self-attention): zero gradients
     const int kv_row = kv0 + row;
     if (kv_row < p.Skv) {
-      for (int e = chalf * (HD / 2); e < (chalf + 1) * (HD / 2); ++e) {
+      for (int e = cq * DQC; e < (cq + 1) * DQC; ++e) {
         p.dk[(long long)b * p.dk_sb + (long long)kv_row * p.dk_ss + (long long)h * p.dk_sh + e] = __float2bfloat16(0.f);
         p.dv[(long long)b * p.dv_sb + (long long)kv_row * p.dv_ss + (long long)h * p.dv_sh + e] = __float2bfloat16(0.f);
       }
@@ -400,7 +396,7 @@ static int launch_bwd(const FlashArgs& a, cudaStream_t st) {
   p.B = a.B; p.H = a.H; p.Sq = a.Sq; p.Skv = a.Skv;
   p.scale = a.scale; p.scale_log2 = a.scale * 1.4426950408889634f; p.status = a.status;
   const long long grid = (long long)((a.Skv + 127) / 128) * a.H * a.B;
-  kfn<<<(unsigned)grid, 256, SMEM, st>>>(tmQ, tmK, tmV, tmdO, p);
+  kfn<<<(unsigned)grid, 512, SMEM, st>>>(tmQ, tmK, tmV, tmdO, p);
   long long total = (long long)a.B * a.Sq * a.H * (a.hd / 8);
   long long g = (total + 255) / 256; if (g > 148 * 16) g = 148 * 16;
   flash_dq_convert_kernel<<<(unsigned)g, 256, 0, st>>>(a.dq_accum, (__nv_bfloat16*)a.dq.ptr, a.dq.sb, a.dq.ss, a.dq.sh,

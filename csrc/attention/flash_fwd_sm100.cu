@@ -96,27 +96,27 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
     for (int a = 0; a < KA; ++a) tma_load_4d(sV + st * KV_BYTES + a * (BN * 128), &tmV, &v_bar[st], a * 64, h, j * BN, b);
   };
+  // MMA issue is one thread's serial instruction stream on the critical path: descriptors are a base word plus
+  // an immediate, accumulate flags are compile-time.
   auto issue_s = [&](int j) {   // S = Q K_j^T
     const int st = j & 1;
-    const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK + st * KV_BYTES);
+    const uint32_t lQ = sdesc_lo(smem_u32(sQ), 0), lK = sdesc_lo(smem_u32(sK + st * KV_BYTES), 0);
 #pragma unroll
     for (int k = 0; k < HD / 16; ++k) {
-      const int atom = k >> 2, kk = k & 3;
-      uint64_t da = make_sdesc_sw128(aQ + atom * (BMQ * 128) + kk * 32, 0, 1024);
-      uint64_t db = make_sdesc_sw128(aK + atom * (BN * 128) + kk * 32, 0, 1024);
-      umma_f16(tmem_base, da, db, idesc_s, k > 0 ? 1u : 0u);
+      const uint32_t advq = (k >> 2) * (BMQ * 128) + (k & 3) * 32, advk = (k >> 2) * (BN * 128) + (k & 3) * 32;
+      if (k == 0) umma_f16_c<false>(tmem_base, sdesc_at<1024>(lQ, advq), sdesc_at<1024>(lK, advk), idesc_s);
+      else umma_f16_c<true>(tmem_base, sdesc_at<1024>(lQ, advq), sdesc_at<1024>(lK, advk), idesc_s);
     }
     tc_commit(s_bar);
   };
-  auto issue_pv = [&](int j) {  // PV = P V_j
+  auto issue_pv = [&](int j) {  // O (+)= P V_j
     const int st = j & 1;
-    const uint32_t aP = smem_u32(sP), aV = smem_u32(sV + st * KV_BYTES);
+    const uint32_t lP = sdesc_lo(smem_u32(sP), 0), mV = sdesc_lo(smem_u32(sV + st * KV_BYTES), BN * 128);
 #pragma unroll
     for (int k = 0; k < BN / 16; ++k) {
-      const int atom = k >> 2, kk = k & 3;
-      uint64_t da = make_sdesc_sw128(aP + atom * (BMQ * 128) + kk * 32, 0, 1024);
-      uint64_t db = make_sdesc_sw128(aV + k * 2048, BN * 128, 1024);
-      umma_f16(tmem_base + PV_COL, da, db, idesc_pv, (k > 0 || j > 0) ? 1u : 0u);
+      const uint32_t advp = (k >> 2) * (BMQ * 128) + (k & 3) * 32;
+      if (k == 0 && j == 0) umma_f16_c<false>(tmem_base + PV_COL, sdesc_at<1024>(lP, 0), sdesc_at<1024>(mV, 0), idesc_pv);
+      else umma_f16_c<true>(tmem_base + PV_COL, sdesc_at<1024>(lP, advp), sdesc_at<1024>(mV, k * 2048), idesc_pv);
     }
     tc_commit(pv_bar);
   };
@@ -164,9 +164,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (col >= p.Skv || (CAUSAL && col > q_row)) s[i] = -INFINITY;
       }
     }
-    float mx = s[0];
+    // four independent chains: a 128-long dependent fmax chain would cost its latency 128 times over
+    float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
 #pragma unroll
-    for (int i = 1; i < BN; ++i) mx = fmaxf(mx, s[i]);
+    for (int i = 4; i < BN; i += 4) { mx0 = fmaxf(mx0, s[i]); mx1 = fmaxf(mx1, s[i + 1]); mx2 = fmaxf(mx2, s[i + 2]); mx3 = fmaxf(mx3, s[i + 3]); }
+    const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
     const float m_new = fmaxf(m_used, mx * c);
     const bool grow = m_new > m_used + 8.f;                     // also true on the first finite maximum (m_used = -inf)
     if (__any_sync(0xffffffffu, grow)) {                        // TMEM accesses are warp-wide: the warp rescales together
@@ -187,10 +189,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       m_used = m_new;
     }
     const float m_ref = (m_used == -INFINITY) ? 0.f : m_used;
-    float rs = 0.f;
+    float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
 #pragma unroll
-    for (int i = 0; i < BN; ++i) { s[i] = ex2_approx(fmaf(s[i], c, -m_ref)); rs += s[i]; }
-    l_run += rs;
+    for (int i = 0; i < BN; i += 4) {
+      s[i] = ex2_approx(fmaf(s[i], c, -m_ref)); s[i + 1] = ex2_approx(fmaf(s[i + 1], c, -m_ref));
+      s[i + 2] = ex2_approx(fmaf(s[i + 2], c, -m_ref)); s[i + 3] = ex2_approx(fmaf(s[i + 3], c, -m_ref));
+      rs0 += s[i]; rs1 += s[i + 1]; rs2 += s[i + 2]; rs3 += s[i + 3];
+    }
+    l_run += (rs0 + rs1) + (rs2 + rs3);
     // bf16 P tile into shared memory (K-major, 128B swizzle)
 #pragma unroll
     for (int g = 0; g < BN / 8; ++g) {

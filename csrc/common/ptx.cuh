@@ -183,6 +183,30 @@ __device__ __forceinline__ uint64_t make_sdesc_sw128(uint32_t smem_addr, uint32_
   return d;
 }
 
+// Cheap descriptor arithmetic for MMA issue loops: all tiles live below 256 KB of shared memory, so the
+// 14-bit address field never carries and a K step is one 32-bit add on the low word. `sdesc_lo` is computed
+// once per operand tile, `sdesc_at(lo, adv_bytes)` yields the descriptor `adv_bytes` further into the tile.
+__device__ __forceinline__ uint32_t sdesc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return (smem_addr >> 4) | ((lbo_bytes >> 4) << 16);
+}
+template <uint32_t SBO_BYTES>
+__device__ __forceinline__ uint64_t sdesc_at(uint32_t lo, uint32_t adv_bytes) {
+  constexpr uint32_t hi = ((SBO_BYTES >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);   // sbo | version 1 (bit 46) | SWIZZLE_128B (bits 61-63)
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo + (adv_bytes >> 4)), "r"(hi));
+  return d;
+}
+// umma_f16 with the accumulate flag known at compile time (no runtime predicate set-up)
+template <bool ACC>
+__device__ __forceinline__ void umma_f16_c(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "n"(ACC ? 1 : 0)
+      : "memory");
+}
+
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread. accumulate=0 overwrites D.
 __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                          uint32_t accumulate) {

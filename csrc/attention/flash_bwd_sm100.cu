@@ -4,9 +4,8 @@
 // rust-nn src/tensor.rs:1468-1554, assumes a uniform upstream gradient; the oracle here is autograd
 // through dense fp32 softmax attention.)
 //
-// One CTA = one (batch, head, 128-key block), 512 threads (four warps per TMEM lane quarter, each owning a quarter
-// of the columns: 16 warps hide the TMEM / MUFU / shared-memory latencies of the softmax phase), looping over the
-// query blocks that see it.
+// One CTA = one (batch, head, 128-key block), 128 * CG threads (CG warps per TMEM lane quarter, each owning 1/CG of
+// the columns; CG = 2 measured faster than 4), looping over the query blocks that see it.
 // Per query block, five tensor-core products, all operands fed from 128B-swizzled shared memory:
 //   S  = Q K^T            dP = dO V^T                      (K-major x K-major)        -> TMEM
 //   P  = exp2(S*c - lse)  dS = P * (dP - delta)            (tcgen05.ld, registers, bf16 tiles to smem)
@@ -74,8 +73,10 @@ __global__ void flash_dq_convert_kernel(const float* __restrict__ acc, __nv_bflo
   }
 }
 
+constexpr int BWD_CG = 2;                       // column groups per row: threads = 128 * BWD_CG
+
 template <int HD, bool CAUSAL>
-__global__ void __launch_bounds__(512, 1)
+__global__ void __launch_bounds__(128 * BWD_CG, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, BwdParams p) {
   constexpr int BLK = 128;
@@ -106,8 +107,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int quarter = warp & 3, cq = warp >> 2;   // TMEM lane quarter (rows) and column quarter of this warp
-  constexpr int DQC = HD / 4;                     // dQ / dK / dV columns per thread: 16 or 32
+  const int quarter = warp & 3, cq = warp >> 2;   // TMEM lane quarter (rows) and column group of this warp
+  constexpr int CG = BWD_CG;
+  constexpr int SC = 128 / CG;                    // S / dP columns per thread (32 or 64)
+  constexpr int DQC = HD / CG;                    // dQ / dK / dV columns per thread (16 .. 64)
   const int row = quarter * 32 + lane;          // row of the 128-row tile this thread owns
   const int n_kv_blocks = (p.Skv + BLK - 1) / BLK;
   const int m_blocks = (p.Sq + BLK - 1) / BLK;
@@ -202,7 +205,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t dq_col = PIPE ? COL_DQ + (uint32_t)(it & 1) * 64u : COL_DQ;
     float* dst = p.dq_accum + ((((long long)b * p.Sq + q_row) * p.H + h) * HD) + cq * DQC;
     uint32_t v[DQC];
-    if constexpr (DQC == 16) tmem_ld_x16(tmem_row + dq_col + cq * DQC, v); else tmem_ld_x32(tmem_row + dq_col + cq * DQC, v);
+    if constexpr (DQC == 16) tmem_ld_x16(tmem_row + dq_col + cq * DQC, v);
+    else {
+#pragma unroll
+      for (int c = 0; c < DQC / 32; ++c) tmem_ld_x32(tmem_row + dq_col + cq * DQC + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+    }
     tmem_ld_wait();
     if (q_row < p.Sq) {
 #pragma unroll
@@ -216,23 +223,27 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   // P = exp2(S c - lse), dS = P (dP - delta) for this thread's row and column half -> bf16 tiles in shared memory
   auto softmax_block = [&](auto masked, int q_row, bool row_ok, float lse2, float dlt) {
     constexpr bool MASK = decltype(masked)::value;
-    const int colbase = cq * 32;                 // this thread's 32 key columns
-    uint32_t sv[32], dv[32];
-    tmem_ld_x32(tmem_row + COL_S + colbase, sv);
-    tmem_ld_x32(tmem_row + COL_DP + colbase, dv);
+    const int col0 = cq * SC;                    // this thread's SC key columns
+    // every TMEM load of the thread goes out before the single wait: one exposed latency
+    uint32_t sv[SC], dv[SC];
+#pragma unroll
+    for (int c = 0; c < SC / 32; ++c) {
+      tmem_ld_x32(tmem_row + COL_S + col0 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[c * 32]));
+      tmem_ld_x32(tmem_row + COL_DP + col0 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&dv[c * 32]));
+    }
     tmem_ld_wait();
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
+    for (int g = 0; g < SC / 8; ++g) {
       float pp[8], ds[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         const int e = g * 8 + u;
         float pr = ex2_approx(fmaf(__uint_as_float(sv[e]), p.scale_log2, -lse2));
-        if (MASK) { if (!row_ok || (CAUSAL && (kv0 + colbase + e > q_row))) pr = 0.f; }
+        if (MASK) { if (!row_ok || (CAUSAL && (kv0 + col0 + e > q_row))) pr = 0.f; }
         pp[u] = pr;
         ds[u] = pr * (__uint_as_float(dv[e]) - dlt);
       }
-      const int cc = (colbase >> 3) + g;
+      const int cc = (col0 >> 3) + g;
       const int atom = cc >> 3, chunk = cc & 7;
       const uint32_t off = atom * (BLK * 128) + sw128_offset(row, chunk);
       *reinterpret_cast<uint4*>(sP + off) = make_uint4(pack_bf16x2(pp[0], pp[1]), pack_bf16x2(pp[2], pp[3]), pack_bf16x2(pp[4], pp[5]), pack_bf16x2(pp[6], pp[7]));
@@ -327,7 +338,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int colbase = cq * DQC;
     uint32_t vk[DQC], vv[DQC];
     if constexpr (DQC == 16) { tmem_ld_x16(tmem_row + COL_DK + colbase, vk); tmem_ld_x16(tmem_row + COL_DV + colbase, vv); }
-    else { tmem_ld_x32(tmem_row + COL_DK + colbase, vk); tmem_ld_x32(tmem_row + COL_DV + colbase, vv); }
+    else {
+#pragma unroll
+      for (int c = 0; c < DQC / 32; ++c) {
+        tmem_ld_x32(tmem_row + COL_DK + colbase + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&vk[c * 32]));
+        tmem_ld_x32(tmem_row + COL_DV + colbase + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&vv[c * 32]));
+      }
+    }
     tmem_ld_wait();
     if (kv_row < p.Skv) {
       __nv_bfloat16* dkp = p.dk + (long long)b * p.dk_sb + (long long)kv_row * p.dk_ss + (long long)h * p.dk_sh + colbase;
@@ -396,7 +413,7 @@ static int launch_bwd(const FlashArgs& a, cudaStream_t st) {
   p.B = a.B; p.H = a.H; p.Sq = a.Sq; p.Skv = a.Skv;
   p.scale = a.scale; p.scale_log2 = a.scale * 1.4426950408889634f; p.status = a.status;
   const long long grid = (long long)((a.Skv + 127) / 128) * a.H * a.B;
-  kfn<<<(unsigned)grid, 512, SMEM, st>>>(tmQ, tmK, tmV, tmdO, p);
+  kfn<<<(unsigned)grid, 128 * BWD_CG, SMEM, st>>>(tmQ, tmK, tmV, tmdO, p);
   long long total = (long long)a.B * a.Sq * a.H * (a.hd / 8);
   long long g = (total + 255) / 256; if (g > 148 * 16) g = 148 * 16;
   flash_dq_convert_kernel<<<(unsigned)g, 256, 0, st>>>(a.dq_accum, (__nv_bfloat16*)a.dq.ptr, a.dq.sb, a.dq.ss, a.dq.sh,

@@ -178,6 +178,97 @@ layernorm_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
   }
 }
 
+// bf16 rows whose length is a multiple of 256: every lane owns 8 contiguous columns per 256-column chunk and
+// moves them with one 16-byte load / store (4x fewer memory instructions than the 2-column variant above).
+template <int J2>
+__global__ void __launch_bounds__(256)
+layernorm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
+                         const float* __restrict__ mean_in, const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                         float* __restrict__ dgamma, float* __restrict__ dbeta, const __nv_bfloat16* __restrict__ dres,
+                         long long rows, int d) {
+  extern __shared__ float sh[];   // [warps][2][d]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps_per_block = blockDim.x >> 5;
+  float gam[J2][8], adg[J2][8], adb[J2][8];
+#pragma unroll
+  for (int j = 0; j < J2; ++j) {
+    const int c = 8 * lane + 256 * j;
+    const float4 g0 = *reinterpret_cast<const float4*>(gamma + c), g1 = *reinterpret_cast<const float4*>(gamma + c + 4);
+    gam[j][0] = g0.x; gam[j][1] = g0.y; gam[j][2] = g0.z; gam[j][3] = g0.w; gam[j][4] = g1.x; gam[j][5] = g1.y; gam[j][6] = g1.z; gam[j][7] = g1.w;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { adg[j][e] = 0.f; adb[j][e] = 0.f; }
+  }
+  const float inv_d = 1.f / d;
+  auto unpack8 = [](const uint4& u, float (&o)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { o[2 * i] = __uint_as_float(w[i] << 16); o[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+  };
+  long long row = (long long)blockIdx.x * warps_per_block + warp;
+  const long long row_stride = (long long)gridDim.x * warps_per_block;
+  for (; row < rows; row += row_stride) {
+    const __nv_bfloat16* xr = x + row * d; const __nv_bfloat16* gr = dy + row * d;
+    uint4 xu[J2], gu[J2], ru[J2];
+#pragma unroll
+    for (int j = 0; j < J2; ++j) {            // all loads of the row first: maximum memory-level parallelism
+      const int c = 8 * lane + 256 * j;
+      xu[j] = __ldg(reinterpret_cast<const uint4*>(xr + c));
+      gu[j] = __ldg(reinterpret_cast<const uint4*>(gr + c));
+      if (dres) ru[j] = __ldg(reinterpret_cast<const uint4*>(dres + row * d + c));
+    }
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float xh[J2][8], g[J2][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < J2; ++j) {
+      float xv[8];
+      unpack8(xu[j], xv); unpack8(gu[j], g[j]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        xh[j][e] = (xv[e] - mean) * rstd;
+        const float gg = g[j][e] * gam[j][e];
+        s1 += gg; s2 += gg * xh[j][e];
+        adg[j][e] += g[j][e] * xh[j][e];
+        adb[j][e] += g[j][e];
+      }
+    }
+    s1 = wsum(s1) * inv_d; s2 = wsum(s2) * inv_d;
+    __nv_bfloat16* dxr = dx + row * d;
+#pragma unroll
+    for (int j = 0; j < J2; ++j) {
+      const int c = 8 * lane + 256 * j;
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = rstd * (g[j][e] * gam[j][e] - s1 - xh[j][e] * s2);
+      if (dres) {
+        float rr[8];
+        unpack8(ru[j], rr);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] += rr[e];
+      }
+      uint4 ou;
+      __nv_bfloat162 t0 = __floats2bfloat162_rn(o[0], o[1]), t1 = __floats2bfloat162_rn(o[2], o[3]);
+      __nv_bfloat162 t2 = __floats2bfloat162_rn(o[4], o[5]), t3 = __floats2bfloat162_rn(o[6], o[7]);
+      ou.x = *reinterpret_cast<uint32_t*>(&t0); ou.y = *reinterpret_cast<uint32_t*>(&t1);
+      ou.z = *reinterpret_cast<uint32_t*>(&t2); ou.w = *reinterpret_cast<uint32_t*>(&t3);
+      *reinterpret_cast<uint4*>(dxr + c) = ou;
+    }
+  }
+  float* my = sh + (size_t)warp * 2 * d;
+#pragma unroll
+  for (int j = 0; j < J2; ++j) {
+    const int c = 8 * lane + 256 * j;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { my[c + e] = adg[j][e]; my[d + c + e] = adb[j][e]; }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 2 * d; c += blockDim.x) {
+    float acc = 0.f;
+    for (int w = 0; w < warps_per_block; ++w) acc += sh[(size_t)w * 2 * d + c];
+    atomicAdd(c < d ? dgamma + c : dbeta + (c - d), acc);
+  }
+}
+
 // ------------------------------------------------------------------ BatchNorm1D  x:[batch, n]
 // one thread per feature column; coalesced across threads for every row
 template <typename T>
@@ -259,6 +350,17 @@ int b200_layernorm_bwd(const void* dy, const void* x, const float* gamma, const 
   if (rows <= 0) return 0;
   const int block = 256, wpb = block / 32;
   long long g = (rows + wpb - 1) / wpb; if (g > 148 * 2) g = 148 * 2;
+  const bool aligned16 = ((uintptr_t)dy % 16 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)dx % 16 == 0) && (!dres || (uintptr_t)dres % 16 == 0) &&
+                         ((uintptr_t)gamma % 16 == 0);
+  if (is_bf16 && d % 256 == 0 && d <= 1024 && aligned16) {
+    const size_t sm = (size_t)wpb * 2 * d * sizeof(float);
+#define B200_LNV(JJ) { auto k = layernorm_bwd_vec_kernel<JJ>; \
+      if (sm > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); if (e != cudaSuccess) return (int)e; } \
+      k<<<(int)g, block, sm, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, gamma, mean, rstd, (__nv_bfloat16*)dx, dgamma, dbeta, (const __nv_bfloat16*)dres, rows, d); }
+    switch (d / 256) { case 1: B200_LNV(1) break; case 2: B200_LNV(2) break; case 3: B200_LNV(3) break; default: B200_LNV(4) break; }
+#undef B200_LNV
+    return (int)cudaGetLastError();
+  }
   if (d % 2 == 0 && d <= 1024) {
     const size_t sm = (size_t)wpb * 2 * d * sizeof(float);   // <= 64 KB
 #define B200_LNB(TT, JJ) { auto k = layernorm_bwd_reg_kernel<TT, JJ>; \

@@ -68,6 +68,66 @@ __global__ void layernorm_fwd_kernel(const T* __restrict__ x, const float* __res
   }
 }
 
+// bf16 rows whose length is a multiple of 256: the row lives in registers (8 contiguous columns per lane and
+// 256-column chunk, one 16-byte load each), so x is read once and mean / variance / output need no second pass.
+template <int J2>
+__global__ void __launch_bounds__(256)
+layernorm_fwd_vec_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                         __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                         long long rows, int d, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  float gam[J2][8], bet[J2][8];
+#pragma unroll
+  for (int j = 0; j < J2; ++j) {
+    const int c = 8 * lane + 256 * j;
+    const float4 g0 = *reinterpret_cast<const float4*>(gamma + c), g1 = *reinterpret_cast<const float4*>(gamma + c + 4);
+    const float4 b0 = *reinterpret_cast<const float4*>(beta + c), b1 = *reinterpret_cast<const float4*>(beta + c + 4);
+    gam[j][0] = g0.x; gam[j][1] = g0.y; gam[j][2] = g0.z; gam[j][3] = g0.w; gam[j][4] = g1.x; gam[j][5] = g1.y; gam[j][6] = g1.z; gam[j][7] = g1.w;
+    bet[j][0] = b0.x; bet[j][1] = b0.y; bet[j][2] = b0.z; bet[j][3] = b0.w; bet[j][4] = b1.x; bet[j][5] = b1.y; bet[j][6] = b1.z; bet[j][7] = b1.w;
+  }
+  const float inv_d = 1.f / d;
+  long long row = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const long long row_stride = (long long)gridDim.x * warps_per_block;
+  for (; row < rows; row += row_stride) {
+    const __nv_bfloat16* xr = x + row * d;
+    uint4 xu[J2];
+#pragma unroll
+    for (int j = 0; j < J2; ++j) xu[j] = __ldg(reinterpret_cast<const uint4*>(xr + 8 * lane + 256 * j));
+    float v[J2][8];
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < J2; ++j) {
+      const uint32_t w[4] = {xu[j].x, xu[j].y, xu[j].z, xu[j].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { v[j][2 * i] = __uint_as_float(w[i] << 16); v[j][2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s += v[j][e];
+    }
+    const float mean = wsum(s) * inv_d;
+    float q = 0.f;
+#pragma unroll
+    for (int j = 0; j < J2; ++j)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { const float a = v[j][e] - mean; q += a * a; }
+    const float rstd = rsqrtf(wsum(q) * inv_d + eps);
+    __nv_bfloat16* yr = y + row * d;
+#pragma unroll
+    for (int j = 0; j < J2; ++j) {
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = (v[j][e] - mean) * rstd * gam[j][e] + bet[j][e];
+      __nv_bfloat162 t0 = __floats2bfloat162_rn(o[0], o[1]), t1 = __floats2bfloat162_rn(o[2], o[3]);
+      __nv_bfloat162 t2 = __floats2bfloat162_rn(o[4], o[5]), t3 = __floats2bfloat162_rn(o[6], o[7]);
+      uint4 ou;
+      ou.x = *reinterpret_cast<uint32_t*>(&t0); ou.y = *reinterpret_cast<uint32_t*>(&t1);
+      ou.z = *reinterpret_cast<uint32_t*>(&t2); ou.w = *reinterpret_cast<uint32_t*>(&t3);
+      *reinterpret_cast<uint4*>(yr + 8 * lane + 256 * j) = ou;
+    }
+    if (lane == 0) { if (mean_out) mean_out[row] = mean; if (rstd_out) rstd_out[row] = rstd; }
+  }
+}
+
 template <typename T>
 __global__ void layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ gamma,
                                      const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
@@ -338,6 +398,12 @@ int b200_layernorm_fwd(const void* x, const float* gamma, const float* beta, voi
   if (rows <= 0) return 0;
   const int block = 256, wpb = block / 32;
   long long g = (rows + wpb - 1) / wpb; if (g > 148 * 8) g = 148 * 8;
+  if (is_bf16 && d % 256 == 0 && d <= 1024 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)gamma % 16 == 0 && (uintptr_t)beta % 16 == 0) {
+#define B200_LNF(JJ) layernorm_fwd_vec_kernel<JJ><<<(int)g, block, 0, st>>>((const __nv_bfloat16*)x, gamma, beta, (__nv_bfloat16*)y, mean, rstd, rows, d, eps);
+    switch (d / 256) { case 1: B200_LNF(1) break; case 2: B200_LNF(2) break; case 3: B200_LNF(3) break; default: B200_LNF(4) break; }
+#undef B200_LNF
+    return (int)cudaGetLastError();
+  }
   if (is_bf16) layernorm_fwd_kernel<__nv_bfloat16><<<(int)g, block, 0, st>>>((const __nv_bfloat16*)x, gamma, beta, (__nv_bfloat16*)y, mean, rstd, rows, d, eps);
   else layernorm_fwd_kernel<float><<<(int)g, block, 0, st>>>((const float*)x, gamma, beta, (float*)y, mean, rstd, rows, d, eps);
   return (int)cudaGetLastError();

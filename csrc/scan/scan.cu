@@ -275,6 +275,275 @@ selective_scan_bwd_kernel(ScanArgs a) {
   }
 }
 
+// ---------------------------------------------------------------------------- lane-per-state scan (N == 16, no fused gate)
+// The thread-per-channel kernels above expose B*D threads (32768 for the Mamba configuration) and every step
+// waits on the previous one: they are latency-bound at a few percent of the machine. Here a lane owns ONE state
+// (channel, n): a warp carries 2 channels x 16 states, 16x the threads, one MUFU ex2 and three FMAs per lane
+// and step. The sum over n that y_t (forward) and d delta_t / d u_t (backward) need is taken 16 steps at a time
+// with a transpose-reduce inside each half-warp (15 shuffles for 16 sums) instead of 4 shuffles per step.
+// u / delta / B / C move through shared-memory tiles filled with coalesced loads while the previous tile is
+// being processed. The checkpoint layout is the one of the kernels above, so either backward can follow either
+// forward.
+constexpr float SCAN_LOG2E = 1.4426950408889634f;
+__device__ __forceinline__ float scan_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+
+// sums 16 per-lane values over the 16 lanes of a half-warp; lane j (mod 16) ends with the total of v[j]
+__device__ __forceinline__ float transpose_reduce16(float (&v)[16], int lane) {
+#pragma unroll
+  for (int step = 0; step < 4; ++step) {
+    const int half = 8 >> step;
+    const bool upper = (lane & half) != 0;
+#pragma unroll
+    for (int i = 0; i < half; ++i) {
+      const float send = upper ? v[i] : v[i + half];
+      const float keep = upper ? v[i + half] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+    }
+  }
+  return v[0];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+scan_fwd_lanes_kernel(ScanArgs a) {
+  constexpr int DB = 16, TT = 32;
+  __shared__ float2 s_x[2][TT][DB];                   // (delta, delta * u)
+  __shared__ float2 s_BC[2][TT][SCAN_N];
+  __shared__ float s_u[2][TT][DB], s_y[TT][DB];
+  const int b = blockIdx.y, d0 = blockIdx.x * DB;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = lane & 15, ch = warp * 2 + (lane >> 4);
+  const int d = d0 + ch;
+  const bool active = d < a.D;
+  const float A2 = active ? a.A[(long long)d * SCAN_N + n] * SCAN_LOG2E : 0.f;
+  const float dsk = (active && a.Dskip) ? a.Dskip[d] : 0.f;
+  const int n_ck = (a.S + SCAN_CK - 1) / SCAN_CK;
+  float h = 0.f;
+  // loader role: thread -> (row lt of the tile, channel / state pair lp)
+  const int lt = threadIdx.x >> 3, lp = threadIdx.x & 7;
+  const int ld0 = d0 + 2 * lp, ld1 = ld0 + 1;
+  const float db0 = (a.delta_bias && ld0 < a.D) ? a.delta_bias[ld0] : 0.f, db1 = (a.delta_bias && ld1 < a.D) ? a.delta_bias[ld1] : 0.f;
+  const long long rb = (long long)b * a.S;
+  const T* up = (const T*)a.u; const T* dp = (const T*)a.delta; const T* Bp = (const T*)a.Bm; const T* Cp = (const T*)a.Cm;
+  float r[8];
+  auto load_tile = [&](int t0) {
+    const int t = t0 + lt;
+    const bool ok = t < a.S;
+    const long long row = rb + t;
+    r[0] = (ok && ld0 < a.D) ? s_ld(up + row * a.u_ld + ld0) : 0.f;
+    r[1] = (ok && ld1 < a.D) ? s_ld(up + row * a.u_ld + ld1) : 0.f;
+    float x0 = (ok && ld0 < a.D) ? s_ld(dp + row * a.delta_ld + ld0) + db0 : 0.f;
+    float x1 = (ok && ld1 < a.D) ? s_ld(dp + row * a.delta_ld + ld1) + db1 : 0.f;
+    if (a.delta_softplus) { x0 = softplus20(x0); x1 = softplus20(x1); }
+    r[2] = (ok && ld0 < a.D) ? x0 : 0.f; r[3] = (ok && ld1 < a.D) ? x1 : 0.f;
+    r[4] = ok ? s_ld(Bp + row * a.b_ld + 2 * lp) : 0.f; r[5] = ok ? s_ld(Bp + row * a.b_ld + 2 * lp + 1) : 0.f;
+    r[6] = ok ? s_ld(Cp + row * a.c_ld + 2 * lp) : 0.f; r[7] = ok ? s_ld(Cp + row * a.c_ld + 2 * lp + 1) : 0.f;
+  };
+  auto put_tile = [&](int buf) {
+    s_u[buf][lt][2 * lp] = r[0]; s_u[buf][lt][2 * lp + 1] = r[1];
+    s_x[buf][lt][2 * lp] = make_float2(r[2], r[2] * r[0]); s_x[buf][lt][2 * lp + 1] = make_float2(r[3], r[3] * r[1]);
+    s_BC[buf][lt][2 * lp] = make_float2(r[4], r[6]); s_BC[buf][lt][2 * lp + 1] = make_float2(r[5], r[7]);
+  };
+  const int n_tiles = (a.S + TT - 1) / TT;
+  load_tile(0); put_tile(0);
+  __syncthreads();
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    const int cur = tile & 1, t0 = tile * TT;
+    if (tile + 1 < n_tiles) load_tile(t0 + TT);            // in flight while this tile is processed
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      float p[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int t = half * 16 + i;
+        if ((t % SCAN_CK) == 0 && a.hck && active && t0 + t < a.S)
+          a.hck[(((long long)b * n_ck + (t0 + t) / SCAN_CK) * a.D + d) * SCAN_N + n] = h;      // state BEFORE step t
+        const float2 x = s_x[cur][t][ch], bc = s_BC[cur][t][n];
+        h = fmaf(scan_ex2(x.x * A2), h, x.y * bc.x);
+        p[i] = h * bc.y;
+      }
+      const float y = transpose_reduce16(p, lane);         // lane n: sum over the states for step half*16 + n
+      const int t = half * 16 + n;
+      s_y[t][ch] = y + dsk * s_u[cur][t][ch];
+    }
+    __syncthreads();
+    {
+      const int t = t0 + lt;
+      if (t < a.S) {
+        T* yp = (T*)a.y + (rb + t) * a.y_ld;
+        if (ld0 < a.D) s_st(yp + ld0, s_y[lt][2 * lp]);
+        if (ld1 < a.D) s_st(yp + ld1, s_y[lt][2 * lp + 1]);
+      }
+    }
+    if (tile + 1 < n_tiles) put_tile(cur ^ 1);
+    __syncthreads();
+  }
+}
+
+// Backward. A block owns 64 channels and walks the checkpoint intervals from the last to the first. Per interval
+// each lane re-runs 8 steps of its state from the checkpoint, then runs the adjoint recurrence in reverse; it does so
+// for 4 channels in turn (pass p: channel p*16 + 2*warp + lane/16) so that the per-(t, n) sums dB / dC, which run
+// over ALL channels, gather 4 channels in registers before they touch shuffles, shared memory and finally one atomic
+// per (t, n) and block. The next interval's u / delta / dy / B / C rows and checkpoints are fetched into registers
+// while the current one is processed.
+template <typename T>
+__global__ void __launch_bounds__(256, 2)
+scan_bwd_lanes_kernel(ScanArgs a) {
+  constexpr int DB = 64, CK = SCAN_CK, WARPS = 8, PASSES = 4;
+  __shared__ float4 s_in[CK][DB];                    // (delta, delta * u, u, dy) per (t, channel)
+  __shared__ float s_draw[CK][DB];                   // delta before softplus
+  __shared__ float2 s_BC[CK][SCAN_N];
+  __shared__ float2 s_out[CK][DB];                   // (d delta_raw, d u without the skip term)
+  __shared__ float2 s_dBC[WARPS][CK][SCAN_N];
+  const int b = blockIdx.y, d0 = blockIdx.x * DB;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = lane & 15, chw = warp * 2 + (lane >> 4);     // channel inside a pass
+  const int n_ck = (a.S + CK - 1) / CK;
+  const long long rb = (long long)b * a.S;
+  float Araw[PASSES], g_acc[PASSES], dA_acc[PASSES], ddb_acc[PASSES], dD_acc[PASSES], hnext[PASSES];
+#pragma unroll
+  for (int p = 0; p < PASSES; ++p) {
+    const int d = d0 + p * 16 + chw;
+    Araw[p] = d < a.D ? a.A[(long long)d * SCAN_N + n] : 0.f;
+    g_acc[p] = dA_acc[p] = ddb_acc[p] = dD_acc[p] = 0.f;
+  }
+  // loader / storer role: rows lt and lt + 4 of channel lc; threads 0..127 also fetch B, 128..255 C
+  const int lc = threadIdx.x & 63, lt = threadIdx.x >> 6;
+  const int ldd = d0 + lc;
+  const bool ch_ok = ldd < a.D;
+  const float dbias = (a.delta_bias && ch_ok) ? a.delta_bias[ldd] : 0.f;
+  const float dsk = (a.Dskip && ch_ok) ? a.Dskip[ldd] : 0.f;
+  const int bt = (threadIdx.x & 127) >> 4, bn = threadIdx.x & 15;
+  float pu[2], pd[2], pg[2], pbc;
+  auto prefetch = [&](int c) {
+    const int t0 = c * CK;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int t = t0 + lt + 4 * k;
+      const bool ok = t < a.S && ch_ok;
+      const long long row = rb + t;
+      pu[k] = ok ? s_ld((const T*)a.u + row * a.u_ld + ldd) : 0.f;
+      pd[k] = ok ? s_ld((const T*)a.delta + row * a.delta_ld + ldd) : 0.f;
+      pg[k] = ok ? s_ld((const T*)a.dy + row * a.dy_ld + ldd) : 0.f;
+    }
+    const bool okb = t0 + bt < a.S;
+    if (threadIdx.x < 128) pbc = okb ? s_ld((const T*)a.Bm + (rb + t0 + bt) * a.b_ld + bn) : 0.f;
+    else pbc = okb ? s_ld((const T*)a.Cm + (rb + t0 + bt) * a.c_ld + bn) : 0.f;
+#pragma unroll
+    for (int p = 0; p < PASSES; ++p) {
+      const int d = d0 + p * 16 + chw;
+      hnext[p] = d < a.D ? a.hck[(((long long)b * n_ck + c) * a.D + d) * SCAN_N + n] : 0.f;
+    }
+  };
+  prefetch(n_ck - 1);
+  for (int c = n_ck - 1; c >= 0; --c) {
+    const int t0 = c * CK;
+    __syncthreads();                                  // the previous interval's tiles are no longer read
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int t = t0 + lt + 4 * k;
+      const bool ok = t < a.S && ch_ok;
+      const float draw = ok ? pd[k] + dbias : 0.f;
+      const float dl = ok ? (a.delta_softplus ? softplus20(draw) : draw) : 0.f;
+      s_in[lt + 4 * k][lc] = make_float4(dl, dl * pu[k], pu[k], pg[k]);
+      s_draw[lt + 4 * k][lc] = draw;
+    }
+    if (threadIdx.x < 128) s_BC[bt][bn].x = pbc; else s_BC[bt][bn].y = pbc;
+    float h0[PASSES];
+#pragma unroll
+    for (int p = 0; p < PASSES; ++p) h0[p] = hnext[p];
+    __syncthreads();
+    if (c > 0) prefetch(c - 1);                       // in flight during the passes below
+    float dBp[CK], dCp[CK];
+#pragma unroll
+    for (int i = 0; i < CK; ++i) dBp[i] = dCp[i] = 0.f;
+#pragma unroll
+    for (int p = 0; p < PASSES; ++p) {
+      const int ch = p * 16 + chw;
+      const float A2 = Araw[p] * SCAN_LOG2E;
+      float hs[CK + 1], av[CK];
+      hs[0] = h0[p];
+#pragma unroll
+      for (int i = 0; i < CK; ++i) {
+        const float4 x = s_in[i][ch];
+        av[i] = scan_ex2(x.x * A2);
+        hs[i + 1] = fmaf(av[i], hs[i], x.y * s_BC[i][n].x);
+      }
+      float red[16];
+      float g = g_acc[p], dA = dA_acc[p];
+#pragma unroll
+      for (int i = CK - 1; i >= 0; --i) {
+        const float4 x = s_in[i][ch];                 // (dl, dl*u, u, gy)
+        const float2 bc = s_BC[i][n];
+        const float dhn = fmaf(x.w, bc.y, g);
+        const float t1 = dhn * hs[i] * av[i];
+        const float xb = dhn * bc.x;
+        red[i] = fmaf(t1, Araw[p], xb * x.z);         // d delta_t, this state's share
+        red[CK + i] = xb * x.x;                       // d u_t, this state's share
+        dA = fmaf(t1, x.x, dA);
+        dBp[i] = fmaf(dhn, x.y, dBp[i]);
+        dCp[i] = fmaf(x.w, hs[i + 1], dCp[i]);
+        g = dhn * av[i];
+      }
+      g_acc[p] = g; dA_acc[p] = dA;
+      const float tot = transpose_reduce16(red, lane);   // lane j < 8: d delta of step j; j >= 8: d u of step j - 8
+      const int j = lane & 15;
+      if (j < CK) {
+        float ddraw = tot;
+        if (a.delta_softplus) ddraw *= sigmoidf_(s_draw[j][ch]);
+        s_out[j][ch].x = ddraw;
+        ddb_acc[p] += ddraw;
+        const float4 x = s_in[j][ch];
+        dD_acc[p] = fmaf(x.w, x.z, dD_acc[p]);
+      } else {
+        s_out[j - CK][ch].y = tot;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < CK; ++i) {
+      dBp[i] += __shfl_xor_sync(0xffffffffu, dBp[i], 16);    // the warp's two channel groups
+      dCp[i] += __shfl_xor_sync(0xffffffffu, dCp[i], 16);
+      if (lane < 16) s_dBC[warp][i][n] = make_float2(dBp[i], dCp[i]);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int tt = lt + 4 * k, t = t0 + tt;
+      if (t < a.S && ch_ok) {
+        const float2 o = s_out[tt][lc];
+        s_st((T*)a.ddelta + (rb + t) * a.ddelta_ld + ldd, o.x);
+        s_st((T*)a.du + (rb + t) * a.du_ld + ldd, fmaf(dsk, s_in[tt][lc].w, o.y));
+      }
+    }
+    if (t0 + bt < a.S) {
+      float acc = 0.f;
+      if (threadIdx.x < 128) {
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) acc += s_dBC[w][bt][bn].x;
+        atomicAdd(a.dB + (rb + t0 + bt) * SCAN_N + bn, acc);
+      } else {
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) acc += s_dBC[w][bt][bn].y;
+        atomicAdd(a.dC + (rb + t0 + bt) * SCAN_N + bn, acc);
+      }
+    }
+  }
+#pragma unroll
+  for (int p = 0; p < PASSES; ++p) {
+    const int d = d0 + p * 16 + chw;
+    float v0 = ddb_acc[p], v1 = dD_acc[p];            // per-channel sums sit in lanes j < 8 of each half-warp
+#pragma unroll
+    for (int o = 8; o; o >>= 1) { v0 += __shfl_xor_sync(0xffffffffu, v0, o); v1 += __shfl_xor_sync(0xffffffffu, v1, o); }
+    if (d < a.D) {
+      atomicAdd(a.dA + (long long)d * SCAN_N + n, dA_acc[p]);
+      if (n == 0) {
+        if (a.ddelta_bias) atomicAdd(a.ddelta_bias + d, v0);
+        if (a.dDskip) atomicAdd(a.dDskip + d, v1);
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------- causal depthwise conv1d
 // y[b,t,c] = act( bias[c] + sum_k w[c,k] * x[b, t-(K-1)+k, c] ), K <= 8, act in {none, silu}
 // (rust-nn src/tensor.rs:903-944; its MambaBlock applies SiLU right after, src/mamba.rs:95-98)
@@ -394,6 +663,12 @@ int b200_selective_scan_fwd(const ScanArgs* a, int is_bf16, cudaStream_t st) {
   if (a->B <= 0 || a->S <= 0 || a->D <= 0) return 0;
   if (a->N < 1 || a->N > SCAN_N) return -1;
   dim3 grid((a->D + SCAN_THREADS - 1) / SCAN_THREADS, a->B);
+  if (a->N == SCAN_N && !a->z) {       // lane-per-state kernel
+    dim3 g2((a->D + 15) / 16, a->B);
+    if (is_bf16) scan_fwd_lanes_kernel<__nv_bfloat16><<<g2, 256, 0, st>>>(*a);
+    else scan_fwd_lanes_kernel<float><<<g2, 256, 0, st>>>(*a);
+    return (int)cudaGetLastError();
+  }
   if (is_bf16) selective_scan_fwd_kernel<__nv_bfloat16><<<grid, SCAN_THREADS, 0, st>>>(*a);
   else selective_scan_fwd_kernel<float><<<grid, SCAN_THREADS, 0, st>>>(*a);
   return (int)cudaGetLastError();
@@ -402,6 +677,12 @@ int b200_selective_scan_fwd(const ScanArgs* a, int is_bf16, cudaStream_t st) {
 int b200_selective_scan_bwd(const ScanArgs* a, int is_bf16, cudaStream_t st) {
   if (a->B <= 0 || a->S <= 0 || a->D <= 0) return 0;
   if (a->N < 1 || a->N > SCAN_N || !a->hck) return -1;
+  if (a->N == SCAN_N && !a->z) {       // lane-per-state kernel
+    dim3 g2((a->D + 63) / 64, a->B);
+    if (is_bf16) scan_bwd_lanes_kernel<__nv_bfloat16><<<g2, 256, 0, st>>>(*a);
+    else scan_bwd_lanes_kernel<float><<<g2, 256, 0, st>>>(*a);
+    return (int)cudaGetLastError();
+  }
   dim3 grid((a->D + SCAN_THREADS - 1) / SCAN_THREADS, a->B);
   const int smem = ((SCAN_CK + 1) * SCAN_N * SCAN_THREADS + 2 * SCAN_CK * SCAN_N) * sizeof(float);
   static bool attr = false;

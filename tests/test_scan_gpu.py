@@ -15,7 +15,8 @@ def rel_err(a, b):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("B,S,D,N,full", [(2, 64, 128, 16, True), (1, 37, 70, 8, True), (2, 130, 256, 16, False), (1, 8, 33, 4, True)])
+@pytest.mark.parametrize("B,S,D,N,full", [(2, 64, 128, 16, True), (1, 37, 70, 8, True), (2, 130, 256, 16, False), (1, 8, 33, 4, True),
+                                          (1, 45, 70, 16, True), (3, 257, 100, 16, True), (2, 1024, 64, 16, False)])
 def test_selective_scan_fwd_bwd(B, S, D, N, full, dtype):
     torch.manual_seed(0)
     dev = "cuda"

@@ -87,20 +87,108 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def torch_arm(args):
+    """The library baseline: same model, shapes, precision policy and timing rules, stock PyTorch kernels only."""
+    import torch
+    import torch.distributed as dist
+    from baseline.torch_lm import TorchLoopedLM, TorchStep
+
+    world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0")); local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = dict(CONFIG)
+    if args.small:
+        cfg.update(vocab=2048, d_model=128, heads=2, ff_dim=256, layers_per_block=2, loops=2, seq_len=256, global_batch=8)
+    if args.global_batch > 0:
+        cfg["global_batch"] = args.global_batch
+    local_batch, S = cfg["global_batch"] // world, cfg["seq_len"]
+    torch.manual_seed(1234)
+    model = TorchLoopedLM(cfg["vocab"], cfg["d_model"], cfg["heads"], cfg["ff_dim"], cfg["layers_per_block"], cfg["loops"], S).to(dev)
+    step = TorchStep(model, local_batch, S, dev, world, graph=not args.no_graph)
+    g = torch.Generator().manual_seed(1000 + rank)
+    pool = 4
+    host_ids = [torch.randint(0, cfg["vocab"], (local_batch, S), generator=g).pin_memory() for _ in range(pool)]
+    host_lab = [torch.randint(0, cfg["vocab"], (local_batch, S), generator=g).pin_memory() for _ in range(pool)]
+    dev_ids, dev_lab = [t.to(dev) for t in host_ids], [t.to(dev) for t in host_lab]
+    step.ids.copy_(dev_ids[0]); step.labels.copy_(dev_lab[0])
+    step.warmup(args.warmup)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start(); time.sleep(0.3)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step.step_device(dev_ids[i % pool], dev_lab[i % pool])
+    e1.record()
+    barrier()
+    dev_ms = max_over_ranks(e0.elapsed_time(e1))
+    barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    last = 0.0
+    for i in range(args.steps):
+        last = float(step.step_device(host_ids[i % pool], host_lab[i % pool]).item())
+    t1.record()
+    barrier()
+    e2e_ms = max_over_ranks(t0.elapsed_time(t1))
+    if rank == 0:
+        sampler.stop()
+        tokens = cfg["global_batch"] * S * args.steps
+        print(json.dumps({
+            "metric": METRIC, "value": tokens / (dev_ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic uniform token ids, random-init N(0,0.02) weights", "impl": "torch",
+            "config": {"model": "looped-transformer LM d512 h8 hd64, 4 layers x 6 loops, ff2048, vocab32000 (stock PyTorch: cuBLAS, SDPA, fused Adam, DDP)",
+                       "global_batch": cfg["global_batch"], "seq_len": S, "parallelism": f"dp{world}" + ("-ddp-nccl" if world > 1 else ""),
+                       "l2_policy": "inputs larger than L2 (multi-GB activation working set per step)", "cuda_graph": step.graph is not None,
+                       "small": bool(args.small)},
+            "clocks": sampler.summary(),
+            "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
+                    "h2d_bytes_per_step": host_ids[0].numel() * 8 * 2, "d2h_bytes_per_step": 4},
+            "gpu_launches": 0, "loss_last": last}), flush=True)
+    if world > 1:
+        barrier()
+        sys.stdout.flush()
+        os._exit(0)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "torch"],
+                    help="b200: this package; reference: the unmodified upstream; torch: stock PyTorch (cuBLAS, SDPA, fused Adam, DDP) on the same model")
     ap.add_argument("--no-graph", action="store_true", help="run eagerly instead of replaying a captured CUDA graph")
     ap.add_argument("--dp", default="fused", choices=["fused", "nccl"], help="data-parallel gradient path for N > 1")
+    ap.add_argument("--global-batch", type=int, default=0, help="override the global batch (diagnostics; the headline configuration is 64)")
     ap.add_argument("--small", action="store_true", help="tiny configuration for smoke tests (NOT a valid bench number)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
     if args.warmup < 3:
         args.warmup = 3
+    if args.impl == "torch":
+        return torch_arm(args)
 
     import torch
     import torch.distributed as dist
@@ -125,6 +213,8 @@ def main():
     cfg = dict(CONFIG)
     if args.small:
         cfg.update(vocab=2048, d_model=128, heads=2, ff_dim=256, layers_per_block=2, loops=2, seq_len=256, global_batch=8)
+    if args.global_batch > 0:
+        cfg["global_batch"] = args.global_batch
     assert cfg["global_batch"] % world == 0
     local_batch = cfg["global_batch"] // world
     S = cfg["seq_len"]

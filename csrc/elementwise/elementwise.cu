@@ -161,6 +161,52 @@ __global__ void colsum_kernel(const T* __restrict__ x, float* __restrict__ out, 
   atomicAdd(out + c, acc);
 }
 
+// bf16 column sum with 16-byte loads: a warp covers 256 columns of one row per load, the block's 8 warps
+// take rows w, w + 8, ... of the block's slab (4 rows in flight per lane), then the warps' partial sums meet in
+// shared memory and leave as one atomic per column. Needs cols % 8 == 0, ld % 8 == 0 and a 16-byte aligned base.
+__global__ void __launch_bounds__(256)
+colsum_vec_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, long long rows, int cols, long long ld, int rows_per_block) {
+  __shared__ float sh[8][256 + 8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c0 = blockIdx.x * 256 + lane * 8;
+  const long long r0 = (long long)blockIdx.y * rows_per_block;
+  long long r1 = r0 + rows_per_block; if (r1 > rows) r1 = rows;
+  float acc[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+  if (c0 < cols) {
+    const __nv_bfloat16* xp = x + c0;
+    long long r = r0 + warp;
+    for (; r + 24 < r1; r += 32) {
+      uint4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = __ldg(reinterpret_cast<const uint4*>(xp + (r + 8 * j) * ld));
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { acc[2 * k] += __uint_as_float(w[k] << 16); acc[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u); }
+      }
+    }
+    for (; r < r1; r += 8) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(xp + r * ld));
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) { acc[2 * k] += __uint_as_float(w[k] << 16); acc[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u); }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) sh[warp][lane * 8 + k] = acc[k];
+  __syncthreads();
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += sh[w][threadIdx.x];
+    atomicAdd(out + c, t);
+  }
+}
+
 // batched column sum: out[z, c] += sum_r x[z, r, c]  (per-expert bias gradients)
 template <typename T>
 __global__ void colsum_batched_kernel(const T* __restrict__ x, float* __restrict__ out, long long rows, int cols,
@@ -352,6 +398,14 @@ int b200_cast(const void* x, void* y, long long n, float scale, int dir, cudaStr
 // out must be zero-initialised (or hold a running sum) by the caller
 int b200_colsum(const void* x, float* out, long long rows, int cols, long long ld, int is_bf16, cudaStream_t st) {
   if (rows <= 0 || cols <= 0) return 0;
+  if (is_bf16 && cols % 8 == 0 && ld % 8 == 0 && ((uintptr_t)x & 15) == 0) {
+    const int cb = (cols + 255) / 256;
+    long long rpb = (rows * cb + 148LL * 8 - 1) / (148LL * 8);      // about 8 blocks per SM
+    rpb = rpb < 32 ? 32 : rpb > 1024 ? 1024 : (rpb + 31) / 32 * 32;
+    dim3 g(cb, (unsigned)((rows + rpb - 1) / rpb));
+    colsum_vec_kernel<<<g, 256, 0, st>>>((const __nv_bfloat16*)x, out, rows, cols, ld, (int)rpb);
+    return (int)cudaGetLastError();
+  }
   int rpb = 256;
   dim3 grid((cols + 127) / 128, (unsigned)((rows + rpb - 1) / rpb));
   if (is_bf16) colsum_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, out, rows, cols, ld, rpb);

@@ -136,6 +136,19 @@ def test_colsum_reduce_cast():
     assert torch.equal(K.cast(x, torch.bfloat16), x.bfloat16())
 
 
+@pytest.mark.parametrize("rows,cols", [(8192, 512), (1000, 264), (77, 40), (5, 2048), (65536, 1536), (3001, 8)])
+def test_colsum_bf16_vector_path(rows, cols):
+    torch.manual_seed(rows + cols)
+    x = torch.randn(rows, cols, device=DEV).bfloat16()
+    want = x.double().sum(0)
+    assert float((K.colsum(x).double() - want).abs().max()) < 2e-4 * math.sqrt(rows) + 1e-3
+    wide = torch.randn(rows, cols + 16, device=DEV).bfloat16()
+    view = wide[:, 8:8 + cols]                        # strided rows, 16-byte aligned start
+    acc = torch.ones(cols, device=DEV)
+    K.colsum(view, out=acc)
+    assert float((acc.double() - 1.0 - view.double().sum(0)).abs().max()) < 2e-4 * math.sqrt(rows) + 1e-3
+
+
 def test_embedding():
     table = lcg_tensor((1000, 64), seed=25).to(DEV).bfloat16()
     ids = torch.randint(0, 1000, (4, 77), device=DEV)

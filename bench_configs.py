@@ -1,0 +1,176 @@
+"""Benchmarks of the configurations beside the headline one (which `bench.py` measures).
+
+    python bench_configs.py mlp                     784-256-128-10 MLP, fp32/TF32, batch 32, Adam, CUDA-graph step
+    python bench_configs.py moe_lm   [--batch B]    FineGrainedMoE transformer LM (64 routed top-6 + 2 shared)
+    python bench_configs.py mamba_lm [--batch B]    Mamba (S6) LM, d 2048, 24 layers, seq 4096
+    python bench_configs.py attention --seq 4096 --head-dim 64      forward+backward: flash vs causal linear attention
+
+Every run prints one JSON line. Steps are timed on the device with CUDA events after >= 3 warm-up steps; the
+training configurations move hundreds of MB to GB per step, far above the 126 MB L2; the attention sweep flushes
+L2 between iterations. One GPU per process; launch the LM configurations under torch.distributed.run for
+data-parallel runs (`DistributedAdam` picks the fused reduce-scatter + Adam kernel).
+"""
+from __future__ import annotations
+
+import argparse
+import dataclasses
+import json
+import os
+import sys
+
+import torch
+
+
+def _events():
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def run_lm(name, args):
+    import torch.distributed as dist
+    from rust_neural_network_b200 import _native as nv
+    from rust_neural_network_b200.config import PRESETS, build_model
+    from rust_neural_network_b200.optim import Adam
+    from rust_neural_network_b200.train import Trainer
+
+    world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", "1"), ("RANK", "0"), ("LOCAL_RANK", "0")))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    over = {}
+    if args.layers:
+        over["layers"] = args.layers
+    if args.seq:
+        over["seq_len"] = args.seq
+    torch.manual_seed(1234)
+    model, cfg = build_model(name, dev, **over)
+    batch = args.batch or cfg.batch_per_gpu
+    if world > 1:
+        from rust_neural_network_b200.parallel.ddp import DistributedAdam
+        opt = DistributedAdam(model.parameters(), lr=1e-3)
+    else:
+        opt = Adam(model.parameters(), lr=1e-3)
+    tr = Trainer(model, opt, loss_fn=None, use_cuda_graph=not args.no_graph)
+    g = torch.Generator().manual_seed(1000 + rank)
+    ids = [torch.randint(0, cfg.vocab, (batch, cfg.seq_len), generator=g).pin_memory() for _ in range(2)]
+    lab = [torch.randint(0, cfg.vocab, (batch, cfg.seq_len), generator=g).pin_memory() for _ in range(2)]
+    first = None
+    for i in range(max(args.warmup, 3)):
+        l = tr.train_step(ids[i % 2], lab[i % 2])
+        first = float(l) if first is None else first
+    torch.cuda.synchronize()
+    nv.check_status()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = _events()
+    e0.record()
+    last = 0.0
+    for i in range(args.steps):
+        last = float(tr.train_step(ids[i % 2], lab[i % 2]).item())
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    nv.check_status()
+    n_params = sum(p.numel() for p in model.parameters())
+    if rank == 0:
+        print(json.dumps({"config": name, "impl": "b200", "n_gpus": world, "batch_per_gpu": batch, "seq_len": cfg.seq_len,
+                          "preset": dataclasses.asdict(cfg), "params": n_params, "ms_per_step": ms,
+                          "tokens_per_s": world * batch * cfg.seq_len / ms * 1e3, "end_to_end": True, "cuda_graph": tr._graph is not None,
+                          "launches_per_step": tr.launches_per_step, "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
+                          "loss_first": first, "loss_last": last}), flush=True)
+    if world > 1:
+        tr._graph = None
+        sys.stdout.flush()
+        os._exit(0)
+
+
+def run_mlp(args):
+    from rust_neural_network_b200 import _native as nv
+    from rust_neural_network_b200 import loss as L
+    from rust_neural_network_b200.config import build_model
+    from rust_neural_network_b200.optim import Adam
+    from rust_neural_network_b200.train import Trainer
+
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    model, cfg = build_model("mlp", dev)
+    tr = Trainer(model, Adam(model.parameters(), lr=cfg.lr), L.CrossEntropyLoss(), use_cuda_graph=not args.no_graph)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(cfg.batch, cfg.dims[0], generator=g).pin_memory()
+    y = torch.nn.functional.one_hot(torch.randint(0, cfg.dims[-1], (cfg.batch,), generator=g), cfg.dims[-1]).float().pin_memory()
+    first = float(tr.train_step(x, y))
+    for _ in range(4):
+        tr.train_step(x, y)
+    torch.cuda.synchronize()
+    e0, e1 = _events()
+    e0.record()
+    for _ in range(cfg.steps):
+        l = tr.train_step(x, y)
+    e1.record()
+    torch.cuda.synchronize()
+    nv.check_status()
+    ms = e0.elapsed_time(e1) / cfg.steps
+    print(json.dumps({"config": "mlp", "impl": "b200", "dims": list(cfg.dims), "batch": cfg.batch, "dtype": "fp32 storage, TF32 tensor-core products",
+                      "us_per_step": ms * 1e3, "samples_per_s": cfg.batch / ms * 1e3, "steps": cfg.steps, "cuda_graph": tr._graph is not None,
+                      "launches_per_step": tr.launches_per_step, "loss_first": first, "loss_last": float(l)}), flush=True)
+
+
+def run_attention(args):
+    from rust_neural_network_b200 import _native as nv
+    from rust_neural_network_b200.ops import functional as F
+    from rust_neural_network_b200.ops import linear_attention as LA
+    from rust_neural_network_b200.utils.kernel_bench import time_fn
+
+    dev = torch.device("cuda", 0)
+    B, H, S, d = args.batch or 8, 16, args.seq or 4096, args.head_dim
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(B, S, H, d, device=dev).bfloat16().requires_grad_(True) for _ in range(3))
+    w = torch.randn(B, S, H, d, device=dev).bfloat16()
+    out = {"config": "attention", "batch": B, "heads": H, "seq": S, "head_dim": d, "dtype": "bf16", "l2_policy": "L2 flushed between iterations"}
+
+    def fb(fn):
+        def run():
+            for t in (q, k, v):
+                t.grad = None
+            fn().backward(w)
+        return run
+
+    flops_flash = 4.0 * B * H * S * S * d / 2 * 3.5                     # causal: forward 1x, backward 2.5x of 4 S^2 d / 2
+    ms = time_fn(fb(lambda: F.flash_attention(q, k, v, causal=True)), args.iters)
+    out["flash_causal_fwd_bwd_ms"] = ms
+    out["flash_tflops"] = flops_flash / ms / 1e9
+    for kind in ("elu", "relu2"):
+        ms = time_fn(fb(lambda: LA.linear_attention(q, k, v, kind=kind, causal=True)), args.iters)
+        out[f"linear_{kind}_causal_fwd_bwd_ms"] = ms
+    nv.check_status()
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("config", choices=["mlp", "moe_lm", "mamba_lm", "attention"])
+    ap.add_argument("--batch", type=int, default=0)
+    ap.add_argument("--seq", type=int, default=0)
+    ap.add_argument("--layers", type=int, default=0, help="override the preset's layer count (diagnostics)")
+    ap.add_argument("--head-dim", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    if args.config == "mlp":
+        run_mlp(args)
+    elif args.config == "attention":
+        run_attention(args)
+    else:
+        run_lm(args.config, args)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -207,6 +207,84 @@ colsum_vec_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, 
   }
 }
 
+// Activation backward + bias gradient in one pass: g[r, c] *= act'(saved[r, c]) in place and dbias[c] += the column
+// sums of the result. A GEMM epilogue that reads `saved` is latency-bound (each epilogue warp has 4 KB outstanding);
+// as a streaming kernel the same work runs at copy bandwidth, and the column sum costs no extra pass.
+// Same thread layout as colsum_vec_kernel. OP is OP_GELU_BWD / OP_SILU_BWD / OP_RELU_BWD; the derivatives use the
+// hardware tanh / exp approximations (relative error ~2^-11, below the bf16 result's own rounding).
+template <int OP>
+__device__ __forceinline__ float dact_fast(float a, float s) {
+  if constexpr (OP == OP_RELU_BWD) return s > 0.f ? a : 0.f;
+  else if constexpr (OP == OP_GELU_BWD) {
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(k0 * (s + k1 * s * s * s)));
+    return a * (0.5f * (1.f + t) + 0.5f * s * (1.f - t * t) * (k0 * (1.f + 3.f * k1 * s * s)));
+  } else {
+    const float sg = __fdividef(1.f, 1.f + __expf(-s));
+    return a * sg * (1.f + s * (1.f - sg));
+  }
+}
+template <int OP>
+__global__ void __launch_bounds__(256)
+dact_colsum_kernel(__nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ saved, float* __restrict__ dbias, long long rows, int cols,
+                   long long ld_g, long long ld_s, int rows_per_block) {
+  __shared__ float sh[8][256 + 8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c0 = blockIdx.x * 256 + lane * 8;
+  const long long r0 = (long long)blockIdx.y * rows_per_block;
+  long long r1 = r0 + rows_per_block; if (r1 > rows) r1 = rows;
+  float acc[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+  if (c0 < cols) {
+    auto one = [&](uint4& gv, const uint4& sv) {
+      uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+      const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float lo = dact_fast<OP>(__uint_as_float(gw[k] << 16), __uint_as_float(sw[k] << 16));
+        const float hi = dact_fast<OP>(__uint_as_float(gw[k] & 0xffff0000u), __uint_as_float(sw[k] & 0xffff0000u));
+        const __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
+        gw[k] = *reinterpret_cast<const uint32_t*>(&pk);
+        acc[2 * k] += __low2float(pk); acc[2 * k + 1] += __high2float(pk);       // sums of the ROUNDED values, as a later colsum would see
+      }
+      gv = make_uint4(gw[0], gw[1], gw[2], gw[3]);
+    };
+    long long r = r0 + warp;
+    for (; r + 8 < r1; r += 16) {
+      uint4 gv[2], sv[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        gv[j] = *reinterpret_cast<const uint4*>(g + (r + 8 * j) * ld_g + c0);
+        sv[j] = __ldg(reinterpret_cast<const uint4*>(saved + (r + 8 * j) * ld_s + c0));
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        one(gv[j], sv[j]);
+        *reinterpret_cast<uint4*>(g + (r + 8 * j) * ld_g + c0) = gv[j];
+      }
+    }
+    for (; r < r1; r += 8) {
+      uint4 gv = *reinterpret_cast<const uint4*>(g + r * ld_g + c0);
+      const uint4 sv = __ldg(reinterpret_cast<const uint4*>(saved + r * ld_s + c0));
+      one(gv, sv);
+      *reinterpret_cast<uint4*>(g + r * ld_g + c0) = gv;
+    }
+  }
+  if (dbias == nullptr) return;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) sh[warp][lane * 8 + k] = acc[k];
+  __syncthreads();
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += sh[w][threadIdx.x];
+    atomicAdd(dbias + c, t);
+  }
+}
+
 // batched column sum: out[z, c] += sum_r x[z, r, c]  (per-expert bias gradients)
 template <typename T>
 __global__ void colsum_batched_kernel(const T* __restrict__ x, float* __restrict__ out, long long rows, int cols,
@@ -392,6 +470,25 @@ int b200_cast(const void* x, void* y, long long n, float scale, int dir, cudaStr
   if (n <= 0) return 0;
   if (dir == 0) cast_kernel<float, __nv_bfloat16><<<grid_for(n, 256), 256, 0, st>>>((const float*)x, (__nv_bfloat16*)y, n, scale);
   else cast_kernel<__nv_bfloat16, float><<<grid_for(n, 256), 256, 0, st>>>((const __nv_bfloat16*)x, (float*)y, n, scale);
+  return (int)cudaGetLastError();
+}
+
+// g (bf16, in place) *= act'(saved); dbias (fp32, may be null) += column sums. Needs cols % 8 == 0, both leading
+// dimensions % 8 == 0, 16-byte aligned bases and op in {relu, gelu, silu}_bwd (returns -1 otherwise: the caller falls
+// back to two kernels).
+int b200_dact_colsum(void* g, const void* saved, float* dbias, long long rows, int cols, long long ld_g, long long ld_s, int op, cudaStream_t st) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (cols % 8 || ld_g % 8 || ld_s % 8 || ((uintptr_t)g & 15) || ((uintptr_t)saved & 15)) return -1;
+  const int cb = (cols + 255) / 256;
+  long long rpb = (rows * cb + 148LL * 8 - 1) / (148LL * 8);
+  rpb = rpb < 16 ? 16 : rpb > 512 ? 512 : (rpb + 15) / 16 * 16;
+  dim3 grid(cb, (unsigned)((rows + rpb - 1) / rpb));
+  __nv_bfloat16* gp = (__nv_bfloat16*)g;
+  const __nv_bfloat16* sp = (const __nv_bfloat16*)saved;
+  if (op == OP_GELU_BWD) dact_colsum_kernel<OP_GELU_BWD><<<grid, 256, 0, st>>>(gp, sp, dbias, rows, cols, ld_g, ld_s, (int)rpb);
+  else if (op == OP_SILU_BWD) dact_colsum_kernel<OP_SILU_BWD><<<grid, 256, 0, st>>>(gp, sp, dbias, rows, cols, ld_g, ld_s, (int)rpb);
+  else if (op == OP_RELU_BWD) dact_colsum_kernel<OP_RELU_BWD><<<grid, 256, 0, st>>>(gp, sp, dbias, rows, cols, ld_g, ld_s, (int)rpb);
+  else return -1;
   return (int)cudaGetLastError();
 }
 

@@ -142,6 +142,30 @@ def colsum(x2d, out=None):
     return out
 
 
+def dact_colsum(g, saved, act, bias_grad=None, want_bias_grad=True):
+    """In place g *= act'(saved) for act in {"relu", "gelu", "silu"} (saved = the pre-activation) and, in the same
+    pass, the column sums of the result (the bias gradient), added into `bias_grad` when given. Returns (g, dbias).
+
+    This replaces a GEMM epilogue that multiplies by act'(saved): the epilogue version waits on DRAM for every panel
+    (measured 0.49 ms for a 65536 x 2048 output against 0.13 ms for the plain GEMM), the streaming version runs at
+    copy bandwidth and makes the separate column-sum pass unnecessary."""
+    rows, cols = g.shape
+    op = OPS[act + "_bwd"]
+    if g.is_cuda and g.dtype == torch.bfloat16 and saved.dtype == torch.bfloat16 and g.stride(1) == 1 and saved.stride(1) == 1:
+        db = bias_grad if bias_grad is not None else (torch.zeros(cols, dtype=torch.float32, device=g.device) if want_bias_grad else None)
+        rc = nv.cuda().b200_dact_colsum(g.data_ptr(), saved.data_ptr(), nv.ptr(db), rows, cols, g.stride(0), saved.stride(0), op, nv.stream_ptr())
+        if rc == 0:
+            nv.count_launch()
+            return g, (None if bias_grad is not None else db)
+        if rc != -1:
+            nv.check(rc, "dact_colsum")
+    r = binary(g, saved, act + "_bwd")
+    if bias_grad is not None:
+        colsum(r, out=bias_grad)
+        return r, None
+    return r, (colsum(r) if want_bias_grad else None)
+
+
 def reduce_all(x, what="sum", out=None):
     """Full reduction to a 0-d fp32 tensor: sum | sumsq | max | min."""
     code = {"sum": 0, "sumsq": 1, "max": 2, "min": 3}[what]

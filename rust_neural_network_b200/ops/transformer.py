@@ -87,9 +87,10 @@ class TransformerBlockFn(Function):
         # ---- feed-forward
         dw2 = _wgrad(dy2, a, w2)
         db2 = _bgrad(dy2, b2)
-        dpre = gemm(dy2, lp(w2), b_mn=True, aux_in=pre, dact="gelu")      # (dy W2) * gelu'(pre)
+        # (dy W2) * gelu'(pre): the product is a plain GEMM, the derivative and the bias gradient are one streaming pass
+        fused_b1 = getattr(b1, "_fused_grad", False) and b1.grad is not None
+        dpre, db1 = K.dact_colsum(gemm(dy2, lp(w2), b_mn=True), pre, "gelu", bias_grad=b1.grad if fused_b1 else None)
         dw1 = _wgrad(dpre, h2, w1)
-        db1 = _bgrad(dpre, b1)
         dh2 = gemm(dpre, lp(w1), b_mn=True)
         fused_ln2 = getattr(g2, "_fused_grad", False) and g2.grad is not None
         dy1, dg2, dbe2 = K.layernorm_bwd(dh2, y1, g2.detach(), mean2, rstd2, dres=dy2,

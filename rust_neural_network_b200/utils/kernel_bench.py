@@ -91,6 +91,7 @@ def main(argv=None):
     ap.add_argument("--bias", action="store_true")
     ap.add_argument("--residual", action="store_true")
     ap.add_argument("--act", default="none")
+    ap.add_argument("--dact", default="none", help="multiply the GEMM result by act'(saved pre-activation) in the epilogue (fused activation backward)")
     ap.add_argument("--a-mn", action="store_true")
     ap.add_argument("--b-mn", action="store_true")
     ap.add_argument("--f32-out", action="store_true")
@@ -112,11 +113,12 @@ def main(argv=None):
         b = torch.randn((Kd, N) if args.b_mn else (N, Kd), device=dev).bfloat16()
         bias = torch.randn(N, device=dev) if args.bias else None
         res = torch.randn(M, N, device=dev).bfloat16() if args.residual else None
+        aux_in = torch.randn(M, N, device=dev).bfloat16() if args.dact != "none" else None
         kw = dict(a_mn=args.a_mn, b_mn=args.b_mn, bias=bias, act=args.act, residual=res, want_aux=args.act in ("gelu", "silu"),
-                  out_dtype=torch.float32 if args.f32_out else None, bn=args.bn)
+                  out_dtype=torch.float32 if args.f32_out else None, bn=args.bn, aux_in=aux_in, dact=args.dact)
         ms = time_fn(lambda: G.gemm(a, b, **kw), args.iters)
         flops = 2.0 * M * N * Kd
-        byts = 2.0 * (M * Kd + N * Kd) + (4.0 if args.f32_out else 2.0) * M * N * (2 if kw["want_aux"] else 1) + (2.0 * M * N if res is not None else 0)
+        byts = 2.0 * (M * Kd + N * Kd) + (4.0 if args.f32_out else 2.0) * M * N * (2 if kw["want_aux"] else 1) + (2.0 * M * N if res is not None else 0) + (2.0 * M * N if aux_in is not None else 0)
         out.update(shape=[M, N, Kd], ms=ms, tflops=flops / ms / 1e9, frac_of_bf16_peak=flops / ms / 1e9 / pk["bf16_tflops"],
                    gbs=byts / ms / 1e6, frac_of_hbm_peak=byts / ms / 1e6 / pk["hbm_gbs"])
     elif args.kernel in ("flash_fwd", "flash_bwd"):

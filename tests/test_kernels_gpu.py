@@ -149,6 +149,23 @@ def test_colsum_bf16_vector_path(rows, cols):
     assert float((acc.double() - 1.0 - view.double().sum(0)).abs().max()) < 2e-4 * math.sqrt(rows) + 1e-3
 
 
+@pytest.mark.parametrize("act", ["gelu", "silu", "relu"])
+@pytest.mark.parametrize("rows,cols", [(8192, 2048), (1000, 264), (77, 40), (33, 20)])
+def test_dact_colsum_matches_reference(rows, cols, act):
+    torch.manual_seed(rows + cols)
+    g = torch.randn(rows, cols, device=DEV).bfloat16()
+    pre = (torch.randn(rows, cols, device=DEV) * 1.5).bfloat16()
+    want = (g.float() * G.dact_ref(pre.float(), act)).bfloat16()
+    acc = torch.full((cols,), 2.0, device=DEV)
+    got, none = K.dact_colsum(g.clone(), pre, act, bias_grad=acc)
+    assert none is None
+    assert float((got.float() - want.float()).abs().max()) < 2e-2 * max(1.0, float(want.float().abs().max()))
+    tol = 4e-2 * math.sqrt(rows) + 1e-2
+    assert float((acc - 2.0 - want.float().sum(0)).abs().max()) < tol
+    got2, db = K.dact_colsum(g.clone(), pre, act)
+    assert torch.equal(got2, got) and float((db - want.float().sum(0)).abs().max()) < tol
+
+
 def test_embedding():
     table = lcg_tensor((1000, 64), seed=25).to(DEV).bfloat16()
     ids = torch.randint(0, 1000, (4, 77), device=DEV)

@@ -81,7 +81,7 @@ def run_lm(name, args):
         print(json.dumps({"config": name, "impl": "b200", "n_gpus": world, "batch_per_gpu": batch, "seq_len": cfg.seq_len,
                           "preset": dataclasses.asdict(cfg), "params": n_params, "ms_per_step": ms,
                           "tokens_per_s": world * batch * cfg.seq_len / ms * 1e3, "end_to_end": True, "cuda_graph": tr._graph is not None,
-                          "launches_per_step": tr.launches_per_step, "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
+                          "launches_per_step": getattr(tr, "launches_per_step", None), "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
                           "loss_first": first, "loss_last": last}), flush=True)
     if world > 1:
         tr._graph = None
@@ -117,7 +117,7 @@ def run_mlp(args):
     ms = e0.elapsed_time(e1) / cfg.steps
     print(json.dumps({"config": "mlp", "impl": "b200", "dims": list(cfg.dims), "batch": cfg.batch, "dtype": "fp32 storage, TF32 tensor-core products",
                       "us_per_step": ms * 1e3, "samples_per_s": cfg.batch / ms * 1e3, "steps": cfg.steps, "cuda_graph": tr._graph is not None,
-                      "launches_per_step": tr.launches_per_step, "loss_first": first, "loss_last": float(l)}), flush=True)
+                      "launches_per_step": getattr(tr, "launches_per_step", None), "loss_first": first, "loss_last": float(l)}), flush=True)
 
 
 def run_attention(args):

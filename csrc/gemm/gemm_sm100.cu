@@ -271,8 +271,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
     const long long row_bytes = (long long)p.K * 2;                      // bf16 rows, K % 8 == 0
     const long long blk_vec = (long long)BM * row_bytes / 16;            // 16-byte vectors per row block
     constexpr int UNROLL = 8;
-    // a system-scope fence drains every outstanding NVLink store, so it is paid once per GROUP row blocks
-    constexpr int GROUP = 4;
+    // a system-scope fence drains every outstanding NVLink store, so it is paid once per GROUP row blocks; the group
+    // shrinks when there are fewer row blocks than 4 per gather CTA, so that every gather CTA has work
+    const int GROUP = max(1, min(4, tp.blocks_per_rank / max(n_copy, 1)));
     const int n_groups = (tp.blocks_per_rank + GROUP - 1) / GROUP;
     for (int jg = (int)blockIdx.x; jg < n_groups; jg += n_copy) {
       const int j0 = jg * GROUP;

@@ -44,7 +44,7 @@ def main():
     ap.add_argument("--ncols", type=int, default=2048)          # global N of the column-parallel layer
     ap.add_argument("--iters", type=int, default=0)         # > 0: also time fused vs baseline
     ap.add_argument("--moe", type=int, default=1)
-    ap.add_argument("--copy-ctas", type=int, default=16)
+    ap.add_argument("--copy-ctas", type=int, default=0)        # 0: the context's own choice
     ap.add_argument("--copy-sweep", default="")             # e.g. "16,32,64,96": time all-gather -> GEMM at each gather-CTA count
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -101,12 +101,12 @@ def main():
         mine.copy_(xs)
         out["ms_ag_gemm_fused"] = timed(lambda: ctx.all_gather_gemm(mine, w1s, bias=b1s, act="gelu"), args.iters, dev)
         if args.copy_sweep:
-            sweep = {}
+            sweep, keep = {}, ctx.copy_ctas
             for c in (int(v) for v in args.copy_sweep.split(",")):
                 ctx.copy_ctas = c
                 got = ctx.all_gather_gemm(mine, w1s, bias=b1s, act="gelu")
                 sweep[str(c)] = {"ms": timed(lambda: ctx.all_gather_gemm(mine, w1s, bias=b1s, act="gelu"), args.iters, dev), "rel_err": rel(got, want_h)}
-            ctx.copy_ctas = args.copy_ctas
+            ctx.copy_ctas = keep
             out["ag_gemm_copy_sweep"] = sweep
         out["ms_ag_gemm_nccl"] = timed(lambda: base.all_gather_gemm(xs, w1s, bias=b1s, act="gelu"), args.iters, dev)
         out["ms_gemm_rs_fused"] = timed(lambda: ctx.gemm_reduce_scatter(h, w2s, bias=b2, residual=res), args.iters, dev)

@@ -70,30 +70,37 @@ __global__ void layernorm_fwd_kernel(const T* __restrict__ x, const float* __res
 
 // bf16 rows whose length is a multiple of 256: the row lives in registers (8 contiguous columns per lane and
 // 256-column chunk, one 16-byte load each), so x is read once and mean / variance / output need no second pass.
-template <int J2>
+// J2 16-byte pieces per lane and W warps per row: d = 256 * J2 * W. With W > 1 the warps of a row meet twice per row
+// in shared memory (mean, then variance); every warp of the block runs the same number of iterations so that the
+// block-wide barriers line up.
+template <int J2, int W>
 __global__ void __launch_bounds__(256)
 layernorm_fwd_vec_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
                          __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
                          long long rows, int d, float eps) {
-  const int lane = threadIdx.x & 31;
-  const int warps_per_block = blockDim.x >> 5;
+  __shared__ float red[2][2][8];              // [row parity][mean | variance][warp]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int groups_per_block = (blockDim.x >> 5) / W, grp = warp / W, wi = warp % W;
   float gam[J2][8], bet[J2][8];
 #pragma unroll
   for (int j = 0; j < J2; ++j) {
-    const int c = 8 * lane + 256 * j;
+    const int c = 8 * lane + 256 * (j * W + wi);
     const float4 g0 = *reinterpret_cast<const float4*>(gamma + c), g1 = *reinterpret_cast<const float4*>(gamma + c + 4);
     const float4 b0 = *reinterpret_cast<const float4*>(beta + c), b1 = *reinterpret_cast<const float4*>(beta + c + 4);
     gam[j][0] = g0.x; gam[j][1] = g0.y; gam[j][2] = g0.z; gam[j][3] = g0.w; gam[j][4] = g1.x; gam[j][5] = g1.y; gam[j][6] = g1.z; gam[j][7] = g1.w;
     bet[j][0] = b0.x; bet[j][1] = b0.y; bet[j][2] = b0.z; bet[j][3] = b0.w; bet[j][4] = b1.x; bet[j][5] = b1.y; bet[j][6] = b1.z; bet[j][7] = b1.w;
   }
   const float inv_d = 1.f / d;
-  long long row = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-  const long long row_stride = (long long)gridDim.x * warps_per_block;
-  for (; row < rows; row += row_stride) {
+  const long long row_stride = (long long)gridDim.x * groups_per_block;
+  const long long n_iter = (rows + row_stride - 1) / row_stride;
+  for (long long it = 0; it < n_iter; ++it) {
+    const long long row = it * row_stride + (long long)blockIdx.x * groups_per_block + grp;
+    const bool valid = row < rows;
+    if (W == 1 && !valid) break;
     const __nv_bfloat16* xr = x + row * d;
     uint4 xu[J2];
 #pragma unroll
-    for (int j = 0; j < J2; ++j) xu[j] = __ldg(reinterpret_cast<const uint4*>(xr + 8 * lane + 256 * j));
+    for (int j = 0; j < J2; ++j) xu[j] = valid ? __ldg(reinterpret_cast<const uint4*>(xr + 8 * lane + 256 * (j * W + wi))) : make_uint4(0u, 0u, 0u, 0u);
     float v[J2][8];
     float s = 0.f;
 #pragma unroll
@@ -104,13 +111,30 @@ layernorm_fwd_vec_kernel(const __nv_bfloat16* __restrict__ x, const float* __res
 #pragma unroll
       for (int e = 0; e < 8; ++e) s += v[j][e];
     }
-    const float mean = wsum(s) * inv_d;
+    s = wsum(s);
+    if constexpr (W > 1) {
+      if (lane == 0) red[it & 1][0][warp] = s;
+      __syncthreads();
+      s = 0.f;
+#pragma unroll
+      for (int k = 0; k < W; ++k) s += red[it & 1][0][grp * W + k];
+    }
+    const float mean = s * inv_d;
     float q = 0.f;
 #pragma unroll
     for (int j = 0; j < J2; ++j)
 #pragma unroll
       for (int e = 0; e < 8; ++e) { const float a = v[j][e] - mean; q += a * a; }
-    const float rstd = rsqrtf(wsum(q) * inv_d + eps);
+    q = wsum(q);
+    if constexpr (W > 1) {
+      if (lane == 0) red[it & 1][1][warp] = q;
+      __syncthreads();
+      q = 0.f;
+#pragma unroll
+      for (int k = 0; k < W; ++k) q += red[it & 1][1][grp * W + k];
+      if (!valid) continue;
+    }
+    const float rstd = rsqrtf(q * inv_d + eps);
     __nv_bfloat16* yr = y + row * d;
 #pragma unroll
     for (int j = 0; j < J2; ++j) {
@@ -122,9 +146,9 @@ layernorm_fwd_vec_kernel(const __nv_bfloat16* __restrict__ x, const float* __res
       uint4 ou;
       ou.x = *reinterpret_cast<uint32_t*>(&t0); ou.y = *reinterpret_cast<uint32_t*>(&t1);
       ou.z = *reinterpret_cast<uint32_t*>(&t2); ou.w = *reinterpret_cast<uint32_t*>(&t3);
-      *reinterpret_cast<uint4*>(yr + 8 * lane + 256 * j) = ou;
+      *reinterpret_cast<uint4*>(yr + 8 * lane + 256 * (j * W + wi)) = ou;
     }
-    if (lane == 0) { if (mean_out) mean_out[row] = mean; if (rstd_out) rstd_out[row] = rstd; }
+    if (lane == 0 && wi == 0) { if (mean_out) mean_out[row] = mean; if (rstd_out) rstd_out[row] = rstd; }
   }
 }
 
@@ -240,19 +264,20 @@ layernorm_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
 
 // bf16 rows whose length is a multiple of 256: every lane owns 8 contiguous columns per 256-column chunk and
 // moves them with one 16-byte load / store (4x fewer memory instructions than the 2-column variant above).
-template <int J2>
+template <int J2, int W>
 __global__ void __launch_bounds__(256)
 layernorm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
                          const float* __restrict__ mean_in, const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
                          float* __restrict__ dgamma, float* __restrict__ dbeta, const __nv_bfloat16* __restrict__ dres,
                          long long rows, int d) {
-  extern __shared__ float sh[];   // [warps][2][d]
+  extern __shared__ float sh[];   // [row groups][2][d]
+  __shared__ float red[2][2][8];  // [row parity][s1 | s2][warp]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int warps_per_block = blockDim.x >> 5;
+  const int groups_per_block = (blockDim.x >> 5) / W, grp = warp / W, wi = warp % W;
   float gam[J2][8], adg[J2][8], adb[J2][8];
 #pragma unroll
   for (int j = 0; j < J2; ++j) {
-    const int c = 8 * lane + 256 * j;
+    const int c = 8 * lane + 256 * (j * W + wi);
     const float4 g0 = *reinterpret_cast<const float4*>(gamma + c), g1 = *reinterpret_cast<const float4*>(gamma + c + 4);
     gam[j][0] = g0.x; gam[j][1] = g0.y; gam[j][2] = g0.z; gam[j][3] = g0.w; gam[j][4] = g1.x; gam[j][5] = g1.y; gam[j][6] = g1.z; gam[j][7] = g1.w;
 #pragma unroll
@@ -264,19 +289,25 @@ layernorm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat
 #pragma unroll
     for (int i = 0; i < 4; ++i) { o[2 * i] = __uint_as_float(w[i] << 16); o[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
   };
-  long long row = (long long)blockIdx.x * warps_per_block + warp;
-  const long long row_stride = (long long)gridDim.x * warps_per_block;
-  for (; row < rows; row += row_stride) {
+  const long long row_stride = (long long)gridDim.x * groups_per_block;
+  const long long n_iter = (rows + row_stride - 1) / row_stride;
+  for (long long it = 0; it < n_iter; ++it) {
+    const long long row = it * row_stride + (long long)blockIdx.x * groups_per_block + grp;
+    const bool valid = row < rows;
+    if (W == 1 && !valid) break;
     const __nv_bfloat16* xr = x + row * d; const __nv_bfloat16* gr = dy + row * d;
     uint4 xu[J2], gu[J2], ru[J2];
 #pragma unroll
     for (int j = 0; j < J2; ++j) {            // all loads of the row first: maximum memory-level parallelism
-      const int c = 8 * lane + 256 * j;
-      xu[j] = __ldg(reinterpret_cast<const uint4*>(xr + c));
-      gu[j] = __ldg(reinterpret_cast<const uint4*>(gr + c));
-      if (dres) ru[j] = __ldg(reinterpret_cast<const uint4*>(dres + row * d + c));
+      const int c = 8 * lane + 256 * (j * W + wi);
+      xu[j] = gu[j] = ru[j] = make_uint4(0u, 0u, 0u, 0u);
+      if (valid) {
+        xu[j] = __ldg(reinterpret_cast<const uint4*>(xr + c));
+        gu[j] = __ldg(reinterpret_cast<const uint4*>(gr + c));
+        if (dres) ru[j] = __ldg(reinterpret_cast<const uint4*>(dres + row * d + c));
+      }
     }
-    const float mean = mean_in[row], rstd = rstd_in[row];
+    const float mean = valid ? mean_in[row] : 0.f, rstd = valid ? rstd_in[row] : 0.f;
     float xh[J2][8], g[J2][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
@@ -292,11 +323,20 @@ layernorm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat
         adb[j][e] += g[j][e];
       }
     }
-    s1 = wsum(s1) * inv_d; s2 = wsum(s2) * inv_d;
+    s1 = wsum(s1); s2 = wsum(s2);
+    if constexpr (W > 1) {
+      if (lane == 0) { red[it & 1][0][warp] = s1; red[it & 1][1][warp] = s2; }
+      __syncthreads();
+      s1 = s2 = 0.f;
+#pragma unroll
+      for (int k = 0; k < W; ++k) { s1 += red[it & 1][0][grp * W + k]; s2 += red[it & 1][1][grp * W + k]; }
+      if (!valid) continue;
+    }
+    s1 *= inv_d; s2 *= inv_d;
     __nv_bfloat16* dxr = dx + row * d;
 #pragma unroll
     for (int j = 0; j < J2; ++j) {
-      const int c = 8 * lane + 256 * j;
+      const int c = 8 * lane + 256 * (j * W + wi);
       float o[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) o[e] = rstd * (g[j][e] * gam[j][e] - s1 - xh[j][e] * s2);
@@ -314,17 +354,17 @@ layernorm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat
       *reinterpret_cast<uint4*>(dxr + c) = ou;
     }
   }
-  float* my = sh + (size_t)warp * 2 * d;
+  float* my = sh + (size_t)grp * 2 * d;
 #pragma unroll
   for (int j = 0; j < J2; ++j) {
-    const int c = 8 * lane + 256 * j;
+    const int c = 8 * lane + 256 * (j * W + wi);
 #pragma unroll
     for (int e = 0; e < 8; ++e) { my[c + e] = adg[j][e]; my[d + c + e] = adb[j][e]; }
   }
   __syncthreads();
   for (int c = threadIdx.x; c < 2 * d; c += blockDim.x) {
     float acc = 0.f;
-    for (int w = 0; w < warps_per_block; ++w) acc += sh[(size_t)w * 2 * d + c];
+    for (int w = 0; w < groups_per_block; ++w) acc += sh[(size_t)w * 2 * d + c];
     atomicAdd(c < d ? dgamma + c : dbeta + (c - d), acc);
   }
 }
@@ -398,9 +438,14 @@ int b200_layernorm_fwd(const void* x, const float* gamma, const float* beta, voi
   if (rows <= 0) return 0;
   const int block = 256, wpb = block / 32;
   long long g = (rows + wpb - 1) / wpb; if (g > 148 * 8) g = 148 * 8;
-  if (is_bf16 && d % 256 == 0 && d <= 1024 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)gamma % 16 == 0 && (uintptr_t)beta % 16 == 0) {
-#define B200_LNF(JJ) layernorm_fwd_vec_kernel<JJ><<<(int)g, block, 0, st>>>((const __nv_bfloat16*)x, gamma, beta, (__nv_bfloat16*)y, mean, rstd, rows, d, eps);
-    switch (d / 256) { case 1: B200_LNF(1) break; case 2: B200_LNF(2) break; case 3: B200_LNF(3) break; default: B200_LNF(4) break; }
+  const bool fwd_vec_d = d % 256 == 0 && (d <= 1024 || d == 1536 || d == 2048 || d == 3072 || d == 4096);
+  if (is_bf16 && fwd_vec_d && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)gamma % 16 == 0 && (uintptr_t)beta % 16 == 0) {
+#define B200_LNF(JJ, WW) { const int gpb = wpb / WW; long long gg = (rows + gpb - 1) / gpb; if (gg > 148 * 8) gg = 148 * 8; \
+      layernorm_fwd_vec_kernel<JJ, WW><<<(int)gg, block, 0, st>>>((const __nv_bfloat16*)x, gamma, beta, (__nv_bfloat16*)y, mean, rstd, rows, d, eps); }
+    switch (d / 256) {
+      case 1: B200_LNF(1, 1) break; case 2: B200_LNF(2, 1) break; case 3: B200_LNF(3, 1) break; case 4: B200_LNF(4, 1) break;
+      case 6: B200_LNF(3, 2) break; case 8: B200_LNF(4, 2) break; case 12: B200_LNF(3, 4) break; default: B200_LNF(4, 4) break;
+    }
 #undef B200_LNF
     return (int)cudaGetLastError();
   }
@@ -418,19 +463,24 @@ int b200_layernorm_bwd(const void* dy, const void* x, const float* gamma, const 
   long long g = (rows + wpb - 1) / wpb; if (g > 148 * 2) g = 148 * 2;
   const bool aligned16 = ((uintptr_t)dy % 16 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)dx % 16 == 0) && (!dres || (uintptr_t)dres % 16 == 0) &&
                          ((uintptr_t)gamma % 16 == 0);
-  if (is_bf16 && d % 256 == 0 && d <= 1024 && aligned16) {
-    const size_t sm = (size_t)wpb * 2 * d * sizeof(float);
-#define B200_LNV(JJ) { auto k = layernorm_bwd_vec_kernel<JJ>; \
-      if (sm > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); if (e != cudaSuccess) return (int)e; } \
-      k<<<(int)g, block, sm, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, gamma, mean, rstd, (__nv_bfloat16*)dx, dgamma, dbeta, (const __nv_bfloat16*)dres, rows, d); }
-    switch (d / 256) { case 1: B200_LNV(1) break; case 2: B200_LNV(2) break; case 3: B200_LNV(3) break; default: B200_LNV(4) break; }
+  const bool bwd_vec_d = d % 256 == 0 && (d <= 1024 || d == 1536 || d == 2048 || d == 3072 || d == 4096);
+  if (is_bf16 && bwd_vec_d && aligned16) {
+#define B200_LNV(JJ, WW) { auto k = layernorm_bwd_vec_kernel<JJ, WW>; const int gpb = wpb / WW; \
+      const size_t sm = (size_t)gpb * 2 * d * sizeof(float); \
+      long long gg = (rows + gpb - 1) / gpb; if (gg > 148 * 2) gg = 148 * 2; \
+      if (sm + 256 > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); if (e != cudaSuccess) return (int)e; } \
+      k<<<(int)gg, block, sm, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, gamma, mean, rstd, (__nv_bfloat16*)dx, dgamma, dbeta, (const __nv_bfloat16*)dres, rows, d); }
+    switch (d / 256) {
+      case 1: B200_LNV(1, 1) break; case 2: B200_LNV(2, 1) break; case 3: B200_LNV(3, 1) break; case 4: B200_LNV(4, 1) break;
+      case 6: B200_LNV(3, 2) break; case 8: B200_LNV(4, 2) break; case 12: B200_LNV(3, 4) break; default: B200_LNV(4, 4) break;
+    }
 #undef B200_LNV
     return (int)cudaGetLastError();
   }
   if (d % 2 == 0 && d <= 1024) {
     const size_t sm = (size_t)wpb * 2 * d * sizeof(float);   // <= 64 KB
 #define B200_LNB(TT, JJ) { auto k = layernorm_bwd_reg_kernel<TT, JJ>; \
-      if (sm > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); if (e != cudaSuccess) return (int)e; } \
+      if (sm + 256 > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); if (e != cudaSuccess) return (int)e; } \
       k<<<(int)g, block, sm, st>>>((const TT*)dy, (const TT*)x, gamma, mean, rstd, (TT*)dx, dgamma, dbeta, (const TT*)dres, rows, d); }
     if (is_bf16) { if (d <= 256) B200_LNB(__nv_bfloat16, 4) else if (d <= 512) B200_LNB(__nv_bfloat16, 8) else B200_LNB(__nv_bfloat16, 16) }
     else { if (d <= 256) B200_LNB(float, 4) else if (d <= 512) B200_LNB(float, 8) else B200_LNB(float, 16) }

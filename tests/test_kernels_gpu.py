@@ -190,7 +190,8 @@ def test_dropout_and_fake_quant():
 
 # ----------------------------------------------------------------------------- norms
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("rows,d", [(64, 512), (1000, 384), (33, 129), (17, 2048)])
+@pytest.mark.parametrize("rows,d", [(64, 512), (1000, 384), (33, 129), (17, 2048), (1237, 2048), (301, 1536), (77, 3072), (130, 4096), (5000, 1024),
+                                    (9, 1280)])
 def test_layernorm(rows, d, dtype):
     x = (lcg_tensor((rows, d), seed=30) * 2 + 0.5).to(DEV).to(dtype)
     gamma = (lcg_tensor((d,), seed=31) + 1.5).to(DEV)

@@ -77,7 +77,11 @@ template <int J2, int W>
 __global__ void __launch_bounds__(256)
 layernorm_fwd_vec_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
                          __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
-                         long long rows, int d, float eps) {
+                         long long rows, int d, float eps,
+                         const __nv_bfloat16* __restrict__ res = nullptr, __nv_bfloat16* __restrict__ sum_out = nullptr) {
+  // with `res`: the normalised row is x + res (rounded to bf16 first, so that it equals what `sum_out` stores and what
+  // the backward pass will read); `sum_out` receives that sum. This is the residual add of the layer before, moved
+  // out of its GEMM epilogue.
   __shared__ float red[2][2][8];              // [row parity][mean | variance][warp]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int groups_per_block = (blockDim.x >> 5) / W, grp = warp / W, wi = warp % W;
@@ -108,6 +112,19 @@ layernorm_fwd_vec_kernel(const __nv_bfloat16* __restrict__ x, const float* __res
       const uint32_t w[4] = {xu[j].x, xu[j].y, xu[j].z, xu[j].w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) { v[j][2 * i] = __uint_as_float(w[i] << 16); v[j][2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+      if (res != nullptr) {
+        const int c = 8 * lane + 256 * (j * W + wi);
+        const uint4 ru = valid ? __ldg(reinterpret_cast<const uint4*>(res + row * d + c)) : make_uint4(0u, 0u, 0u, 0u);
+        const uint32_t rw[4] = {ru.x, ru.y, ru.z, ru.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const __nv_bfloat162 t = __floats2bfloat162_rn(v[j][2 * i] + __uint_as_float(rw[i] << 16), v[j][2 * i + 1] + __uint_as_float(rw[i] & 0xffff0000u));
+          ow[i] = *reinterpret_cast<const uint32_t*>(&t);
+          v[j][2 * i] = __low2float(t); v[j][2 * i + 1] = __high2float(t);
+        }
+        if (valid && sum_out != nullptr) *reinterpret_cast<uint4*>(sum_out + row * d + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      }
 #pragma unroll
       for (int e = 0; e < 8; ++e) s += v[j][e];
     }
@@ -433,15 +450,39 @@ using namespace b200;
 
 extern "C" {
 
+static int layernorm_fwd_vec_dispatch(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd,
+                                      long long rows, int d, float eps, const void* res, void* sum_out, cudaStream_t st);
+
+// y = LayerNorm(x + res), sum_out = x + res (bf16 only, row width as the 16-byte-access kernel takes it; -1 otherwise)
+int b200_add_layernorm_fwd(const void* x, const void* res, const float* gamma, const float* beta, void* sum_out, void* y, float* mean,
+                           float* rstd, long long rows, int d, float eps, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (((uintptr_t)res | (uintptr_t)sum_out) % 16) return -1;
+  return layernorm_fwd_vec_dispatch(x, gamma, beta, y, mean, rstd, rows, d, eps, res, sum_out, st);
+}
+
 int b200_layernorm_fwd(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd,
                        long long rows, int d, float eps, int is_bf16, cudaStream_t st) {
   if (rows <= 0) return 0;
   const int block = 256, wpb = block / 32;
   long long g = (rows + wpb - 1) / wpb; if (g > 148 * 8) g = 148 * 8;
+  if (is_bf16) {
+    const int rc = layernorm_fwd_vec_dispatch(x, gamma, beta, y, mean, rstd, rows, d, eps, nullptr, nullptr, st);
+    if (rc != -1) return rc;
+  }
+  if (is_bf16) layernorm_fwd_kernel<__nv_bfloat16><<<(int)g, block, 0, st>>>((const __nv_bfloat16*)x, gamma, beta, (__nv_bfloat16*)y, mean, rstd, rows, d, eps);
+  else layernorm_fwd_kernel<float><<<(int)g, block, 0, st>>>((const float*)x, gamma, beta, (float*)y, mean, rstd, rows, d, eps);
+  return (int)cudaGetLastError();
+}
+
+
+static int layernorm_fwd_vec_dispatch(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd,
+                                      long long rows, int d, float eps, const void* res, void* sum_out, cudaStream_t st) {
+  const int block = 256, wpb = block / 32;
   const bool fwd_vec_d = d % 256 == 0 && (d <= 1024 || d == 1536 || d == 2048 || d == 3072 || d == 4096);
-  if (is_bf16 && fwd_vec_d && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)gamma % 16 == 0 && (uintptr_t)beta % 16 == 0) {
+  if (fwd_vec_d && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)gamma % 16 == 0 && (uintptr_t)beta % 16 == 0) {
 #define B200_LNF(JJ, WW) { const int gpb = wpb / WW; long long gg = (rows + gpb - 1) / gpb; if (gg > 148 * 8) gg = 148 * 8; \
-      layernorm_fwd_vec_kernel<JJ, WW><<<(int)gg, block, 0, st>>>((const __nv_bfloat16*)x, gamma, beta, (__nv_bfloat16*)y, mean, rstd, rows, d, eps); }
+      layernorm_fwd_vec_kernel<JJ, WW><<<(int)gg, block, 0, st>>>((const __nv_bfloat16*)x, gamma, beta, (__nv_bfloat16*)y, mean, rstd, rows, d, eps, (const __nv_bfloat16*)res, (__nv_bfloat16*)sum_out); }
     switch (d / 256) {
       case 1: B200_LNF(1, 1) break; case 2: B200_LNF(2, 1) break; case 3: B200_LNF(3, 1) break; case 4: B200_LNF(4, 1) break;
       case 6: B200_LNF(3, 2) break; case 8: B200_LNF(4, 2) break; case 12: B200_LNF(3, 4) break; default: B200_LNF(4, 4) break;
@@ -449,9 +490,7 @@ int b200_layernorm_fwd(const void* x, const float* gamma, const float* beta, voi
 #undef B200_LNF
     return (int)cudaGetLastError();
   }
-  if (is_bf16) layernorm_fwd_kernel<__nv_bfloat16><<<(int)g, block, 0, st>>>((const __nv_bfloat16*)x, gamma, beta, (__nv_bfloat16*)y, mean, rstd, rows, d, eps);
-  else layernorm_fwd_kernel<float><<<(int)g, block, 0, st>>>((const float*)x, gamma, beta, (float*)y, mean, rstd, rows, d, eps);
-  return (int)cudaGetLastError();
+  return -1;
 }
 
 // dgamma / dbeta are accumulated into (caller zero-initialises for a fresh gradient)

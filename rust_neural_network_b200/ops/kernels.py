@@ -247,6 +247,28 @@ def layernorm_fwd(x2d, gamma, beta, eps):
     return y, mean, rstd
 
 
+def add_layernorm_fwd(x2d, res2d, gamma, beta, eps):
+    """(s, y, mean, rstd) with s = x + res and y = LayerNorm(s): the residual add of the layer before and the
+    normalisation in one pass over the row (bf16 rows of a width the 16-byte-access kernel takes; two kernels
+    otherwise). A residual add inside a GEMM epilogue is latency-bound; here it costs one extra streamed read."""
+    rows, d = x2d.shape
+    if x2d.is_cuda and x2d.dtype == torch.bfloat16 and res2d.dtype == torch.bfloat16 and x2d.is_contiguous() and res2d.is_contiguous():
+        s = torch.empty_like(x2d)
+        y = torch.empty_like(x2d)
+        mean = torch.empty(rows, dtype=torch.float32, device=x2d.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x2d.device)
+        rc = nv.cuda().b200_add_layernorm_fwd(x2d.data_ptr(), res2d.data_ptr(), gamma.data_ptr(), beta.data_ptr(), s.data_ptr(), y.data_ptr(),
+                                              mean.data_ptr(), rstd.data_ptr(), rows, d, float(eps), nv.stream_ptr())
+        if rc == 0:
+            nv.count_launch()
+            return s, y, mean, rstd
+        if rc != -1:
+            nv.check(rc, "add_layernorm_fwd")
+    s = binary(x2d, res2d, "add") if x2d.is_cuda else (x2d.float() + res2d.float()).to(x2d.dtype)
+    y, mean, rstd = layernorm_fwd(s, gamma, beta, eps)
+    return s, y, mean, rstd
+
+
 def layernorm_bwd(dy2d, x2d, gamma, mean, rstd, dres=None, dgamma=None, dbeta=None):
     """Returns (dx [+ dres], dgamma, dbeta). `dres` is an optional gradient of the same shape that is
     added to dx in the same pass (the residual branch); dgamma/dbeta may be existing fp32

@@ -66,8 +66,8 @@ class TransformerBlockFn(Function):
         qkv5 = qkv.view(B, S, 3, heads, hd)
         o, lse = K.flash_fwd(qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2], 1.0 / math.sqrt(hd), causal)
         o2 = o.view(T, d)
-        y1 = gemm(o2, lp(wo), bias=bo.detach(), residual=x2)              # x + attn
-        h2, mean2, rstd2 = K.layernorm_fwd(y1, g2.detach(), be2.detach(), eps)
+        # x + attn and its LayerNorm in one pass: the add is cheaper here than in the projection's epilogue
+        y1, h2, mean2, rstd2 = K.add_layernorm_fwd(gemm(o2, lp(wo), bias=bo.detach()), x2, g2.detach(), be2.detach(), eps)
         a, pre = gemm(h2, lp(w1), bias=b1.detach(), act="gelu", want_aux=True)
         y2 = gemm(a, lp(w2), bias=b2.detach(), residual=y1)               # h + ff
         ctx.save_for_backward(x2, mean1, rstd1, h1, qkv, o, lse, y1, mean2, rstd2, h2, pre, a,

@@ -65,7 +65,10 @@ class TPContext:
                 raise ValueError(f"rows ({max_rows}) must be a multiple of world * {BM}")
             self.rows_per_rank = max_rows // self.world
             dev = self.device
-            self.stage = SymmetricBuffer(max_rows * max_k, torch.bfloat16, dev, self.group)                 # all-gather staging [M, K]
+            # all-gather staging [2][M, K]: calls alternate between the halves, so the gathered rows of a call stay
+            # readable (e.g. for the weight gradient that follows) until the call after the next one
+            self.stage = SymmetricBuffer(2 * max_rows * max_k, torch.bfloat16, dev, self.group)
+            self.ag_calls = 0
             self.slots = SymmetricBuffer(2 * self.world * self.rows_per_rank * max_n, torch.bfloat16, dev, self.group)
             self.flags = SymmetricBuffer(2 * TP_MAX_WORLD + max_rows // BM, torch.int32, dev, self.group)   # handshake words, then ready[m_blocks]
             self.local = torch.zeros(8, dtype=torch.int32, device=dev)                                       # go, done_ctr
@@ -81,8 +84,12 @@ class TPContext:
         activation shard here (peers read it in place)."""
         if rows_local * self.world > self.max_rows or k > self.max_k:
             raise ValueError("call exceeds the context's capacity")
+        return self._stage_view(self.ag_calls & 1, rows_local, k)[self.rank * rows_local:(self.rank + 1) * rows_local]
+
+    def _stage_view(self, half: int, rows_local: int, k: int) -> torch.Tensor:
         m = rows_local * self.world
-        return self.stage.tensor[: m * k].view(m, k)[self.rank * rows_local:(self.rank + 1) * rows_local]
+        off = half * self.max_rows * self.max_k
+        return self.stage.tensor[off: off + m * k].view(m, k)
 
     def _tp(self, mode: int, rows_local: int) -> TpParams:
         self.epoch += 1
@@ -98,28 +105,40 @@ class TPContext:
             tp.ready_peer[r] = self.flags.ptrs[r] + 4 * 2 * TP_MAX_WORLD
         return tp
 
-    def all_gather_gemm(self, x_shard: torch.Tensor, w_shard: torch.Tensor, bias=None, act: str = "none", want_aux: bool = False):
+    def all_gather_gemm(self, x_shard: torch.Tensor, w_shard: torch.Tensor, bias=None, act: str = "none", want_aux: bool = False,
+                        return_gathered: bool = False):
         """x_shard [rows_local, K] (this rank's rows; if it is not already `ag_input(...)` it is copied there),
-        w_shard [N_local, K] -> act(gather(x) @ w_shard^T + bias) [rows_local * world, N_local] bf16."""
+        w_shard [N_local, K] -> act(gather(x) @ w_shard^T + bias) [rows_local * world, N_local] bf16.
+        `return_gathered` appends gather(x) [M, K] to the result: on the fused path a view of the staging half of this
+        call, valid until the call after the next one on this context."""
         rows_local, k = x_shard.shape
         n = w_shard.shape[0]
         m = rows_local * self.world
         if self.backend != "fused":
             xs = [torch.empty_like(x_shard) for _ in range(self.world)]
             dist.all_gather(xs, x_shard.contiguous(), group=self.group)
-            return G.gemm(torch.cat(xs, 0), w_shard, bias=bias, act=act, want_aux=want_aux)
+            xg = torch.cat(xs, 0)
+            res = G.gemm(xg, w_shard, bias=bias, act=act, want_aux=want_aux)
+            if not return_gathered:
+                return res
+            return (*res, xg) if want_aux else (res, xg)
         if rows_local % BM != 0 or k % 8 != 0 or n % 8 != 0:
             raise ValueError("fused all_gather_gemm needs rows_local % 128 == 0 and K, N % 8 == 0")
         mine = self.ag_input(rows_local, k)
         if x_shard.data_ptr() != mine.data_ptr():
             mine.copy_(x_shard)
+        half = self.ag_calls & 1
+        self.ag_calls += 1
         tp = self._tp(TP_AG_GEMM, rows_local)
         for r in range(self.world):
-            tp.stage_peer[r] = self.stage.ptrs[r]
+            tp.stage_peer[r] = self.stage.ptrs[r] + half * self.max_rows * self.max_k * 2
         out = torch.empty(m, n, dtype=torch.bfloat16, device=self.device)
         aux = torch.empty(m, n, dtype=torch.bfloat16, device=self.device) if want_aux else None
-        self._launch(tp, mine, w_shard, m, n, k, out, bias, act, None, aux)
-        return (out, aux) if want_aux else out
+        self._launch(tp, self._stage_view(half, rows_local, k), w_shard, m, n, k, out, bias, act, None, aux)
+        res = (out, aux) if want_aux else (out,)
+        if return_gathered:
+            res = (*res, self._stage_view(half, rows_local, k))
+        return res if len(res) > 1 else res[0]
 
     # ------------------------------------------------------------------ GEMM -> reduce-scatter
     def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, bias=None, residual=None) -> torch.Tensor:
@@ -179,3 +198,138 @@ class TPContext:
         nv.check(rc, "b200_gemm_tp_launch")
         nv.count_launch()
         self._keep = (a, b, bias, residual, out, aux)          # alive until the next call on this context
+
+
+# ------------------------------------------------------------------------------------------------------------
+# Differentiable sharded layers. The backward of each fused op is the OTHER fused op:
+#   column-parallel  Y = gather(X_s) W_s^T     dX_s = reduce_scatter(dY W_s)        dW_s = dY^T gather(X_s)
+#   row-parallel     Z_s = reduce_scatter(H W_s^T)   dH = gather(dZ_s) W_s            dW_s = gather(dZ_s)^T H
+# so a sharded MLP trains with four fused GEMM + collective kernels and two local weight-gradient GEMMs per step.
+class _ColumnParallelFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_shard, w, b, tpc, act):
+        from ..ops.functional import compute_weight
+        W = compute_weight(w, x_shard)
+        bias = b.detach() if b is not None else None
+        if act in ("gelu", "silu"):
+            y, pre, xg = tpc.all_gather_gemm(x_shard, W, bias=bias, act=act, want_aux=True, return_gathered=True)
+        else:
+            y, xg = tpc.all_gather_gemm(x_shard, W, bias=bias, act=act, return_gathered=True)
+            pre = y if act == "relu" else None
+        # the gathered input is needed for the weight gradient long after the staging half has been reused
+        ctx.save_for_backward(xg.clone(), w, b if b is not None else torch.empty(0), pre if pre is not None else torch.empty(0))
+        ctx.tpc, ctx.act = tpc, act
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops import kernels as K
+        from ..ops.functional import compute_weight
+        xg, w, b, pre = ctx.saved_tensors
+        tpc, act = ctx.tpc, ctx.act
+        dy = dy.contiguous()
+        db = None
+        if act != "none":
+            dy, db = K.dact_colsum(dy.clone(), pre, act, want_bias_grad=b.numel() > 0)
+        elif b.numel() > 0:
+            db = K.colsum(dy)
+        dw = G.gemm(dy, xg, a_mn=True, b_mn=True, out_dtype=torch.float32)                  # [N_local, K]
+        wt = compute_weight(w, dy).t().contiguous()                                         # [K, N_local]
+        dx = tpc.gemm_reduce_scatter(dy, wt)                                                # [rows_local, K]
+        return dx, dw.to(w.dtype), (db.to(b.dtype) if db is not None and b.numel() > 0 else None), None, None
+
+
+class _RowParallelFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, w, b, residual, tpc):
+        from ..ops.functional import compute_weight
+        z = tpc.gemm_reduce_scatter(h, compute_weight(w, h), bias=b.detach() if b is not None else None, residual=residual)
+        ctx.save_for_backward(h, w, b if b is not None else torch.empty(0))
+        ctx.tpc, ctx.has_res = tpc, residual is not None
+        return z
+
+    @staticmethod
+    def backward(ctx, dz):
+        from ..ops import kernels as K
+        from ..ops.functional import compute_weight
+        h, w, b = ctx.saved_tensors
+        tpc = ctx.tpc
+        dz = dz.contiguous()
+        wt = compute_weight(w, dz).t().contiguous()                                         # [K_local, N]
+        dh, dzg = tpc.all_gather_gemm(dz, wt, return_gathered=True)                         # [M, K_local], gather(dz) [M, N]
+        dw = G.gemm(dzg, h, a_mn=True, b_mn=True, out_dtype=torch.float32)                  # [N, K_local]
+        db = K.colsum(dzg).to(b.dtype) if b.numel() > 0 else None                           # replicated bias: every rank sums all rows
+        return dh, dw.to(w.dtype), db, (dz if ctx.has_res else None), None
+
+
+class ColumnParallelLinear:
+    """Linear whose OUTPUT features are sharded: this rank holds rows [rank * N/world, (rank + 1) * N/world) of the
+    weight. Input: this rank's rows of a row-sharded activation [rows_local, K]; output: all rows, local features
+    [rows_local * world, N/world]. `full_weight` / `full_bias`, when given, are sliced (same values on every rank)."""
+
+    def __init__(self, in_features: int, out_features: int, tpc: TPContext, bias: bool = True, act: str = "none",
+                 full_weight: Optional[torch.Tensor] = None, full_bias: Optional[torch.Tensor] = None, init_std: float = 0.02):
+        if out_features % tpc.world:
+            raise ValueError("out_features must divide by the tensor-parallel world size")
+        n_local = out_features // tpc.world
+        lo = tpc.rank * n_local
+        dev = tpc.device
+        if full_weight is None:
+            g = torch.Generator().manual_seed(1234)
+            full_weight = torch.randn(out_features, in_features, generator=g) * init_std
+        self.weight = full_weight[lo:lo + n_local].detach().clone().to(dev, torch.float32).requires_grad_(True)
+        self.bias = None
+        if bias:
+            fb = full_bias if full_bias is not None else torch.zeros(out_features)
+            self.bias = fb[lo:lo + n_local].detach().clone().to(dev, torch.float32).requires_grad_(True)
+        self.tpc, self.act = tpc, act
+
+    def parameters(self):
+        return [self.weight] + ([self.bias] if self.bias is not None else [])
+
+    def __call__(self, x_shard: torch.Tensor) -> torch.Tensor:
+        return _ColumnParallelFn.apply(x_shard, self.weight, self.bias, self.tpc, self.act)
+
+
+class RowParallelLinear:
+    """Linear whose INPUT features are sharded: this rank holds columns [rank * K/world, ...) of the weight. Input:
+    all rows, local features [M, K/world]; output: this rank's rows of the full sum [M / world, N] (+ bias, + this
+    rank's rows of a residual)."""
+
+    def __init__(self, in_features: int, out_features: int, tpc: TPContext, bias: bool = True,
+                 full_weight: Optional[torch.Tensor] = None, full_bias: Optional[torch.Tensor] = None, init_std: float = 0.02):
+        if in_features % tpc.world:
+            raise ValueError("in_features must divide by the tensor-parallel world size")
+        k_local = in_features // tpc.world
+        lo = tpc.rank * k_local
+        dev = tpc.device
+        if full_weight is None:
+            g = torch.Generator().manual_seed(4321)
+            full_weight = torch.randn(out_features, in_features, generator=g) * init_std
+        self.weight = full_weight[:, lo:lo + k_local].detach().clone().to(dev, torch.float32).requires_grad_(True)
+        self.bias = None
+        if bias:
+            fb = full_bias if full_bias is not None else torch.zeros(out_features)
+            self.bias = fb.detach().clone().to(dev, torch.float32).requires_grad_(True)
+        self.tpc = tpc
+
+    def parameters(self):
+        return [self.weight] + ([self.bias] if self.bias is not None else [])
+
+    def __call__(self, h: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return _RowParallelFn.apply(h, self.weight, self.bias, residual, self.tpc)
+
+
+class TensorParallelMLP:
+    """x_s + W2 act(W1 gather(x_s)) on row-sharded activations: all-gather -> GEMM (+bias, activation), then
+    GEMM -> reduce-scatter (+bias, +residual). Forward and backward are four fused kernels and two local GEMMs."""
+
+    def __init__(self, d_model: int, hidden: int, tpc: TPContext, act: str = "gelu", w1=None, b1=None, w2=None, b2=None):
+        self.up = ColumnParallelLinear(d_model, hidden, tpc, act=act, full_weight=w1, full_bias=b1)
+        self.down = RowParallelLinear(hidden, d_model, tpc, full_weight=w2, full_bias=b2)
+
+    def parameters(self):
+        return self.up.parameters() + self.down.parameters()
+
+    def __call__(self, x_shard: torch.Tensor, residual: bool = True) -> torch.Tensor:
+        return self.down(self.up(x_shard), x_shard if residual else None)

@@ -209,6 +209,19 @@ def test_layernorm(rows, d, dtype):
     assert rel_err(db, br.grad) < 1e-3
 
 
+@pytest.mark.parametrize("rows,d", [(1000, 512), (77, 2048), (33, 384), (65, 129)])
+def test_add_layernorm_fwd(rows, d):
+    torch.manual_seed(d)
+    x = torch.randn(rows, d, device=DEV).bfloat16(); r = torch.randn(rows, d, device=DEV).bfloat16()
+    gamma = torch.rand(d, device=DEV) + 0.5; beta = torch.randn(d, device=DEV)
+    s, y, mean, rstd = K.add_layernorm_fwd(x, r, gamma, beta, 1e-5)
+    want_s = (x.float() + r.float()).bfloat16()
+    assert torch.equal(s, want_s)
+    ref = torch.nn.functional.layer_norm(want_s.float(), (d,), gamma, beta, 1e-5)
+    assert torch.allclose(y.float(), ref, atol=3e-2, rtol=3e-2)
+    assert torch.allclose(mean, want_s.float().mean(1), atol=1e-4) and torch.allclose(rstd, torch.rsqrt(want_s.float().var(1, unbiased=False) + 1e-5), rtol=1e-3)
+
+
 def test_batchnorm():
     x = (lcg_tensor((64, 300), seed=34) * 2 + 1).to(DEV)
     gamma = (lcg_tensor((300,), seed=35) + 1.5).to(DEV); beta = lcg_tensor((300,), seed=36).to(DEV)

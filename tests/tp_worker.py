@@ -115,6 +115,37 @@ def main():
         out["ms_gemm_local_row"] = timed(lambda: G.gemm(h, w2s), args.iters, dev)
         nv.check_status()
 
+    # ---- differentiable sharded MLP (forward + backward = four fused kernels) against the unsharded layers
+    if args.moe:
+        from rust_neural_network_b200.parallel.tp import TensorParallelMLP
+        Mm, dm, hm = world * 256, 256, 1024
+        gm = torch.Generator().manual_seed(21)
+        Xm = (torch.randn(Mm, dm, generator=gm) * 0.5).to(torch.bfloat16).to(dev)
+        Wa, ba = torch.randn(hm, dm, generator=gm) * 0.05, torch.randn(hm, generator=gm) * 0.1
+        Wb, bb = torch.randn(dm, hm, generator=gm) * 0.05, torch.randn(dm, generator=gm) * 0.1
+        GYm = torch.randn(Mm, dm, generator=gm).to(torch.bfloat16).to(dev)
+        ref_p = [t.to(dev).float().requires_grad_(True) for t in (Wa, ba, Wb, bb)]
+        xr = Xm.float().requires_grad_(True)
+        yr = xr + torch.nn.functional.gelu(xr @ ref_p[0].t() + ref_p[1], approximate="tanh") @ ref_p[2].t() + ref_p[3]
+        yr.backward(GYm.float())
+        mctx = TPContext(Mm, hm, hm, device=dev, backend="fused")
+        mlp = TensorParallelMLP(dm, hm, mctx, act="gelu", w1=Wa, b1=ba, w2=Wb, b2=bb)
+        rl, hl = Mm // world, hm // world
+        xs_m = Xm[rank * rl:(rank + 1) * rl].clone().requires_grad_(True)
+        for _ in range(2):                                   # twice: staging halves and epochs alternate
+            for t in [xs_m] + mlp.parameters():
+                t.grad = None
+            ym = mlp(xs_m)
+            ym.backward(GYm[rank * rl:(rank + 1) * rl])
+        torch.cuda.synchronize()
+        nv.check_status()
+        out["tpmlp_fwd_rel_err"] = rel(ym, yr[rank * rl:(rank + 1) * rl])
+        out["tpmlp_dx_rel_err"] = rel(xs_m.grad, xr.grad[rank * rl:(rank + 1) * rl])
+        out["tpmlp_dW1_rel_err"] = rel(mlp.up.weight.grad, ref_p[0].grad[rank * hl:(rank + 1) * hl])
+        out["tpmlp_db1_rel_err"] = rel(mlp.up.bias.grad, ref_p[1].grad[rank * hl:(rank + 1) * hl])
+        out["tpmlp_dW2_rel_err"] = rel(mlp.down.weight.grad, ref_p[2].grad[:, rank * hl:(rank + 1) * hl])
+        out["tpmlp_db2_rel_err"] = rel(mlp.down.bias.grad, ref_p[3].grad)
+
     # ---- expert parallelism: dispatch / combine over peer memory
     if args.moe:
         from rust_neural_network_b200.models.moe import FineGrainedMoE

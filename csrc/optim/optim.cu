@@ -27,8 +27,10 @@ __global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, 
   long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4;
   const long long stride = (long long)gridDim.x * blockDim.x * 4;
   for (; i + 3 < n; i += stride) {
-    float4 pp = *reinterpret_cast<float4*>(p + i), gg = *reinterpret_cast<const float4*>(g + i);
-    float4 mm = *reinterpret_cast<float4*>(m + i), vv = *reinterpret_cast<float4*>(v + i);
+    // every byte is touched once per step: streaming loads / stores keep the 4 read and 4 write streams from evicting
+    // one another (and the bf16 shadow, which the next forward reads) out of L2
+    float4 pp = __ldcs(reinterpret_cast<const float4*>(p + i)), gg = __ldcs(reinterpret_cast<const float4*>(g + i));
+    float4 mm = __ldcs(reinterpret_cast<const float4*>(m + i)), vv = __ldcs(reinterpret_cast<const float4*>(v + i));
     float* P = &pp.x; float* G = &gg.x; float* M = &mm.x; float* V = &vv.x;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -38,7 +40,7 @@ __global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, 
       V[j] = h.b2 * V[j] + ob2 * gr * gr;
       P[j] -= lr_t * M[j] / (sqrtf(V[j]) * c2 + h.eps);
     }
-    *reinterpret_cast<float4*>(p + i) = pp; *reinterpret_cast<float4*>(m + i) = mm; *reinterpret_cast<float4*>(v + i) = vv;
+    __stcs(reinterpret_cast<float4*>(p + i), pp); __stcs(reinterpret_cast<float4*>(m + i), mm); __stcs(reinterpret_cast<float4*>(v + i), vv);
     if (shadow) {
       __nv_bfloat162 a = __floats2bfloat162_rn(pp.x, pp.y), b = __floats2bfloat162_rn(pp.z, pp.w);
       uint2 o; o.x = *reinterpret_cast<uint32_t*>(&a); o.y = *reinterpret_cast<uint32_t*>(&b);

@@ -116,8 +116,17 @@ class TransformerBlockFn(Function):
         if not fused_w:
             dwqkv = gemm(dqkv, h1, a_mn=True, b_mn=True, out_dtype=torch.float32)
             dwq, dwk, dwv = dwqkv[:d], dwqkv[d:2 * d], dwqkv[2 * d:]
-        dbqkv = K.colsum(dqkv)
-        dbq, dbk, dbv = dbqkv[:d], dbqkv[d:2 * d], dbqkv[2 * d:]
+        fused_b = all(getattr(t, "_fused_grad", False) and t.grad is not None for t in (bq, bk, bv))
+        if fused_b:
+            gb = _fused_vec(bq, bk, bv, lambda t: t.grad)
+            if gb.data_ptr() == bq.grad.data_ptr():                     # adjacent in the flat gradient buffer: accumulate in place
+                K.colsum(dqkv, out=gb)
+                dbq = dbk = dbv = None
+            else:
+                fused_b = False
+        if not fused_b:
+            dbqkv = K.colsum(dqkv)
+            dbq, dbk, dbv = dbqkv[:d], dbqkv[d:2 * d], dbqkv[2 * d:]
         dh1 = gemm(dqkv, _fused_qkv(wq, wk, wv, lp), b_mn=True)
         fused_ln1 = getattr(g1, "_fused_grad", False) and g1.grad is not None
         dx, dg1, dbe1 = K.layernorm_bwd(dh1, x2, g1.detach(), mean1, rstd1, dres=dy1,

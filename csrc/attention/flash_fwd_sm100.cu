@@ -24,6 +24,7 @@ struct FwdParams {
   int B, H, Sq, Skv;
   float scale_log2;
   uint32_t* status;
+  int global_order;      // causal: schedule ALL heads' heaviest query blocks first (only while K and V of all heads fit L2-ish)
 };
 
 template <int HD, int BN, bool CAUSAL>
@@ -55,7 +56,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int m_blocks = (p.Sq + BMQ - 1) / BMQ;
   int bid = blockIdx.x;
   // heavy (late, causal) query blocks first
-  const int qb = m_blocks - 1 - (bid % m_blocks); bid /= m_blocks;
+  const int n_bh = p.B * p.H;
+  // heavy (late, causal) query blocks first: across all heads when their K / V stay cache-resident (the last wave is
+  // then made of the lightest CTAs), else per head (CTAs of one head run together and share its K / V in L2)
+  const bool glob = CAUSAL && p.global_order;
+  const int qb = glob ? m_blocks - 1 - bid / n_bh : m_blocks - 1 - (bid % m_blocks);
+  bid = glob ? bid % n_bh : bid / m_blocks;
   const int h = bid % p.H; const int b = bid / p.H;
   const int q0 = qb * BMQ;
 
@@ -279,6 +285,7 @@ static int launch_fwd(const FlashArgs& a, cudaStream_t st) {
   p.o = (__nv_bfloat16*)a.o.ptr; p.o_sb = a.o.sb; p.o_ss = a.o.ss; p.o_sh = a.o.sh;
   p.lse = a.lse; p.B = a.B; p.H = a.H; p.Sq = a.Sq; p.Skv = a.Skv;
   p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.global_order = ((long long)a.B * a.H * a.Skv * a.hd * 4 <= 300ll * 1024 * 1024) ? 1 : 0;
   p.status = a.status;
   const long long grid = (long long)((a.Sq + 127) / 128) * a.H * a.B;
   kfn<<<(unsigned)grid, 128, SMEM, st>>>(tmQ, tmK, tmV, p);

@@ -603,34 +603,40 @@ __global__ void conv1d_bwd_kernel(const T* __restrict__ x, long long x_ld, const
   T* dxp = dx + (long long)b * S * dx_ld + c;
   const int t1 = min(t0 + CONV_TCHUNK, S);
   float dbacc = 0.f;
-  // dpre at time t (0 outside [0,S)); recomputes the convolution at t
-  auto dpre_at = [&](int t) -> float {
-    if (t < 0 || t >= S) return 0.f;
-    float g = s_ld(gp + (long long)t * dy_ld);
+  // Sliding windows, one new x and one new dy per time step:
+  //   xw[i]   = x[t - (K-1) + i], i in [0, 2K-1)   (0 outside [0, S)): covers the taps of dpre[t + K-1] and of dw at t
+  //   dwin[i] = dpre[t + i],      i in [0, K)        with dpre = dy * act'(pre), pre recomputed from the window
+  float xw[2 * K - 1], dwin[K];
+#pragma unroll
+  for (int i = 0; i < 2 * K - 2; ++i) { const int tx = t0 - (K - 1) + i; xw[i] = (tx >= 0 && tx < S) ? s_ld(xp + (long long)tx * x_ld) : 0.f; }
+  auto dpre_from = [&](int t, const float* xtaps) -> float {          // xtaps[j] = x[t - (K-1) + j]
+    if (t >= S) return 0.f;
+    const float g = s_ld(gp + (long long)t * dy_ld);
     if (!act) return g;
     float pre = bs;
 #pragma unroll
-    for (int k = 0; k < K; ++k) { const int tx = t - (K - 1) + k; if (tx >= 0) pre += wk[k] * s_ld(xp + (long long)tx * x_ld); }
+    for (int j = 0; j < K; ++j) pre = fmaf(wk[j], xtaps[j], pre);
     const float sg = sigmoidf_(pre);
     return g * sg * (1.f + pre * (1.f - sg));
   };
-  // sliding window dwin[i] = dpre[t + i], i in [0, K)
-  float dwin[K];
 #pragma unroll
-  for (int k = 0; k < K - 1; ++k) dwin[k] = dpre_at(t0 + k);
+  for (int k = 0; k < K - 1; ++k) dwin[k] = dpre_from(t0 + k, xw + k);
   for (int t = t0; t < t1; ++t) {
-    dwin[K - 1] = dpre_at(t + K - 1);
+    const int tn = t + K - 1;
+    xw[2 * K - 2] = tn < S ? s_ld(xp + (long long)tn * x_ld) : 0.f;
+    dwin[K - 1] = dpre_from(tn, xw + K - 1);
     float acc = 0.f;
 #pragma unroll
-    for (int k = 0; k < K; ++k) acc += wk[k] * dwin[K - 1 - k];
+    for (int k = 0; k < K; ++k) acc = fmaf(wk[k], dwin[K - 1 - k], acc);
     s_st(dxp + (long long)t * dx_ld, acc);
-    // weight / bias gradients use dpre[t] (= dwin[0]) against x[t-(K-1)+k]
-    const float dp = dwin[0];
+    const float dp = dwin[0];                              // dpre[t] against x[t - (K-1) + k] = xw[k]
     dbacc += dp;
 #pragma unroll
-    for (int k = 0; k < K; ++k) { const int tx = t - (K - 1) + k; if (tx >= 0) dwk[k] += dp * s_ld(xp + (long long)tx * x_ld); }
+    for (int k = 0; k < K; ++k) dwk[k] = fmaf(dp, xw[k], dwk[k]);
 #pragma unroll
     for (int k = 0; k < K - 1; ++k) dwin[k] = dwin[k + 1];
+#pragma unroll
+    for (int i = 0; i < 2 * K - 2; ++i) xw[i] = xw[i + 1];
   }
 #pragma unroll
   for (int k = 0; k < K; ++k) atomicAdd(dw + c * K + k, dwk[k]);

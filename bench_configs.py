@@ -4,6 +4,8 @@
     python bench_configs.py moe_lm   [--batch B]    FineGrainedMoE transformer LM (64 routed top-6 + 2 shared)
     python bench_configs.py mamba_lm [--batch B]    Mamba (S6) LM, d 2048, 24 layers, seq 4096
     python bench_configs.py attention --seq 4096 --head-dim 64      forward+backward: flash vs causal linear attention
+    python -m torch.distributed.run --nproc-per-node 8 ... bench_configs.py attention_sp --seq 65536
+                                                    sequence-parallel causal linear attention (KV-state exchange kernel)
 
 Every run prints one JSON line. Steps are timed on the device with CUDA events after >= 3 warm-up steps; the
 training configurations move hundreds of MB to GB per step, far above the 126 MB L2; the attention sweep flushes
@@ -151,9 +153,53 @@ def run_attention(args):
     print(json.dumps(out), flush=True)
 
 
+def run_attention_sp(args):
+    """Causal linear attention over a sequence sharded across the ranks (launch under torch.distributed.run): every rank
+    holds seq / world tokens; only the d x (d + 8) KV states cross NVLink (one fused exchange kernel per direction)."""
+    import torch.distributed as dist
+    from rust_neural_network_b200 import _native as nv
+    from rust_neural_network_b200.ops import linear_attention as LA
+    from rust_neural_network_b200.parallel.sp import SPContext
+
+    world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", "1"), ("RANK", "0"), ("LOCAL_RANK", "0")))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=dev)
+    B, H, S, d = args.batch or 8, 16, args.seq or 65536, args.head_dim
+    s_loc = S // world
+    torch.manual_seed(rank)
+    q, k, v = (torch.randn(B, s_loc, H, d, device=dev).bfloat16().requires_grad_(True) for _ in range(3))
+    w = torch.randn(B, s_loc, H, d, device=dev).bfloat16()
+    sp = SPContext(B * H * d * (d + 8), device=dev, backend="fused")
+    out = {"config": "attention_sp", "n_gpus": world, "batch": B, "heads": H, "seq": S, "seq_per_gpu": s_loc, "head_dim": d, "dtype": "bf16"}
+    for kind in ("elu", "relu2"):
+        def step():
+            for t in (q, k, v):
+                t.grad = None
+            LA.linear_attention(q, k, v, kind=kind, causal=True, sp=sp).backward(w)
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = _events()
+        e0.record()
+        for _ in range(args.iters):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / args.iters], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out[f"linear_{kind}_causal_fwd_bwd_ms"] = float(t.item())
+    nv.check_status()
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    sys.stdout.flush()
+    os._exit(0)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("config", choices=["mlp", "moe_lm", "mamba_lm", "attention"])
+    ap.add_argument("config", choices=["mlp", "moe_lm", "mamba_lm", "attention", "attention_sp"])
     ap.add_argument("--batch", type=int, default=0)
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="override the preset's layer count (diagnostics)")
@@ -167,6 +213,8 @@ def main():
         run_mlp(args)
     elif args.config == "attention":
         run_attention(args)
+    elif args.config == "attention_sp":
+        run_attention_sp(args)
     else:
         run_lm(args.config, args)
     return 0

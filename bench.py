@@ -36,6 +36,8 @@ METRIC = "train tokens/s (looped-transformer LM, device-timed, max over ranks)"
 def reference_arm(args):
     # The reference is a Rust crate (Cargo.toml, no setup.py / pyproject.toml): pip cannot install it and
     # there is no cargo / rustc in this image, so it cannot be built or run here.
+    if int(os.environ.get("RANK", "0")) != 0:          # under torch.distributed.run only rank 0 reports
+        return 0
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference is a Rust crate: pip install fails (no setup.py/pyproject.toml) and no cargo/rustc toolchain is available offline",
                       "metric": METRIC, "n_gpus": args.gpus}))

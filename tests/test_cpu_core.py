@@ -349,3 +349,25 @@ def test_alibi_sinusoidal_learned_carope():
     c = CARoPE(8, 5, 12).with_spread(0.2)
     out = c.apply(torch.randn(2, 7, 8), torch.randn(7, 5))
     assert out.shape == (2, 7, 8) and len(c.parameters()) == 1
+
+
+def test_dact_colsum_and_add_layernorm_reference_paths():
+    """CPU restatements of the two streaming kernels that took work out of GEMM epilogues."""
+    import torch
+    from rust_neural_network_b200.ops import gemm as G
+    from rust_neural_network_b200.ops import kernels as K
+    torch.manual_seed(0)
+    g, pre = torch.randn(37, 24), torch.randn(37, 24)
+    for act in ("relu", "gelu", "silu"):
+        want = g * G.dact_ref(pre, act)
+        acc = torch.ones(24)
+        got, none = K.dact_colsum(g.clone(), pre, act, bias_grad=acc)
+        assert none is None and torch.allclose(got, want, atol=1e-5)
+        assert torch.allclose(acc, 1.0 + want.sum(0), atol=1e-4)
+        got2, db = K.dact_colsum(g.clone(), pre, act)
+        assert torch.allclose(db, want.sum(0), atol=1e-4) and torch.allclose(got2, want, atol=1e-5)
+    x, r = torch.randn(9, 16), torch.randn(9, 16)
+    gamma, beta = torch.rand(16) + 0.5, torch.randn(16)
+    s, y, mean, rstd = K.add_layernorm_fwd(x, r, gamma, beta, 1e-5)
+    assert torch.allclose(s, x + r) and torch.allclose(y, torch.nn.functional.layer_norm(x + r, (16,), gamma, beta, 1e-5), atol=1e-5)
+    assert torch.allclose(mean, (x + r).mean(1), atol=1e-6)

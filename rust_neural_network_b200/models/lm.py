@@ -12,6 +12,7 @@ import torch
 from .. import nn
 from ..ops import functional as F
 from ..ops.transformer import lm_head_ce
+from ..parallel.ddp import mark
 from .looped_transformer import LoopedTransformer, _add_row
 
 
@@ -38,7 +39,14 @@ class LoopedTransformerLM(nn.Module):
         pos = F.embedding(torch.arange(S, device=ids.device), self.pos.weight, self.compute_dtype)
         h = _add_rows(h, pos)
         h, _ = self.core.trunk(h)
-        return self.core.ln_final(h)
+        return self.core.ln_final(mark(h, 1))
+
+    def dp_groups(self):
+        """Parameter groups in the order their gradients complete LAST -> FIRST during backward (group 1 is final as
+        soon as backward has passed the trunk's output; the shared block accumulates over all loops)."""
+        c = self.core
+        return [self.tok.parameters() + self.pos.parameters() + c.block.parameters() + c.time_proj.parameters(),
+                c.ln_final.parameters() + self.lm_head.parameters()]
 
     def forward(self, ids):
         return self.lm_head(self.hidden(ids))

@@ -25,6 +25,7 @@ from .. import nn
 from ..ops import functional as F
 from ..ops.scan import causal_conv1d, selective_scan
 from ..ops.transformer import lm_head_ce
+from ..parallel.ddp import mark
 from .looped_transformer import _add
 
 
@@ -153,9 +154,15 @@ class MambaLM(nn.Module):
 
     def hidden(self, ids):
         h = self.tok(ids)
-        for n, b in zip(self.norms, self.blocks):
+        for i, (n, b) in enumerate(zip(self.norms, self.blocks)):
+            h = mark(h, i + 1)
             h = _add(h, b(n(h)))
-        return self.ln_final(h)
+        return self.ln_final(mark(h, len(self.blocks) + 1))
+
+    def dp_groups(self):
+        """Parameter groups in forward order; `mark(h, k)` sits in front of group k."""
+        return ([self.tok.parameters()] + [n.parameters() + b.parameters() for n, b in zip(self.norms, self.blocks)]
+                + [self.ln_final.parameters() + self.lm_head.parameters()])
 
     def forward(self, ids):
         return self.lm_head(self.hidden(ids))

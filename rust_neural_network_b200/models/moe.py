@@ -396,12 +396,20 @@ class MoETransformerLM(nn.Module):
         h = self.tok(ids)
         h = _add_rows(h, F.embedding(torch.arange(S, device=ids.device), self.pos.weight, self.compute_dtype))
         aux = None
-        for ln1, at, ln2, moe in zip(self.ln1, self.attn, self.ln2, self.moe):
+        from ..parallel.ddp import mark
+        for i, (ln1, at, ln2, moe) in enumerate(zip(self.ln1, self.attn, self.ln2, self.moe)):
+            h = mark(h, i + 1)
             h = at(ln1(h), residual=h)
             h = F_add(h, moe(ln2(h)))
             if moe.last_aux_loss is not None:
                 aux = moe.last_aux_loss if aux is None else aux + moe.last_aux_loss
-        return self.ln_final(h), aux
+        return self.ln_final(mark(h, len(self.moe) + 1)), aux
+
+    def dp_groups(self):
+        """Parameter groups in forward order; `mark(h, k)` sits in front of group k."""
+        layers = [a.parameters() + b.parameters() + c.parameters() + d.parameters()
+                  for a, b, c, d in zip(self.ln1, self.attn, self.ln2, self.moe)]
+        return [self.tok.parameters() + self.pos.parameters()] + layers + [self.ln_final.parameters() + self.lm_head.parameters()]
 
     def loss(self, ids, labels):
         from ..ops.transformer import lm_head_ce

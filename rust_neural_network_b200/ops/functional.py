@@ -36,7 +36,12 @@ def lp(p: torch.Tensor) -> torch.Tensor:
 
 
 def compute_weight(w: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
-    return lp(w) if like.dtype == torch.bfloat16 else w.detach()
+    if like.dtype == torch.bfloat16:
+        return lp(w)
+    if getattr(w, "_dp_sharded", False):
+        raise RuntimeError("fp32 compute reads the fp32 master weights, which a sharded data-parallel optimizer keeps "
+                           "current only on the owning rank: use bf16 compute, or DistributedAdam(mode='nccl')")
+    return w.detach()
 
 
 def _wgrad(g2, x2, w, alpha_t=None):

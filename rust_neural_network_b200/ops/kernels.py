@@ -171,7 +171,12 @@ def reduce_all(x, what="sum", out=None):
     code = {"sum": 0, "sumsq": 1, "max": 2, "min": 3}[what]
     if not x.is_cuda:
         f = x.float()
-        return {"sum": f.sum, "sumsq": lambda: (f * f).sum(), "max": f.max, "min": f.min}[what]()
+        r = {"sum": f.sum, "sumsq": lambda: (f * f).sum(), "max": f.max, "min": f.min}[what]()
+        if out is not None:                    # same contract as the kernel: combine into the caller's accumulator
+            o = out.view(())
+            o.copy_({0: o + r, 1: o + r, 2: torch.maximum(o, r), 3: torch.minimum(o, r)}[code])
+            return o
+        return r
     x = x.contiguous()
     if out is None:
         init = {0: 0.0, 1: 0.0, 2: -math.inf, 3: math.inf}[code]

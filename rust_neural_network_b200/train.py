@@ -44,6 +44,8 @@ class Trainer:
         self.model, self.optimizer, self.loss_fn = model, optimizer, loss_fn
         self.use_cuda_graph = use_cuda_graph
         self.grad_clip = grad_clip
+        if grad_clip is not None and hasattr(optimizer, "max_grad_norm"):
+            optimizer.max_grad_norm = float(grad_clip)      # sharded optimizers clip inside their reduce passes
         self._graph = None
         self._static = None
         self.steps = 0

@@ -68,6 +68,7 @@ struct DpFusedArgs {
   float clip_max_norm;                    // scale_mode 1: > 0 clips, <= 0 only reports the norm
   float* norm_out;                        // optional: the global gradient norm (written by CTA 0)
   int bump_pass;                          // 1: this launch closes a two-pass step (bump words[2])
+  float red_scale;                        // multiplies the summed gradient: 1/world (mean over ranks) or 1 (sum)
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -227,7 +228,7 @@ __global__ void __launch_bounds__(DP_THREADS, 1) dp_fused_adam_kernel(const __gr
   const uint32_t epoch = a.words[0] + 1u;
   if (!handshake(a, 0, epoch)) { retire(a); return; }
   const Hyper h = make_hyper(a);
-  const float gs = h.gs / (float)a.world;
+  const float gs = h.gs * a.red_scale;
 
   const long long shard = (a.end - a.begin) / a.world;
   const long long base = a.begin + shard * a.rank;
@@ -284,7 +285,7 @@ __global__ void __launch_bounds__(DP_THREADS, 1) dp_reduce_kernel(const __grid_c
   const int par = a.words[2] & 1;
   const int table = a.nseg > 0 ? a.nseg : 1;
   float* my_partial = a.partial[a.rank] + (size_t)par * table;
-  const float inv_w = 1.f / (float)a.world;
+  const float inv_w = a.red_scale;
 
   const long long shard = (a.end - a.begin) / a.world;
   const long long base = a.begin + shard * a.rank;

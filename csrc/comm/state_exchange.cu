@@ -27,9 +27,11 @@ struct StateExchangeArgs {
   long long numel;                  // multiple of 4
   int rank, world;
   int mode;                         // 0: sum of ranks < rank, 1: sum of ranks > rank, 2: sum of all ranks
-  uint32_t epoch;
+  uint32_t epoch;                   // used when `words` is null (a caller that numbers its calls itself)
   long long wait_cycles;
   uint32_t* status;
+  uint32_t* words;                  // local device words: [0] calls so far (this call's epoch is [0] + 1; the last CTA to
+                                    // retire stores it back, so a replayed launch gets a fresh epoch), [1] retired CTAs
 };
 
 __device__ __forceinline__ void sx_st_release(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
@@ -39,7 +41,7 @@ __device__ __forceinline__ uint32_t sx_ld_acquire(const uint32_t* p) {
   return v;
 }
 
-__device__ __forceinline__ bool sx_handshake(const StateExchangeArgs& a, int phase) {
+__device__ __forceinline__ bool sx_handshake(const StateExchangeArgs& a, int phase, uint32_t epoch) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
@@ -48,9 +50,9 @@ __device__ __forceinline__ bool sx_handshake(const StateExchangeArgs& a, int pha
     const size_t out_slot = ((size_t)phase * SX_MAX_WORLD + a.rank) * SX_MAX_CTAS + blockIdx.x;
     const size_t in_slot = ((size_t)phase * SX_MAX_WORLD + peer) * SX_MAX_CTAS + blockIdx.x;
     __threadfence_system();
-    sx_st_release(a.flags[peer] + out_slot, a.epoch);
+    sx_st_release(a.flags[peer] + out_slot, epoch);
     const long long t0 = clock64();
-    while ((int32_t)(sx_ld_acquire(a.flags[a.rank] + in_slot) - a.epoch) < 0) {
+    while ((int32_t)(sx_ld_acquire(a.flags[a.rank] + in_slot) - epoch) < 0) {
       if (clock64() - t0 > a.wait_cycles) { s_ok = 0; if (a.status) atomicCAS(a.status, 0u, (uint32_t)ST_TIMEOUT_PEER_FLAG); break; }
       __nanosleep(64);
     }
@@ -60,15 +62,16 @@ __device__ __forceinline__ bool sx_handshake(const StateExchangeArgs& a, int pha
 }
 
 __global__ void __launch_bounds__(256, 1) state_exchange_kernel(const __grid_constant__ StateExchangeArgs a) {
+  const uint32_t epoch = a.words ? *reinterpret_cast<volatile const uint32_t*>(a.words) + 1u : a.epoch;
   const long long n4 = a.numel / 4;
   const long long stride = (long long)gridDim.x * blockDim.x;
   const long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   // 1. publish. Each CTA publishes and later reads the SAME index range, so the per-CTA handshake orders them.
   for (long long i = i0; i < n4; i += stride)
     reinterpret_cast<float4*>(a.slot[a.rank])[i] = reinterpret_cast<const float4*>(a.inp)[i];
-  if (!sx_handshake(a, 0)) return;
+  const bool ok = sx_handshake(a, 0, epoch);
   // 3. sum the peers this rank needs
-  for (long long i = i0; i < n4; i += stride) {
+  for (long long i = i0; i < n4 && ok; i += stride) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int r = 0; r < a.world; ++r) {
       const bool take = a.mode == 2 || (a.mode == 0 && r < a.rank) || (a.mode == 1 && r > a.rank);
@@ -78,7 +81,11 @@ __global__ void __launch_bounds__(256, 1) state_exchange_kernel(const __grid_con
     }
     reinterpret_cast<float4*>(a.out)[i] = acc;
   }
-  sx_handshake(a, 1);
+  if (ok) sx_handshake(a, 1, epoch);
+  if (a.words && threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(a.words + 1, 1u) == gridDim.x - 1) { a.words[1] = 0u; __threadfence(); a.words[0] = epoch; }
+  }
 }
 
 }  // namespace b200

@@ -201,13 +201,13 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t want, long
   return true;
 }
 // one thread: tell every peer `which` (0: shard ready, 1: done) and, if `wait`, wait for all of them
-__device__ __forceinline__ bool peer_handshake(const TpParams& tp, int which, bool wait, uint32_t* status) {
+__device__ __forceinline__ bool peer_handshake(const TpParams& tp, uint32_t epoch, int which, bool wait, uint32_t* status) {
   __threadfence_system();
-  for (int r = 0; r < tp.world; ++r) st_release_sys_u32(tp.flags[r] + which * TP_MAX_WORLD + tp.rank, tp.epoch);
+  for (int r = 0; r < tp.world; ++r) st_release_sys_u32(tp.flags[r] + which * TP_MAX_WORLD + tp.rank, epoch);
   bool ok = true;
   if (wait)
     for (int r = 0; r < tp.world && ok; ++r)
-      ok = wait_flag<true>(tp.flags[tp.rank] + which * TP_MAX_WORLD + r, tp.epoch, tp.wait_cycles, status, ST_TIMEOUT_PEER_FLAG);
+      ok = wait_flag<true>(tp.flags[tp.rank] + which * TP_MAX_WORLD + r, epoch, tp.wait_cycles, status, ST_TIMEOUT_PEER_FLAG);
   return ok;
 }
 
@@ -245,6 +245,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
   const int cta = (int)blockIdx.x - n_copy;
   const int n_ctas = (int)gridDim.x - n_copy;
   const int tp_shift = (TP == TP_AG_GEMM) ? tpp->rank * tpp->blocks_per_rank : 0;   // start with the local rows
+  // The handshake epoch of a tensor-parallel call lives in device memory (one word per context) and is advanced by the
+  // call's last CTA, so a CUDA-graph replay of the launch sees a fresh epoch every time.
+  const uint32_t tp_epoch = (TP != TP_NONE) ? *reinterpret_cast<volatile const uint32_t*>(tpp->epoch_ptr) + 1u : 0u;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
@@ -303,7 +306,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
       __syncthreads();
       if (threadIdx.x == 0)
         for (int rr = 1; rr < tp.world; ++rr)
-          for (int q = 0; q < nblk; ++q) st_release_sys_u32(tp.ready_peer[(tp.rank + rr) % tp.world] + mbg + q, tp.epoch);
+          for (int q = 0; q < nblk; ++q) st_release_sys_u32(tp.ready_peer[(tp.rank + rr) % tp.world] + mbg + q, tp_epoch);
       __syncthreads();
     }
   } else if (warp == 0) {
@@ -321,7 +324,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         if constexpr (TP == TP_AG_GEMM) {
           // rows of another rank: wait until the gather CTAs have landed this row block
           if (mb / tpp->blocks_per_rank != tpp->rank) {
-            if (!wait_flag<true>(tpp->ready_peer[tpp->rank] + mb, tpp->epoch, tpp->wait_cycles, p.status, ST_TIMEOUT_PEER_FLAG)) { ok = false; break; }
+            if (!wait_flag<true>(tpp->ready_peer[tpp->rank] + mb, tp_epoch, tpp->wait_cycles, p.status, ST_TIMEOUT_PEER_FLAG)) { ok = false; break; }
             fence_proxy_async_all();
           }
         }
@@ -548,7 +551,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
             const TpParams& tp = *tpp;
             const int owner = mb / tp.blocks_per_rank;
             const long long rows_per_rank = (long long)tp.blocks_per_rank * BM;
-            const long long slot = ((long long)(tp.epoch & 1u) * tp.world + tp.rank) * rows_per_rank;
+            const long long slot = ((long long)(tp_epoch & 1u) * tp.world + tp.rank) * rows_per_rank;
             cp = reinterpret_cast<__nv_bfloat16*>(tp.slots_peer[owner]) + (slot + (row0 - owner * rows_per_rank)) * p.ldc + col0;
           }
           if (staged) panel_store<PW>(sbuf, lane, f, cp, p.ldc, rows_valid, chunks_valid);
@@ -597,7 +600,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
       __threadfence();
       if (atomicAdd(tpp->done_ctr, 1u) == gridDim.x - 1) {
         *tpp->done_ctr = 0u;
-        peer_handshake(*tpp, 1, true, p.status);
+        peer_handshake(*tpp, tp_epoch, 1, true, p.status);
+        *tpp->epoch_ptr = tp_epoch;
       }
     }
   }
@@ -610,18 +614,19 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
       __threadfence_system();                                    // this CTA's peer stores are out
       if (atomicAdd(tp.done_ctr, 1u) == gridDim.x - 1) {
         *tp.done_ctr = 0u;
-        const bool ok = peer_handshake(tp, 1, true, p.status);   // every rank has stored all its partials
+        const bool ok = peer_handshake(tp, tp_epoch, 1, true, p.status);   // every rank has stored all its partials
         __threadfence();
-        if (ok) st_release_gpu_u32(tp.go, tp.epoch);
+        *tp.epoch_ptr = tp_epoch;                                   // every CTA has read the old value long ago
+        if (ok) st_release_gpu_u32(tp.go, tp_epoch);
       }
-      if (!wait_flag<false>(tp.go, tp.epoch, 2 * tp.wait_cycles, p.status, ST_TIMEOUT_PEER_FLAG)) s_go = 0;
+      if (!wait_flag<false>(tp.go, tp_epoch, 2 * tp.wait_cycles, p.status, ST_TIMEOUT_PEER_FLAG)) s_go = 0;
       __threadfence();
     }
     __syncthreads();
     if (s_go) {
       const long long rows_per_rank = (long long)tp.blocks_per_rank * BM;
       const long long n8 = rows_per_rank * p.N / 8;              // N % 8 == 0, ldc == N
-      const __nv_bfloat16* slots = reinterpret_cast<const __nv_bfloat16*>(tp.slots_peer[tp.rank]) + (long long)(tp.epoch & 1u) * tp.world * rows_per_rank * p.N;
+      const __nv_bfloat16* slots = reinterpret_cast<const __nv_bfloat16*>(tp.slots_peer[tp.rank]) + (long long)(tp_epoch & 1u) * tp.world * rows_per_rank * p.N;
       const __nv_bfloat16* res = reinterpret_cast<const __nv_bfloat16*>(p.residual);
       __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(tp.out);
       for (long long i = (long long)blockIdx.x * GEMM_THREADS + threadIdx.x; i < n8; i += (long long)gridDim.x * GEMM_THREADS) {

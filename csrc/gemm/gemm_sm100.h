@@ -42,7 +42,7 @@ constexpr int TP_MAX_WORLD = 8;
 struct TpParams {
   int mode, rank, world, copy_ctas;
   int blocks_per_rank;               // row blocks of 128 rows per rank (M / world / 128)
-  uint32_t epoch;                    // strictly increasing per call (flags compare >=)
+  uint32_t* epoch_ptr;               // local device word: calls so far on this context; the call uses *epoch_ptr + 1 and stores it back
   long long wait_cycles;             // clock64 budget of one wait
   // TP_AG_GEMM
   void* stage_peer[TP_MAX_WORLD];    // every rank's staging buffer [M, K] bf16 (peer-mapped); rank r fills rows r*M/world.. of

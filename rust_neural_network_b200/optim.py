@@ -131,8 +131,57 @@ class Optimizer:
     def state_tensors(self) -> dict:
         return {"step": self.step_t}
 
+    def snapshot_tensors(self) -> list:
+        """Every tensor a step changes (weights, shadows, optimizer state): what `Trainer.capture` saves before its
+        warm-up steps and restores after them."""
+        flat = getattr(self, "flat", None)
+        ts = []
+        if flat is not None:
+            ts.append(flat.master)
+            if flat.shadow is not None:
+                ts.append(flat.shadow)
+        return ts + [t for t in self.state_tensors().values() if isinstance(t, torch.Tensor)]
+
     def step(self):
         raise NotImplementedError
+
+
+class MultiOptimizer(Optimizer):
+    """Several optimizers stepped as one (e.g. a tensor-parallel model: a sharded data-parallel optimizer for the
+    replicated parameters next to a local one for the parameters each rank owns outright)."""
+
+    def __init__(self, optimizers: Sequence[Optimizer]):
+        self.opts = list(optimizers)
+        self.params = [p for o in self.opts for p in o.params]
+        self.flat = None
+        self.lr = self.opts[0].lr
+
+    def zero_grad(self):
+        for o in self.opts:
+            o.zero_grad()
+
+    def step(self):
+        for o in self.opts:
+            o.step()
+
+    def set_lr(self, lr: float):
+        self.lr = float(lr)
+        for o in self.opts:
+            o.set_lr(lr)
+
+    def clip_grad_norm(self, max_norm: float):
+        raise NotImplementedError("a global norm across several optimizers is not implemented")
+
+    def state_tensors(self) -> dict:
+        return {f"{k}@{j}": v for j, o in enumerate(self.opts) for k, v in o.state_tensors().items()}
+
+    def snapshot_tensors(self) -> list:
+        return [t for o in self.opts for t in o.snapshot_tensors()]
+
+    def prepare_checkpoint(self):
+        for o in self.opts:
+            if hasattr(o, "prepare_checkpoint"):
+                o.prepare_checkpoint()
 
 
 class SGD(Optimizer):

@@ -60,7 +60,7 @@ class DpFusedArgs(C.Structure):
         ("wait_cycles", C.c_longlong),
         ("seg_off", C.c_void_p), ("blk_seg", C.c_void_p), ("nseg", C.c_int), ("first_rep_seg", C.c_int),
         ("red_rep", C.c_void_p), ("rep_sumsq", C.c_void_p), ("clip_max_norm", C.c_float), ("norm_out", C.c_void_p),
-        ("bump_pass", C.c_int),
+        ("bump_pass", C.c_int), ("red_scale", C.c_float),
     ]
 
 
@@ -126,13 +126,15 @@ class _Bucket:
 
 
 class DistributedOptimizer(Optimizer):
-    """Shared machinery of the data-parallel optimizers. `rule` is "adam" or "muon"."""
+    """Shared machinery of the data-parallel optimizers. `rule` is "adam" or "muon". `average=False` SUMS the ranks'
+    gradients instead of averaging them: the setting for the replicated parameters of a tensor / sequence parallel
+    model, where every rank holds the gradient contribution of its own rows of one global batch."""
 
     def __init__(self, params, lr: float, rule: str, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0,
                  torch_compat: bool = False, momentum: float = 0.95, mode: str = "fused", group=None,
                  use_multimem: Optional[bool] = None, wait_seconds: float = 2.0, grid: int = 128,
                  groups: Optional[Sequence[Sequence[torch.Tensor]]] = None, bucket_mb: float = 32.0,
-                 max_grad_norm: Optional[float] = None, overlap_grid: int = 32):
+                 max_grad_norm: Optional[float] = None, overlap_grid: int = 32, average: bool = True):
         global _ACTIVE
         self.group = group or dist.group.WORLD
         self.world = dist.get_world_size(self.group)
@@ -145,6 +147,7 @@ class DistributedOptimizer(Optimizer):
         self.b1, self.b2 = (betas if rule == "adam" else (float(momentum), 0.0))
         self.eps, self.weight_decay, self.torch_compat = eps, weight_decay, torch_compat
         self.max_grad_norm = max_grad_norm
+        self.red_scale = 1.0 / self.world if average else 1.0
         if rule == "muon" and max_grad_norm is not None:
             raise ValueError("Muon normalises every tensor's gradient by its RMS; clipping has no effect on it")
 
@@ -271,6 +274,7 @@ class DistributedOptimizer(Optimizer):
         a.scale_mode = 0 if pass_id == 0 else (2 if self.rule == "muon" else 1)
         a.clip_max_norm = float(self.max_grad_norm) if self.max_grad_norm is not None else 0.0
         a.bump_pass = int(bump)
+        a.red_scale = self.red_scale
         nv.check(nv.cuda().b200_dp_fused_launch(C.byref(a), pass_id, grid, nv.stream_ptr()), "dp_fused_launch")
         nv.count_launch()
 
@@ -314,14 +318,14 @@ class DistributedOptimizer(Optimizer):
         g = self.flat.grad
         if self.world > 1:
             dist.all_reduce(g, group=self.group)
-        scale = torch.full((1,), 1.0 / self.world, dtype=torch.float32, device=g.device)
+        scale = torch.full((1,), self.red_scale, dtype=torch.float32, device=g.device)
         if self.grad_scale is not None:
             scale = scale * self.grad_scale
         if self.max_grad_norm is not None:
             # norm of the AVERAGED gradient (src/distributed.rs:507-523 clips after averaging)
             self._scalars.zero_()
             K.reduce_all(g, "sumsq", out=self._scalars[0:1])
-            self._scalars[0:1].mul_(1.0 / (self.world * self.world))
+            self._scalars[0:1].mul_(self.red_scale * self.red_scale)
             K.clip_coef(self._scalars, self.max_grad_norm)
             scale = scale * self._scalars[1:2]
         if self.rule == "adam":

@@ -24,7 +24,7 @@ SX_MAX_WORLD, SX_MAX_CTAS = 8, 64
 class StateExchangeArgs(C.Structure):
     _fields_ = [("slot", C.c_void_p * SX_MAX_WORLD), ("flags", C.c_void_p * SX_MAX_WORLD), ("inp", C.c_void_p), ("out", C.c_void_p),
                 ("numel", C.c_longlong), ("rank", C.c_int), ("world", C.c_int), ("mode", C.c_int), ("epoch", C.c_uint32),
-                ("wait_cycles", C.c_longlong), ("status", C.c_void_p)]
+                ("wait_cycles", C.c_longlong), ("status", C.c_void_p), ("words", C.c_void_p)]
 
 
 nv.register_sigs({"b200_state_exchange": [C.POINTER(StateExchangeArgs), C.c_int, C.c_void_p], "b200_state_exchange_flag_words": []})
@@ -51,12 +51,12 @@ class SPContext:
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.backend = backend if self.device.type == "cuda" else "nccl"
         self.max_numel = (max_numel + 3) // 4 * 4
-        self.epoch = 0
         self.grid = min(grid, SX_MAX_CTAS)
         if self.backend == "fused":
             from .ddp import SymmetricBuffer
             self.slot = SymmetricBuffer(self.max_numel, torch.float32, self.device, self.group)
             self.flags = SymmetricBuffer(2 * SX_MAX_WORLD * SX_MAX_CTAS, torch.int32, self.device, self.group)
+            self.words = torch.zeros(4, dtype=torch.int32, device=self.device)     # call epoch + retired-CTA counter, on the device
             self.wait_cycles = int(wait_seconds * torch.cuda.get_device_properties(self.device).clock_rate * 1000)
             dist.barrier(self.group)
             torch.cuda.synchronize()
@@ -75,12 +75,12 @@ class SPContext:
         if n > self.max_numel or n % 4 != 0:
             raise ValueError(f"state of {n} elements does not fit this context ({self.max_numel}) or is not a multiple of 4")
         out = torch.empty_like(t)
-        self.epoch += 1
         a = StateExchangeArgs()
         for r in range(self.world):
             a.slot[r], a.flags[r] = self.slot.ptrs[r], self.flags.ptrs[r]
         a.inp, a.out, a.numel = t.data_ptr(), out.data_ptr(), n
-        a.rank, a.world, a.mode, a.epoch, a.wait_cycles = self.rank, self.world, mode, self.epoch, self.wait_cycles
+        a.rank, a.world, a.mode, a.epoch, a.wait_cycles = self.rank, self.world, mode, 0, self.wait_cycles
+        a.words = self.words.data_ptr()
         a.status = nv.status_word(self.device).data_ptr()
         nv.check(nv.cuda().b200_state_exchange(C.byref(a), self.grid, nv.stream_ptr()), "state_exchange")
         nv.count_launch()

@@ -35,21 +35,31 @@ BM = 128
 class TpParams(C.Structure):
     _fields_ = [
         ("mode", C.c_int), ("rank", C.c_int), ("world", C.c_int), ("copy_ctas", C.c_int),
-        ("blocks_per_rank", C.c_int), ("epoch", C.c_uint32), ("wait_cycles", C.c_longlong),
+        ("blocks_per_rank", C.c_int), ("epoch_ptr", C.c_void_p), ("wait_cycles", C.c_longlong),
         ("stage_peer", C.c_void_p * TP_MAX_WORLD), ("ready_peer", C.c_void_p * TP_MAX_WORLD),
         ("slots_peer", C.c_void_p * TP_MAX_WORLD), ("out", C.c_void_p), ("go", C.c_void_p),
         ("flags", C.c_void_p * TP_MAX_WORLD), ("done_ctr", C.c_void_p),
     ]
 
 
-nv.register_sigs({"b200_gemm_tp_launch": [C.POINTER(nv.GemmArgs), C.POINTER(TpParams), C.c_int, C.c_int, C.c_void_p]})
+AR_MAX_WORLD, AR_MAX_CTAS = 8, 64
+
+
+class AllReduceArgs(C.Structure):
+    _fields_ = [("in_sym", C.c_void_p * AR_MAX_WORLD), ("red_sym", C.c_void_p * AR_MAX_WORLD), ("flags", C.c_void_p * AR_MAX_WORLD),
+                ("inp", C.c_void_p), ("out", C.c_void_p), ("numel", C.c_longlong), ("rank", C.c_int), ("world", C.c_int),
+                ("in_bf16", C.c_int), ("wait_cycles", C.c_longlong), ("status", C.c_void_p), ("words", C.c_void_p)]
+
+
+nv.register_sigs({"b200_gemm_tp_launch": [C.POINTER(nv.GemmArgs), C.POINTER(TpParams), C.c_int, C.c_int, C.c_void_p],
+                  "b200_allreduce_bf16": [C.POINTER(AllReduceArgs), C.c_int, C.c_void_p]})
 
 
 class TPContext:
     """Symmetric buffers and flags of one tensor-parallel group, sized for the largest call it will serve."""
 
     def __init__(self, max_rows: int, max_k: int, max_n: int, device=None, group=None, backend: str = "fused",
-                 wait_seconds: float = 2.0, copy_ctas: int = 0):
+                 wait_seconds: float = 2.0, copy_ctas: int = 0, max_allreduce_numel: int = 0):
         self.group = group or dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
@@ -58,7 +68,6 @@ class TPContext:
         # gather CTAs of the all-gather -> GEMM kernel: 32 of the 148 measured best on 2 GPUs; with more ranks the per-rank GEMM
         # shrinks and the push grows, so more CTAs push
         self.copy_ctas = copy_ctas if copy_ctas > 0 else (32 if self.world <= 2 else 64)
-        self.epoch = 0
         if self.backend == "fused":
             from .ddp import SymmetricBuffer
             if max_rows % (self.world * BM) != 0:
@@ -71,7 +80,21 @@ class TPContext:
             self.ag_calls = 0
             self.slots = SymmetricBuffer(2 * self.world * self.rows_per_rank * max_n, torch.bfloat16, dev, self.group)
             self.flags = SymmetricBuffer(2 * TP_MAX_WORLD + max_rows // BM, torch.int32, dev, self.group)   # handshake words, then ready[m_blocks]
-            self.local = torch.zeros(8, dtype=torch.int32, device=dev)                                       # go, done_ctr
+            # go, done_ctr, call epoch. The epoch is a DEVICE word that each call's last CTA advances, so a captured launch
+            # replays with a fresh epoch; it is shared by both kernels. Reuse rules of the buffers:
+            #  * gather staging: an all-gather call ends with a cross-rank handshake ("my GEMM no longer reads my staging
+            #    copy"), so when it returns every rank may be pushed into again. The two halves exist only so that the
+            #    gathered rows of a call stay readable for the weight-gradient GEMM until the call after the next one.
+            #  * reduce-scatter slots: selected by epoch & 1. Two reduce-scatter calls in a row get different halves; with
+            #    any call in between, that call's handshake orders the second store after the first sum. A rank can be at
+            #    most one call ahead of its slowest peer, because every call waits for all ranks' flags of that epoch.
+            self.local = torch.zeros(8, dtype=torch.int32, device=dev)
+            self.ar_numel = (max_allreduce_numel + 63) // 64 * 64
+            if self.ar_numel:
+                self.ar_in = SymmetricBuffer(self.ar_numel, torch.float32, dev, self.group)
+                self.ar_red = SymmetricBuffer(self.ar_numel, torch.bfloat16, dev, self.group)
+                self.ar_flags = SymmetricBuffer(3 * AR_MAX_WORLD * AR_MAX_CTAS, torch.int32, dev, self.group)
+                self.ar_words = torch.zeros(4, dtype=torch.int32, device=dev)
             self.clock_hz = torch.cuda.get_device_properties(dev).clock_rate * 1000
             self.wait_cycles = int(wait_seconds * self.clock_hz)
             self.sms = torch.cuda.get_device_properties(dev).multi_processor_count
@@ -92,12 +115,11 @@ class TPContext:
         return self.stage.tensor[off: off + m * k].view(m, k)
 
     def _tp(self, mode: int, rows_local: int) -> TpParams:
-        self.epoch += 1
         tp = TpParams()
         tp.mode, tp.rank, tp.world = mode, self.rank, self.world
         tp.copy_ctas = self.copy_ctas if (mode == TP_AG_GEMM and self.world > 1) else 0
         tp.blocks_per_rank = rows_local // BM
-        tp.epoch, tp.wait_cycles = self.epoch, self.wait_cycles
+        tp.epoch_ptr, tp.wait_cycles = self.local.data_ptr() + 8, self.wait_cycles
         tp.go = self.local.data_ptr()
         tp.done_ctr = self.local.data_ptr() + 4
         for r in range(self.world):
@@ -171,6 +193,35 @@ class TPContext:
             residual = residual.to(torch.bfloat16).contiguous()
         dummy = torch.empty(0, dtype=torch.bfloat16, device=self.device)
         self._launch(tp, x.contiguous(), w, m, n, k, dummy, bias if self.rank == 0 else None, "none", residual, None)
+        return out
+
+    # ------------------------------------------------------------------ small all-reduce (replicated activations)
+    def all_reduce(self, part: torch.Tensor) -> torch.Tensor:
+        """Sum of `part` (fp32 or bf16, same shape on every rank) over the group, as bf16. One two-shot kernel over peer
+        memory (csrc/comm/allreduce.cu); every rank receives identical bits."""
+        if self.backend != "fused":
+            t = part.float().contiguous()
+            if self.world > 1:
+                t = t.clone()
+                dist.all_reduce(t, group=self.group)
+            return t.to(torch.bfloat16)
+        n = part.numel()
+        if n > self.ar_numel or n % (8 * self.world) != 0:
+            raise ValueError(f"all_reduce of {n} elements: the context holds {self.ar_numel} and needs a multiple of {8 * self.world}")
+        if part.dtype not in (torch.float32, torch.bfloat16):
+            part = part.float()
+        part = part.contiguous()
+        out = torch.empty(part.shape, dtype=torch.bfloat16, device=self.device)
+        a = AllReduceArgs()
+        for r in range(self.world):
+            a.in_sym[r], a.red_sym[r], a.flags[r] = self.ar_in.ptrs[r], self.ar_red.ptrs[r], self.ar_flags.ptrs[r]
+        a.inp, a.out, a.numel = part.data_ptr(), out.data_ptr(), n
+        a.rank, a.world, a.in_bf16 = self.rank, self.world, int(part.dtype == torch.bfloat16)
+        a.wait_cycles, a.status, a.words = self.wait_cycles, nv.status_word(self.device).data_ptr(), self.ar_words.data_ptr()
+        grid = max(1, min(AR_MAX_CTAS, n // (8 * self.world * 512)))
+        nv.check(nv.cuda().b200_allreduce_bf16(C.byref(a), grid, nv.stream_ptr()), "allreduce_bf16")
+        nv.count_launch()
+        self._keep_ar = (part, out)
         return out
 
     def _launch(self, tp, a, b, m, n, k, out, bias, act, residual, aux):
@@ -260,6 +311,56 @@ class _RowParallelFn(torch.autograd.Function):
         dw = G.gemm(dzg, h, a_mn=True, b_mn=True, out_dtype=torch.float32)                  # [N, K_local]
         db = K.colsum(dzg).to(b.dtype) if b.numel() > 0 else None                           # replicated bias: every rank sums all rows
         return dh, dw.to(w.dtype), db, (dz if ctx.has_res else None), None
+
+
+class _RowParallelAllReduceFn(torch.autograd.Function):
+    """y = all_reduce(h W_s^T): row-parallel Linear whose (narrow) output every rank needs in full. The backward
+    all-reduces the incoming gradient, because every rank consumed y in its own computation."""
+
+    @staticmethod
+    def forward(ctx, h, w, tpc):
+        from ..ops.functional import compute_weight
+        part = G.gemm(h, compute_weight(w, h), out_dtype=torch.float32)
+        ctx.save_for_backward(h, w)
+        ctx.tpc = tpc
+        return tpc.all_reduce(part)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops.functional import _wgrad, compute_weight
+        h, w = ctx.saved_tensors
+        g = ctx.tpc.all_reduce(dy.contiguous())
+        dh = G.gemm(g, compute_weight(w, g), b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = _wgrad(g, h, w) if ctx.needs_input_grad[1] else None
+        return dh, dw, None
+
+
+def row_parallel_all_reduce(h: torch.Tensor, w: torch.Tensor, tpc: "TPContext") -> torch.Tensor:
+    return _RowParallelAllReduceFn.apply(h, w, tpc)
+
+
+def column_parallel(x_shard, w, b, tpc, act="none"):
+    return _ColumnParallelFn.apply(x_shard, w, b, tpc, act)
+
+
+def row_parallel(h, w, b, residual, tpc):
+    return _RowParallelFn.apply(h, w, b, residual, tpc)
+
+
+class _ScaleGradFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, s):
+        ctx.s = s
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g * ctx.s, None
+
+
+def scale_grad(x: torch.Tensor, s: float) -> torch.Tensor:
+    """Identity whose backward multiplies the gradient by `s` (a rank's share of a loss that is a mean over ranks)."""
+    return _ScaleGradFn.apply(x, s)
 
 
 class ColumnParallelLinear:

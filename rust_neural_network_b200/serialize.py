@@ -142,14 +142,15 @@ def read_file(path: str) -> bytes:
     return out[:size].tobytes()
 
 
-def save_checkpoint(path: str, model, optimizer=None, extra: Dict[str, torch.Tensor] | None = None, write_rank: int = 0) -> None:
+def save_checkpoint(path: str, model, optimizer=None, extra: Dict[str, torch.Tensor] | None = None, write_rank: int | None = 0) -> None:
     """Weights to `path` (reference-loadable); optimizer state / step / extras to `path + '.opt'`.
     With a sharded data-parallel optimizer this is a collective: every rank calls it (`prepare_checkpoint`
-    all-gathers the master weights and moments) and only `write_rank` (default: rank 0) writes the files."""
+    all-gathers the master weights and moments) and only `write_rank` (default: rank 0) writes the files;
+    `write_rank=None` lets every rank write (tensor-parallel models: each rank saves its own shards to its own path)."""
     if optimizer is not None and hasattr(optimizer, "prepare_checkpoint"):
         optimizer.prepare_checkpoint()
         import torch.distributed as dist
-        if dist.is_initialized() and dist.get_rank(getattr(optimizer, "group", None)) != write_rank:
+        if write_rank is not None and dist.is_initialized() and dist.get_rank(getattr(optimizer, "group", None)) != write_rank:
             return
     write_file(path, save_model(model))
     if optimizer is not None or extra:
@@ -165,16 +166,19 @@ def _optimizer_named(model, optimizer):
     """Optimizer state as named tensors. State vectors that span the optimizer's flat parameter space are cut into one
     tensor per model parameter (`__opt__.m.param_3`, in `model.parameters()` order), so a file does not depend on how an
     optimizer lays its buffers out (a sharded data-parallel optimizer orders them differently from a local one)."""
-    flat = getattr(optimizer, "flat", None)
     out = []
-    for k, v in optimizer.state_tensors().items():
-        if flat is not None and v.dim() == 1 and v.numel() == flat.numel:
-            for i, p in enumerate(model.parameters()):
-                o = flat.offsets.get(id(p))
-                if o is not None:
-                    out.append((f"__opt__.{k}.param_{i}", v[o:o + p.numel()].view(p.shape)))
-        else:
-            out.append((f"__opt__.{k}", v))
+    subs = getattr(optimizer, "opts", None)
+    for j, opt in enumerate(subs if subs is not None else [optimizer]):
+        flat = getattr(opt, "flat", None)
+        tag = f"@{j}" if subs is not None else ""
+        for k, v in opt.state_tensors().items():
+            if flat is not None and v.dim() == 1 and v.numel() == flat.numel:
+                for i, p in enumerate(model.parameters()):
+                    o = flat.offsets.get(id(p))
+                    if o is not None:
+                        out.append((f"__opt__.{k}.param_{i}", v[o:o + p.numel()].view(p.shape)))
+            else:
+                out.append((f"__opt__.{k}{tag}", v))
     return out
 
 
@@ -183,19 +187,21 @@ def load_checkpoint(path: str, model, optimizer=None) -> Dict[str, torch.Tensor]
     extra = {}
     import os
     if os.path.exists(str(path) + ".opt"):
+        subs = getattr(optimizer, "opts", None) or ([optimizer] if optimizer is not None else [])
         state = optimizer.state_tensors() if optimizer is not None else {}
-        flat = getattr(optimizer, "flat", None)
         params = list(model.parameters())
         for name, t in deserialize(read_file(str(path) + ".opt"), requires_grad=False):
             if name.startswith("__opt__.") and optimizer is not None:
                 key = name[len("__opt__."):]
                 dst = None
-                if ".param_" in key and flat is not None:
+                if ".param_" in key:
                     k, idx = key.rsplit(".param_", 1)
                     p = params[int(idx)] if int(idx) < len(params) else None
-                    o = flat.offsets.get(id(p)) if p is not None else None
-                    if k in state and o is not None:
-                        dst = state[k][o:o + p.numel()]
+                    for opt in subs:                      # the optimizer that owns this parameter
+                        flat = getattr(opt, "flat", None)
+                        o = flat.offsets.get(id(p)) if (flat is not None and p is not None) else None
+                        if o is not None and k in opt.state_tensors():
+                            dst = opt.state_tensors()[k][o:o + p.numel()]
                 else:
                     dst = state.get(key)
                 if dst is not None:
@@ -203,9 +209,10 @@ def load_checkpoint(path: str, model, optimizer=None) -> Dict[str, torch.Tensor]
                         dst.copy_(t.to(dst.device).reshape(dst.shape))
             elif name.startswith("__extra__."):
                 extra[name[len("__extra__."):]] = t
-    if optimizer is not None and getattr(optimizer, "flat", None) is not None and optimizer.flat.shadow is not None:
-        with torch.no_grad():
-            optimizer.flat.shadow.copy_(optimizer.flat.master)
+    for opt in (getattr(optimizer, "opts", None) or ([optimizer] if optimizer is not None else [])):
+        if getattr(opt, "flat", None) is not None and opt.flat.shadow is not None:
+            with torch.no_grad():
+                opt.flat.shadow.copy_(opt.flat.master)
     return extra
 
 

@@ -77,11 +77,9 @@ class Trainer:
         self._static = (torch.empty_like(x, device=dev), torch.empty_like(y, device=dev))
         self._static[0].copy_(x); self._static[1].copy_(y)
         # the warm-up steps below must not count as training: snapshot weights and optimizer state, restore after
-        flat = getattr(self.optimizer, "flat", None)
         snap = []
-        if flat is not None and hasattr(self.optimizer, "state_tensors"):
-            live = [flat.master] + ([flat.shadow] if getattr(flat, "shadow", None) is not None else []) + list(self.optimizer.state_tensors().values())
-            snap = [(t, t.clone()) for t in live if isinstance(t, torch.Tensor)]
+        if hasattr(self.optimizer, "snapshot_tensors"):
+            snap = [(t, t.clone()) for t in self.optimizer.snapshot_tensors()]
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):

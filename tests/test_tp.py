@@ -151,3 +151,41 @@ def test_tensor_parallel_mlp_autograd_two_gloo_ranks():
         assert p.exitcode == 0
     for _, errs in res:
         assert max(errs) < 6e-2, errs          # outputs of the baseline path are rounded to bf16; values are O(1..5)
+
+
+# ------------------------------------------------------------------------------------------------ model level
+MODEL_WORKER = str(Path(__file__).resolve().parent / "par_model_worker.py")
+
+
+def _run_model(nproc, extra, port, timeout=900):
+    env = dict(os.environ)
+    env.update({"MASTER_ADDR": "127.0.0.1", "OMP_NUM_THREADS": "2", "NCCL_NVLS_ENABLE": "0"})
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), MODEL_WORKER] + extra
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith('{"ranks"')][-1]
+    return json.loads(line)["ranks"]
+
+
+def _check_model(r0, key, grad_tol, loss_tol):
+    for k, v in r0["grad_rel_err"].items():
+        assert v < grad_tol, (k, v)
+    for a, b in zip(r0[key], r0["ref_losses"]):
+        assert abs(a - b) < loss_tol, (r0[key], r0["ref_losses"])
+    assert r0["ref_losses"][-1] < r0["ref_losses"][0]
+
+
+def test_tensor_parallel_mamba_lm_two_gloo_ranks():
+    """Channel-sharded Mamba blocks on row-sharded activations against the whole model in one process: gradients of
+    sharded and of replicated parameters, and the loss over three optimizer steps."""
+    r0 = _run_model(2, ["--model", "mamba_tp", "--device", "cpu"], 29661)[0]
+    _check_model(r0, "tp_losses", 2e-2, 2e-3)
+
+
+@pytest.mark.gpu
+def test_tensor_parallel_mamba_lm_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    r0 = _run_model(2, ["--model", "mamba_tp", "--device", "cuda", "--backend", "fused"], 29662)[0]
+    _check_model(r0, "tp_losses", 6e-2, 3e-2)

@@ -3,6 +3,10 @@
     python bench_configs.py mlp                     784-256-128-10 MLP, fp32/TF32, batch 32, Adam, CUDA-graph step
     python bench_configs.py moe_lm   [--batch B]    FineGrainedMoE transformer LM (64 routed top-6 + 2 shared)
     python bench_configs.py mamba_lm [--batch B]    Mamba (S6) LM, d 2048, 24 layers, seq 4096
+    python -m torch.distributed.run --nproc-per-node N ... bench_configs.py moe_lm      expert parallel, 64/N experts per GPU
+    python -m torch.distributed.run --nproc-per-node N ... bench_configs.py mamba_lm    N-way tensor parallel
+        add --impl torch for the NCCL + cuBLAS library arm of either, --comm nccl for this package's kernels with NCCL
+        calls instead of the fused communication kernels
     python bench_configs.py attention --seq 4096 --head-dim 64      forward+backward: flash vs causal linear attention
     python -m torch.distributed.run --nproc-per-node 8 ... bench_configs.py attention_sp --seq 65536
                                                     sequence-parallel causal linear attention (KV-state exchange kernel)
@@ -27,49 +31,32 @@ def _events():
     return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
 
-def run_lm(name, args):
+def _setup_dist():
     import torch.distributed as dist
-    from rust_neural_network_b200 import _native as nv
-    from rust_neural_network_b200.config import PRESETS, build_model
-    from rust_neural_network_b200.optim import Adam
-    from rust_neural_network_b200.train import Trainer
-
     world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", "1"), ("RANK", "0"), ("LOCAL_RANK", "0")))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
-    over = {}
-    if args.layers:
-        over["layers"] = args.layers
-    if args.seq:
-        over["seq_len"] = args.seq
-    torch.manual_seed(1234)
-    model, cfg = build_model(name, dev, **over)
-    batch = args.batch or cfg.batch_per_gpu
-    if world > 1:
-        from rust_neural_network_b200.parallel.ddp import DistributedAdam
-        opt = DistributedAdam(model.parameters(), lr=1e-3)
-    else:
-        opt = Adam(model.parameters(), lr=1e-3)
-    tr = Trainer(model, opt, loss_fn=None, use_cuda_graph=not args.no_graph)
-    g = torch.Generator().manual_seed(1000 + rank)
-    ids = [torch.randint(0, cfg.vocab, (batch, cfg.seq_len), generator=g).pin_memory() for _ in range(2)]
-    lab = [torch.randint(0, cfg.vocab, (batch, cfg.seq_len), generator=g).pin_memory() for _ in range(2)]
+    return world, rank, dev
+
+
+def _time_steps(step, args, world, dev):
+    """>= 3 warm-up steps, then `args.steps` steps between CUDA events; max over ranks. Returns (ms, first loss, last loss)."""
+    import torch.distributed as dist
     first = None
     for i in range(max(args.warmup, 3)):
-        l = tr.train_step(ids[i % 2], lab[i % 2])
+        l = step(i)
         first = float(l) if first is None else first
     torch.cuda.synchronize()
-    nv.check_status()
     if world > 1:
         dist.barrier()
     e0, e1 = _events()
     e0.record()
     last = 0.0
     for i in range(args.steps):
-        last = float(tr.train_step(ids[i % 2], lab[i % 2]).item())
+        last = float(step(i).item())
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
@@ -77,16 +64,107 @@ def run_lm(name, args):
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    return ms, first, last
+
+
+def run_lm(name, args):
+    """b200 arm: this package's kernels. `--parallel` picks the layout for N > 1: `tp` (Mamba: channel-sharded blocks on
+    row-sharded activations, fused all-gather->GEMM / GEMM->reduce-scatter / all-reduce kernels), `ep` (MoE: experts
+    sharded over the ranks, peer-memory dispatch / combine, data-parallel shared parameters), `dp` (plain data parallel).
+    `--comm nccl` keeps the package's kernels but replaces the fused communication kernels by NCCL calls."""
+    import torch.distributed as dist
+    from rust_neural_network_b200 import _native as nv
+    from rust_neural_network_b200.config import PRESETS, build_model
+    from rust_neural_network_b200.optim import Adam
+    from rust_neural_network_b200.train import Trainer
+
+    world, rank, dev = _setup_dist()
+    over = {}
+    if args.layers:
+        over["layers"] = args.layers
+    if args.seq:
+        over["seq_len"] = args.seq
+    cfg = dataclasses.replace(PRESETS[name], **over)
+    batch = args.batch or cfg.batch_per_gpu
+    par = args.parallel if args.parallel != "auto" else (cfg.parallelism if world > 1 else "none")
+    if world == 1:
+        par = "none"
+    torch.manual_seed(1234)
+    extra = {}
+    if par == "tp":
+        from rust_neural_network_b200.parallel.tp import TPContext
+        M = world * batch * cfg.seq_len
+        extra["tp"] = TPContext(M, cfg.d_model, cfg.d_model, device=dev, backend="fused" if args.comm == "fused" else "nccl",
+                                max_allreduce_numel=M * (cfg.dt_rank + 2 * cfg.d_state))
+    elif par == "ep":
+        extra["ep_group"] = dist.group.WORLD
+        extra["ep_backend"] = args.comm
+    model, cfg = build_model(name, dev, **over, **extra)
+    if par in ("tp", "ep"):
+        opt = model.make_optimizer(lr=1e-3) if par == "tp" else model.make_optimizer(lr=1e-3, mode=args.comm)
+    elif world > 1:
+        from rust_neural_network_b200.parallel.ddp import DistributedAdam
+        groups = model.dp_groups() if (args.buckets and hasattr(model, "dp_groups")) else None
+        opt = DistributedAdam(model.parameters(), lr=1e-3, mode=args.comm, groups=groups)
+    else:
+        opt = Adam(model.parameters(), lr=1e-3)
+    graph = not args.no_graph and not (par == "ep" and args.comm == "nccl")     # host-side split sizes cannot be captured
+    tr = Trainer(model, opt, loss_fn=None, use_cuda_graph=graph)
+    g = torch.Generator().manual_seed(1000 + rank)
+    ids = [torch.randint(0, cfg.vocab, (batch, cfg.seq_len), generator=g).pin_memory() for _ in range(2)]
+    lab = [torch.randint(0, cfg.vocab, (batch, cfg.seq_len), generator=g).pin_memory() for _ in range(2)]
+    ms, first, last = _time_steps(lambda i: tr.train_step(ids[i % 2], lab[i % 2]), args, world, dev)
     nv.check_status()
     n_params = sum(p.numel() for p in model.parameters())
     if rank == 0:
-        print(json.dumps({"config": name, "impl": "b200", "n_gpus": world, "batch_per_gpu": batch, "seq_len": cfg.seq_len,
-                          "preset": dataclasses.asdict(cfg), "params": n_params, "ms_per_step": ms,
+        print(json.dumps({"config": name, "impl": "b200", "comm": args.comm, "parallel": par, "n_gpus": world, "batch_per_gpu": batch,
+                          "seq_len": cfg.seq_len, "preset": dataclasses.asdict(cfg), "params_per_rank": n_params, "ms_per_step": ms,
                           "tokens_per_s": world * batch * cfg.seq_len / ms * 1e3, "end_to_end": True, "cuda_graph": tr._graph is not None,
                           "launches_per_step": getattr(tr, "launches_per_step", None), "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
                           "loss_first": first, "loss_last": last}), flush=True)
     if world > 1:
         tr._graph = None
+        sys.stdout.flush()
+        os._exit(0)
+
+
+def run_lm_torch(name, args):
+    """Library arm of the MoE / Mamba configurations (baseline/torch_moe.py, baseline/torch_mamba.py): NCCL collectives
+    around cuBLAS GEMMs, stock PyTorch everywhere it has the op. Same shapes, precision policy and timing rules."""
+    import torch.distributed as dist
+    from rust_neural_network_b200.config import PRESETS
+
+    world, rank, dev = _setup_dist()
+    over = {}
+    if args.layers:
+        over["layers"] = args.layers
+    if args.seq:
+        over["seq_len"] = args.seq
+    cfg = dataclasses.replace(PRESETS[name], **over)
+    batch = args.batch or cfg.batch_per_gpu
+    torch.manual_seed(1234)
+    group = dist.group.WORLD if world > 1 else None
+    if name == "moe_lm":
+        from baseline.torch_moe import TorchMoELM, TorchMoEStep
+        model = TorchMoELM(cfg.vocab, cfg.d_model, cfg.layers, cfg.heads, cfg.num_experts, cfg.top_k, cfg.num_shared, cfg.expert_hidden,
+                           cfg.seq_len, world, rank, group).to(dev)
+        stepper = TorchMoEStep(model, world, group)
+        par = "ep" if world > 1 else "none"
+    else:
+        from baseline.torch_mamba import TorchMambaLM, TorchMambaStep
+        model = TorchMambaLM(cfg.vocab, cfg.d_model, cfg.layers, cfg.d_state, cfg.d_conv, cfg.expand, cfg.dt_rank, world, rank, group).to(dev)
+        stepper = TorchMambaStep(model, world, group)
+        par = "tp" if world > 1 else "none"
+    g = torch.Generator().manual_seed(1000 + rank)
+    ids = [torch.randint(0, cfg.vocab, (batch, cfg.seq_len), generator=g).pin_memory() for _ in range(2)]
+    lab = [torch.randint(0, cfg.vocab, (batch, cfg.seq_len), generator=g).pin_memory() for _ in range(2)]
+    ms, first, last = _time_steps(lambda i: stepper.step(ids[i % 2].to(dev, non_blocking=True), lab[i % 2].to(dev, non_blocking=True)), args, world, dev)
+    if rank == 0:
+        print(json.dumps({"config": name, "impl": "torch", "comm": "nccl", "parallel": par, "n_gpus": world, "batch_per_gpu": batch,
+                          "seq_len": cfg.seq_len, "params_per_rank": sum(p.numel() for p in model.parameters()), "ms_per_step": ms,
+                          "tokens_per_s": world * batch * cfg.seq_len / ms * 1e3, "end_to_end": True, "cuda_graph": False,
+                          "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30, "loss_first": first, "loss_last": last}), flush=True)
+    if world > 1:
         sys.stdout.flush()
         os._exit(0)
 
@@ -208,6 +286,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--impl", default="b200", choices=["b200", "torch"], help="torch: the NCCL + cuBLAS library arm (moe_lm, mamba_lm)")
+    ap.add_argument("--parallel", default="auto", choices=["auto", "dp", "tp", "ep"], help="layout for N > 1 (auto: the preset's)")
+    ap.add_argument("--comm", default="fused", choices=["fused", "nccl"], help="b200 arm: fused peer-memory kernels or NCCL calls")
+    ap.add_argument("--buckets", action="store_true", help="dp: bucketed gradient reduction overlapped with backward")
     args = ap.parse_args()
     if args.config == "mlp":
         run_mlp(args)
@@ -215,6 +297,8 @@ def main():
         run_attention(args)
     elif args.config == "attention_sp":
         run_attention_sp(args)
+    elif args.impl == "torch":
+        run_lm_torch(args.config, args)
     else:
         run_lm(args.config, args)
     return 0

@@ -242,6 +242,40 @@ __global__ void gather_sum_kernel(MoeRead tab, const int* __restrict__ dest, __n
   }
 }
 
+// Cross-rank barrier on the stream: everything this rank launched before it is complete and visible to the peers
+// once they leave it, and nothing launched after it starts before every rank has arrived. Replaces a host barrier
+// between the dispatch / expert-GEMM / combine phases, so an expert-parallel step can be captured into a CUDA graph.
+// The epoch is a device word bumped here (one thread block, one launch at a time per context).
+struct EpBarrierArgs {
+  uint32_t* flags[MOE_MAX_RANKS];   // every rank's flag words [MOE_MAX_RANKS] (peer-mapped): slot r is written by rank r
+  uint32_t* words;                  // local: [0] barriers passed so far
+  int rank, world;
+  long long wait_cycles;
+  uint32_t* status;
+};
+
+__global__ void ep_barrier_kernel(const EpBarrierArgs a) {
+  const uint32_t epoch = a.words[0] + 1u;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < a.world) {
+    const int peer = threadIdx.x;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.flags[peer] + a.rank), "r"(epoch) : "memory");
+    const long long t0 = clock64();
+    for (;;) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.flags[a.rank] + peer) : "memory");
+      if ((int32_t)(v - epoch) >= 0) break;
+      if (clock64() - t0 > a.wait_cycles) { s_ok = 0; if (a.status) atomicCAS(a.status, 0u, 5u); break; }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) { __threadfence_system(); a.words[0] = epoch; }
+}
+
 static inline unsigned warps_grid(long long warps) { return (unsigned)((warps * 32 + 255) / 256); }
 
 }  // namespace b200
@@ -295,6 +329,15 @@ int b200_moe_combine_bwd(void* const* ybuf, void* const* dybuf, int world, const
   MoeRead yt; MoeWrite dt;
   for (int r = 0; r < world; ++r) { yt.ybuf[r] = ybuf[r]; dt.dybuf[r] = dybuf[r]; }
   combine_bwd_kernel<<<warps_grid(tokens * k), 256, 0, st>>>(yt, dt, dest, w, (const __nv_bfloat16*)dout, dw, tokens, k, d, rows_per_rank);
+  return (int)cudaGetLastError();
+}
+
+int b200_ep_barrier(uint32_t* const* flags, int world, int rank, uint32_t* words, long long wait_cycles, uint32_t* status, cudaStream_t st) {
+  if (world < 1 || world > MOE_MAX_RANKS || rank < 0 || rank >= world) return -1;
+  EpBarrierArgs a;
+  for (int r = 0; r < world; ++r) a.flags[r] = flags[r];
+  a.words = words; a.rank = rank; a.world = world; a.wait_cycles = wait_cycles; a.status = status;
+  ep_barrier_kernel<<<1, 32, 0, st>>>(a);
   return (int)cudaGetLastError();
 }
 

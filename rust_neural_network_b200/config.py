@@ -86,8 +86,9 @@ PRESETS: Dict[str, object] = {
 }
 
 
-def build_model(name: str, device="cuda", **overrides):
-    """Instantiates the model of a preset (bf16 compute on CUDA, fp32 on CPU). `overrides` replace preset fields."""
+def build_model(name: str, device="cuda", tp=None, ep_group=None, ep_backend: str = "fused", **overrides):
+    """Instantiates the model of a preset (bf16 compute on CUDA, fp32 on CPU). `overrides` replace preset fields.
+    `tp` (a `parallel.tp.TPContext`) builds the tensor-parallel Mamba LM, `ep_group` the expert-parallel MoE LM."""
     cfg = dataclasses.replace(PRESETS[name], **overrides)
     dev = torch.device(device)
     dt = torch.bfloat16 if dev.type == "cuda" else torch.float32
@@ -106,10 +107,11 @@ def build_model(name: str, device="cuda", **overrides):
         return m.to_device(dev, dt), cfg
     if name == "moe_lm":
         from .models.moe import MoETransformerLM
-        m = MoETransformerLM(cfg.vocab, cfg.d_model, cfg.layers, cfg.heads, cfg.num_experts, cfg.top_k, cfg.num_shared, cfg.expert_hidden, cfg.seq_len)
+        m = MoETransformerLM(cfg.vocab, cfg.d_model, cfg.layers, cfg.heads, cfg.num_experts, cfg.top_k, cfg.num_shared, cfg.expert_hidden, cfg.seq_len,
+                             ep_group=ep_group, ep_backend=ep_backend)
         return m.to_device(dev, dt), cfg
     if name == "mamba_lm":
         from .models.mamba import MambaLM
-        m = MambaLM(cfg.vocab, cfg.d_model, cfg.layers, d_state=cfg.d_state, d_conv=cfg.d_conv, expand=cfg.expand, dt_rank=cfg.dt_rank)
+        m = MambaLM(cfg.vocab, cfg.d_model, cfg.layers, d_state=cfg.d_state, d_conv=cfg.d_conv, expand=cfg.expand, dt_rank=cfg.dt_rank, tp=tp)
         return m.to_device(dev, dt), cfg
     raise KeyError(name)

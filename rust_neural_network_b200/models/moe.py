@@ -37,6 +37,7 @@ nv.register_sigs({
     "b200_moe_combine_fwd": [C.POINTER(_P), C.c_int, _P, _P, _P, C.c_longlong, C.c_int, C.c_int, C.c_longlong, _P],
     "b200_moe_combine_bwd": [C.POINTER(_P), C.POINTER(_P), C.c_int, _P, _P, _P, _P, C.c_longlong, C.c_int, C.c_int, C.c_longlong, _P],
     "b200_moe_gather_sum": [C.POINTER(_P), C.c_int, _P, _P, C.c_longlong, C.c_int, C.c_int, C.c_longlong, _P],
+    "b200_ep_barrier": [C.POINTER(_P), C.c_int, C.c_int, _P, C.c_longlong, _P, _P],
 })
 
 
@@ -111,37 +112,73 @@ class RouterFn(Function):
 
 # ----------------------------------------------------------------------------- dispatch / experts / combine
 class EPContext:
-    """Symmetric (peer-mapped) buffers of an expert-parallel group. `world == 1` needs no peers."""
+    """Symmetric (peer-mapped) buffers of an expert-parallel group. `world == 1` needs no peers.
 
-    def __init__(self, group=None):
+    The phases of a layer (dispatch -> expert GEMMs -> combine, and their adjoints) are separated by `barrier()`: with
+    `backend="fused"` a one-block kernel that exchanges epoch flags with every peer on the stream (bounded wait, status
+    word), so an expert-parallel step has no host synchronisation and can be captured into a CUDA graph;
+    `backend="nccl"` uses a host barrier (the baseline the device protocol replaced)."""
+
+    def __init__(self, group=None, backend: str = "fused", wait_seconds: float = 2.0):
         import torch.distributed as dist
         self.group = group
         self.world = dist.get_world_size(group) if group is not None else 1
         self.rank = dist.get_rank(group) if group is not None else 0
+        self.backend = backend
+        self.wait_seconds = wait_seconds
         self._bufs = {}
+        self._bar = None
+        self.clean = {}          # buffer key -> True while the buffer is known to be all zero on every rank
 
     def buffer(self, key, numel, dtype, device):
         """A zero-initialisable buffer mapped by every rank: returns (local tensor, [address on each rank])."""
         k = (key, numel, dtype)
         if k not in self._bufs:
             if self.world == 1:
-                t = torch.empty(numel, dtype=dtype, device=device)
+                t = torch.zeros(numel, dtype=dtype, device=device)
                 self._bufs[k] = (t, [t.data_ptr()])
             else:
                 from ..parallel.ddp import SymmetricBuffer
                 sb = SymmetricBuffer(numel, dtype, device, self.group)
                 self._bufs[k] = (sb.tensor, sb.ptrs, sb)
+            self.clean[k] = True
         e = self._bufs[k]
         return e[0], e[1]
 
-    def barrier(self):
-        if self.world > 1:
+    def barrier(self, device=None):
+        if self.world == 1:
+            return
+        if self.backend != "fused":
+            import torch.distributed as dist
+            torch.cuda.current_stream().synchronize()
+            dist.barrier(self.group)
+            return
+        if self._bar is None:
+            from ..parallel.ddp import SymmetricBuffer
+            flags = SymmetricBuffer(64, torch.int32, device, self.group)
+            words = torch.zeros(4, dtype=torch.int32, device=device)
+            hz = torch.cuda.get_device_properties(device).clock_rate * 1000
             import torch.distributed as dist
             dist.barrier(self.group)
+            torch.cuda.synchronize()
+            self._bar = (flags, words, int(self.wait_seconds * hz))
+        flags, words, cycles = self._bar
+        nv.check(nv.cuda().b200_ep_barrier(_ptr_array(flags.ptrs), self.world, self.rank, words.data_ptr(), cycles,
+                                           nv.status_word(device).data_ptr(), nv.stream_ptr()), "ep_barrier")
+        nv.count_launch()
 
 
 class MoEExpertsFn(Function):
-    """Routed experts: out[t] = sum_j w[t,j] * FFN_{idx[t,j]}(x[t]).  x [T, d] bf16 (CUDA)."""
+    """Routed experts: out[t] = sum_j w[t,j] * FFN_{idx[t,j]}(x[t]).  x [T, d] bf16 (CUDA).
+
+    Buffer discipline (all buffers are shared by every layer of the model and live in peer-mapped memory):
+      forward   entry: xbuf and fill are zero on every rank.
+                dispatch (remote row stores + remote slot counters) | barrier | expert GEMMs -> ybuf | barrier |
+                combine (remote row loads), then clear xbuf / fill | barrier.
+      backward  ybuf <- y | barrier | combine adjoint (remote loads of ybuf, remote stores into dybuf) | barrier |
+                expert GEMMs, xbuf <- d(expert input) | barrier | dispatch adjoint (remote loads of xbuf), then clear xbuf
+                and dybuf | barrier.
+    The closing barrier of each direction is what lets the next layer's dispatch (or adjoint) write into a peer at once."""
 
     @staticmethod
     def forward(ctx, x, idx, w, W1, b1, W2, b2, act, cap, ep: Optional[EPContext]):
@@ -155,27 +192,27 @@ class MoEExpertsFn(Function):
         xbuf, xptrs = ep.buffer("x", rows * d, torch.bfloat16, dev)
         fill, fptrs = ep.buffer("fill", max(E_local, 4), torch.int32, dev)
         ybuf, yptrs = ep.buffer("y", rows * d, torch.bfloat16, dev)
-        xbuf.zero_(); fill.zero_()
-        ep.barrier()                                              # every rank's buffers are cleared before anyone writes
         dest = torch.empty((T, k), dtype=torch.int32, device=dev)
         lib = nv.cuda()
         xc = x.contiguous()
         nv.check(lib.b200_moe_dispatch(xc.data_ptr(), idx.data_ptr(), dest.data_ptr(), _ptr_array(xptrs), _ptr_array(fptrs), world,
                                        T, k, d, E_local, cap, nv.stream_ptr()), "moe_dispatch")
-        ep.barrier()                                              # all remote rows have landed
+        ep.barrier(dev)                                           # all remote rows have landed
         xb = xbuf.view(E_local, cap, d)
         W1l, W2l = F.lp(W1), F.lp(W2)
         h, pre = gemm(xb, W1l, bias=b1.detach() if b1 is not None else None, act=act, want_aux=True)        # [E, cap, hid]
         y = gemm(h, W2l, bias=b2.detach() if b2 is not None else None)                                       # [E, cap, d]
         ybuf.view(E_local, cap, d).copy_(y)
-        ep.barrier()
+        xsave = xb.clone()
+        ep.barrier(dev)                                           # every rank's expert outputs are in place
         out = torch.empty((T, d), dtype=torch.bfloat16, device=dev)
         wc = w.float().contiguous()
         nv.check(lib.b200_moe_combine_fwd(_ptr_array(yptrs), world, dest.data_ptr(), wc.data_ptr(), out.data_ptr(), T, k, d, rows,
                                           nv.stream_ptr()), "moe_combine_fwd")
         nv.count_launch(2)
-        ep.barrier()
-        ctx.save_for_backward(dest, wc, xb.clone(), h, pre, y, W1, b1, W2, b2)
+        xbuf.zero_(); fill.zero_()
+        ep.barrier(dev)                                           # peers have read my outputs; everyone's input buffers are clear
+        ctx.save_for_backward(dest, wc, xsave, h, pre, y, W1, b1, W2, b2)
         ctx.cfg = (act, cap, ep, T, d, k, E_local, hid)
         return out
 
@@ -187,14 +224,14 @@ class MoEExpertsFn(Function):
         lib = nv.cuda()
         ybuf, yptrs = ep.buffer("y", rows * d, torch.bfloat16, dev)
         dybuf, dyptrs = ep.buffer("dy", rows * d, torch.bfloat16, dev)
+        xbuf, xptrs = ep.buffer("x", rows * d, torch.bfloat16, dev)
         ybuf.view(E_local, cap, d).copy_(y)
-        dybuf.zero_()
-        ep.barrier()
+        ep.barrier(dev)
         dw = torch.empty((T, k), dtype=torch.float32, device=dev)
         dc = dout.contiguous()
         nv.check(lib.b200_moe_combine_bwd(_ptr_array(yptrs), _ptr_array(dyptrs), world, dest.data_ptr(), wc.data_ptr(), dc.data_ptr(),
                                           dw.data_ptr(), T, k, d, rows, nv.stream_ptr()), "moe_combine_bwd")
-        ep.barrier()
+        ep.barrier(dev)
         dy = dybuf.view(E_local, cap, d)
         W1l, W2l = F.lp(W1), F.lp(W2)
         dh = gemm(dy, W2l, b_mn=True, aux_in=pre, dact=act)                                   # [E, cap, hid]
@@ -209,13 +246,13 @@ class MoEExpertsFn(Function):
             db2 = torch.zeros((E_local, d), dtype=torch.float32, device=dev)
             nv.check(lib.b200_colsum_batched(dy.data_ptr(), db2.data_ptr(), E_local, cap, d, d, cap * d, 1, nv.stream_ptr()), "colsum_batched")
         # adjoint of dispatch: pull the token gradients back from the owning ranks (reuses the "x" buffer)
-        xbuf, xptrs = ep.buffer("x", rows * d, torch.bfloat16, dev)
         xbuf.view(E_local, cap, d).copy_(dxb)
-        ep.barrier()
+        ep.barrier(dev)
         dx = torch.empty((T, d), dtype=torch.bfloat16, device=dev)
         nv.check(lib.b200_moe_gather_sum(_ptr_array(xptrs), world, dest.data_ptr(), dx.data_ptr(), T, k, d, rows, nv.stream_ptr()), "moe_gather_sum")
         nv.count_launch(4)
-        ep.barrier()
+        xbuf.zero_(); dybuf.zero_()
+        ep.barrier(dev)
         return dx, None, dw, dW1, db1, dW2, db2, None, None, None
 
 
@@ -254,12 +291,12 @@ class _RoutedMoE(nn.Module):
     """Shared machinery of NormalMoE / FineGrainedMoE."""
 
     def __init__(self, d_in, expert_hidden, num_experts, top_k, act, routing, capacity_factor, aux_coef, renorm, init,
-                 shared_hidden=0, num_shared=0, ep_group=None):
+                 shared_hidden=0, num_shared=0, ep_group=None, ep_backend="fused"):
         self.d_in, self.E, self.top_k, self.act, self.routing = d_in, num_experts, min(top_k, num_experts), act, routing
         self.capacity_factor, self.aux_coef, self.renorm = capacity_factor, aux_coef, renorm
         self.gate = nn.Linear(d_in, num_experts, init=init)
         self.shared = [_Expert(d_in, shared_hidden, act, init) for _ in range(num_shared)]
-        self.ep = EPContext(ep_group) if ep_group is not None else None
+        self.ep = EPContext(ep_group, backend=ep_backend) if ep_group is not None else None
         world = self.ep.world if self.ep is not None else 1
         assert num_experts % world == 0
         self.E_local = num_experts // world
@@ -270,6 +307,9 @@ class _RoutedMoE(nn.Module):
         self.b1 = nn._param(torch.zeros(self.E_local, expert_hidden))
         self.W2 = nn._param(torch.stack([init((d_in, expert_hidden)) for _ in range(self.E_local)]))
         self.b2 = nn._param(torch.zeros(self.E_local, d_in))
+        if self.ep is not None and world > 1:
+            for p in (self.W1, self.b1, self.W2, self.b2):
+                p._ep_sharded = True            # owned by this rank alone: no gradient reduction across the group
         self.last_aux_loss = None
         self.last_counts = None
 
@@ -316,7 +356,9 @@ class _RoutedMoE(nn.Module):
         idx, w, counts, aux = RouterFn.apply(logits, self.top_k, self.renorm, self.aux_coef)
         self.last_aux_loss = aux * self.aux_coef
         self.last_counts = counts
-        if x2.is_cuda and x2.dtype == torch.bfloat16:
+        if self.ep is not None and self.ep.world > 1 and (not x2.is_cuda or self.ep.backend == "nccl"):
+            routed = _experts_all_to_all(x2, idx, w, self.W1, self.b1, self.W2, self.b2, self.act, self.ep)
+        elif x2.is_cuda and x2.dtype == torch.bfloat16:
             routed = MoEExpertsFn.apply(x2, idx, w, self.W1, self.b1, self.W2, self.b2, self.act, self.capacity(x2.shape[0]), self.ep)
         else:
             routed = _experts_dense_autograd(x2, idx, w, self.W1, self.b1, self.W2, self.b2, self.act)
@@ -337,6 +379,67 @@ def _experts_dense_autograd(x, idx, w, W1, b1, W2, b2, act):
     return out.to(x.dtype)
 
 
+class _AllToAllFn(Function):
+    """Differentiable `all_to_all_single` over rows: the backward is the same exchange with the split lists swapped."""
+
+    @staticmethod
+    def forward(ctx, x, send, recv, group):
+        import torch.distributed as dist
+        ctx.cfg = (send, recv, group)
+        out = torch.empty((sum(recv),) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_to_all_single(out, x.contiguous(), output_split_sizes=recv, input_split_sizes=send, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        import torch.distributed as dist
+        send, recv, group = ctx.cfg
+        out = torch.empty((sum(send),) + tuple(g.shape[1:]), dtype=g.dtype, device=g.device)
+        dist.all_to_all_single(out, g.contiguous(), output_split_sizes=send, input_split_sizes=recv, group=group)
+        return out, None, None, None
+
+
+def _experts_all_to_all(x, idx, w, W1, b1, W2, b2, act, ep: "EPContext"):
+    """Expert parallelism the library way: sort the (token, choice) pairs by expert, exchange counts, all-to-all the
+    rows to the ranks that own their experts, run each local expert on its rows, all-to-all back, weight and sum.
+    No capacity limit (no drops). This is the baseline the peer-memory kernels are measured against (NCCL on GPUs) and
+    the path CPU (gloo) ranks take; the split sizes are read on the host, so it cannot be captured in a CUDA graph."""
+    import torch.distributed as dist
+    T, d = x.shape
+    k = idx.shape[1]
+    E_local, world = W1.shape[0], ep.world
+    flat_e = idx.reshape(-1).long()
+    order = torch.argsort(flat_e, stable=True)                     # pairs grouped by global expert id (= by owner rank)
+    tok = torch.div(order, k, rounding_mode="floor")
+    counts = torch.bincount(flat_e, minlength=E_local * world)
+    recv_counts = torch.empty_like(counts)
+    dist.all_to_all_single(recv_counts, counts, group=ep.group)    # [src rank][local expert]
+    send = counts.view(world, E_local).sum(1).tolist()
+    rc = recv_counts.view(world, E_local)
+    recv = rc.sum(1).tolist()
+    rows = _AllToAllFn.apply(x[tok], send, recv, ep.group)         # grouped by source rank, then by local expert
+    # regroup by local expert
+    src_e = torch.repeat_interleave(torch.arange(world * E_local, device=x.device) % E_local, rc.reshape(-1))
+    by_e = torch.argsort(src_e, stable=True)
+    rows_e = rows[by_e]
+    per_e = rc.sum(0).tolist()
+    outs, off = [], 0
+    for e in range(E_local):
+        seg = rows_e[off:off + per_e[e]]
+        off += per_e[e]
+        if seg.shape[0] == 0:
+            outs.append(seg.new_zeros((0, d)))
+            continue
+        hcur = F.linear(seg, W1[e], b1[e] if b1 is not None else None, act, None)
+        outs.append(F.linear(hcur, W2[e], b2[e] if b2 is not None else None, "none", None))
+    y_e = torch.cat(outs, 0) if outs else rows_e
+    y_src = torch.empty_like(y_e).index_copy(0, by_e, y_e) if y_e.shape[0] else y_e
+    back = _AllToAllFn.apply(y_src, recv, send, ep.group)          # in `order` again
+    contrib = back.float() * w.reshape(-1)[order].float().unsqueeze(1)
+    out = torch.zeros((T, d), dtype=torch.float32, device=x.device).index_add(0, tok, contrib)
+    return out.to(x.dtype)
+
+
 def F_add(a, b):
     from .looped_transformer import _add
     return _add(a, b)
@@ -347,9 +450,9 @@ class NormalMoE(_RoutedMoE):
 
     def __init__(self, in_features: int, hidden_features: int, num_experts: int, top_k: int = 2, routing: str = "topk",
                  act: str = "relu", capacity_factor: float = 1.5, aux_coef: float = 0.01, renorm: bool = True,
-                 init=nn.he_normal, ep_group=None):
+                 init=nn.he_normal, ep_group=None, ep_backend="fused"):
         super().__init__(in_features, hidden_features, num_experts, top_k, act, routing, capacity_factor, aux_coef, renorm, init,
-                         ep_group=ep_group)
+                         ep_group=ep_group, ep_backend=ep_backend)
 
 
 class FineGrainedMoE(_RoutedMoE):
@@ -358,9 +461,9 @@ class FineGrainedMoE(_RoutedMoE):
 
     def __init__(self, in_features: int, shared_hidden: int, expert_hidden: int, num_experts: int, top_k: int = 6,
                  num_shared: int = 1, routing: str = "topk", act: str = "relu", capacity_factor: float = 1.25,
-                 aux_coef: float = 0.01, renorm: bool = True, init=nn.he_normal, ep_group=None):
+                 aux_coef: float = 0.01, renorm: bool = True, init=nn.he_normal, ep_group=None, ep_backend="fused"):
         super().__init__(in_features, expert_hidden, num_experts, top_k, act, routing, capacity_factor, aux_coef, renorm, init,
-                         shared_hidden=shared_hidden, num_shared=num_shared, ep_group=ep_group)
+                         shared_hidden=shared_hidden, num_shared=num_shared, ep_group=ep_group, ep_backend=ep_backend)
 
 
 class MoETransformerLM(nn.Module):
@@ -368,7 +471,8 @@ class MoETransformerLM(nn.Module):
     The loss adds the routers' load-balance terms."""
 
     def __init__(self, vocab: int, d_model: int, layers: int, heads: int, num_experts: int, top_k: int, num_shared: int,
-                 expert_hidden: int, max_seq: int, init_std: float = 0.02, ep_group=None, act: str = "silu"):
+                 expert_hidden: int, max_seq: int, init_std: float = 0.02, ep_group=None, act: str = "silu",
+                 capacity_factor: float = 1.25, ep_backend: str = "fused"):
         from .looped_transformer import MultiHeadAttention
         init = nn.normal_init(init_std)
         self.tok = nn.Embedding(vocab, d_model, std=init_std)
@@ -376,8 +480,13 @@ class MoETransformerLM(nn.Module):
         self.ln1 = [nn.LayerNorm(d_model) for _ in range(layers)]
         self.attn = [MultiHeadAttention(d_model, heads, causal=True, init=init) for _ in range(layers)]
         self.ln2 = [nn.LayerNorm(d_model) for _ in range(layers)]
+        self.ep_group = ep_group
         self.moe = [FineGrainedMoE(d_model, expert_hidden, expert_hidden, num_experts, top_k=top_k, num_shared=num_shared, act=act,
-                                   init=init, ep_group=ep_group) for _ in range(layers)]
+                                   init=init, ep_group=ep_group, capacity_factor=capacity_factor, ep_backend=ep_backend) for _ in range(layers)]
+        # one set of dispatch / combine buffers for all layers (they are used one layer at a time)
+        for m in self.moe[1:]:
+            if m.ep is not None:
+                m.ep = self.moe[0].ep
         self.ln_final = nn.LayerNorm(d_model)
         self.lm_head = nn.Linear(d_model, vocab, bias=False, init=init)
 
@@ -410,6 +519,23 @@ class MoETransformerLM(nn.Module):
         layers = [a.parameters() + b.parameters() + c.parameters() + d.parameters()
                   for a, b, c, d in zip(self.ln1, self.attn, self.ln2, self.moe)]
         return [self.tok.parameters() + self.pos.parameters()] + layers + [self.ln_final.parameters() + self.lm_head.parameters()]
+
+    def make_optimizer(self, lr: float = 1e-3, mode: str = "fused", **kw):
+        """The optimizer that matches this model's parallel layout: under expert parallelism every rank trains on its own
+        batch, so the shared parameters (attention, routers, shared experts, embeddings, norms, head) are data-parallel
+        (`DistributedAdam`, gradients averaged) while each routed expert lives on one rank, whose local Adam scales the
+        summed contributions of all ranks' losses by 1/world."""
+        import torch.distributed as dist
+        from ..optim import Adam, MultiOptimizer
+        world = dist.get_world_size(self.ep_group) if self.ep_group is not None else 1
+        if world == 1:
+            return Adam(self.parameters(), lr=lr, **kw)
+        from ..parallel.ddp import DistributedAdam
+        owned = [p for p in self.parameters() if getattr(p, "_ep_sharded", False)]
+        shared = [p for p in self.parameters() if not getattr(p, "_ep_sharded", False)]
+        local = Adam(owned, lr=lr, **kw)
+        local.grad_scale = torch.full((1,), 1.0 / world, dtype=torch.float32, device=owned[0].device)
+        return MultiOptimizer([DistributedAdam(shared, lr=lr, group=self.ep_group, mode=mode, **kw), local])
 
     def loss(self, ids, labels):
         from ..ops.transformer import lm_head_ce

@@ -67,13 +67,13 @@ class DpFusedArgs(C.Structure):
 nv.register_sigs({"b200_dp_fused_launch": [C.POINTER(DpFusedArgs), C.c_int, C.c_int, C.c_void_p], "b200_dp_flag_words": []})
 
 
-def is_replicated(p: torch.Tensor) -> bool:
+def is_replicated(p: torch.Tensor, max_numel: int = REPLICATE_MAX_NUMEL) -> bool:
     """Parameters the forward reads in fp32 (biases, norm gains, conv taps, state matrices, routers) are kept
     identical on every rank instead of being sharded. `p._dp_replicate = True/False` overrides the size rule."""
     flag = getattr(p, "_dp_replicate", None)
     if flag is not None:
         return bool(flag)
-    return p.dim() < 2 or p.numel() <= REPLICATE_MAX_NUMEL
+    return p.dim() < 2 or p.numel() <= max_numel
 
 
 class SymmetricBuffer:
@@ -134,7 +134,8 @@ class DistributedOptimizer(Optimizer):
                  torch_compat: bool = False, momentum: float = 0.95, mode: str = "fused", group=None,
                  use_multimem: Optional[bool] = None, wait_seconds: float = 2.0, grid: int = 128,
                  groups: Optional[Sequence[Sequence[torch.Tensor]]] = None, bucket_mb: float = 32.0,
-                 max_grad_norm: Optional[float] = None, overlap_grid: int = 32, average: bool = True):
+                 max_grad_norm: Optional[float] = None, overlap_grid: int = 32, average: bool = True,
+                 replicate_max_numel: int = REPLICATE_MAX_NUMEL):
         global _ACTIVE
         self.group = group or dist.group.WORLD
         self.world = dist.get_world_size(self.group)
@@ -148,6 +149,8 @@ class DistributedOptimizer(Optimizer):
         self.eps, self.weight_decay, self.torch_compat = eps, weight_decay, torch_compat
         self.max_grad_norm = max_grad_norm
         self.red_scale = 1.0 / self.world if average else 1.0
+        self.is_rep = lambda p: is_replicated(p, replicate_max_numel)
+        is_rep = self.is_rep
         if rule == "muon" and max_grad_norm is not None:
             raise ValueError("Muon normalises every tensor's gradient by its RMS; clipping has no effect on it")
 
@@ -164,15 +167,15 @@ class DistributedOptimizer(Optimizer):
             ordered = rest + ordered
         else:
             ordered, group_of = list(plist), {id(p): -1 for p in plist}
-        sharded = [p for p in ordered if not is_replicated(p)]
-        replicated = [p for p in ordered if is_replicated(p)]
+        sharded = [p for p in ordered if not is_rep(p)]
+        replicated = [p for p in ordered if is_rep(p)]
         self.params = plist
         self.flat = FlatParams(sharded + replicated, pad_to=64)
         fl = self.flat
         n = fl.numel
-        first_rep = next((p for p in fl.order if is_replicated(p)), None)
+        first_rep = next((p for p in fl.order if is_rep(p)), None)
         self.n_shard = fl.offsets[id(first_rep)] if first_rep is not None else n
-        assert self.n_shard % 64 == 0 and all((not is_replicated(p)) == (fl.offsets[id(p)] < self.n_shard) for p in fl.order)
+        assert self.n_shard % 64 == 0 and all((not is_rep(p)) == (fl.offsets[id(p)] < self.n_shard) for p in fl.order)
         self.n = n
 
         # ---- buckets: cut the sharded range at parameter boundaries (never inside a fused group)

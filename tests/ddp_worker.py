@@ -37,7 +37,8 @@ def make_opt(model, args, world_kind):
     clip = args.clip if args.clip > 0 else None
     if world_kind == "single":
         return Adam(model.parameters(), lr=1e-3) if args.opt == "adam" else Muon(model.parameters(), lr=1e-3, momentum=0.9)
-    kw = dict(mode=args.mode, use_multimem=bool(args.multimem), groups=model.dp_groups() if args.groups else None, bucket_mb=0.05)
+    kw = dict(mode=args.mode, use_multimem=bool(args.multimem), groups=model.dp_groups() if args.groups else None, bucket_mb=0.05,
+              replicate_max_numel=1024)        # at this size only biases / norm gains stay replicated: the matrices are sharded
     if args.opt == "adam":
         return DistributedAdam(model.parameters(), lr=1e-3, max_grad_norm=clip, **kw)
     return DistributedMuon(model.parameters(), lr=1e-3, momentum=0.9, **kw)
@@ -157,7 +158,7 @@ def main():
                 continue
             e, u = sq(p - q), sq(f - q)
             num += e; den += sq(q); upd += u
-            if is_replicated(p):
+            if opt.is_rep(p):
                 rep_num += e; rep_upd += u
                 if u > 0:
                     worst_rep = max(worst_rep, (e / u) ** 0.5)

@@ -125,14 +125,17 @@ def moe_ep(args, rank, world, dev, dtype):
     from rust_neural_network_b200.optim import Adam
     V, d, L, H, E, k, hid, S, Bl = 256, 128, 2, 2, 8, 2, 128, 128, 2
     torch.manual_seed(3)
-    model = MoETransformerLM(V, d, L, H, E, k, 1, hid, S, ep_group=dist.group.WORLD, capacity_factor=float(E)).to_device(dev, dtype)
-    opt = model.make_optimizer(lr=1e-3)
+    model = MoETransformerLM(V, d, L, H, E, k, 1, hid, S, ep_group=dist.group.WORLD, capacity_factor=float(E),
+                             ep_backend=args.backend).to_device(dev, dtype)
+    opt = model.make_optimizer(lr=1e-3, mode=args.backend if dev.type == "cuda" else "nccl")
     g = torch.Generator().manual_seed(5)
     ids = torch.randint(0, V, (world * Bl, S), generator=g)
     lab = torch.randint(0, V, (world * Bl, S), generator=g)
     my = slice(rank * Bl, (rank + 1) * Bl)
     out = {"rank": rank, "world": world}
     experts = {}
+    ex_ids = {id(p) for m in model.moe for p in (m.W1, m.b1, m.W2, m.b2)}
+    shared0 = [p.detach().clone() for p in model.parameters() if id(p) not in ex_ids]
     for li, m in enumerate(model.moe):
         for nm in ("W1", "b1", "W2", "b2"):
             experts[f"{li}.{nm}"] = gather_cat(getattr(m, nm), 0, world)
@@ -150,7 +153,7 @@ def moe_ep(args, rank, world, dev, dtype):
     loss0 = ep_step(False)
     if dev.type == "cuda":
         torch.cuda.synchronize(); nv.check_status()
-    gW1 = gather_cat(model.moe[0].W1.grad, 0, world)
+    gW1 = gather_cat(model.moe[0].W1.grad, 0, world) / world     # an expert sums the contributions of every rank's loss
     gate = model.moe[0].gate.weight.grad.detach().float().clone()
     dist.all_reduce(gate)
     gate /= world
@@ -165,8 +168,10 @@ def moe_ep(args, rank, world, dev, dtype):
             for li, m in enumerate(ref.moe):
                 for nm in ("W1", "b1", "W2", "b2"):
                     getattr(m, nm).copy_(experts[f"{li}.{nm}"].to(dev))
-            shared = lambda mod: [p for p in mod.parameters() if not getattr(p, "_ep_sharded", False)]
-            for p, q in zip(shared(ref), shared(model)):
+            def shared(mod):
+                ex = {id(p) for m in mod.moe for p in (m.W1, m.b1, m.W2, m.b2)}
+                return [p for p in mod.parameters() if id(p) not in ex]
+            for p, q in zip(shared(ref), shared0):
                 p.copy_(q)
         ropt = Adam(ref.parameters(), lr=1e-3)
 

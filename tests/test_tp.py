@@ -189,3 +189,19 @@ def test_tensor_parallel_mamba_lm_two_gpus():
         pytest.skip("needs 2 GPUs")
     r0 = _run_model(2, ["--model", "mamba_tp", "--device", "cuda", "--backend", "fused"], 29662)[0]
     _check_model(r0, "tp_losses", 6e-2, 3e-2)
+
+
+def test_expert_parallel_moe_lm_two_gloo_ranks():
+    """Experts sharded over two ranks (all-to-all baseline path on CPU), shared parameters data-parallel, against the
+    same model with every expert local and the whole batch in one process."""
+    r0 = _run_model(2, ["--model", "moe_ep", "--device", "cpu"], 29663)[0]
+    _check_model(r0, "ep_losses", 3e-2, 3e-3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("backend,port", [("fused", 29664), ("nccl", 29665)])
+def test_expert_parallel_moe_lm_two_gpus(backend, port):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    r0 = _run_model(2, ["--model", "moe_ep", "--device", "cuda", "--backend", backend], port)[0]
+    _check_model(r0, "ep_losses", 8e-2, 5e-2)

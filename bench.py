@@ -33,6 +33,26 @@ CONFIG = dict(vocab=32000, d_model=512, heads=8, ff_dim=2048, layers_per_block=4
 METRIC = "train tokens/s (looped-transformer LM, device-timed, max over ranks)"
 
 
+def model_flops_per_token(cfg) -> float:
+    """Forward + backward FLOPs per token: 6 x the matmul parameters a token passes through (every application of the
+    shared block counts) plus causal attention (QK^T and PV, half the square, backward = 2 x forward)."""
+    d, ff, S = cfg["d_model"], cfg["ff_dim"], cfg["seq_len"]
+    apps = cfg["layers_per_block"] * cfg["loops"]
+    matmul_params = apps * (4 * d * d + 2 * d * ff) + d * cfg["vocab"]
+    attn_fwd = apps * 2 * S * d                       # 2 products x 2 FLOP x S x d / 2 (causal)
+    return 6.0 * matmul_params + 3.0 * attn_fwd
+
+
+def sustained_peak_tflops():
+    """(peak, source): the sustained bf16 GEMM throughput measured on this pool (MEASURED_PEAKS.json next to this file)
+    or, when that file is absent, 1400 TFLOP/s from an earlier measurement."""
+    f = Path(__file__).resolve().parent / "MEASURED_PEAKS.json"
+    try:
+        return float(json.loads(f.read_text())["bf16_tflops_sustained"]), "of measured"
+    except Exception:
+        return 1400.0, "of fallback"
+
+
 def reference_arm(args):
     # The reference is a Rust crate (Cargo.toml, no setup.py / pyproject.toml): pip cannot install it and
     # there is no cargo / rustc in this image, so it cannot be built or run here.
@@ -89,8 +109,10 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def torch_arm(args):
-    """The library baseline: same model, shapes, precision policy and timing rules, stock PyTorch kernels only."""
+def torch_arm(args, in_process: bool = False):
+    """The library baseline: same model, shapes, precision policy and timing rules, stock PyTorch kernels only.
+    `in_process`: called from the b200 arm after its own measurement (the process group exists already); returns the
+    record instead of printing it."""
     import torch
     import torch.distributed as dist
     from baseline.torch_lm import TorchLoopedLM, TorchStep
@@ -98,7 +120,7 @@ def torch_arm(args):
     world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0")); local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
+    if world > 1 and not dist.is_initialized():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     cfg = dict(CONFIG)
@@ -151,6 +173,14 @@ def torch_arm(args):
     t1.record()
     barrier()
     e2e_ms = max_over_ranks(t0.elapsed_time(t1))
+    if in_process:
+        if rank == 0:
+            sampler.stop()
+        tokens = cfg["global_batch"] * S * args.steps
+        del step, model
+        torch.cuda.empty_cache()
+        return {"value": tokens / (dev_ms / 1e3), "ms_per_step": dev_ms / args.steps, "e2e_value": tokens / (e2e_ms / 1e3),
+                "e2e_ms_per_step": e2e_ms / args.steps, "loss_last": last}
     if rank == 0:
         sampler.stop()
         tokens = cfg["global_batch"] * S * args.steps
@@ -184,6 +214,7 @@ def main():
     ap.add_argument("--dp", default="fused", choices=["fused", "nccl"], help="data-parallel gradient path for N > 1")
     ap.add_argument("--global-batch", type=int, default=0, help="override the global batch (diagnostics; the headline configuration is 64)")
     ap.add_argument("--small", action="store_true", help="tiny configuration for smoke tests (NOT a valid bench number)")
+    ap.add_argument("--no-torch-arm", action="store_true", help="skip the stock-PyTorch run that follows the measurement (the `torch_arm` / `vs_torch` keys)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -300,6 +331,15 @@ def main():
     tokens_per_step = cfg["global_batch"] * S
     value = tokens_per_step * args.steps / (dev_ms / 1e3)
     e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
+    peak, peak_src = sustained_peak_tflops()
+    tflops_per_gpu = model_flops_per_token(cfg) * value / world / 1e12
+    # the same model on stock PyTorch (cuBLAS, SDPA, fused Adam, DDP), measured in this process right after, same rules
+    torch_rec = None
+    if not args.no_torch_arm:
+        try:
+            torch_rec = torch_arm(args, in_process=True)
+        except Exception as e:                                   # the headline number does not depend on this arm
+            torch_rec = {"error": repr(e)[:200]}
     if rank == 0:
         out = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -315,6 +355,12 @@ def main():
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches),
+            "roofline_pct": 100.0 * tflops_per_gpu / peak,
+            "roofline": {"model_gflop_per_token": model_flops_per_token(cfg) / 1e9, "tflops_per_gpu": tflops_per_gpu,
+                         "peak_tflops_bf16_sustained": peak, "peak_source": peak_src},
+            "torch_arm": torch_rec,
+            "vs_torch": (value / torch_rec["value"]) if torch_rec and "value" in torch_rec else None,
+            "vs_torch_e2e": (e2e_value / torch_rec["e2e_value"]) if torch_rec and "e2e_value" in torch_rec else None,
             "loss_first": loss0, "loss_last": last,
         }
         print(json.dumps(out), flush=True)

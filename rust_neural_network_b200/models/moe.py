@@ -175,10 +175,13 @@ class MoEExpertsFn(Function):
       forward   entry: xbuf and fill are zero on every rank.
                 dispatch (remote row stores + remote slot counters) | barrier | expert GEMMs -> ybuf | barrier |
                 combine (remote row loads), then clear xbuf / fill | barrier.
-      backward  ybuf <- y | barrier | combine adjoint (remote loads of ybuf, remote stores into dybuf) | barrier |
-                expert GEMMs, xbuf <- d(expert input) | barrier | dispatch adjoint (remote loads of xbuf), then clear xbuf
-                and dybuf | barrier.
-    The closing barrier of each direction is what lets the next layer's dispatch (or adjoint) write into a peer at once."""
+      backward  entry: dybuf is zero. ybuf <- y | barrier | combine adjoint (remote loads of ybuf, remote stores into
+                dybuf) | barrier | expert GEMMs, dxbuf <- d(expert input) | barrier | dispatch adjoint (remote loads of
+                dxbuf), then clear dybuf.
+    The closing barrier of the forward is what lets the next layer's dispatch write into a peer at once. The backward needs
+    none: a peer may still be reading this rank's dxbuf when the function returns, but the next writer of dxbuf (the next
+    layer's backward) first passes a barrier that every peer only reaches after it has finished that read, and dybuf is
+    cleared before this rank signals that barrier."""
 
     @staticmethod
     def forward(ctx, x, idx, w, W1, b1, W2, b2, act, cap, ep: Optional[EPContext]):
@@ -224,7 +227,7 @@ class MoEExpertsFn(Function):
         lib = nv.cuda()
         ybuf, yptrs = ep.buffer("y", rows * d, torch.bfloat16, dev)
         dybuf, dyptrs = ep.buffer("dy", rows * d, torch.bfloat16, dev)
-        xbuf, xptrs = ep.buffer("x", rows * d, torch.bfloat16, dev)
+        dxbuf, dxptrs = ep.buffer("dx", rows * d, torch.bfloat16, dev)
         ybuf.view(E_local, cap, d).copy_(y)
         ep.barrier(dev)
         dw = torch.empty((T, k), dtype=torch.float32, device=dev)
@@ -245,14 +248,13 @@ class MoEExpertsFn(Function):
         if b2 is not None:
             db2 = torch.zeros((E_local, d), dtype=torch.float32, device=dev)
             nv.check(lib.b200_colsum_batched(dy.data_ptr(), db2.data_ptr(), E_local, cap, d, d, cap * d, 1, nv.stream_ptr()), "colsum_batched")
-        # adjoint of dispatch: pull the token gradients back from the owning ranks (reuses the "x" buffer)
-        xbuf.view(E_local, cap, d).copy_(dxb)
+        # adjoint of dispatch: pull the token gradients back from the owning ranks
+        dxbuf.view(E_local, cap, d).copy_(dxb)
         ep.barrier(dev)
         dx = torch.empty((T, d), dtype=torch.bfloat16, device=dev)
-        nv.check(lib.b200_moe_gather_sum(_ptr_array(xptrs), world, dest.data_ptr(), dx.data_ptr(), T, k, d, rows, nv.stream_ptr()), "moe_gather_sum")
+        nv.check(lib.b200_moe_gather_sum(_ptr_array(dxptrs), world, dest.data_ptr(), dx.data_ptr(), T, k, d, rows, nv.stream_ptr()), "moe_gather_sum")
         nv.count_launch(4)
-        xbuf.zero_(); dybuf.zero_()
-        ep.barrier(dev)
+        dybuf.zero_()
         return dx, None, dw, dW1, db1, dW2, db2, None, None, None
 
 

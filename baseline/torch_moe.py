@@ -65,7 +65,7 @@ class MoE(tnn.Module):
         self.aux = self.aux_coef * self.E * (f * probs.mean(0)).sum()
         order = torch.argsort(flat_e, stable=True)
         tok = torch.div(order, self.k, rounding_mode="floor")
-        rows = x[tok]
+        rows = (x.to(torch.bfloat16) if x.is_cuda else x)[tok]        # bf16 rows on the wire, like the kernels this is compared with
         if self.world > 1:
             recv_counts = torch.empty_like(counts)
             dist.all_to_all_single(recv_counts, counts, group=self.group)
@@ -87,7 +87,7 @@ class MoE(tnn.Module):
         if self.world > 1:
             y = torch.empty_like(y).index_copy(0, by_e, y)
             y = _A2A.apply(y, recv, send, self.group)
-        contrib = y * w.reshape(-1)[order].to(y.dtype).unsqueeze(1)
+        contrib = (y.float() * w.reshape(-1)[order].float().unsqueeze(1)).to(x.dtype)
         return out + torch.zeros_like(x).index_add(0, tok, contrib)
 
 
@@ -158,6 +158,7 @@ class TorchMoEStep:
             dist.all_reduce(self.flat_grad, group=self.group)
             self.flat_grad.mul_(1.0 / self.world)
             for p in self.owned:
-                p.grad.mul_(1.0 / self.world)
+                if p.grad is not None:
+                    p.grad.mul_(1.0 / self.world)
         self.opt.step()
         return loss.detach()

@@ -1,6 +1,8 @@
 """Benchmarks of the configurations beside the headline one (which `bench.py` measures).
 
     python bench_configs.py mlp                     784-256-128-10 MLP, fp32/TF32, batch 32, Adam, CUDA-graph step
+    python bench_configs.py ref_mlp                 the four MLP shapes the reference publishes step times for: GPU graph step,
+                                                    C++ restatement of the reference's CPU path, published numbers
     python bench_configs.py moe_lm   [--batch B]    FineGrainedMoE transformer LM (64 routed top-6 + 2 shared)
     python bench_configs.py mamba_lm [--batch B]    Mamba (S6) LM, d 2048, 24 layers, seq 4096
     python -m torch.distributed.run --nproc-per-node N ... bench_configs.py moe_lm      expert parallel, 64/N experts per GPU
@@ -200,6 +202,59 @@ def run_mlp(args):
                       "launches_per_step": getattr(tr, "launches_per_step", None), "loss_first": first, "loss_last": float(l)}), flush=True)
 
 
+# MLP shapes the reference publishes step times for (its README: rust-nn autograd / CompiledMLP against PyTorch eager,
+# single CPU thread, Adam + MSE; examples/bench_train.rs:44-47, examples/bench_compiled.rs)
+REF_MLP_SHAPES = [
+    ("tiny", (16, 32, 32, 4), 8, {"rust_nn_ms": 0.032, "pytorch_cpu_ms": 0.770}),
+    ("small", (64, 128, 128, 10), 32, {"rust_nn_ms": 0.35, "pytorch_cpu_ms": 0.82}),
+    ("medium", (128, 256, 256, 10), 32, {"rust_nn_ms": 1.2, "pytorch_cpu_ms": 1.25}),
+    ("large", (256, 512, 512, 256), 64, {"rust_nn_ms": 6.5, "rust_nn_compiled_ms": 4.68, "rust_nn_compiled_2thread_ms": 3.95, "pytorch_cpu_ms": 4.1}),
+]
+
+
+def run_ref_mlp(args):
+    """The four published MLP shapes, three ways: this package on the GPU (`CompiledMLP`: the whole step replayed as one
+    CUDA graph, inputs copied from pinned host memory every step), the C++ restatement of the reference's CPU path
+    (`cpu_ref.CpuMLP`, packed AVX2 sgemm + AVX2 Adam, 1 and 2 threads) on this machine's CPU, and the published numbers."""
+    import time
+    from rust_neural_network_b200 import _native as nv
+    from rust_neural_network_b200 import cpu_ref
+    from rust_neural_network_b200.compiled import CompiledMLP
+    rows = []
+    steps = max(args.steps, 200)
+    for name, dims, batch, pub in REF_MLP_SHAPES:
+        g = torch.Generator().manual_seed(0)
+        x, y = torch.randn(batch, dims[0], generator=g), torch.randn(batch, dims[-1], generator=g)
+        rec = {"shape": name, "dims": list(dims), "batch": batch, "published": pub}
+        for th in (1, 2):
+            net = cpu_ref.CpuMLP(dims, seed=0)
+            for _ in range(20):
+                net.step(x, targets=y, threads=th)
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                net.step(x, targets=y, threads=th)
+            rec[f"cpu_restatement_{th}thread_ms"] = (time.perf_counter() - t0) / steps * 1e3
+        if torch.cuda.is_available():
+            m = CompiledMLP([(dims[i], dims[i + 1]) for i in range(len(dims) - 1)], batch, 1e-3)
+            xp, yp = x.pin_memory(), y.pin_memory()
+            first = m.step(xp, yp)
+            for _ in range(20):
+                m.step_async(xp, yp)
+            torch.cuda.synchronize()
+            e0, e1 = _events()
+            e0.record()
+            for _ in range(steps):
+                l = m.step_async(xp, yp)
+            e1.record()
+            torch.cuda.synchronize()
+            nv.check_status()
+            rec["b200_graph_step_ms"] = e0.elapsed_time(e1) / steps
+            rec["b200_launches_per_step"] = getattr(m.trainer, "launches_per_step", None)
+            rec["loss_first"], rec["loss_last"] = first, float(l)
+        rows.append(rec)
+    print(json.dumps({"config": "ref_mlp", "steps": steps, "rows": rows}), flush=True)
+
+
 def run_attention(args):
     from rust_neural_network_b200 import _native as nv
     from rust_neural_network_b200.ops import functional as F
@@ -277,7 +332,7 @@ def run_attention_sp(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("config", choices=["mlp", "moe_lm", "mamba_lm", "attention", "attention_sp"])
+    ap.add_argument("config", choices=["mlp", "ref_mlp", "moe_lm", "mamba_lm", "attention", "attention_sp"])
     ap.add_argument("--batch", type=int, default=0)
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="override the preset's layer count (diagnostics)")
@@ -293,6 +348,8 @@ def main():
     args = ap.parse_args()
     if args.config == "mlp":
         run_mlp(args)
+    elif args.config == "ref_mlp":
+        run_ref_mlp(args)
     elif args.config == "attention":
         run_attention(args)
     elif args.config == "attention_sp":

@@ -1,0 +1,831 @@
+// A3 / A4: causal linear attention, forward and backward, as fused chunk kernels on tcgen05 / TMEM (sm_100a).
+//
+//   out_t = phi(s q_t) . S_t / (phi(s q_t) . z_t + eps),   S_t = sum_{u<=t} phi(s k_u) (x) v_u,   z_t = sum_{u<=t} phi(s k_u)
+//
+// with phi = ELU + 1 or ReLU^2 (rust-nn src/linear_attention.rs:42-94). The reference runs the causal form as a
+// per-token rank-1 recurrence and its backward stores every S_t (src/linear_attention.rs:214-266, 502-632). Here one
+// CTA owns one (batch, head) and walks its sequence in chunks of 128 tokens; thread t owns token t of the chunk (= TMEM
+// lane t). Per chunk, with Q~ = phi(sQ), K~ = phi(sK) formed in shared memory in place on the TMA tiles:
+//
+//   forward     A = mask(Q~ K~^T)            NUM = Q~ S + A V          den = rowsum(A) + Q~ . z        out = NUM / (den + eps)
+//               S += K~^T V                  z += colsum(K~)
+//   backward 1  (same direction, carries S, z again)      G = dO / D,  dden = -(dO . O) / D
+//               dA = mask(G V^T + dden 1^T)  dQ~ = dA K~ + G S^T + dden (x) z
+//   backward 2  (reverse direction, carries dS = sum_later Q~^T G and dz = sum_later Q~^T dden)
+//               dV = mask(A)^T G + K~ dS     dK~ = mask(dA)^T Q~ + V dS^T + 1 (x) dz
+//               dS += Q~^T G                 dz += Q~^T dden
+//   then dQ = s phi'(sQ) dQ~, dK = s phi'(sK) dK~ in the epilogue.
+//
+// Every product is a tcgen05.mma with fp32 accumulation in TMEM. The running state stays in TMEM in fp32 for the whole
+// sequence; where it enters a product as an operand it is written to shared memory as TWO bf16 tiles (value and
+// rounding remainder) and multiplied twice, so the state contributes ~16 mantissa bits: dQ is a difference of two
+// nearly equal terms (G S^T against dden z) and a single bf16 copy of S loses it. z and dz are applied in fp32 by the
+// threads. The same natural [d_k][d_v] tile serves as MN-major B operand (x S) and as K-major B operand (x S^T).
+// No state is ever stored per token or per chunk: both backward kernels recompute what they need from Q, K, V, dO, O
+// and the saved denominators.
+//
+// `s_in` / `s_out` (optional) are the state before the first token and after the last one; a sequence-parallel rank
+// passes the sum of the lower ranks' states in and hands its own total out. Every wait is bounded (status word).
+#include "../common/ptx.cuh"
+#include "../common/tensormap.h"
+#include "flash_sm100.h"
+
+namespace b200 {
+
+constexpr int LA_C = 128;                    // tokens per chunk = rows of every product = TMEM lanes
+
+struct LinAttnArgs {
+  AttnTensor q, k, v, o;                     // bf16 [B, S, H, hd] (any strides, hd contiguous)
+  AttnTensor dout, dq, dk, dv;               // backward
+  float* den;                                // [B, H, S] fp32: denominators incl. eps (written by forward, read by backward)
+  const float* s_in;                         // optional [B*H][hd*hd + hd] fp32: state (row-major [d_k][d_v]) then z
+  float* s_out;                              // optional, same layout: state after the last token (forward / state pass)
+  const float* ds_in;                        // backward 2, optional: dS, dz flowing in from the tokens after this slice
+  float* ds_out;                             // backward 2, optional: dS, dz at the first token (for the slices before it)
+  int B, H, S, hd;
+  float scale, eps;
+  int kind;                                  // 0: ELU + 1, 1: ReLU^2
+  int state_only;                            // forward: only accumulate the state (reads K, V; writes s_out)
+  uint32_t* status;
+};
+
+__device__ __forceinline__ float la_phi(float x, int kind) { return kind == 0 ? (x > 0.f ? x + 1.f : __expf(x)) : (x > 0.f ? x * x : 0.f); }
+// derivative of phi expressed through its value: ELU+1: 1 for x > 0 (phi > 1) else phi; ReLU^2: 2 sqrt(phi)
+__device__ __forceinline__ float la_dphi_from_phi(float p, int kind) { return kind == 0 ? (p > 1.f ? 1.f : p) : 2.f * sqrtf(p); }
+
+// phi(scale * x) in place on a [128 rows][HD] bf16 tile of 128-byte-swizzled 64-column atoms; thread = row.
+// Rows at or beyond `valid` become zero (TMA fills them with zeros, and phi(0) is 1 for ELU + 1).
+template <int HD>
+__device__ __forceinline__ void la_phi_tile(uint8_t* tile, int row, int valid, float scale, int kind) {
+#pragma unroll
+  for (int a = 0; a < HD / 64; ++a)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      uint4* p = reinterpret_cast<uint4*>(tile + a * (LA_C * 128) + sw128_offset(row, c));
+      uint4 u = *p;
+      uint32_t* w = &u.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(w[j]);
+        w[j] = row < valid ? pack_bf16x2(la_phi(f.x * scale, kind), la_phi(f.y * scale, kind)) : 0u;
+      }
+      *p = u;
+    }
+}
+
+// fp32 row of a tile (thread = row) -> registers
+template <int HD>
+__device__ __forceinline__ void la_read_row(const uint8_t* tile, int row, float* out) {
+#pragma unroll
+  for (int a = 0; a < HD / 64; ++a)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint4 u = *reinterpret_cast<const uint4*>(tile + a * (LA_C * 128) + sw128_offset(row, c));
+      const uint32_t* w = &u.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16x2(w[j]); out[a * 64 + c * 8 + 2 * j] = f.x; out[a * 64 + c * 8 + 2 * j + 1] = f.y; }
+    }
+}
+
+// column sums of a tile: thread k (< HD) returns sum over the 128 rows of element (row, k)
+template <int HD>
+__device__ __forceinline__ float la_colsum(const uint8_t* tile, int k) {
+  const uint8_t* base = tile + (k >> 6) * (LA_C * 128) + (k & 7) * 2;
+  const int chunk = (k & 63) >> 3;
+  float s0 = 0.f, s1 = 0.f;
+#pragma unroll 8
+  for (int r = 0; r < LA_C; r += 2) {
+    s0 += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(base + sw128_offset(r, chunk)));
+    s1 += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(base + sw128_offset(r + 1, chunk)));
+  }
+  return s0 + s1;
+}
+// weighted column sums: sum_r w[r] * tile(r, k)
+template <int HD>
+__device__ __forceinline__ float la_colsum_w(const uint8_t* tile, int k, const float* w) {
+  const uint8_t* base = tile + (k >> 6) * (LA_C * 128) + (k & 7) * 2;
+  const int chunk = (k & 63) >> 3;
+  float s0 = 0.f, s1 = 0.f;
+#pragma unroll 8
+  for (int r = 0; r < LA_C; r += 2) {
+    s0 += w[r] * __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(base + sw128_offset(r, chunk)));
+    s1 += w[r + 1] * __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(base + sw128_offset(r + 1, chunk)));
+  }
+  return s0 + s1;
+}
+
+// One fp32 row of HD values -> bf16 "value" tile and bf16 "remainder" tile (row = thread), [rows][HD] swizzled atoms
+// of `rows` rows each.
+template <int HD>
+__device__ __forceinline__ void la_write_hilo(uint8_t* hi, uint8_t* lo, int rows, int row, const float* v) {
+#pragma unroll
+  for (int g = 0; g < HD / 8; ++g) {
+    uint32_t h[4], l[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = v[g * 8 + 2 * j], b = v[g * 8 + 2 * j + 1];
+      const __nv_bfloat16 ah = __float2bfloat16_rn(a), bh = __float2bfloat16_rn(b);
+      h[j] = pack_bf16x2(__bfloat162float(ah), __bfloat162float(bh));
+      l[j] = pack_bf16x2(a - __bfloat162float(ah), b - __bfloat162float(bh));
+    }
+    const uint32_t off = (g >> 3) * (rows * 128) + sw128_offset(row, g & 7);
+    *reinterpret_cast<uint4*>(hi + off) = make_uint4(h[0], h[1], h[2], h[3]);
+    *reinterpret_cast<uint4*>(lo + off) = make_uint4(l[0], l[1], l[2], l[3]);
+  }
+}
+
+// fp32 row of 128 values -> bf16 K-major [128][128] tile (two atoms), row = thread
+__device__ __forceinline__ void la_write_row128(uint8_t* tile, int row, const float* v) {
+#pragma unroll
+  for (int g = 0; g < 16; ++g) {
+    const uint4 o = make_uint4(pack_bf16x2(v[g * 8], v[g * 8 + 1]), pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]),
+                               pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]), pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]));
+    *reinterpret_cast<uint4*>(tile + (g >> 3) * (LA_C * 128) + sw128_offset(row, g & 7)) = o;
+  }
+}
+
+template <int N>
+__device__ __forceinline__ void la_tmem_row(uint32_t taddr, float* out) {
+#pragma unroll
+  for (int c = 0; c < N / 32; ++c) tmem_ld_x32(taddr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&out[c * 32]));
+  tmem_ld_wait();
+}
+
+// ---- MMA issue helpers (one thread). All tiles: atoms of 64 columns, 128-byte rows, 128-byte swizzle.
+// D[128 x 128] = X Y^T, both operands K-major [128][HD]
+template <int HD>
+__device__ __forceinline__ void la_mma_xyT(uint32_t d, const uint8_t* x, const uint8_t* y) {
+  constexpr uint32_t idesc = make_idesc(128, 128, CFMT_F32, FMT_BF16, FMT_BF16, 0, 0);
+  const uint32_t lx = sdesc_lo(smem_u32(x), 0), ly = sdesc_lo(smem_u32(y), 0);
+#pragma unroll
+  for (int k = 0; k < HD / 16; ++k) {
+    const uint32_t adv = (k >> 2) * (LA_C * 128) + (k & 3) * 32;
+    umma_f16(d, sdesc_at<1024>(lx, adv), sdesc_at<1024>(ly, adv), idesc, k > 0);
+  }
+}
+// D[128 x HD] (+)= P W with P K-major [128][KT] (KT = 128 tokens or HD) and W MN-major: [KT rows][HD], atoms `w_lbo` apart
+template <int HD, int KT>
+__device__ __forceinline__ void la_mma_pw(uint32_t d, const uint8_t* p, const uint8_t* w, uint32_t w_lbo, bool acc) {
+  constexpr uint32_t idesc = make_idesc(128, HD, CFMT_F32, FMT_BF16, FMT_BF16, 0, 1);
+  const uint32_t lp = sdesc_lo(smem_u32(p), 0), lw = sdesc_lo(smem_u32(w), w_lbo);
+#pragma unroll
+  for (int k = 0; k < KT / 16; ++k) {
+    const uint32_t advp = (k >> 2) * (LA_C * 128) + (k & 3) * 32;
+    umma_f16(d, sdesc_at<1024>(lp, advp), sdesc_at<1024>(lw, k * 2048), idesc, acc || k > 0);
+  }
+}
+// D[128 x HD] (+)= X W^T with X K-major [128][HD] and W K-major [HD rows][HD] (atoms of HD rows)
+template <int HD>
+__device__ __forceinline__ void la_mma_xwT(uint32_t d, const uint8_t* x, const uint8_t* w, bool acc) {
+  constexpr uint32_t idesc = make_idesc(128, HD, CFMT_F32, FMT_BF16, FMT_BF16, 0, 0);
+  const uint32_t lx = sdesc_lo(smem_u32(x), 0), lw = sdesc_lo(smem_u32(w), 0);
+#pragma unroll
+  for (int k = 0; k < HD / 16; ++k) {
+    const uint32_t advx = (k >> 2) * (LA_C * 128) + (k & 3) * 32, advw = (k >> 2) * (HD * 128) + (k & 3) * 32;
+    umma_f16(d, sdesc_at<1024>(lx, advx), sdesc_at<1024>(lw, advw), idesc, acc || k > 0);
+  }
+}
+// State update D[128 (d_k, zero-padded) x HD] (+)= X^T W over the 128 tokens: X, W MN-major [128 tokens][HD].
+// `x_lbo` is the distance from X's first 64-column atom to the next one; for HD = 64 it points at a tile of zeros, so
+// that the product has the 128 rows the instruction wants and rows 64..127 of D stay zero.
+template <int HD>
+__device__ __forceinline__ void la_mma_xTw(uint32_t d, const uint8_t* x, uint32_t x_lbo, const uint8_t* w, bool acc) {
+  constexpr uint32_t idesc = make_idesc(128, HD, CFMT_F32, FMT_BF16, FMT_BF16, 1, 1);
+  const uint32_t lx = sdesc_lo(smem_u32(x), x_lbo), lw = sdesc_lo(smem_u32(w), LA_C * 128);
+#pragma unroll
+  for (int k = 0; k < LA_C / 16; ++k)
+    umma_f16(d, sdesc_at<1024>(lx, k * 2048), sdesc_at<1024>(lw, k * 2048), idesc, acc || k > 0);
+}
+
+template <int HD>
+struct LaSmem {
+  static constexpr int TILE = LA_C * HD * 2;          // one [128][HD] operand tile
+  static constexpr int PT = LA_C * LA_C * 2;          // one [128][128] tile
+  static constexpr int ST = HD * HD * 2;              // one state tile [HD][HD]
+  static constexpr int ZERO = HD == 64 ? TILE : 0;    // zero atom that pads the state update to 128 rows
+};
+
+// ---------------------------------------------------------------------------------------------------- forward
+template <int HD>
+__global__ void __launch_bounds__(128, 1)
+linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const LinAttnArgs p) {
+  using L = LaSmem<HD>;
+  constexpr int KA = HD / 64;
+  constexpr uint32_t COL_A = 0, COL_NUM = 128, COL_S = 256;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + L::TILE;                 // 2 stages
+  uint8_t* sZero = sK + 2 * L::TILE;          // HD = 64 only
+  uint8_t* sV = sZero + L::ZERO;
+  uint8_t* sP = sV + L::TILE;
+  uint8_t* sShi = sP + L::PT;
+  uint8_t* sSlo = sShi + L::ST;
+  float* sz = reinterpret_cast<float*>(sSlo + L::ST);      // [HD]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sz + HD);
+  uint64_t* q_bar = bars; uint64_t* k_bar = bars + 1; uint64_t* v_bar = bars + 3; uint64_t* a_bar = bars + 4; uint64_t* b_bar = bars + 5;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
+  const int n_chunks = (p.S + LA_C - 1) / LA_C;
+  const bool full = !p.state_only;
+  if ((smem_u32(smem) & 1023u) != 0) { if (tid == 0 && p.status) atomicCAS(p.status, 0u, (uint32_t)ST_BAD_ARGUMENT); return; }
+  if (tid == 0) {
+    mbar_init(q_bar, 1); mbar_init(&k_bar[0], 1); mbar_init(&k_bar[1], 1); mbar_init(v_bar, 1); mbar_init(a_bar, 1); mbar_init(b_bar, 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+  }
+  if (warp == 0) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  if (HD == 64) for (int i = tid; i < L::ZERO / 16; i += 128) reinterpret_cast<uint4*>(sZero)[i] = make_uint4(0, 0, 0, 0);
+  // state before the first token: TMEM (fp32) and the two bf16 operand tiles
+  const size_t st_stride = (size_t)HD * HD + HD;
+  if (tid < HD) {
+    float s0[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) s0[i] = p.s_in ? p.s_in[bh * st_stride + (size_t)tid * HD + i] : 0.f;
+    la_write_hilo<HD>(sShi, sSlo, HD, tid, s0);
+    sz[tid] = p.s_in ? p.s_in[bh * st_stride + (size_t)HD * HD + tid] : 0.f;
+  }
+  tc_fence_before_sync();
+  fence_proxy_async_smem();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t trow = tmem_base + (uint32_t(warp * 32) << 16);
+  if (p.s_in) {                                     // TMEM accesses are warp-wide: every lane stores (rows >= HD: zeros)
+#pragma unroll
+    for (int c = 0; c < HD / 32; ++c) {
+      uint32_t r[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) r[i] = tid < HD ? __float_as_uint(p.s_in[bh * st_stride + (size_t)tid * HD + c * 32 + i]) : 0u;
+      tmem_st_x32(trow + COL_S + c * 32, r);
+    }
+    tmem_st_wait();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+
+  auto load = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int chunk) {
+    mbar_expect_tx(bar, L::TILE);
+#pragma unroll
+    for (int a = 0; a < KA; ++a) tma_load_4d(dst + a * (LA_C * 128), tm, bar, a * 64, h, chunk * LA_C, b);
+  };
+  const uint32_t k_lbo[2] = {HD == 64 ? uint32_t(2 * L::TILE) : uint32_t(LA_C * 128), HD == 64 ? uint32_t(L::TILE) : uint32_t(LA_C * 128)};
+  if (tid == 0) {
+    if (full) load(sQ, &tmQ, q_bar, 0);
+    load(sK, &tmK, &k_bar[0], 0);
+    load(sV, &tmV, v_bar, 0);
+    if (n_chunks > 1) load(sK + L::TILE, &tmK, &k_bar[1], 1);
+  }
+  bool ok = true;
+  const bool have_state0 = p.s_in != nullptr;
+  for (int c = 0; c < n_chunks; ++c) {
+    const int st = c & 1;
+    uint8_t* sKc = sK + st * L::TILE;
+    const int valid = min(LA_C, p.S - c * LA_C);
+    // ---- phi in place
+    if (full && !mbar_wait(q_bar, c & 1, p.status, ST_TIMEOUT_TMA_FULL)) ok = false;
+    if (ok && !mbar_wait(&k_bar[st], (c >> 1) & 1, p.status, ST_TIMEOUT_TMA_FULL)) ok = false;
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    if (full) la_phi_tile<HD>(sQ, tid, LA_C, p.scale, p.kind);
+    la_phi_tile<HD>(sKc, tid, valid, p.scale, p.kind);
+    fence_proxy_async_smem();
+    __syncthreads();
+    float den = p.eps;
+    if (full) {
+      if (tid == 0) {
+        tc_fence_after_sync();
+        la_mma_xyT<HD>(tmem_base + COL_A, sQ, sKc);                                   // A = Q~ K~^T
+        la_mma_pw<HD, HD>(tmem_base + COL_NUM, sQ, sShi, HD * 128, false);            // NUM = Q~ S (value + remainder)
+        la_mma_pw<HD, HD>(tmem_base + COL_NUM, sQ, sSlo, HD * 128, true);
+        tc_commit(a_bar);                                                             // covers every reader of Q~
+      }
+      // Q~ . z in fp32 while the tensor core works
+      float qrow[HD];
+      la_read_row<HD>(sQ, tid, qrow);
+#pragma unroll
+      for (int i = 0; i < HD; ++i) den = fmaf(qrow[i], sz[i], den);
+      if (!mbar_wait(a_bar, c & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
+      if (__syncthreads_or(!ok)) { ok = false; break; }
+      tc_fence_after_sync();
+      if (tid == 0 && c + 1 < n_chunks) load(sQ, &tmQ, q_bar, c + 1);              // Q~ has been consumed
+      float a[LA_C];
+      la_tmem_row<LA_C>(trow + COL_A, a);
+      float r0 = 0.f, r1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < LA_C; i += 2) {
+        if (i > tid) a[i] = 0.f;
+        if (i + 1 > tid) a[i + 1] = 0.f;
+        r0 += a[i]; r1 += a[i + 1];
+      }
+      den += r0 + r1;
+      la_write_row128(sP, tid, a);
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+    }
+    __syncthreads();
+    if (tid == 0) {
+      ok = mbar_wait(v_bar, c & 1, p.status, ST_TIMEOUT_TMA_FULL);
+      if (ok) {
+        tc_fence_after_sync();
+        if (full) la_mma_pw<HD, LA_C>(tmem_base + COL_NUM, sP, sV, LA_C * 128, true);                 // NUM += A V
+        la_mma_xTw<HD>(tmem_base + COL_S, sKc, k_lbo[st], sV, have_state0 || c > 0);                   // S += K~^T V
+        tc_commit(b_bar);
+      }
+    }
+    // z += colsum(K~) while the products run; the new z is first read after the barrier below
+    float zk = 0.f;
+    if (tid < HD) zk = la_colsum<HD>(sKc, tid);
+    if (!mbar_wait(b_bar, c & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    tc_fence_after_sync();
+    if (tid == 0) {                                                           // K~ and V of this chunk are free
+      if (c + 1 < n_chunks) load(sV, &tmV, v_bar, c + 1);
+      if (c + 2 < n_chunks) load(sKc, &tmK, &k_bar[st], c + 2);
+    }
+    if (full) {
+      float num[HD];
+      la_tmem_row<HD>(trow + COL_NUM, num);
+      const int tok = c * LA_C + tid;
+      if (tok < p.S) {
+        const float inv = 1.f / den;
+        __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.o.ptr) + (long long)b * p.o.sb + (long long)tok * p.o.ss + (long long)h * p.o.sh;
+#pragma unroll
+        for (int i = 0; i < HD; i += 8)
+          *reinterpret_cast<uint4*>(op + i) = make_uint4(pack_bf16x2(num[i] * inv, num[i + 1] * inv), pack_bf16x2(num[i + 2] * inv, num[i + 3] * inv),
+                                                         pack_bf16x2(num[i + 4] * inv, num[i + 5] * inv), pack_bf16x2(num[i + 6] * inv, num[i + 7] * inv));
+        if (p.den) p.den[((long long)b * p.H + h) * p.S + tok] = den;
+      }
+    }
+    if (tid < HD) sz[tid] += zk;
+    if (full && c + 1 < n_chunks) {                                           // operand copies of the new state
+      float srow[HD];
+      la_tmem_row<HD>(trow + COL_S, srow);
+      if (tid < HD) la_write_hilo<HD>(sShi, sSlo, HD, tid, srow);
+      fence_proxy_async_smem();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+  }
+  if (ok && p.s_out) {
+    tc_fence_after_sync();
+    float srow[HD];
+    la_tmem_row<HD>(trow + COL_S, srow);
+    if (tid < HD) {
+#pragma unroll
+      for (int i = 0; i < HD; i += 4)
+        *reinterpret_cast<float4*>(p.s_out + bh * st_stride + (size_t)tid * HD + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
+      p.s_out[bh * st_stride + (size_t)HD * HD + tid] = sz[tid];
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) { tc_fence_after_sync(); tmem_dealloc(tmem_base, 512); }
+}
+
+// dO and O rows of one token -> G = dO / D (bf16 tile row), returns dden = -(dO . O) / D. Tokens past the end give zeros.
+template <int HD>
+__device__ __forceinline__ float la_load_g(const LinAttnArgs& p, int b, int h, int tok, uint8_t* sG, int row) {
+  float g[HD];
+  float dden = 0.f;
+  if (tok < p.S) {
+    const __nv_bfloat16* dp = reinterpret_cast<const __nv_bfloat16*>(p.dout.ptr) + (long long)b * p.dout.sb + (long long)tok * p.dout.ss + (long long)h * p.dout.sh;
+    const __nv_bfloat16* op = reinterpret_cast<const __nv_bfloat16*>(p.o.ptr) + (long long)b * p.o.sb + (long long)tok * p.o.ss + (long long)h * p.o.sh;
+    const float inv = 1.f / p.den[((long long)b * p.H + h) * p.S + tok];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < HD; i += 8) {
+      const uint4 du = *reinterpret_cast<const uint4*>(dp + i), ou = *reinterpret_cast<const uint4*>(op + i);
+      const uint32_t* dw = &du.x; const uint32_t* ow = &ou.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 d2 = unpack_bf16x2(dw[j]), o2 = unpack_bf16x2(ow[j]);
+        dot = fmaf(d2.x, o2.x, dot); dot = fmaf(d2.y, o2.y, dot);
+        g[i + 2 * j] = d2.x * inv; g[i + 2 * j + 1] = d2.y * inv;
+      }
+    }
+    dden = -dot * inv;
+  } else {
+#pragma unroll
+    for (int i = 0; i < HD; ++i) g[i] = 0.f;
+  }
+#pragma unroll
+  for (int gi = 0; gi < HD / 8; ++gi)
+    *reinterpret_cast<uint4*>(sG + (gi >> 3) * (LA_C * 128) + sw128_offset(row, gi & 7)) =
+        make_uint4(pack_bf16x2(g[gi * 8], g[gi * 8 + 1]), pack_bf16x2(g[gi * 8 + 2], g[gi * 8 + 3]),
+                   pack_bf16x2(g[gi * 8 + 4], g[gi * 8 + 5]), pack_bf16x2(g[gi * 8 + 6], g[gi * 8 + 7]));
+  return dden;
+}
+
+// grad[i] <- scale * phi'(scale * x_i) * grad[i] with x the raw (bf16) row in global memory, then store as bf16
+template <int HD>
+__device__ __forceinline__ void la_store_dphi(const AttnTensor& x, const AttnTensor& dx, int b, int h, int tok, const float* grad, float scale, int kind) {
+  const __nv_bfloat16* xp = reinterpret_cast<const __nv_bfloat16*>(x.ptr) + (long long)b * x.sb + (long long)tok * x.ss + (long long)h * x.sh;
+  __nv_bfloat16* gp = reinterpret_cast<__nv_bfloat16*>(dx.ptr) + (long long)b * dx.sb + (long long)tok * dx.ss + (long long)h * dx.sh;
+#pragma unroll
+  for (int i = 0; i < HD; i += 8) {
+    const uint4 xu = *reinterpret_cast<const uint4*>(xp + i);
+    const uint32_t* xw = &xu.x;
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x2 = unpack_bf16x2(xw[j]);
+      const float a = x2.x * scale, c = x2.y * scale;
+      const float da = kind == 0 ? (a > 0.f ? 1.f : __expf(a)) : (a > 0.f ? 2.f * a : 0.f);
+      const float dc = kind == 0 ? (c > 0.f ? 1.f : __expf(c)) : (c > 0.f ? 2.f * c : 0.f);
+      o[j] = pack_bf16x2(grad[i + 2 * j] * da * scale, grad[i + 2 * j + 1] * dc * scale);
+    }
+    *reinterpret_cast<uint4*>(gp + i) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------- backward 1: dQ
+template <int HD>
+__global__ void __launch_bounds__(128, 1)
+linattn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const LinAttnArgs p) {
+  using L = LaSmem<HD>;
+  constexpr int KA = HD / 64;
+  constexpr uint32_t COL_A = 0, COL_DQ = 128, COL_S = 256;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sG = smem;
+  uint8_t* sK = sG + L::TILE;                 // 2 stages
+  uint8_t* sZero = sK + 2 * L::TILE;
+  uint8_t* sV = sZero + L::ZERO;
+  uint8_t* sP = sV + L::TILE;
+  uint8_t* sShi = sP + L::PT;
+  uint8_t* sSlo = sShi + L::ST;
+  float* sz = reinterpret_cast<float*>(sSlo + L::ST);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sz + HD);
+  uint64_t* k_bar = bars; uint64_t* v_bar = bars + 2; uint64_t* a_bar = bars + 3; uint64_t* b_bar = bars + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
+  const int n_chunks = (p.S + LA_C - 1) / LA_C;
+  if ((smem_u32(smem) & 1023u) != 0) { if (tid == 0 && p.status) atomicCAS(p.status, 0u, (uint32_t)ST_BAD_ARGUMENT); return; }
+  if (tid == 0) {
+    mbar_init(&k_bar[0], 1); mbar_init(&k_bar[1], 1); mbar_init(v_bar, 1); mbar_init(a_bar, 1); mbar_init(b_bar, 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+  }
+  if (warp == 0) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  if (HD == 64) for (int i = tid; i < L::ZERO / 16; i += 128) reinterpret_cast<uint4*>(sZero)[i] = make_uint4(0, 0, 0, 0);
+  const size_t st_stride = (size_t)HD * HD + HD;
+  if (tid < HD) {
+    float s0[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) s0[i] = p.s_in ? p.s_in[bh * st_stride + (size_t)tid * HD + i] : 0.f;
+    la_write_hilo<HD>(sShi, sSlo, HD, tid, s0);
+    sz[tid] = p.s_in ? p.s_in[bh * st_stride + (size_t)HD * HD + tid] : 0.f;
+  }
+  tc_fence_before_sync();
+  fence_proxy_async_smem();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t trow = tmem_base + (uint32_t(warp * 32) << 16);
+  if (p.s_in) {
+#pragma unroll
+    for (int c = 0; c < HD / 32; ++c) {
+      uint32_t r[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) r[i] = tid < HD ? __float_as_uint(p.s_in[bh * st_stride + (size_t)tid * HD + c * 32 + i]) : 0u;
+      tmem_st_x32(trow + COL_S + c * 32, r);
+    }
+    tmem_st_wait();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+
+  auto load = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int chunk) {
+    mbar_expect_tx(bar, L::TILE);
+#pragma unroll
+    for (int a = 0; a < KA; ++a) tma_load_4d(dst + a * (LA_C * 128), tm, bar, a * 64, h, chunk * LA_C, b);
+  };
+  const uint32_t k_lbo[2] = {HD == 64 ? uint32_t(2 * L::TILE) : uint32_t(LA_C * 128), HD == 64 ? uint32_t(L::TILE) : uint32_t(LA_C * 128)};
+  if (tid == 0) {
+    load(sK, &tmK, &k_bar[0], 0);
+    load(sV, &tmV, v_bar, 0);
+    if (n_chunks > 1) load(sK + L::TILE, &tmK, &k_bar[1], 1);
+  }
+  bool ok = true;
+  const bool have_state0 = p.s_in != nullptr;
+  for (int c = 0; c < n_chunks; ++c) {
+    const int st = c & 1;
+    uint8_t* sKc = sK + st * L::TILE;
+    const int valid = min(LA_C, p.S - c * LA_C);
+    const int tok = c * LA_C + tid;
+    // G and dden of this thread's token come straight from global memory while the TMA tiles land
+    const float dden = la_load_g<HD>(p, b, h, tok, sG, tid);
+    if (!mbar_wait(&k_bar[st], (c >> 1) & 1, p.status, ST_TIMEOUT_TMA_FULL)) ok = false;
+    if (ok && !mbar_wait(v_bar, c & 1, p.status, ST_TIMEOUT_TMA_FULL)) ok = false;
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    la_phi_tile<HD>(sKc, tid, valid, p.scale, p.kind);
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after_sync();
+      la_mma_xyT<HD>(tmem_base + COL_A, sG, sV);                                      // T = G V^T
+      la_mma_xwT<HD>(tmem_base + COL_DQ, sG, sShi, false);                            // dQ~ = G S^T (value + remainder)
+      la_mma_xwT<HD>(tmem_base + COL_DQ, sG, sSlo, true);
+      tc_commit(a_bar);
+    }
+    if (!mbar_wait(a_bar, c & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    tc_fence_after_sync();
+    {
+      float a[LA_C];
+      la_tmem_row<LA_C>(trow + COL_A, a);
+#pragma unroll
+      for (int i = 0; i < LA_C; ++i) a[i] = i > tid ? 0.f : a[i] + dden;
+      la_write_row128(sP, tid, a);
+    }
+    tc_fence_before_sync();
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after_sync();
+      la_mma_pw<HD, LA_C>(tmem_base + COL_DQ, sP, sKc, LA_C * 128, true);             // dQ~ += dA K~
+      la_mma_xTw<HD>(tmem_base + COL_S, sKc, k_lbo[st], sV, have_state0 || c > 0);    // S += K~^T V
+      tc_commit(b_bar);
+    }
+    float zk = 0.f;
+    if (tid < HD) zk = la_colsum<HD>(sKc, tid);
+    if (!mbar_wait(b_bar, c & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    tc_fence_after_sync();
+    if (tid == 0) {
+      if (c + 1 < n_chunks) load(sV, &tmV, v_bar, c + 1);
+      if (c + 2 < n_chunks) load(sKc, &tmK, &k_bar[st], c + 2);
+    }
+    {
+      float dq[HD];
+      la_tmem_row<HD>(trow + COL_DQ, dq);
+      if (tok < p.S) {
+#pragma unroll
+        for (int i = 0; i < HD; ++i) dq[i] = fmaf(dden, sz[i], dq[i]);               // z of the chunks before this one
+        la_store_dphi<HD>(p.q, p.dq, b, h, tok, dq, p.scale, p.kind);
+      }
+    }
+    __syncthreads();                                                                  // every thread has read the old z
+    if (tid < HD) sz[tid] += zk;
+    if (c + 1 < n_chunks) {
+      float srow[HD];
+      la_tmem_row<HD>(trow + COL_S, srow);
+      if (tid < HD) la_write_hilo<HD>(sShi, sSlo, HD, tid, srow);
+      fence_proxy_async_smem();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) { tc_fence_after_sync(); tmem_dealloc(tmem_base, 512); }
+}
+
+// ---------------------------------------------------------------------------------------------------- backward 2: dK, dV
+template <int HD>
+__global__ void __launch_bounds__(128, 1)
+linattn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                       const __grid_constant__ CUtensorMap tmV, const LinAttnArgs p) {
+  using L = LaSmem<HD>;
+  constexpr int KA = HD / 64;
+  constexpr uint32_t COL_T = 0, COL_DV = 128, COL_DK = 128 + HD, COL_DS = 128 + 2 * HD;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sZero = sQ + L::TILE;               // HD = 64: pads Q~^T G to 128 rows
+  uint8_t* sK = sZero + L::ZERO;
+  uint8_t* sV = sK + L::TILE;
+  uint8_t* sG = sV + L::TILE;
+  uint8_t* sP = sG + L::TILE;
+  uint8_t* sDhi = sP + L::PT;
+  uint8_t* sDlo = sDhi + L::ST;
+  float* sdz = reinterpret_cast<float*>(sDlo + L::ST);     // [HD]
+  float* sdden = sdz + HD;                                  // [128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdden + LA_C);
+  uint64_t* ld_bar = bars; uint64_t* t_bar = bars + 1; uint64_t* u_bar = bars + 2; uint64_t* b_bar = bars + 3;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
+  const int n_chunks = (p.S + LA_C - 1) / LA_C;
+  const bool full = !p.state_only;               // state_only: only dS / dz of this slice (reads Q, dO, O)
+  if ((smem_u32(smem) & 1023u) != 0) { if (tid == 0 && p.status) atomicCAS(p.status, 0u, (uint32_t)ST_BAD_ARGUMENT); return; }
+  if (tid == 0) {
+    mbar_init(ld_bar, 1); mbar_init(t_bar, 1); mbar_init(u_bar, 1); mbar_init(b_bar, 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+  }
+  if (warp == 0) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  if (HD == 64) for (int i = tid; i < L::ZERO / 16; i += 128) reinterpret_cast<uint4*>(sZero)[i] = make_uint4(0, 0, 0, 0);
+  const size_t st_stride = (size_t)HD * HD + HD;
+  if (tid < HD) {
+    float s0[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) s0[i] = p.ds_in ? p.ds_in[bh * st_stride + (size_t)tid * HD + i] : 0.f;
+    la_write_hilo<HD>(sDhi, sDlo, HD, tid, s0);
+    sdz[tid] = p.ds_in ? p.ds_in[bh * st_stride + (size_t)HD * HD + tid] : 0.f;
+  }
+  tc_fence_before_sync();
+  fence_proxy_async_smem();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t trow = tmem_base + (uint32_t(warp * 32) << 16);
+  if (p.ds_in) {
+#pragma unroll
+    for (int c = 0; c < HD / 32; ++c) {
+      uint32_t r[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) r[i] = tid < HD ? __float_as_uint(p.ds_in[bh * st_stride + (size_t)tid * HD + c * 32 + i]) : 0u;
+      tmem_st_x32(trow + COL_DS + c * 32, r);
+    }
+    tmem_st_wait();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+
+  auto load_all = [&](int chunk) {                      // Q, K, V tiles of one chunk on one barrier
+    mbar_expect_tx(ld_bar, 3 * L::TILE);
+#pragma unroll
+    for (int a = 0; a < KA; ++a) {
+      tma_load_4d(sQ + a * (LA_C * 128), &tmQ, ld_bar, a * 64, h, chunk * LA_C, b);
+      tma_load_4d(sK + a * (LA_C * 128), &tmK, ld_bar, a * 64, h, chunk * LA_C, b);
+      tma_load_4d(sV + a * (LA_C * 128), &tmV, ld_bar, a * 64, h, chunk * LA_C, b);
+    }
+  };
+  const uint32_t q_lbo = HD == 64 ? uint32_t(L::TILE) : uint32_t(LA_C * 128);
+  if (tid == 0) load_all(n_chunks - 1);
+  bool ok = true;
+  const bool have_state0 = p.ds_in != nullptr;
+  uint32_t t_phase = 0;
+  for (int it = 0; it < n_chunks; ++it) {
+    const int c = n_chunks - 1 - it;
+    const int valid = min(LA_C, p.S - c * LA_C);
+    const int tok = c * LA_C + tid;
+    const float dden = la_load_g<HD>(p, b, h, tok, sG, tid);
+    sdden[tid] = dden;
+    if (!mbar_wait(ld_bar, it & 1, p.status, ST_TIMEOUT_TMA_FULL)) ok = false;
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    la_phi_tile<HD>(sQ, tid, LA_C, p.scale, p.kind);
+    if (full) la_phi_tile<HD>(sK, tid, valid, p.scale, p.kind);
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (full) {
+    if (tid == 0) {
+      tc_fence_after_sync();
+      la_mma_xyT<HD>(tmem_base + COL_T, sK, sQ);                                      // A^T = K~ Q~^T   [key][query]
+      tc_commit(t_bar);
+      la_mma_pw<HD, HD>(tmem_base + COL_DV, sK, sDhi, HD * 128, false);               // dV = K~ dS (value + remainder)
+      la_mma_pw<HD, HD>(tmem_base + COL_DV, sK, sDlo, HD * 128, true);
+      la_mma_xwT<HD>(tmem_base + COL_DK, sV, sDhi, false);                            // dK~ = V dS^T
+      la_mma_xwT<HD>(tmem_base + COL_DK, sV, sDlo, true);
+    }
+    if (!mbar_wait(t_bar, t_phase, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
+    t_phase ^= 1;
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    tc_fence_after_sync();
+    {
+      float a[LA_C];
+      la_tmem_row<LA_C>(trow + COL_T, a);
+#pragma unroll
+      for (int i = 0; i < LA_C; ++i) if (i < tid) a[i] = 0.f;                        // keep queries at or after this key
+      la_write_row128(sP, tid, a);
+    }
+    tc_fence_before_sync();
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after_sync();
+      la_mma_pw<HD, LA_C>(tmem_base + COL_DV, sP, sG, LA_C * 128, true);              // dV += mask(A)^T G
+      tc_commit(u_bar);
+      la_mma_xyT<HD>(tmem_base + COL_T, sV, sG);                                      // (G V^T)^T = V G^T   [key][query]
+      tc_commit(t_bar);
+    }
+    if (!mbar_wait(t_bar, t_phase, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;      // implies u_bar: the tensor core runs in order
+    t_phase ^= 1;
+    if (ok && !mbar_wait(u_bar, it & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    tc_fence_after_sync();
+    {
+      float a[LA_C];
+      la_tmem_row<LA_C>(trow + COL_T, a);
+#pragma unroll
+      for (int i = 0; i < LA_C; ++i) a[i] = i < tid ? 0.f : a[i] + sdden[i];
+      la_write_row128(sP, tid, a);
+    }
+    tc_fence_before_sync();
+    fence_proxy_async_smem();
+    }
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after_sync();
+      if (full) la_mma_pw<HD, LA_C>(tmem_base + COL_DK, sP, sQ, LA_C * 128, true);    // dK~ += mask(dA)^T Q~
+      la_mma_xTw<HD>(tmem_base + COL_DS, sQ, q_lbo, sG, have_state0 || it > 0);       // dS += Q~^T G
+      tc_commit(b_bar);
+    }
+    float dzk = 0.f;
+    if (tid < HD) dzk = la_colsum_w<HD>(sQ, tid, sdden);                              // dz += Q~^T dden, fp32
+    if (!mbar_wait(b_bar, it & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    tc_fence_after_sync();
+    if (tid == 0 && c > 0) load_all(c - 1);
+    if (full) {
+      float g[HD];
+      la_tmem_row<HD>(trow + COL_DV, g);
+      if (tok < p.S) {
+        __nv_bfloat16* vp = reinterpret_cast<__nv_bfloat16*>(p.dv.ptr) + (long long)b * p.dv.sb + (long long)tok * p.dv.ss + (long long)h * p.dv.sh;
+#pragma unroll
+        for (int i = 0; i < HD; i += 8)
+          *reinterpret_cast<uint4*>(vp + i) = make_uint4(pack_bf16x2(g[i], g[i + 1]), pack_bf16x2(g[i + 2], g[i + 3]),
+                                                         pack_bf16x2(g[i + 4], g[i + 5]), pack_bf16x2(g[i + 6], g[i + 7]));
+      }
+      la_tmem_row<HD>(trow + COL_DK, g);
+      if (tok < p.S) {
+#pragma unroll
+        for (int i = 0; i < HD; ++i) g[i] += sdz[i];                                   // dz of the chunks after this one
+        la_store_dphi<HD>(p.k, p.dk, b, h, tok, g, p.scale, p.kind);
+      }
+    }
+    __syncthreads();                                                                  // every thread has read the old dz
+    if (tid < HD) sdz[tid] += dzk;
+    if (full && c > 0) {
+      float srow[HD];
+      la_tmem_row<HD>(trow + COL_DS, srow);
+      if (tid < HD) la_write_hilo<HD>(sDhi, sDlo, HD, tid, srow);
+      fence_proxy_async_smem();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+  }
+  if (ok && p.ds_out) {
+    tc_fence_after_sync();
+    float srow[HD];
+    la_tmem_row<HD>(trow + COL_DS, srow);
+    if (tid < HD) {
+#pragma unroll
+      for (int i = 0; i < HD; i += 4)
+        *reinterpret_cast<float4*>(p.ds_out + bh * st_stride + (size_t)tid * HD + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
+      p.ds_out[bh * st_stride + (size_t)HD * HD + tid] = sdz[tid];
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) { tc_fence_after_sync(); tmem_dealloc(tmem_base, 512); }
+}
+
+// ---------------------------------------------------------------------------------------------------- host side
+template <int HD> constexpr int la_fwd_smem() { return 4 * LaSmem<HD>::TILE + LaSmem<HD>::ZERO + LaSmem<HD>::PT + 2 * LaSmem<HD>::ST + HD * 4 + 128; }
+template <int HD> constexpr int la_dkv_smem() { return 4 * LaSmem<HD>::TILE + LaSmem<HD>::ZERO + LaSmem<HD>::PT + 2 * LaSmem<HD>::ST + (HD + LA_C) * 4 + 128; }
+
+static int la_maps(const LinAttnArgs& a, CUtensorMap* tq, CUtensorMap* tk, CUtensorMap* tv) {
+  const auto BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if (tq && make_tmap_attn(tq, a.q.ptr, BF, 2, a.hd, a.H, a.S, a.B, a.q.sh, a.q.ss, a.q.sb, 64, LA_C, CU_TENSOR_MAP_SWIZZLE_128B)) return 101;
+  if (make_tmap_attn(tk, a.k.ptr, BF, 2, a.hd, a.H, a.S, a.B, a.k.sh, a.k.ss, a.k.sb, 64, LA_C, CU_TENSOR_MAP_SWIZZLE_128B)) return 102;
+  if (make_tmap_attn(tv, a.v.ptr, BF, 2, a.hd, a.H, a.S, a.B, a.v.sh, a.v.ss, a.v.sb, 64, LA_C, CU_TENSOR_MAP_SWIZZLE_128B)) return 103;
+  return 0;
+}
+
+template <int HD>
+static int la_set_attrs() {
+  static bool done = false;
+  if (done) return 0;
+  (void)cudaGetLastError();
+  if (cudaFuncSetAttribute(linattn_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, la_fwd_smem<HD>()) != cudaSuccess) return 1;
+  if (cudaFuncSetAttribute(linattn_bwd_dq_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, la_fwd_smem<HD>()) != cudaSuccess) return 1;
+  if (cudaFuncSetAttribute(linattn_bwd_dkv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, la_dkv_smem<HD>()) != cudaSuccess) return 1;
+  done = true;
+  return 0;
+}
+
+template <int HD>
+static int la_launch(const LinAttnArgs& a, int which, cudaStream_t st) {
+  if (la_set_attrs<HD>()) return 104;
+  CUtensorMap tq, tk, tv;
+  const bool need_q = which != 1 && !(which == 0 && a.state_only);
+  if (int rc = la_maps(a, need_q ? &tq : nullptr, &tk, &tv)) return rc;
+  if (!need_q) tq = tk;
+  const unsigned grid = (unsigned)(a.B * a.H);
+  if (which == 0) linattn_fwd_kernel<HD><<<grid, 128, la_fwd_smem<HD>(), st>>>(tq, tk, tv, a);
+  else if (which == 1) linattn_bwd_dq_kernel<HD><<<grid, 128, la_fwd_smem<HD>(), st>>>(tk, tv, a);
+  else linattn_bwd_dkv_kernel<HD><<<grid, 128, la_dkv_smem<HD>(), st>>>(tq, tk, tv, a);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+}  // namespace b200
+
+// which: 0 forward (or state-only pass), 1 backward dQ, 2 backward dK / dV. Causal form; hd 64 or 128; bf16.
+extern "C" int b200_linattn(const b200::LinAttnArgs* a, int which, cudaStream_t st) {
+  using namespace b200;
+  if (a->B <= 0 || a->H <= 0 || a->S <= 0) return 0;
+  if (which < 0 || which > 2) return -2;
+  if (a->hd == 64) return la_launch<64>(*a, which, st);
+  if (a->hd == 128) return la_launch<128>(*a, which, st);
+  return -3;
+}
+extern "C" int b200_linattn_init() { return b200::la_set_attrs<64>() | b200::la_set_attrs<128>(); }

@@ -122,7 +122,7 @@ def cuda():
             torch.cuda.init()
             # load every tensor-core kernel variant and opt in to its shared-memory carve-out now,
             # from the importing thread, instead of lazily from an autograd worker thread
-            for name in ("b200_gemm_init", "b200_flash_fwd_init", "b200_flash_bwd_init"):
+            for name in ("b200_gemm_init", "b200_flash_fwd_init", "b200_flash_bwd_init", "b200_linattn_init"):
                 fn = getattr(_cuda_lib, name)
                 fn.argtypes, fn.restype = [], c_int
                 rc = fn()

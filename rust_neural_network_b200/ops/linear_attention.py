@@ -7,7 +7,12 @@ causal and non-causal, forward and backward.
 per-token rank-1 recurrence and its backward stores all seq*d^2 states (src/linear_attention.rs:214-266,
 502-632). Here the causal form is CHUNKED: tokens are grouped into chunks of C; inside a chunk the
 masked C x C product (phi Q)(phi K)^T is applied to [V | 1] (the extra ones column yields the
-denominator for free), between chunks a d x (d+8) state is carried by an exclusive prefix sum. Every
+denominator for free), between chunks a d x (d+8) state is carried by an exclusive prefix sum.
+
+On a GPU the causal bf16 form with head_dim 64 or 128 runs on the FUSED chunk kernels of
+csrc/attention/linattn_sm100.cu (`FusedCausalLinearAttnFn`): phi in the prologue, all products on tcgen05 with the
+state in TMEM in fp32, the division in the epilogue, one launch forward and two backward. Everything else (non-causal,
+other head sizes, fp32, CPU) takes the composition below, in which every
 product is a batched call of the tcgen05 GEMM kernel (NT for (phi Q)(phi K)^T, TN for the chunk states,
 NN for applying them); the feature maps and the mask are this package's elementwise kernels. The
 backward is the autograd composition of the same kernels (each GEMM's backward is two more GEMMs).
@@ -21,10 +26,96 @@ import math
 import torch
 from torch.autograd import Function
 
+import ctypes as C
+
+from .. import _native as nv
 from . import kernels as K
 from .functional import matmul
 
 CHUNK = 128
+
+
+class LinAttnArgs(C.Structure):
+    _fields_ = [("q", nv.AttnTensor), ("k", nv.AttnTensor), ("v", nv.AttnTensor), ("o", nv.AttnTensor),
+                ("dout", nv.AttnTensor), ("dq", nv.AttnTensor), ("dk", nv.AttnTensor), ("dv", nv.AttnTensor),
+                ("den", C.c_void_p), ("s_in", C.c_void_p), ("s_out", C.c_void_p), ("ds_in", C.c_void_p), ("ds_out", C.c_void_p),
+                ("B", C.c_int), ("H", C.c_int), ("S", C.c_int), ("hd", C.c_int), ("scale", C.c_float), ("eps", C.c_float),
+                ("kind", C.c_int), ("state_only", C.c_int), ("status", C.c_void_p)]
+
+
+nv.register_sigs({"b200_linattn": [C.POINTER(LinAttnArgs), C.c_int, C.c_void_p], "b200_linattn_init": []})
+
+
+def _attn_t(t):
+    """[B, S, H, d] tensor with unit inner stride -> AttnTensor (strides in elements); TMA wants 16-byte multiples."""
+    a = nv.AttnTensor()
+    a.ptr, a.sb, a.ss, a.sh = t.data_ptr(), t.stride(0), t.stride(1), t.stride(2)
+    return a
+
+
+def _tma_ok(t):
+    return t.stride(3) == 1 and all(t.stride(i) % 8 == 0 for i in range(3)) and t.data_ptr() % 16 == 0
+
+
+def fused_supported(q, causal) -> bool:
+    return bool(causal and q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128))
+
+
+def _launch(which, q, k, v, scale, eps, kind, o=None, den=None, dout=None, dq=None, dk=None, dv=None, s_in=None, s_out=None,
+            ds_in=None, ds_out=None, state_only=False):
+    B, S, H, d = q.shape
+    a = LinAttnArgs()
+    a.q, a.k, a.v = _attn_t(q), _attn_t(k), _attn_t(v)
+    for name, t in (("o", o), ("dout", dout), ("dq", dq), ("dk", dk), ("dv", dv)):
+        if t is not None:
+            setattr(a, name, _attn_t(t))
+    a.den, a.s_in, a.s_out, a.ds_in, a.ds_out = nv.ptr(den), nv.ptr(s_in), nv.ptr(s_out), nv.ptr(ds_in), nv.ptr(ds_out)
+    a.B, a.H, a.S, a.hd, a.scale, a.eps = B, H, S, d, float(scale), float(eps)
+    a.kind, a.state_only = (0 if kind == "elu" else 1), int(state_only)
+    a.status = nv.status_word(q.device).data_ptr()
+    nv.check(nv.cuda().b200_linattn(C.byref(a), which, nv.stream_ptr()), "linattn")
+    nv.count_launch()
+
+
+class FusedCausalLinearAttnFn(Function):
+    """Causal linear attention on the fused chunk kernels (csrc/attention/linattn_sm100.cu): one forward kernel, two
+    backward kernels (dQ in sequence order, dK / dV in reverse order), state carried in fp32, nothing stored per chunk.
+    With `sp` the rank's tokens are one slice of a longer sequence: a state-only pass produces the slice's total state,
+    one exchange kernel turns the totals into prefixes (suffixes in the backward), and the main pass starts from them."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, scale, eps, kind, sp):
+        B, S, H, d = q.shape
+        q, k, v = (t if _tma_ok(t) else t.contiguous() for t in (q, k, v))
+        dev = q.device
+        o = torch.empty((B, S, H, d), dtype=torch.bfloat16, device=dev)
+        den = torch.empty((B, H, S), dtype=torch.float32, device=dev)
+        s_in = None
+        if sp is not None and sp.world > 1:
+            tot = torch.empty((B * H, d * d + d), dtype=torch.float32, device=dev)
+            _launch(0, q, k, v, scale, eps, kind, s_out=tot, state_only=True)
+            s_in = sp._exchange(tot, 0)                         # sum of the lower ranks' totals
+        _launch(0, q, k, v, scale, eps, kind, o=o, den=den, s_in=s_in)
+        ctx.save_for_backward(q, k, v, o, den, s_in if s_in is not None else torch.empty(0))
+        ctx.cfg = (scale, eps, kind, sp)
+        return o
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, o, den, s_in = ctx.saved_tensors
+        scale, eps, kind, sp = ctx.cfg
+        s_in = s_in if s_in.numel() else None
+        B, S, H, d = q.shape
+        dout = dout if (_tma_ok(dout) and dout.dtype == torch.bfloat16) else dout.to(torch.bfloat16).contiguous()
+        dq, dk, dv = torch.empty_like(o), torch.empty_like(o), torch.empty_like(o)
+        _launch(1, q, k, v, scale, eps, kind, o=o, den=den, dout=dout, dq=dq, s_in=s_in)
+        ds_in = None
+        if sp is not None and sp.world > 1:
+            tot = torch.empty((B * H, d * d + d), dtype=torch.float32, device=q.device)
+            _launch(2, q, k, v, scale, eps, kind, o=o, den=den, dout=dout, ds_out=tot, state_only=True)
+            ds_in = sp._exchange(tot, 1)                        # sum of the higher ranks' totals
+        _launch(2, q, k, v, scale, eps, kind, o=o, den=den, dout=dout, dk=dk, dv=dv, ds_in=ds_in)
+        return dq, dk, dv, None, None, None, None
 
 
 class _PhiFn(Function):
@@ -92,6 +183,8 @@ def linear_attention(q, k, v, scale: float = 1.0, eps: float = 1e-6, causal: boo
     sequence - the KV states of the other ranks then enter through one state exchange."""
     B, S, H, d = q.shape
     dtype = q.dtype
+    if fused_supported(q, causal) and k.dtype == v.dtype == torch.bfloat16:
+        return FusedCausalLinearAttnFn.apply(q, k, v, float(scale), float(eps), kind, sp)
     pq = _heads_first(phi(q, scale, kind))                  # [BH, S, d]
     pk = _heads_first(phi(k, scale, kind))
     vh = _heads_first(v)

@@ -1,0 +1,106 @@
+"""Fused causal linear attention (csrc/attention/linattn_sm100.cu) against the fp32 O(S^2) oracle: forward and all three
+gradients, both feature maps, head sizes 64 and 128, sequence lengths that are not chunk multiples, a long sequence where
+the state carries most of the mass, the state-in / state-out interface a sequence-parallel rank uses, and bit-exact
+repeatability (nothing in these kernels accumulates with atomics)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+
+
+def _inputs(B, S, H, d, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    mk = lambda: (torch.randn(B, S, H, d, generator=g) * 0.7).to(torch.bfloat16).cuda()
+    return mk(), mk(), mk(), mk()
+
+
+@pytest.mark.parametrize("S,hd", [(128, 64), (300, 64), (1024, 64), (257, 128), (1024, 128)])
+@pytest.mark.parametrize("kind", ["elu", "relu2"])
+def test_fused_forward_backward_match_fp32_oracle(S, hd, kind):
+    from rust_neural_network_b200 import _native as nv
+    from rust_neural_network_b200.ops.linear_attention import FusedCausalLinearAttnFn, linear_attention_ref
+    q, k, v, w = _inputs(2, S, 3, hd)
+    scale = hd ** -0.5
+    qi, ki, vi = (t.clone().requires_grad_(True) for t in (q, k, v))
+    out = FusedCausalLinearAttnFn.apply(qi, ki, vi, scale, 1e-6, kind, None)
+    out.backward(w)
+    torch.cuda.synchronize(); nv.check_status()
+    qr, kr, vr = (t.float().clone().requires_grad_(True) for t in (q, k, v))
+    ref = linear_attention_ref(qr, kr, vr, scale=scale, causal=True, kind=kind)
+    ref.backward(w.float())
+    assert _rel(out, ref) < 1e-2
+    for name, a, b in (("dq", qi.grad, qr.grad), ("dk", ki.grad, kr.grad), ("dv", vi.grad, vr.grad)):
+        assert _rel(a, b) < 2e-2, (name, _rel(a, b))
+
+
+def test_long_sequence_gradients_stay_within_two_percent():
+    """8192 tokens: almost all of every output comes through the carried state (64 chunks)."""
+    from rust_neural_network_b200 import _native as nv
+    from rust_neural_network_b200.ops.linear_attention import FusedCausalLinearAttnFn, linear_attention_ref
+    q, k, v, w = _inputs(1, 8192, 2, 64, seed=3)
+    qi, ki, vi = (t.clone().requires_grad_(True) for t in (q, k, v))
+    out = FusedCausalLinearAttnFn.apply(qi, ki, vi, 0.125, 1e-6, "elu", None)
+    out.backward(w)
+    torch.cuda.synchronize(); nv.check_status()
+    qr, kr, vr = (t.float().clone().requires_grad_(True) for t in (q, k, v))
+    ref = linear_attention_ref(qr, kr, vr, scale=0.125, causal=True, kind="elu")
+    ref.backward(w.float())
+    assert _rel(out, ref) < 1e-2
+    assert _rel(qi.grad, qr.grad) < 2e-2 and _rel(ki.grad, kr.grad) < 2e-2 and _rel(vi.grad, vr.grad) < 2e-2
+
+
+def test_state_in_state_out_equals_one_long_sequence():
+    """Two slices chained through s_out -> s_in (forward) and ds_out -> ds_in (backward) reproduce the unsplit run: what
+    a sequence-parallel rank does with the exchanged states."""
+    from rust_neural_network_b200 import _native as nv
+    from rust_neural_network_b200.ops import linear_attention as LA
+    B, S, H, d = 2, 768, 2, 64
+    q, k, v, w = _inputs(B, S, H, d, seed=5)
+    full_in = [t.clone().requires_grad_(True) for t in (q, k, v)]
+    full = LA.FusedCausalLinearAttnFn.apply(*full_in, 0.125, 1e-6, "elu", None)
+    full.backward(w)
+    h = 384
+    lo, hi = slice(0, h), slice(h, S)
+    st = torch.empty(B * H, d * d + d, device="cuda")
+    o0, o1 = torch.empty_like(q[:, lo]), torch.empty_like(q[:, hi])
+    den0, den1 = torch.empty(B, H, h, device="cuda"), torch.empty(B, H, S - h, device="cuda")
+    cq, ck, cv, cw = (lambda s: [t[:, s].contiguous() for t in (q, k, v, w)])(lo)
+    dq_, dk_, dv_, dw_ = (lambda s: [t[:, s].contiguous() for t in (q, k, v, w)])(hi)
+    LA._launch(0, cq, ck, cv, 0.125, 1e-6, "elu", o=o0, den=den0, s_out=st)
+    LA._launch(0, dq_, dk_, dv_, 0.125, 1e-6, "elu", o=o1, den=den1, s_in=st)
+    assert _rel(torch.cat([o0, o1], 1), full) < 2e-3
+    # backward: the later slice first, its dS / dz flow into the earlier one
+    g = {n: torch.empty_like(q) for n in ("dq", "dk", "dv")}
+    dst = torch.empty_like(st)
+    gq1, gk1, gv1 = (torch.empty_like(o1) for _ in range(3))
+    LA._launch(1, dq_, dk_, dv_, 0.125, 1e-6, "elu", o=o1, den=den1, dout=dw_, dq=gq1, s_in=st)
+    LA._launch(2, dq_, dk_, dv_, 0.125, 1e-6, "elu", o=o1, den=den1, dout=dw_, dk=gk1, dv=gv1, ds_out=dst)
+    gq0, gk0, gv0 = (torch.empty_like(o0) for _ in range(3))
+    LA._launch(1, cq, ck, cv, 0.125, 1e-6, "elu", o=o0, den=den0, dout=cw, dq=gq0)
+    LA._launch(2, cq, ck, cv, 0.125, 1e-6, "elu", o=o0, den=den0, dout=cw, dk=gk0, dv=gv0, ds_in=dst)
+    torch.cuda.synchronize(); nv.check_status()
+    for a, b, name in ((torch.cat([gq0, gq1], 1), full_in[0].grad, "dq"), (torch.cat([gk0, gk1], 1), full_in[1].grad, "dk"),
+                       (torch.cat([gv0, gv1], 1), full_in[2].grad, "dv")):
+        assert _rel(a, b) < 5e-3, (name, _rel(a, b))
+    # the state-only pass yields the same total state as the full pass
+    st2 = torch.empty_like(st)
+    LA._launch(0, cq, ck, cv, 0.125, 1e-6, "elu", s_out=st2, state_only=True)
+    torch.cuda.synchronize()
+    assert _rel(st2, st) < 1e-5
+
+
+def test_run_twice_is_bit_identical():
+    from rust_neural_network_b200.ops.linear_attention import FusedCausalLinearAttnFn
+    q, k, v, w = _inputs(2, 640, 2, 64, seed=9)
+    res = []
+    for _ in range(2):
+        qi, ki, vi = (t.clone().requires_grad_(True) for t in (q, k, v))
+        out = FusedCausalLinearAttnFn.apply(qi, ki, vi, 0.125, 1e-6, "elu", None)
+        out.backward(w)
+        res.append((out.detach().clone(), qi.grad.clone(), ki.grad.clone(), vi.grad.clone()))
+    for a, b in zip(*res):
+        assert torch.equal(a, b)

@@ -37,6 +37,9 @@ constexpr int LA_C = 128;                    // tokens per chunk = rows of every
 struct LinAttnArgs {
   AttnTensor q, k, v, o;                     // bf16 [B, S, H, hd] (any strides, hd contiguous)
   AttnTensor dout, dq, dk, dv;               // backward
+  AttnTensor o_lo;                           // optional bf16 remainder O - bf16(O): written by forward, read by backward.
+                                             // dden = -(dO . O) / D is one half of a difference of nearly equal terms
+                                             // (S^T G against (G . O) z); 8 mantissa bits of O are not enough for it
   float* den;                                // [B, H, S] fp32: denominators incl. eps (written by forward, read by backward)
   const float* s_in;                         // optional [B*H][hd*hd + hd] fp32: state (row-major [d_k][d_v]) then z
   float* s_out;                              // optional, same layout: state after the last token (forward / state pass)
@@ -352,10 +355,20 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (tok < p.S) {
         const float inv = 1.f / den;
         __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.o.ptr) + (long long)b * p.o.sb + (long long)tok * p.o.ss + (long long)h * p.o.sh;
+        __nv_bfloat16* lp = p.o_lo.ptr ? reinterpret_cast<__nv_bfloat16*>(p.o_lo.ptr) + (long long)b * p.o_lo.sb + (long long)tok * p.o_lo.ss + (long long)h * p.o_lo.sh : nullptr;
 #pragma unroll
-        for (int i = 0; i < HD; i += 8)
-          *reinterpret_cast<uint4*>(op + i) = make_uint4(pack_bf16x2(num[i] * inv, num[i + 1] * inv), pack_bf16x2(num[i + 2] * inv, num[i + 3] * inv),
-                                                         pack_bf16x2(num[i + 4] * inv, num[i + 5] * inv), pack_bf16x2(num[i + 6] * inv, num[i + 7] * inv));
+        for (int i = 0; i < HD; i += 8) {
+          uint32_t hi[4], lo[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float x = num[i + 2 * j] * inv, y = num[i + 2 * j + 1] * inv;
+            hi[j] = pack_bf16x2(x, y);
+            const float2 r = unpack_bf16x2(hi[j]);
+            lo[j] = pack_bf16x2(x - r.x, y - r.y);
+          }
+          *reinterpret_cast<uint4*>(op + i) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+          if (lp) *reinterpret_cast<uint4*>(lp + i) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        }
         if (p.den) p.den[((long long)b * p.H + h) * p.S + tok] = den;
       }
     }
@@ -388,34 +401,39 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 // dO and O rows of one token -> G = dO / D (bf16 tile row), returns dden = -(dO . O) / D. Tokens past the end give zeros.
 template <int HD>
 __device__ __forceinline__ float la_load_g(const LinAttnArgs& p, int b, int h, int tok, uint8_t* sG, int row) {
-  float g[HD];
+  uint32_t g[HD / 2];
   float dden = 0.f;
   if (tok < p.S) {
     const __nv_bfloat16* dp = reinterpret_cast<const __nv_bfloat16*>(p.dout.ptr) + (long long)b * p.dout.sb + (long long)tok * p.dout.ss + (long long)h * p.dout.sh;
     const __nv_bfloat16* op = reinterpret_cast<const __nv_bfloat16*>(p.o.ptr) + (long long)b * p.o.sb + (long long)tok * p.o.ss + (long long)h * p.o.sh;
+    const __nv_bfloat16* lp = p.o_lo.ptr ? reinterpret_cast<const __nv_bfloat16*>(p.o_lo.ptr) + (long long)b * p.o_lo.sb + (long long)tok * p.o_lo.ss + (long long)h * p.o_lo.sh : nullptr;
     const float inv = 1.f / p.den[((long long)b * p.H + h) * p.S + tok];
     float dot = 0.f;
 #pragma unroll
     for (int i = 0; i < HD; i += 8) {
       const uint4 du = *reinterpret_cast<const uint4*>(dp + i), ou = *reinterpret_cast<const uint4*>(op + i);
-      const uint32_t* dw = &du.x; const uint32_t* ow = &ou.x;
+      const uint4 lu = lp ? *reinterpret_cast<const uint4*>(lp + i) : make_uint4(0, 0, 0, 0);
+      const uint32_t* dw = &du.x; const uint32_t* ow = &ou.x; const uint32_t* lw = &lu.x;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float2 d2 = unpack_bf16x2(dw[j]), o2 = unpack_bf16x2(ow[j]);
-        dot = fmaf(d2.x, o2.x, dot); dot = fmaf(d2.y, o2.y, dot);
-        g[i + 2 * j] = d2.x * inv; g[i + 2 * j + 1] = d2.y * inv;
+        const float2 d2 = unpack_bf16x2(dw[j]), o2 = unpack_bf16x2(ow[j]), l2 = unpack_bf16x2(lw[j]);
+        // the SAME rounded G enters G V^T on the tensor core and the dot product here, so that the two halves of
+        // dA = G . (V_s - O_t) see one dO; O carries its remainder
+        const uint32_t gp = pack_bf16x2(d2.x * inv, d2.y * inv);
+        const float2 gr = unpack_bf16x2(gp);
+        g[(i >> 1) + j] = gp;
+        dot = fmaf(gr.x, o2.x + l2.x, dot); dot = fmaf(gr.y, o2.y + l2.y, dot);
       }
     }
-    dden = -dot * inv;
+    dden = -dot;
   } else {
 #pragma unroll
-    for (int i = 0; i < HD; ++i) g[i] = 0.f;
+    for (int i = 0; i < HD / 2; ++i) g[i] = 0u;
   }
 #pragma unroll
   for (int gi = 0; gi < HD / 8; ++gi)
     *reinterpret_cast<uint4*>(sG + (gi >> 3) * (LA_C * 128) + sw128_offset(row, gi & 7)) =
-        make_uint4(pack_bf16x2(g[gi * 8], g[gi * 8 + 1]), pack_bf16x2(g[gi * 8 + 2], g[gi * 8 + 3]),
-                   pack_bf16x2(g[gi * 8 + 4], g[gi * 8 + 5]), pack_bf16x2(g[gi * 8 + 6], g[gi * 8 + 7]));
+        make_uint4(g[gi * 4], g[gi * 4 + 1], g[gi * 4 + 2], g[gi * 4 + 3]);
   return dden;
 }
 

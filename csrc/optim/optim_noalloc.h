@@ -13,7 +13,8 @@
 //     launches nothing;
 //   * the library keeps B200_NOALLOC_MAX_SEGMENTS * 4 bytes per GPU for the life of the process;
 //   * the first call on each device resolves the array's device address and should be made before
-//     any stream capture begins;
+//     any stream capture begins; the address is cached per device ordinal without a lock (two threads
+//     racing on a device's first call both look up, and store, the same value);
 //   * the array is shared by all calls and is cleared on the caller's stream at the start of each
 //     call; calls that may overlap on the GPU must be ordered by the caller.
 #pragma once
@@ -33,5 +34,11 @@ enum {
 //   shadow_bf16 : optional flat bf16 copy of the parameters, rewritten by the same kernel (or null)
 //   seg_off     : device array of nseg [begin, end) element ranges (int64 pairs)
 // Returns 0 on success, one of the codes above, or a CUDA error code from the launch.
-extern "C" int b200_muon_rms_noalloc(float* p, const float* g, float* buf, void* shadow_bf16, const long long* seg_off,
-                                     int nseg, float lr, float momentum, float eps, cudaStream_t st);
+#ifdef __cplusplus
+extern "C" {
+#endif
+int b200_muon_rms_noalloc(float* p, const float* g, float* buf, void* shadow_bf16, const long long* seg_off,
+                          int nseg, float lr, float momentum, float eps, cudaStream_t st);
+#ifdef __cplusplus
+}
+#endif

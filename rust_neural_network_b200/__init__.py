@@ -46,8 +46,8 @@ _EXPORTS = {
     "nn": "attention flash_attention BatchNorm1D Dropout FakeQuantize Flatten LayerNorm Linear Module RNNCell ReLU Recursive Sequential "
           "Sigmoid Softmax Tanh CSA GELU HCA SiLU Embedding",
     "offload": "MemoryTier OffloadConfig OffloadModel SsdTensor TieredStore TieredTensor",
-    "optim": "Adam Muon Optimizer RMSprop SGD",
-    "parallel.ddp": "DistributedAdam",
+    "optim": "Adam Muon MultiOptimizer Optimizer RMSprop SGD",
+    "parallel.ddp": "DistributedAdam DistributedMuon",
     "position": "AlibiBias CARoPE LearnedPE PositionalEncoding RoPE SinusoidalPE",
     "quant": "Rotor RotorQuant",
     "quantize": "QuantFormat QuantizedLinear QuantizedModel QuantizedTensor",      # `quantize` itself: the (callable) submodule
@@ -65,7 +65,7 @@ _ALIASES = {"blas_matmul": ("blas", "matmul")}        # `pub use blas::matmul as
 
 _WHERE = {name: (mod, name) for mod, names in _EXPORTS.items() for name in names.split()}
 _WHERE.update(_ALIASES)
-_SUBMODULES = {"activations", "blas", "compiled", "compression", "data", "distill", "distributed", "error", "finetune", "fused", "gpu", "gpu_kernels",
+_SUBMODULES = {"activations", "blas", "compiled", "cpu_ref", "config", "compression", "data", "distill", "distributed", "error", "finetune", "fused", "gpu", "gpu_kernels",
                "grpo", "gui", "int8", "interactive", "linear_attention", "loss", "nn", "offload", "optim", "position", "quant", "quantize", "rl",
                "quantize", "self_improve", "serialize", "simd", "tensor", "ternary", "tokenizer", "train", "models", "ops", "parallel", "utils"}
 _MODEL_MODULES = {"looped_transformer", "mamba", "diffusion", "reasoning"}       # crate-root modules that live under models/

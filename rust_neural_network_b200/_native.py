@@ -186,6 +186,28 @@ def check(rc: int, what: str) -> None:
         raise RuntimeError(f"{what} failed with code {rc}")
 
 
+NVTX_ENABLED = os.environ.get("B200NN_NVTX", "0") == "1"
+
+
+def traced(family: str):
+    """Decorator: run the function inside an NVTX range named after its kernel family when tracing is on
+    (`utils.metrics.enable_nvtx()` or B200NN_NVTX=1); one boolean test otherwise."""
+    def deco(fn):
+        import functools
+
+        @functools.wraps(fn)
+        def wrapper(*a, **kw):
+            if not NVTX_ENABLED:
+                return fn(*a, **kw)
+            torch.cuda.nvtx.range_push(family)
+            try:
+                return fn(*a, **kw)
+            finally:
+                torch.cuda.nvtx.range_pop()
+        return wrapper
+    return deco
+
+
 _status_words: dict = {}
 
 

@@ -146,8 +146,10 @@ def clip_grad_norm(params, max_norm: float) -> float:
 
 
 class FastTrainer:
-    def __init__(self, model, config: Optional[FastTrainConfig] = None):
+    def __init__(self, model, config: Optional[FastTrainConfig] = None, logger=None):
+        """`logger`: a `utils.metrics.MetricsLogger`; every recorded `TrainPoint` is also appended to it as one JSON line."""
         self._model = model
+        self.logger = logger
         self.config = config or FastTrainConfig()
         self._history: List[TrainPoint] = []
         self._total_steps = 0
@@ -196,6 +198,8 @@ class FastTrainer:
                         elapsed = time.time() - start
                         pt = TrainPoint(epoch, step, float(torch.stack(losses).mean()), lr, elapsed)
                         self._history.append(pt)
+                        if self.logger is not None:
+                            self.logger.log(step, epoch=epoch, loss=pt.loss, lr=pt.lr, steps_per_s=step / max(elapsed, 1e-9))
                         if cfg.verbose:
                             print(f"  Epoch {epoch + 1} Step {step}: loss={pt.loss:.4f} lr={pt.lr:.6f} ({step / max(elapsed, 1e-9):.1f} steps/s)")
             if accum > 0:

@@ -121,6 +121,7 @@ def _tma_ready(t: torch.Tensor) -> torch.Tensor:
     return buf[..., : t.shape[-1]]
 
 
+@nv.traced("gemm")
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias=None, act: str = "none",
          residual=None, aux_in=None, dact: str = "none", want_aux: bool = False, alpha: float = 1.0,
          out_dtype=None, accumulate_into=None, splits: int = 0, bn: int = 0, alpha_t=None, row_scale=None, col_scale=None):

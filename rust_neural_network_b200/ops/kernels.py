@@ -234,6 +234,7 @@ def embedding_bwd(grad_out, ids, vocab):
 
 
 # ----------------------------------------------------------------------------- normalisation
+@nv.traced("norm")
 def layernorm_fwd(x2d, gamma, beta, eps):
     rows, d = x2d.shape
     if not x2d.is_cuda:
@@ -252,6 +253,7 @@ def layernorm_fwd(x2d, gamma, beta, eps):
     return y, mean, rstd
 
 
+@nv.traced("norm")
 def add_layernorm_fwd(x2d, res2d, gamma, beta, eps):
     """(s, y, mean, rstd) with s = x + res and y = LayerNorm(s): the residual add of the layer before and the
     normalisation in one pass over the row (bf16 rows of a width the 16-byte-access kernel takes; two kernels
@@ -274,6 +276,7 @@ def add_layernorm_fwd(x2d, res2d, gamma, beta, eps):
     return s, y, mean, rstd
 
 
+@nv.traced("norm")
 def layernorm_bwd(dy2d, x2d, gamma, mean, rstd, dres=None, dgamma=None, dbeta=None):
     """Returns (dx [+ dres], dgamma, dbeta). `dres` is an optional gradient of the same shape that is
     added to dx in the same pass (the residual branch); dgamma/dbeta may be existing fp32
@@ -347,6 +350,7 @@ def batchnorm_bwd(dy2d, x2d, gamma, mean, rstd, training):
 
 
 # ----------------------------------------------------------------------------- losses
+@nv.traced("loss")
 def ce_label(logits2d, labels, want_grad=True):
     """Mean cross-entropy over rows with integer labels; returns (loss 0-d fp32, dlogits or None).
     dlogits already carries the 1/rows factor."""
@@ -442,6 +446,7 @@ def attention_ref(q, k, v, scale, causal):
     return (p @ vf).permute(0, 2, 1, 3)
 
 
+@nv.traced("flash_attention")
 def flash_fwd(q, k, v, scale, causal):
     """q,k,v: [B, S, H, hd] bf16 views (hd contiguous). Returns (o [B,S,H,hd] bf16, lse [B,H,S] fp32)."""
     B, Sq, H, hd = q.shape
@@ -465,6 +470,7 @@ def flash_fwd(q, k, v, scale, causal):
     return o, lse
 
 
+@nv.traced("flash_attention")
 def flash_bwd(dout, q, k, v, o, lse, scale, causal, dq=None, dk=None, dv=None):
     """Gradients of flash_fwd. dq/dk/dv may be preallocated strided views (e.g. slices of a fused dQKV)."""
     B, Sq, H, hd = q.shape
@@ -489,6 +495,7 @@ def flash_bwd(dout, q, k, v, o, lse, scale, causal, dq=None, dk=None, dv=None):
 
 
 # ----------------------------------------------------------------------------- optimizers (flat buffers)
+@nv.traced("optimizer")
 def adam_step(p, g, m, v, shadow, lr, b1, b2, eps, weight_decay, torch_form, step_t, grad_scale=None):
     """One fused Adam step over flat fp32 buffers; `step_t` is a 1-element fp32 device tensor holding
     the number of steps taken so far (incremented here)."""

@@ -37,7 +37,7 @@ CHUNK = 128
 
 class LinAttnArgs(C.Structure):
     _fields_ = [("q", nv.AttnTensor), ("k", nv.AttnTensor), ("v", nv.AttnTensor), ("o", nv.AttnTensor),
-                ("dout", nv.AttnTensor), ("dq", nv.AttnTensor), ("dk", nv.AttnTensor), ("dv", nv.AttnTensor),
+                ("dout", nv.AttnTensor), ("dq", nv.AttnTensor), ("dk", nv.AttnTensor), ("dv", nv.AttnTensor), ("o_lo", nv.AttnTensor),
                 ("den", C.c_void_p), ("s_in", C.c_void_p), ("s_out", C.c_void_p), ("ds_in", C.c_void_p), ("ds_out", C.c_void_p),
                 ("B", C.c_int), ("H", C.c_int), ("S", C.c_int), ("hd", C.c_int), ("scale", C.c_float), ("eps", C.c_float),
                 ("kind", C.c_int), ("state_only", C.c_int), ("status", C.c_void_p)]
@@ -61,12 +61,13 @@ def fused_supported(q, causal) -> bool:
     return bool(causal and q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128))
 
 
+@nv.traced("linear_attention")
 def _launch(which, q, k, v, scale, eps, kind, o=None, den=None, dout=None, dq=None, dk=None, dv=None, s_in=None, s_out=None,
-            ds_in=None, ds_out=None, state_only=False):
+            ds_in=None, ds_out=None, state_only=False, o_lo=None):
     B, S, H, d = q.shape
     a = LinAttnArgs()
     a.q, a.k, a.v = _attn_t(q), _attn_t(k), _attn_t(v)
-    for name, t in (("o", o), ("dout", dout), ("dq", dq), ("dk", dk), ("dv", dv)):
+    for name, t in (("o", o), ("dout", dout), ("dq", dq), ("dk", dk), ("dv", dv), ("o_lo", o_lo)):
         if t is not None:
             setattr(a, name, _attn_t(t))
     a.den, a.s_in, a.s_out, a.ds_in, a.ds_out = nv.ptr(den), nv.ptr(s_in), nv.ptr(s_out), nv.ptr(ds_in), nv.ptr(ds_out)
@@ -95,26 +96,30 @@ class FusedCausalLinearAttnFn(Function):
             tot = torch.empty((B * H, d * d + d), dtype=torch.float32, device=dev)
             _launch(0, q, k, v, scale, eps, kind, s_out=tot, state_only=True)
             s_in = sp._exchange(tot, 0)                         # sum of the lower ranks' totals
-        _launch(0, q, k, v, scale, eps, kind, o=o, den=den, s_in=s_in)
-        ctx.save_for_backward(q, k, v, o, den, s_in if s_in is not None else torch.empty(0))
+        # the backward needs more of O than its bf16 value (see csrc/attention/linattn_sm100.cu: o_lo): keep the remainder
+        need_grad = any(t.requires_grad for t in (q, k, v))
+        o_lo = torch.empty_like(o) if need_grad else None
+        _launch(0, q, k, v, scale, eps, kind, o=o, den=den, s_in=s_in, o_lo=o_lo)
+        ctx.save_for_backward(q, k, v, o, den, s_in if s_in is not None else torch.empty(0), o_lo if o_lo is not None else torch.empty(0))
         ctx.cfg = (scale, eps, kind, sp)
         return o
 
     @staticmethod
     def backward(ctx, dout):
-        q, k, v, o, den, s_in = ctx.saved_tensors
+        q, k, v, o, den, s_in, o_lo = ctx.saved_tensors
         scale, eps, kind, sp = ctx.cfg
         s_in = s_in if s_in.numel() else None
+        o_lo = o_lo if o_lo.numel() else None
         B, S, H, d = q.shape
         dout = dout if (_tma_ok(dout) and dout.dtype == torch.bfloat16) else dout.to(torch.bfloat16).contiguous()
         dq, dk, dv = torch.empty_like(o), torch.empty_like(o), torch.empty_like(o)
-        _launch(1, q, k, v, scale, eps, kind, o=o, den=den, dout=dout, dq=dq, s_in=s_in)
+        _launch(1, q, k, v, scale, eps, kind, o=o, den=den, dout=dout, dq=dq, s_in=s_in, o_lo=o_lo)
         ds_in = None
         if sp is not None and sp.world > 1:
             tot = torch.empty((B * H, d * d + d), dtype=torch.float32, device=q.device)
-            _launch(2, q, k, v, scale, eps, kind, o=o, den=den, dout=dout, ds_out=tot, state_only=True)
+            _launch(2, q, k, v, scale, eps, kind, o=o, den=den, dout=dout, ds_out=tot, state_only=True, o_lo=o_lo)
             ds_in = sp._exchange(tot, 1)                        # sum of the higher ranks' totals
-        _launch(2, q, k, v, scale, eps, kind, o=o, den=den, dout=dout, dk=dk, dv=dv, ds_in=ds_in)
+        _launch(2, q, k, v, scale, eps, kind, o=o, den=den, dout=dout, dk=dk, dv=dv, ds_in=ds_in, o_lo=o_lo)
         return dq, dk, dv, None, None, None, None
 
 
@@ -225,10 +230,20 @@ def linear_attention(q, k, v, scale: float = 1.0, eps: float = 1e-6, causal: boo
     return out.to(dtype).reshape(B, H, S, d).permute(0, 2, 1, 3)
 
 
-def linear_attention_ref(q, k, v, scale=1.0, eps=1e-6, causal=False, kind="elu"):
-    """O(S^2) fp32 reference (the role of `naive_reference`, src/linear_attention.rs:684-719)."""
+def linear_attention_ref(q, k, v, scale=1.0, eps=1e-6, causal=False, kind="elu", feature_dtype=None):
+    """O(S^2) fp32 reference (the role of `naive_reference`, src/linear_attention.rs:684-719). `feature_dtype=torch.bfloat16`
+    rounds phi(sQ) and phi(sK) to bf16 (straight-through for the gradient) and computes everything else in fp32: the
+    function a kernel with bf16 tensor-core operands evaluates. ELU + 1 features sit near 1, where bf16 resolves 2^-8, while
+    dQ / dK are differences of nearly equal sums over them, so this rounding alone moves dQ by a few per cent."""
     f = (lambda x: torch.where(x > 0, x + 1, torch.exp(x))) if kind == "elu" else (lambda x: torch.relu(x) ** 2)
-    pq = f(q.float() * scale).permute(0, 2, 1, 3); pk = f(k.float() * scale).permute(0, 2, 1, 3); vv = v.float().permute(0, 2, 1, 3)
+
+    def feat(x):
+        p = f(x.float() * scale)
+        if feature_dtype is not None:
+            p = p + (p.to(feature_dtype).float() - p).detach()
+        return p.permute(0, 2, 1, 3)
+
+    pq, pk, vv = feat(q), feat(k), v.float().permute(0, 2, 1, 3)
     a = pq @ pk.transpose(-1, -2)
     if causal:
         S = a.shape[-1]

@@ -90,6 +90,7 @@ def _isbf(t):
     raise TypeError("scan kernels take bf16 or fp32")
 
 
+@nv.traced("selective_scan")
 def scan_fwd_raw(u, delta, A, Bm, Cm, Dskip, z, delta_bias, delta_softplus, save_ck):
     Bsz, S, D = u.shape
     N = A.shape[1]
@@ -116,6 +117,7 @@ def scan_fwd_raw(u, delta, A, Bm, Cm, Dskip, z, delta_bias, delta_softplus, save
     return y, hck
 
 
+@nv.traced("selective_scan")
 def scan_bwd_raw(dy, u, delta, A, Bm, Cm, Dskip, z, delta_bias, delta_softplus, hck):
     Bsz, S, D = u.shape
     N = A.shape[1]

@@ -40,8 +40,14 @@ class Trainer:
     """`Trainer(model, optimizer, loss_fn)`; if `loss_fn` is None the model must expose
     `loss(inputs, targets)` (the fused LM head + cross-entropy path)."""
 
-    def __init__(self, model, optimizer, loss_fn=None, use_cuda_graph: bool = False, grad_clip: Optional[float] = None):
+    def __init__(self, model, optimizer, loss_fn=None, use_cuda_graph: bool = False, grad_clip: Optional[float] = None,
+                 logger=None, log_every: int = 1, tokens_per_step: int = 0):
+        """`logger`: a `utils.metrics.MetricsLogger`; every `log_every` steps one record (step, loss, ms per step since the
+        last record measured with CUDA events, tokens/s when `tokens_per_step` is given, kernel launches per step) is
+        appended. Reading the loss for the record synchronises, so leave `logger` off in timed runs."""
         self.model, self.optimizer, self.loss_fn = model, optimizer, loss_fn
+        self.logger, self.log_every, self.tokens_per_step = logger, max(1, int(log_every)), int(tokens_per_step)
+        self._log_event = None
         self.use_cuda_graph = use_cuda_graph
         self.grad_clip = grad_clip
         if grad_clip is not None and hasattr(optimizer, "max_grad_norm"):
@@ -52,16 +58,39 @@ class Trainer:
 
     # -- one optimisation step on device tensors
     def _step_device(self, x, y):
-        self.optimizer.zero_grad()
-        if self.loss_fn is None:
-            loss = self.model.loss(x, y)
-        else:
-            loss = self.loss_fn(self.model(x), y)
-        loss.backward()
-        if self.grad_clip is not None:
-            self.optimizer.clip_grad_norm(self.grad_clip)
-        self.optimizer.step()
+        from .utils.metrics import nvtx_range
+        with nvtx_range("zero_grad"):
+            self.optimizer.zero_grad()
+        with nvtx_range("forward"):
+            if self.loss_fn is None:
+                loss = self.model.loss(x, y)
+            else:
+                loss = self.loss_fn(self.model(x), y)
+        with nvtx_range("backward"):
+            loss.backward()
+        with nvtx_range("optimizer"):
+            if self.grad_clip is not None:
+                self.optimizer.clip_grad_norm(self.grad_clip)
+            self.optimizer.step()
         return loss.detach()
+
+    def _log(self, loss):
+        if self.logger is None or self.steps % self.log_every:
+            return
+        rec = {"loss": float(loss)}
+        if torch.cuda.is_available() and self.model.device.type == "cuda":
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            ev.synchronize()
+            if self._log_event is not None:
+                ms = self._log_event.elapsed_time(ev) / self.log_every
+                rec["ms_per_step"] = ms
+                if self.tokens_per_step:
+                    rec["tokens_per_s"] = self.tokens_per_step / ms * 1e3
+            self._log_event = ev
+        if getattr(self, "launches_per_step", None):
+            rec["launches_per_step"] = self.launches_per_step
+        self.logger.log(self.steps, **rec)
 
     def _to_device(self, t, like_dtype=None):
         dev = self.model.device
@@ -106,9 +135,11 @@ class Trainer:
             self._static[1].copy_(targets, non_blocking=True)
             self._graph.replay()
             self.steps += 1
+            self._log(self._static_loss)
             return self._static_loss
         loss = self._step_device(self._to_device(inputs, cd), self._to_device(targets))
         self.steps += 1
+        self._log(loss)
         return loss
 
     def train_epoch(self, loader) -> float:

@@ -5,6 +5,7 @@ line and the same numbers feed the HTML dashboards of `gui`.
 """
 from __future__ import annotations
 
+import contextlib
 import json
 import os
 import time
@@ -17,8 +18,9 @@ ROOT = Path(__file__).resolve().parents[2]
 
 
 def measured_peaks() -> Dict[str, float]:
-    """Roofline denominators: the copy bandwidth and bf16 GEMM throughput measured on this pool's GPUs when the
-    file exists, otherwise the documented fallback (`kind` says which)."""
+    """Roofline denominators: the copy bandwidth and bf16 GEMM throughput recorded for this installation's GPUs in
+    `MEASURED_PEAKS.json` at the repository root when that file exists, otherwise the documented fallback (`kind` says
+    which)."""
     f = ROOT / "MEASURED_PEAKS.json"
     if f.exists():
         d = json.loads(f.read_text())
@@ -89,3 +91,44 @@ class MetricsLogger:
 
     def losses(self):
         return [r["loss"] for r in self.records if "loss" in r]
+
+
+# ----------------------------------------------------------------------------------------------- tracing
+def enable_nvtx(on: bool = True) -> None:
+    """Turn on NVTX ranges around this package's kernel families (gemm, flash attention, linear attention, scan, norm,
+    loss, optimizer, collectives) and around the phases of `Trainer` steps. Off by default: a range costs about a
+    microsecond on the host."""
+    from .. import _native as nv
+    nv.NVTX_ENABLED = bool(on) and torch.cuda.is_available()
+
+
+@contextlib.contextmanager
+def nvtx_range(name: str):
+    """An NVTX range that is free when tracing is off or no GPU is present."""
+    from .. import _native as nv
+    if nv.NVTX_ENABLED:
+        torch.cuda.nvtx.range_push(name)
+        try:
+            yield
+        finally:
+            torch.cuda.nvtx.range_pop()
+    else:
+        yield
+
+
+@contextlib.contextmanager
+def profile_to(path: str, with_stack: bool = False):
+    """Record everything inside the block with `torch.profiler` (CPU + CUDA activities, this package's NVTX ranges as
+    user annotations) and export a Chrome trace to `path`."""
+    from torch.profiler import ProfilerActivity, profile
+    acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if torch.cuda.is_available() else [])
+    from .. import _native as nv
+    was = nv.NVTX_ENABLED
+    enable_nvtx(True)
+    try:
+        with profile(activities=acts, with_stack=with_stack) as prof:
+            yield prof
+        os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+        prof.export_chrome_trace(path)
+    finally:
+        nv.NVTX_ENABLED = was

@@ -40,3 +40,44 @@ def test_config_presets():
     assert tuple(mm(ids).shape) == (2, 16, 64)
     mo, _ = config.build_model("moe_lm", device="cpu", vocab=64, d_model=32, layers=1, heads=2, num_experts=4, top_k=2, num_shared=1, expert_hidden=16, seq_len=16)
     assert tuple(mo(ids).shape) == (2, 16, 64)
+
+
+def test_trainer_and_fast_trainer_write_metrics_lines(tmp_path):
+    """The JSONL logger is fed by the training loops themselves (one record per logged step)."""
+    import json
+
+    import torch
+
+    from rust_neural_network_b200 import nn
+    from rust_neural_network_b200.finetune import FastTrainConfig, FastTrainer
+    from rust_neural_network_b200.loss import MSELoss
+    from rust_neural_network_b200.optim import Adam
+    from rust_neural_network_b200.train import SimpleDataLoader, Trainer
+    from rust_neural_network_b200.utils.metrics import MetricsLogger
+    torch.manual_seed(0)
+    model = nn.Sequential().add(nn.Linear(4, 8)).add(nn.ReLU()).add(nn.Linear(8, 1))
+    x, y = torch.randn(16, 4), torch.randn(16, 1)
+    log = MetricsLogger(str(tmp_path / "train.jsonl"))
+    tr = Trainer(model, Adam(model.parameters(), lr=1e-2), MSELoss("mean"), logger=log, log_every=2)
+    tr.train_epoch(SimpleDataLoader(x, y, 4))
+    lines = [json.loads(l) for l in (tmp_path / "train.jsonl").read_text().splitlines()]
+    assert [r["step"] for r in lines] == [2, 4] and all("loss" in r for r in lines)
+    log2 = MetricsLogger(str(tmp_path / "fast.jsonl"))
+    cfg = FastTrainConfig()
+    cfg.epochs, cfg.micro_batch_size, cfg.log_every = 2, 4, 1
+    FastTrainer(model, cfg, logger=log2).fit(SimpleDataLoader(x, y, 4), Adam(model.parameters(), lr=1e-2), MSELoss("mean"))
+    assert len(log2.records) >= 2 and all("lr" in r for r in log2.records)
+
+
+def test_nvtx_ranges_are_free_without_a_gpu_and_profile_exports_a_trace(tmp_path):
+    import json
+
+    import torch
+
+    from rust_neural_network_b200.ops.gemm import gemm
+    from rust_neural_network_b200.utils import metrics
+    with metrics.nvtx_range("anything"):
+        pass
+    with metrics.profile_to(str(tmp_path / "trace.json")):
+        gemm(torch.randn(8, 8), torch.randn(8, 8))
+    assert "traceEvents" in json.loads((tmp_path / "trace.json").read_text())

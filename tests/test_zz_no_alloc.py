@@ -31,9 +31,12 @@ def _symbols():
     return noalloc, regular
 
 
-def test_noalloc_matches_regular_entry_point_on_two_calls():
+@pytest.mark.parametrize("index", range(max(1, torch.cuda.device_count())))
+def test_noalloc_matches_regular_entry_point_on_two_calls(index):
+    """On every visible device: the built-in scratch is one array per GPU, looked up on that GPU's first call."""
     noalloc, regular = _symbols()
-    dev = torch.device("cuda")
+    dev = torch.device("cuda", index)
+    torch.cuda.set_device(dev)
     torch.manual_seed(0)
     sizes = [1000, 64, 7, 4096, 333]
     offs, begin = [], 0
@@ -49,7 +52,7 @@ def test_noalloc_matches_regular_entry_point_on_two_calls():
     pb, bufb = p0.clone(), torch.zeros(n, device=dev)
     shb = torch.zeros(n, dtype=torch.bfloat16, device=dev)
     scratch = torch.empty(len(sizes), device=dev)                 # caller-provided scratch of the regular entry
-    stream = torch.cuda.current_stream().cuda_stream
+    stream = torch.cuda.current_stream(dev).cuda_stream
     for g in grads:                                               # two calls in a row
         rc = noalloc(pa.data_ptr(), g.data_ptr(), bufa.data_ptr(), sha.data_ptr(), seg.data_ptr(), len(sizes), 0.02, 0.95, 1e-8, stream)
         assert rc == 0
@@ -64,6 +67,7 @@ def test_noalloc_matches_regular_entry_point_on_two_calls():
     for a, b in offs:
         gap[a:b] = False
     assert torch.equal(pa[gap], p0[gap])                          # elements outside the segments are not touched
+    torch.cuda.set_device(0)
 
 
 def test_noalloc_rejects_more_segments_than_the_builtin_scratch():

@@ -442,6 +442,64 @@ static inline int grid_for(long long work, int block, int max_blocks = 148 * 16)
   return (int)g;
 }
 
+
+// Row softmax over the last axis (rust-nn src/activations.rs:23-62 is forward-only; here it has a backward). One block
+// per row; the row is read twice (maximum + sum, then normalise), fp32 arithmetic. `scale` multiplies the input first;
+// `causal_period` > 0 masks column j of row r when j > r % causal_period (rows of [.., S, S] score matrices).
+template <typename T>
+__global__ void softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int cols, float scale, int causal_period) {
+  const long long r = blockIdx.x;
+  const T* xr = x + r * cols; T* yr = y + r * cols;
+  const int limit = causal_period > 0 ? min(cols, (int)(r % causal_period) + 1) : cols;
+  __shared__ float sh[33];
+  float m = -INFINITY;
+  for (int j = threadIdx.x; j < limit; j += blockDim.x) m = fmaxf(m, to_f(xr[j]) * scale);
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? sh[threadIdx.x] : -INFINITY;
+    for (int o = 16; o > 0; o >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
+    if (threadIdx.x == 0) sh[32] = t;
+  }
+  __syncthreads();
+  m = sh[32];
+  __syncthreads();
+  float sum = 0.f;
+  for (int j = threadIdx.x; j < limit; j += blockDim.x) sum += __expf(to_f(xr[j]) * scale - m);
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? sh[threadIdx.x] : 0.f;
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (threadIdx.x == 0) sh[32] = t;
+  }
+  __syncthreads();
+  const float inv = 1.f / sh[32];
+  for (int j = threadIdx.x; j < cols; j += blockDim.x) yr[j] = from_f<T>(j < limit ? __expf(to_f(xr[j]) * scale - m) * inv : 0.f);
+}
+// dx = scale * y * (dy - sum_j dy_j y_j)
+template <typename T>
+__global__ void softmax_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __restrict__ dx, int cols, float scale) {
+  const long long r = blockIdx.x;
+  const T* gr = dy + r * cols; const T* yr = y + r * cols; T* dr = dx + r * cols;
+  __shared__ float sh[33];
+  float dot = 0.f;
+  for (int j = threadIdx.x; j < cols; j += blockDim.x) dot += to_f(gr[j]) * to_f(yr[j]);
+  for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = dot;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? sh[threadIdx.x] : 0.f;
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (threadIdx.x == 0) sh[32] = t;
+  }
+  __syncthreads();
+  dot = sh[32];
+  for (int j = threadIdx.x; j < cols; j += blockDim.x) dr[j] = from_f<T>(scale * to_f(yr[j]) * (to_f(gr[j]) - dot));
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -524,6 +582,22 @@ int b200_reduce(const void* x, float* out, long long n, int what, int is_bf16, c
   if (n <= 0) return 0;
   if (is_bf16) reduce_kernel<__nv_bfloat16><<<grid_for(n, 256, 592), 256, 0, st>>>((const __nv_bfloat16*)x, out, n, what);
   else reduce_kernel<float><<<grid_for(n, 256, 592), 256, 0, st>>>((const float*)x, out, n, what);
+  return (int)cudaGetLastError();
+}
+
+int b200_softmax_fwd(const void* x, void* y, long long rows, int cols, float scale, int causal_period, int is_bf16, cudaStream_t st) {
+  if (rows <= 0 || cols <= 0) return 0;
+  const int threads = cols >= 1024 ? 256 : 128;
+  if (is_bf16) softmax_fwd_kernel<__nv_bfloat16><<<(unsigned)rows, threads, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, cols, scale, causal_period);
+  else softmax_fwd_kernel<float><<<(unsigned)rows, threads, 0, st>>>((const float*)x, (float*)y, cols, scale, causal_period);
+  return (int)cudaGetLastError();
+}
+
+int b200_softmax_bwd(const void* dy, const void* y, void* dx, long long rows, int cols, float scale, int is_bf16, cudaStream_t st) {
+  if (rows <= 0 || cols <= 0) return 0;
+  const int threads = cols >= 1024 ? 256 : 128;
+  if (is_bf16) softmax_bwd_kernel<__nv_bfloat16><<<(unsigned)rows, threads, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)y, (__nv_bfloat16*)dx, cols, scale);
+  else softmax_bwd_kernel<float><<<(unsigned)rows, threads, 0, st>>>((const float*)dy, (const float*)y, (float*)dx, cols, scale);
   return (int)cudaGetLastError();
 }
 

@@ -68,6 +68,8 @@ _SIGS = {
     "b200_colsum_batched": [c_void_p, c_void_p, c_int, c_ll, c_int, c_ll, c_ll, c_int, c_void_p],
     "b200_reduce": [c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p],
     "b200_dropout": [c_void_p, c_void_p, c_ll, c_float, c_ull, c_int, c_void_p],
+    "b200_softmax_fwd": [c_void_p, c_void_p, c_ll, c_int, c_float, c_int, c_int, c_void_p],
+    "b200_softmax_bwd": [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_float, c_int, c_void_p],
     "b200_fake_quant": [c_void_p, c_void_p, c_ll, c_float, c_float, c_float, c_int, c_void_p],
     "b200_embedding_fwd": [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_ll, c_int, c_void_p],
     "b200_embedding_bwd": [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_ll, c_int, c_void_p],

@@ -17,4 +17,4 @@ def softmax(x):
         return torch.ones(1, dtype=x.dtype, device=x.device)
     if x.shape[-1] == 0:
         return x
-    return torch.softmax(x.float(), -1).to(x.dtype)
+    return F.softmax(x)

@@ -230,7 +230,7 @@ class Softmax(Module):
     """Softmax over the last axis (differentiable; the reference's is forward-only, src/activations.rs:23-62)."""
 
     def forward(self, x):
-        return torch.softmax(x.float(), -1).to(x.dtype)
+        return F.softmax(x)
 
     def parameters(self):
         return []
@@ -411,11 +411,9 @@ def flash_attention(q, k, v, causal: bool = False):
     d = q.shape[-1]
     if q.is_cuda and d not in (64, 128):
         # other head sizes: dense path through the GEMM kernel
-        s = F.matmul(q, k.transpose(1, 2).contiguous()) * (1.0 / math.sqrt(d))
-        if causal:
-            S = s.shape[-1]
-            s = s.masked_fill(~torch.ones(S, S, dtype=torch.bool, device=s.device).tril(), float("-inf"))
-        return F.matmul(torch.softmax(s.float(), -1).to(q.dtype), v.contiguous())
+        # (scores on the tcgen05 GEMM, scale + causal mask + softmax in one row kernel, then the second GEMM)
+        s = F.matmul(q, k.transpose(1, 2).contiguous())
+        return F.matmul(F.softmax(s, 1.0 / math.sqrt(d), s.shape[-2] if causal else 0), v.contiguous())
     o = F.flash_attention(q.unsqueeze(2), k.unsqueeze(2), v.unsqueeze(2), 1.0 / math.sqrt(d), causal)
     return o.squeeze(2)
 

@@ -231,6 +231,26 @@ class FakeQuantFn(Function):
 def fake_quantize(x, scale, qmin, qmax): return FakeQuantFn.apply(x, scale, qmin, qmax)
 
 
+# ----------------------------------------------------------------------------- softmax
+class SoftmaxFn(Function):
+    """softmax(scale * x) over the last axis, optionally with the causal mask of [.., S, S] score matrices."""
+
+    @staticmethod
+    def forward(ctx, x, scale, causal_period):
+        y = K.softmax_fwd(x, scale, causal_period)
+        ctx.save_for_backward(y)
+        ctx.scale = scale
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        (y,) = ctx.saved_tensors
+        return K.softmax_bwd(g, y, ctx.scale), None, None
+
+
+def softmax(x, scale: float = 1.0, causal_period: int = 0): return SoftmaxFn.apply(x, float(scale), int(causal_period))
+
+
 # ----------------------------------------------------------------------------- embedding
 class EmbeddingFn(Function):
     @staticmethod

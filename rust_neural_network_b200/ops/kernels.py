@@ -186,6 +186,34 @@ def reduce_all(x, what="sum", out=None):
     return out.view(())
 
 
+def softmax_fwd(x, scale=1.0, causal_period=0):
+    """Row softmax over the last axis of `scale * x`; `causal_period` = S masks column j of row r when j > r % S."""
+    cols = x.shape[-1]
+    if not x.is_cuda:
+        f = x.float() * scale
+        if causal_period:
+            S = causal_period
+            f = f.reshape(-1, S, cols).masked_fill(~torch.ones(S, cols, dtype=torch.bool).tril(), float("-inf")).reshape(x.shape)
+        return torch.softmax(f, -1).to(x.dtype)
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    nv.check(nv.cuda().b200_softmax_fwd(x.data_ptr(), y.data_ptr(), x.numel() // cols, cols, float(scale), int(causal_period), _isbf(x), nv.stream_ptr()), "softmax_fwd")
+    nv.count_launch()
+    return y
+
+
+def softmax_bwd(dy, y, scale=1.0):
+    cols = y.shape[-1]
+    if not y.is_cuda:
+        yf, gf = y.float(), dy.float()
+        return (scale * yf * (gf - (gf * yf).sum(-1, keepdim=True))).to(y.dtype)
+    dy = dy.contiguous().to(y.dtype)
+    dx = torch.empty_like(y)
+    nv.check(nv.cuda().b200_softmax_bwd(dy.data_ptr(), y.data_ptr(), dx.data_ptr(), y.numel() // cols, cols, float(scale), _isbf(y), nv.stream_ptr()), "softmax_bwd")
+    nv.count_launch()
+    return dx
+
+
 def dropout_mask_apply(x, p, seed):
     if not x.is_cuda:
         g = torch.Generator().manual_seed(int(seed) & 0x7FFFFFFF)

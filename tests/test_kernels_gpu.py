@@ -343,3 +343,24 @@ def test_flash_forward_backward(B, S, H, hd, causal):
     assert rel_err(dv, vr.grad) < 2e-2
     assert rel_err(dk, kr.grad) < 2e-2
     assert rel_err(dq, qr.grad) < 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,cols,causal", [(64, 37, 0), (256, 1024, 0), (96, 48, 48), (8, 4099, 0)])
+def test_softmax_rows_forward_backward(dtype, rows, cols, causal):
+    """Row softmax kernel (scale, optional causal mask) against fp32 torch, forward and backward."""
+    from rust_neural_network_b200.ops import functional as F
+    torch.manual_seed(0)
+    x = torch.randn(rows, cols, device="cuda").to(dtype).requires_grad_(True)
+    w = torch.randn(rows, cols, device="cuda").to(dtype)
+    y = F.softmax(x, 0.7, causal)
+    y.backward(w)
+    xr = x.detach().float().requires_grad_(True)
+    s = xr * 0.7
+    if causal:
+        s = s.reshape(-1, causal, cols).masked_fill(~torch.ones(causal, cols, dtype=torch.bool, device="cuda").tril(), float("-inf")).reshape(rows, cols)
+    ref = torch.softmax(s, -1)
+    ref.backward(w.float())
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert torch.allclose(y.float(), ref, atol=tol, rtol=tol)
+    assert torch.allclose(x.grad.float(), xr.grad, atol=tol * 4, rtol=tol * 4)

@@ -11,7 +11,7 @@ from rust_neural_network_b200 import Adam, CrossEntropyLoss, Linear, ReLU, Seque
 dev = _common.device()
 torch.manual_seed(1)
 ds = make_classification(600, 8, 3)
-train, test = ds.train_test_split(0.2)
+train, test = ds.train_test_split(0.8)
 features = [f"f{j}" for j in range(8)]
 
 

@@ -25,10 +25,16 @@ enum : int { IO_OK = 0, IO_BAD_MAGIC = 1, IO_BAD_VERSION = 2, IO_TRUNCATED = 3, 
 inline void put_u32(uint8_t*& p, uint32_t v) { memcpy(p, &v, 4); p += 4; }
 inline void put_u64(uint8_t*& p, uint64_t v) { memcpy(p, &v, 8); p += 8; }
 inline bool get_u32(const uint8_t* b, int64_t len, int64_t& off, uint32_t& v) {
-  if (off + 4 > len) return false; memcpy(&v, b + off, 4); off += 4; return true;
+  if (off + 4 > len) return false;
+  memcpy(&v, b + off, 4);
+  off += 4;
+  return true;
 }
 inline bool get_u64(const uint8_t* b, int64_t len, int64_t& off, uint64_t& v) {
-  if (off + 8 > len) return false; memcpy(&v, b + off, 8); off += 8; return true;
+  if (off + 8 > len) return false;
+  memcpy(&v, b + off, 8);
+  off += 8;
+  return true;
 }
 
 }  // namespace
@@ -208,9 +214,13 @@ int b200_safetensors_index(const unsigned char* buf, long long len, int cap, lon
   long long n = (long long)hl, i = 0;
   auto skip_ws = [&]() { while (i < n && (s[i] == ' ' || s[i] == '\n' || s[i] == '\t' || s[i] == '\r')) ++i; };
   auto parse_string = [&](long long& b, long long& e) -> bool {
-    skip_ws(); if (i >= n || s[i] != '"') return false; ++i; b = i;
+    skip_ws();
+    if (i >= n || s[i] != '"') return false;
+    ++i; b = i;
     while (i < n && s[i] != '"') { if (s[i] == '\\') ++i; ++i; }
-    if (i >= n) return false; e = i; ++i; return true;
+    if (i >= n) return false;
+    e = i; ++i;
+    return true;
   };
   // skip any JSON value (used for __metadata__ and unknown keys)
   auto skip_value = [&]() -> bool {

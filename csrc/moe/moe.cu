@@ -256,9 +256,6 @@ struct EpBarrierArgs {
 
 __global__ void ep_barrier_kernel(const EpBarrierArgs a) {
   const uint32_t epoch = a.words[0] + 1u;
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) s_ok = 1;
-  __syncthreads();
   if ((int)threadIdx.x < a.world) {
     const int peer = threadIdx.x;
     __threadfence_system();
@@ -268,7 +265,7 @@ __global__ void ep_barrier_kernel(const EpBarrierArgs a) {
       uint32_t v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.flags[a.rank] + peer) : "memory");
       if ((int32_t)(v - epoch) >= 0) break;
-      if (clock64() - t0 > a.wait_cycles) { s_ok = 0; if (a.status) atomicCAS(a.status, 0u, 5u); break; }
+      if (clock64() - t0 > a.wait_cycles) { if (a.status) atomicCAS(a.status, 0u, 5u); break; }
       __nanosleep(64);
     }
   }

@@ -149,7 +149,8 @@ def host():
     """Return the host-side C++ runtime library (no CUDA dependency)."""
     global _host_lib
     if _host_lib is None:
-        path = LIBDIR / "libb200nn_host.so"
+        # B200NN_HOST_LIB selects another build of the host runtime (the sanitizer build of `_build.build_host_sanitized`)
+        path = Path(os.environ.get("B200NN_HOST_LIB") or (LIBDIR / "libb200nn_host.so"))
         if not path.exists():
             raise RuntimeError(f"{path} is missing: run the in-tree build first")
         _host_lib = C.CDLL(str(path))

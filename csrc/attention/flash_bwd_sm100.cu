@@ -15,6 +15,7 @@
 // the column half w/4. Every wait is bounded.
 #include <type_traits>
 #include "../common/ptx.cuh"
+#include "../common/launch.cuh"
 #include "../common/tensormap.h"
 #include "flash_sm100.h"
 
@@ -59,6 +60,8 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, long lon
 // dq[b,s,h,:] (bf16, strided) = dq_accum[b,s,h,:] (fp32, contiguous)
 __global__ void flash_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long sb,
                                         long long ss, long long sh, int B, int S, int H, int hd) {
+  pdl_trigger();
+  pdl_wait();
   const long long total = (long long)B * S * H * (hd / 8);
   long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -107,6 +110,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  pdl_trigger();
   const int quarter = warp & 3, cq = warp >> 2;   // TMEM lane quarter (rows) and column group of this warp
   constexpr int CG = BWD_CG;
   constexpr int SC = 128 / CG;                    // S / dP columns per thread (32 or 64)
@@ -136,6 +140,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_row = tmem_base + (uint32_t(quarter * 32) << 16);
+  pdl_wait();
 
   const int i_start = CAUSAL ? (kv0 / BLK) : 0;
   const int n_iter = m_blocks - i_start;
@@ -413,11 +418,11 @@ static int launch_bwd(const FlashArgs& a, cudaStream_t st) {
   p.B = a.B; p.H = a.H; p.Sq = a.Sq; p.Skv = a.Skv;
   p.scale = a.scale; p.scale_log2 = a.scale * 1.4426950408889634f; p.status = a.status;
   const long long grid = (long long)((a.Skv + 127) / 128) * a.H * a.B;
-  kfn<<<(unsigned)grid, 128 * BWD_CG, SMEM, st>>>(tmQ, tmK, tmV, tmdO, p);
+  launch_pdl(kfn, dim3((unsigned)grid), dim3(128 * BWD_CG), SMEM, st, tmQ, tmK, tmV, tmdO, p);
   long long total = (long long)a.B * a.Sq * a.H * (a.hd / 8);
   long long g = (total + 255) / 256; if (g > 148 * 16) g = 148 * 16;
-  flash_dq_convert_kernel<<<(unsigned)g, 256, 0, st>>>(a.dq_accum, (__nv_bfloat16*)a.dq.ptr, a.dq.sb, a.dq.ss, a.dq.sh,
-                                                        a.B, a.Sq, a.H, a.hd);
+  launch_pdl(flash_dq_convert_kernel, dim3((unsigned)g), dim3(256), 0, st, (const float*)a.dq_accum, (__nv_bfloat16*)a.dq.ptr, a.dq.sb, a.dq.ss, a.dq.sh,
+             a.B, a.Sq, a.H, a.hd);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }

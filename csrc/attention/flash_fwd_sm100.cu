@@ -13,6 +13,7 @@
 // S_{j+1} is issued right behind P V_j, K/V tiles are double-buffered by TMA, and two CTAs share an SM
 // (TMEM 2 x 256 columns) so one CTA's exponentials overlap the other's MMAs. Every wait is bounded.
 #include "../common/ptx.cuh"
+#include "../common/launch.cuh"
 #include "../common/tensormap.h"
 #include "flash_sm100.h"
 
@@ -53,6 +54,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
 
   const int tid = threadIdx.x, warp = tid >> 5;
+  pdl_trigger();
   const int m_blocks = (p.Sq + BMQ - 1) / BMQ;
   int bid = blockIdx.x;
   // heavy (late, causal) query blocks first
@@ -83,6 +85,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_row = tmem_base + (uint32_t(warp * 32) << 16);
+  pdl_wait();
 
   int n_blocks = (p.Skv + BN - 1) / BN;
   if (CAUSAL) { int lim = (q0 + BMQ + BN - 1) / BN; if (lim < n_blocks) n_blocks = lim; }
@@ -288,8 +291,8 @@ static int launch_fwd(const FlashArgs& a, cudaStream_t st) {
   p.global_order = ((long long)a.B * a.H * a.Skv * a.hd * 4 <= 300ll * 1024 * 1024) ? 1 : 0;
   p.status = a.status;
   const long long grid = (long long)((a.Sq + 127) / 128) * a.H * a.B;
-  kfn<<<(unsigned)grid, 128, SMEM, st>>>(tmQ, tmK, tmV, p);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(kfn, dim3((unsigned)grid), dim3(128), SMEM, st, tmQ, tmK, tmV, p);
+  if (e == cudaSuccess) e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }
 

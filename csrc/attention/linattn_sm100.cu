@@ -147,6 +147,24 @@ __device__ __forceinline__ void la_write_row128(uint8_t* tile, int row, const fl
   }
 }
 
+// fp32 row of 128 values -> bf16 value tile and bf16 remainder tile (both K-major [128][128]), row = thread
+__device__ __forceinline__ void la_write_row128_hilo(uint8_t* hi, uint8_t* lo, int row, const float* v) {
+#pragma unroll
+  for (int g = 0; g < 16; ++g) {
+    uint32_t h[4], l[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = v[g * 8 + 2 * j], b = v[g * 8 + 2 * j + 1];
+      h[j] = pack_bf16x2(a, b);
+      const float2 r = unpack_bf16x2(h[j]);
+      l[j] = pack_bf16x2(a - r.x, b - r.y);
+    }
+    const uint32_t off = (g >> 3) * (LA_C * 128) + sw128_offset(row, g & 7);
+    *reinterpret_cast<uint4*>(hi + off) = make_uint4(h[0], h[1], h[2], h[3]);
+    *reinterpret_cast<uint4*>(lo + off) = make_uint4(l[0], l[1], l[2], l[3]);
+  }
+}
+
 template <int N>
 __device__ __forceinline__ void la_tmem_row(uint32_t taddr, float* out) {
 #pragma unroll
@@ -206,6 +224,11 @@ struct LaSmem {
   static constexpr int PT = LA_C * LA_C * 2;          // one [128][128] tile
   static constexpr int ST = HD * HD * 2;              // one state tile [HD][HD]
   static constexpr int ZERO = HD == 64 ? TILE : 0;    // zero atom that pads the state update to 128 rows
+  // The masked [128][128] tile of a chunk (A in the forward, dA in the dQ kernel) enters its product as value + remainder
+  // like the state does: dQ is a difference of nearly equal sums, and one bf16 copy of the tile costs it ~2 % each way.
+  // With head_dim 64 the remainder tile has its own buffer; with 128 (shared memory is full) it reuses the tile of the
+  // operand that is dead by then (Q~ in the forward, G in the dQ kernel).
+  static constexpr int PLO = HD == 64 ? PT : 0;
 };
 
 // ---------------------------------------------------------------------------------------------------- forward
@@ -224,7 +247,8 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint8_t* sP = sV + L::TILE;
   uint8_t* sShi = sP + L::PT;
   uint8_t* sSlo = sShi + L::ST;
-  float* sz = reinterpret_cast<float*>(sSlo + L::ST);      // [HD]
+  uint8_t* sPlo = HD == 64 ? sSlo + L::ST : sQ;
+  float* sz = reinterpret_cast<float*>(sSlo + L::ST + L::PLO);      // [HD]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sz + HD);
   uint64_t* q_bar = bars; uint64_t* k_bar = bars + 1; uint64_t* v_bar = bars + 3; uint64_t* a_bar = bars + 4; uint64_t* b_bar = bars + 5;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
@@ -313,7 +337,7 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (!mbar_wait(a_bar, c & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
       if (__syncthreads_or(!ok)) { ok = false; break; }
       tc_fence_after_sync();
-      if (tid == 0 && c + 1 < n_chunks) load(sQ, &tmQ, q_bar, c + 1);              // Q~ has been consumed
+      if (HD == 64 && tid == 0 && c + 1 < n_chunks) load(sQ, &tmQ, q_bar, c + 1);  // Q~ has been consumed
       float a[LA_C];
       la_tmem_row<LA_C>(trow + COL_A, a);
       float r0 = 0.f, r1 = 0.f;
@@ -324,7 +348,7 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         r0 += a[i]; r1 += a[i + 1];
       }
       den += r0 + r1;
-      la_write_row128(sP, tid, a);
+      la_write_row128_hilo(sP, sPlo, tid, a);
       tc_fence_before_sync();
       fence_proxy_async_smem();
     }
@@ -333,7 +357,10 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       ok = mbar_wait(v_bar, c & 1, p.status, ST_TIMEOUT_TMA_FULL);
       if (ok) {
         tc_fence_after_sync();
-        if (full) la_mma_pw<HD, LA_C>(tmem_base + COL_NUM, sP, sV, LA_C * 128, true);                 // NUM += A V
+        if (full) {                                                                                    // NUM += A V (value + remainder)
+          la_mma_pw<HD, LA_C>(tmem_base + COL_NUM, sP, sV, LA_C * 128, true);
+          la_mma_pw<HD, LA_C>(tmem_base + COL_NUM, sPlo, sV, LA_C * 128, true);
+        }
         la_mma_xTw<HD>(tmem_base + COL_S, sKc, k_lbo[st], sV, have_state0 || c > 0);                   // S += K~^T V
         tc_commit(b_bar);
       }
@@ -345,6 +372,7 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (__syncthreads_or(!ok)) { ok = false; break; }
     tc_fence_after_sync();
     if (tid == 0) {                                                           // K~ and V of this chunk are free
+      if (HD == 128 && full && c + 1 < n_chunks) load(sQ, &tmQ, q_bar, c + 1);  // (its buffer held the remainder tile)
       if (c + 1 < n_chunks) load(sV, &tmV, v_bar, c + 1);
       if (c + 2 < n_chunks) load(sKc, &tmK, &k_bar[st], c + 2);
     }
@@ -474,7 +502,8 @@ linattn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   uint8_t* sP = sV + L::TILE;
   uint8_t* sShi = sP + L::PT;
   uint8_t* sSlo = sShi + L::ST;
-  float* sz = reinterpret_cast<float*>(sSlo + L::ST);
+  uint8_t* sPlo = HD == 64 ? sSlo + L::ST : sG;
+  float* sz = reinterpret_cast<float*>(sSlo + L::ST + L::PLO);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sz + HD);
   uint64_t* k_bar = bars; uint64_t* v_bar = bars + 2; uint64_t* a_bar = bars + 3; uint64_t* b_bar = bars + 4;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
@@ -559,14 +588,15 @@ linattn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       la_tmem_row<LA_C>(trow + COL_A, a);
 #pragma unroll
       for (int i = 0; i < LA_C; ++i) a[i] = i > tid ? 0.f : a[i] + dden;
-      la_write_row128(sP, tid, a);
+      la_write_row128_hilo(sP, sPlo, tid, a);
     }
     tc_fence_before_sync();
     fence_proxy_async_smem();
     __syncthreads();
     if (tid == 0) {
       tc_fence_after_sync();
-      la_mma_pw<HD, LA_C>(tmem_base + COL_DQ, sP, sKc, LA_C * 128, true);             // dQ~ += dA K~
+      la_mma_pw<HD, LA_C>(tmem_base + COL_DQ, sP, sKc, LA_C * 128, true);             // dQ~ += dA K~ (value + remainder)
+      la_mma_pw<HD, LA_C>(tmem_base + COL_DQ, sPlo, sKc, LA_C * 128, true);
       la_mma_xTw<HD>(tmem_base + COL_S, sKc, k_lbo[st], sV, have_state0 || c > 0);    // S += K~^T V
       tc_commit(b_bar);
     }
@@ -797,7 +827,7 @@ linattn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 }
 
 // ---------------------------------------------------------------------------------------------------- host side
-template <int HD> constexpr int la_fwd_smem() { return 4 * LaSmem<HD>::TILE + LaSmem<HD>::ZERO + LaSmem<HD>::PT + 2 * LaSmem<HD>::ST + HD * 4 + 128; }
+template <int HD> constexpr int la_fwd_smem() { return 4 * LaSmem<HD>::TILE + LaSmem<HD>::ZERO + LaSmem<HD>::PT + LaSmem<HD>::PLO + 2 * LaSmem<HD>::ST + HD * 4 + 128; }
 template <int HD> constexpr int la_dkv_smem() { return 4 * LaSmem<HD>::TILE + LaSmem<HD>::ZERO + LaSmem<HD>::PT + 2 * LaSmem<HD>::ST + (HD + LA_C) * 4 + 128; }
 
 static int la_maps(const LinAttnArgs& a, CUtensorMap* tq, CUtensorMap* tk, CUtensorMap* tv) {

@@ -7,6 +7,7 @@
 #include <cuda_bf16.h>
 #include <cstdint>
 #include "../gemm/gemm_sm100.h"
+#include "../common/launch.cuh"
 
 namespace b200 {
 
@@ -112,6 +113,8 @@ __global__ void unary_kernel(const T* __restrict__ x, T* __restrict__ y, long lo
 template <typename T>
 __global__ void binary_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ y, long long n,
                               int op, long long b_period) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int N = Vec<T>::N;
   using P = Pack<T, N>;
   long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -167,6 +170,8 @@ __global__ void colsum_kernel(const T* __restrict__ x, float* __restrict__ out, 
 __global__ void __launch_bounds__(256)
 colsum_vec_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, long long rows, int cols, long long ld, int rows_per_block) {
   __shared__ float sh[8][256 + 8];
+  pdl_trigger();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c0 = blockIdx.x * 256 + lane * 8;
   const long long r0 = (long long)blockIdx.y * rows_per_block;
@@ -230,6 +235,8 @@ __global__ void __launch_bounds__(256)
 dact_colsum_kernel(__nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ saved, float* __restrict__ dbias, long long rows, int cols,
                    long long ld_g, long long ld_s, int rows_per_block) {
   __shared__ float sh[8][256 + 8];
+  pdl_trigger();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c0 = blockIdx.x * 256 + lane * 8;
   const long long r0 = (long long)blockIdx.y * rows_per_block;
@@ -518,8 +525,8 @@ int b200_binary(const void* a, const void* b, void* y, long long n, int op, long
   if (n <= 0) return 0;
   const int vw = is_bf16 ? 8 : 4;
   long long work = (b_period && (b_period % vw || n % vw)) ? n : n / vw + 1;
-  if (is_bf16) binary_kernel<__nv_bfloat16><<<grid_for(work, 256), 256, 0, st>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, n, op, b_period);
-  else binary_kernel<float><<<grid_for(work, 256), 256, 0, st>>>((const float*)a, (const float*)b, (float*)y, n, op, b_period);
+  if (is_bf16) launch_pdl(binary_kernel<__nv_bfloat16>, dim3(grid_for(work, 256)), dim3(256), 0, st, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, n, op, b_period);
+  else launch_pdl(binary_kernel<float>, dim3(grid_for(work, 256)), dim3(256), 0, st, (const float*)a, (const float*)b, (float*)y, n, op, b_period);
   return (int)cudaGetLastError();
 }
 
@@ -543,9 +550,9 @@ int b200_dact_colsum(void* g, const void* saved, float* dbias, long long rows, i
   dim3 grid(cb, (unsigned)((rows + rpb - 1) / rpb));
   __nv_bfloat16* gp = (__nv_bfloat16*)g;
   const __nv_bfloat16* sp = (const __nv_bfloat16*)saved;
-  if (op == OP_GELU_BWD) dact_colsum_kernel<OP_GELU_BWD><<<grid, 256, 0, st>>>(gp, sp, dbias, rows, cols, ld_g, ld_s, (int)rpb);
-  else if (op == OP_SILU_BWD) dact_colsum_kernel<OP_SILU_BWD><<<grid, 256, 0, st>>>(gp, sp, dbias, rows, cols, ld_g, ld_s, (int)rpb);
-  else if (op == OP_RELU_BWD) dact_colsum_kernel<OP_RELU_BWD><<<grid, 256, 0, st>>>(gp, sp, dbias, rows, cols, ld_g, ld_s, (int)rpb);
+  if (op == OP_GELU_BWD) launch_pdl(dact_colsum_kernel<OP_GELU_BWD>, grid, dim3(256), 0, st, gp, sp, dbias, rows, cols, ld_g, ld_s, (int)rpb);
+  else if (op == OP_SILU_BWD) launch_pdl(dact_colsum_kernel<OP_SILU_BWD>, grid, dim3(256), 0, st, gp, sp, dbias, rows, cols, ld_g, ld_s, (int)rpb);
+  else if (op == OP_RELU_BWD) launch_pdl(dact_colsum_kernel<OP_RELU_BWD>, grid, dim3(256), 0, st, gp, sp, dbias, rows, cols, ld_g, ld_s, (int)rpb);
   else return -1;
   return (int)cudaGetLastError();
 }
@@ -558,7 +565,7 @@ int b200_colsum(const void* x, float* out, long long rows, int cols, long long l
     long long rpb = (rows * cb + 148LL * 8 - 1) / (148LL * 8);      // about 8 blocks per SM
     rpb = rpb < 32 ? 32 : rpb > 1024 ? 1024 : (rpb + 31) / 32 * 32;
     dim3 g(cb, (unsigned)((rows + rpb - 1) / rpb));
-    colsum_vec_kernel<<<g, 256, 0, st>>>((const __nv_bfloat16*)x, out, rows, cols, ld, (int)rpb);
+    launch_pdl(colsum_vec_kernel, g, dim3(256), 0, st, (const __nv_bfloat16*)x, out, rows, cols, ld, (int)rpb);
     return (int)cudaGetLastError();
   }
   int rpb = 256;
@@ -600,6 +607,9 @@ int b200_softmax_bwd(const void* dy, const void* y, void* dx, long long rows, in
   else softmax_bwd_kernel<float><<<(unsigned)rows, threads, 0, st>>>((const float*)dy, (const float*)y, (float*)dx, cols, scale);
   return (int)cudaGetLastError();
 }
+
+// Programmatic dependent launch on (1, default) or off (0) for every kernel of this library that supports it.
+int b200_set_pdl(int on) { b200::g_pdl_enabled = on ? 1 : 0; return 0; }
 
 int b200_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, int is_bf16, cudaStream_t st) {
   if (n <= 0) return 0;

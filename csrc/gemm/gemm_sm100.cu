@@ -21,6 +21,7 @@
 //                               accumulation) are written straight from registers.
 // All waits are bounded; on expiry a code lands in the status word and the CTA unwinds.
 #include "../common/ptx.cuh"
+#include "../common/launch.cuh"
 #include "../common/tensormap.h"
 #include "gemm_sm100.h"
 
@@ -233,6 +234,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  pdl_trigger();
 
   const int m_blocks = (p.M + BM - 1) / BM;
   const int n_blocks = (p.N + BN - 1) / BN;
@@ -264,6 +266,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                      // everything above overlapped the previous kernel; global memory is touched from here on
 
   if (TP == TP_AG_GEMM && cta < 0) {
     // ------------------------------------------------------------------ gather CTAs (all-gather half of TP_AG_GEMM)
@@ -706,8 +709,8 @@ static int launch_one(const GemmArgs& a, cudaStream_t stream, int num_sms) {
   const long long tiles = m_blocks * n_blocks * p.splits * p.batch;
   int grid = (int)(tiles < num_sms ? tiles : num_sms);
   if (grid < 1) grid = 1;
-  kfn<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, p);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(kfn, dim3(grid), dim3(GEMM_THREADS), S::TOTAL, stream, tmA, tmB, p);
+  if (e == cudaSuccess) e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }
 

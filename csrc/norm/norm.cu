@@ -7,6 +7,7 @@
 // pass hits L1), statistics are fp32, gamma/beta are fp32. dgamma/dbeta are reduced in shared
 // memory per block and flushed with one fp32 atomic per column per block.
 #include <cuda_runtime.h>
+#include "../common/launch.cuh"
 #include <cuda_bf16.h>
 #include <cstdint>
 
@@ -83,6 +84,8 @@ layernorm_fwd_vec_kernel(const __nv_bfloat16* __restrict__ x, const float* __res
   // the backward pass will read); `sum_out` receives that sum. This is the residual add of the layer before, moved
   // out of its GEMM epilogue.
   __shared__ float red[2][2][8];              // [row parity][mean | variance][warp]
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int groups_per_block = (blockDim.x >> 5) / W, grp = warp / W, wi = warp % W;
   float gam[J2][8], bet[J2][8];
@@ -289,6 +292,8 @@ layernorm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat
                          long long rows, int d) {
   extern __shared__ float sh[];   // [row groups][2][d]
   __shared__ float red[2][2][8];  // [row parity][s1 | s2][warp]
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int groups_per_block = (blockDim.x >> 5) / W, grp = warp / W, wi = warp % W;
   float gam[J2][8], adg[J2][8], adb[J2][8];
@@ -482,7 +487,7 @@ static int layernorm_fwd_vec_dispatch(const void* x, const float* gamma, const f
   const bool fwd_vec_d = d % 256 == 0 && (d <= 1024 || d == 1536 || d == 2048 || d == 3072 || d == 4096);
   if (fwd_vec_d && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)gamma % 16 == 0 && (uintptr_t)beta % 16 == 0) {
 #define B200_LNF(JJ, WW) { const int gpb = wpb / WW; long long gg = (rows + gpb - 1) / gpb; if (gg > 148 * 8) gg = 148 * 8; \
-      layernorm_fwd_vec_kernel<JJ, WW><<<(int)gg, block, 0, st>>>((const __nv_bfloat16*)x, gamma, beta, (__nv_bfloat16*)y, mean, rstd, rows, d, eps, (const __nv_bfloat16*)res, (__nv_bfloat16*)sum_out); }
+      launch_pdl(layernorm_fwd_vec_kernel<JJ, WW>, dim3((int)gg), dim3(block), 0, st, (const __nv_bfloat16*)x, gamma, beta, (__nv_bfloat16*)y, mean, rstd, rows, d, eps, (const __nv_bfloat16*)res, (__nv_bfloat16*)sum_out); }
     switch (d / 256) {
       case 1: B200_LNF(1, 1) break; case 2: B200_LNF(2, 1) break; case 3: B200_LNF(3, 1) break; case 4: B200_LNF(4, 1) break;
       case 6: B200_LNF(3, 2) break; case 8: B200_LNF(4, 2) break; case 12: B200_LNF(3, 4) break; default: B200_LNF(4, 4) break;
@@ -508,7 +513,7 @@ int b200_layernorm_bwd(const void* dy, const void* x, const float* gamma, const 
       const size_t sm = (size_t)gpb * 2 * d * sizeof(float); \
       long long gg = (rows + gpb - 1) / gpb; if (gg > 148 * 2) gg = 148 * 2; \
       if (sm + 256 > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); if (e != cudaSuccess) return (int)e; } \
-      k<<<(int)gg, block, sm, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, gamma, mean, rstd, (__nv_bfloat16*)dx, dgamma, dbeta, (const __nv_bfloat16*)dres, rows, d); }
+      launch_pdl(k, dim3((int)gg), dim3(block), sm, st, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, gamma, (const float*)mean, (const float*)rstd, (__nv_bfloat16*)dx, dgamma, dbeta, (const __nv_bfloat16*)dres, rows, d); }
     switch (d / 256) {
       case 1: B200_LNV(1, 1) break; case 2: B200_LNV(2, 1) break; case 3: B200_LNV(3, 1) break; case 4: B200_LNV(4, 1) break;
       case 6: B200_LNV(3, 2) break; case 8: B200_LNV(4, 2) break; case 12: B200_LNV(3, 4) break; default: B200_LNV(4, 4) break;

@@ -130,10 +130,22 @@ def cuda():
                 rc = fn()
                 if rc != 0:
                     raise RuntimeError(f"{name} failed with CUDA error {rc}")
+            if os.environ.get("B200NN_PDL", "1") == "0":
+                set_pdl(False)
     return _cuda_lib
 
 
 _EXTRA_SIGS: dict = {}
+
+
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch for the kernels that support it (GEMM, flash attention, LayerNorm, the streaming
+    backward helpers): each such kernel may be dispatched, and run its prologue, while its predecessor is still running.
+    On by default; `B200NN_PDL=0` in the environment turns it off."""
+    lib = _cuda_lib if _cuda_lib is not None else cuda()
+    fn = lib.b200_set_pdl
+    fn.argtypes, fn.restype = [c_int], c_int
+    fn(1 if on else 0)
 
 
 def register_sigs(sigs: dict) -> None:

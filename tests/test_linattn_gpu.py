@@ -29,7 +29,7 @@ def _check(S, hd, kind, B=2, H=3, seed=0):
     """Two oracles. (1) fp32 everything. (2) fp32 arithmetic on bf16-ROUNDED feature maps: the function a kernel with bf16
     tensor-core operands evaluates. dQ and dK are differences of nearly equal sums over the features; ELU + 1 features sit
     near 1, where bf16 resolves 2^-8, so the rounding of the operands alone moves dQ by a few per cent against (1). Against
-    (2) only the kernel's own arithmetic is left (fp32 state, remainder of O, rounded dA inside a chunk)."""
+    (2) only the kernel's own arithmetic is left (fp32 state; state, masked tile and O carried as value + remainder)."""
     from rust_neural_network_b200 import _native as nv
     from rust_neural_network_b200.ops.linear_attention import FusedCausalLinearAttnFn, linear_attention_ref
     q, k, v, w = _inputs(B, S, H, hd, seed)
@@ -48,20 +48,20 @@ def _check(S, hd, kind, B=2, H=3, seed=0):
 @pytest.mark.parametrize("kind", ["elu", "relu2"])
 def test_fused_forward_backward_match_fp32_oracle(S, hd, kind):
     e32, e16 = _check(S, hd, kind)
-    # inside a chunk the masked dA tile enters its product as bf16: a few per cent while a sequence is a chunk or two long
-    tol16 = 4e-2 if S < 512 else 2e-2
-    assert all(e < tol16 for e in e16.values()), ("vs fp32 arithmetic on bf16 features", e16)
-    assert e32["dk"] < 2e-2 and e32["dv"] < 2e-2, e32
-    assert e32["dq"] < (2e-2 if kind == "relu2" and S >= 512 else 8e-2), e32
+    # the kernel's own arithmetic (fp32 state, value + remainder operands): 0.25 % measured on every case
+    assert all(e < 6e-3 for e in e16.values()), ("vs fp32 arithmetic on bf16 features", e16)
+    assert e32["dk"] < 8e-3 and e32["dv"] < 8e-3, e32
+    # rounding phi(Q), phi(K) to bf16 is what is left against the all-fp32 oracle: 2-3 % of dQ for ELU + 1 (features near 1)
+    assert e32["dq"] < (8e-3 if kind == "relu2" else 4.5e-2), e32
 
 
 def test_long_sequence_gradients():
     """8192 tokens: almost all of every output comes through the carried state (64 chunks)."""
     e32, e16 = _check(8192, 64, "elu", B=1, H=2, seed=3)
-    assert all(e < 1.5e-2 for e in e16.values()), e16
-    assert e32["dk"] < 2e-2 and e32["dv"] < 2e-2 and e32["dq"] < 5e-2, e32
+    assert all(e < 6e-3 for e in e16.values()), e16
+    assert e32["dk"] < 8e-3 and e32["dv"] < 8e-3 and e32["dq"] < 4e-2, e32
     e32, e16 = _check(8192, 64, "relu2", B=1, H=2, seed=3)
-    assert all(e < 2e-2 for e in e32.values()), e32
+    assert all(e < 8e-3 for e in e32.values()), e32
 
 
 def test_state_in_state_out_equals_one_long_sequence():

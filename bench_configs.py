@@ -69,6 +69,28 @@ def _time_steps(step, args, world, dev):
     return ms, first, last
 
 
+def _kernel_table(step, path, rank):
+    """One more step under `torch.profiler` (after the timed region; never a timed number): device time per kernel name,
+    largest first, written by rank 0. Shares of the step, for deciding which kernel to look at next."""
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        step()
+        torch.cuda.synchronize()
+    if rank != 0:
+        return
+    rows = {}
+    for ka in prof.key_averages():
+        t = getattr(ka, "self_device_time_total", 0) or 0
+        if t:
+            rows[ka.key] = (float(t), int(ka.count))
+    total = sum(v[0] for v in rows.values()) or 1.0
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    with open(path, "w") as f:
+        f.write(f"# device time by kernel over one step, total {total / 1e3:.2f} ms (profiler run: shares, not a timing)\n")
+        for name, (t, c) in sorted(rows.items(), key=lambda kv: -kv[1][0])[:60]:
+            f.write(f"{100 * t / total:6.2f} %  {t / 1e3:9.3f} ms  x{c:<5d} {name[:150]}\n")
+
+
 def run_lm(name, args):
     """b200 arm: this package's kernels. `--parallel` picks the layout for N > 1: `tp` (Mamba: channel-sharded blocks on
     row-sharded activations, fused all-gather->GEMM / GEMM->reduce-scatter / all-reduce kernels), `ep` (MoE: experts
@@ -117,6 +139,8 @@ def run_lm(name, args):
     lab = [torch.randint(0, cfg.vocab, (batch, cfg.seq_len), generator=g).pin_memory() for _ in range(2)]
     ms, first, last = _time_steps(lambda i: tr.train_step(ids[i % 2], lab[i % 2]), args, world, dev)
     nv.check_status()
+    if args.kernel_table:
+        _kernel_table(lambda: tr.train_step(ids[0], lab[0]), args.kernel_table, rank)
     n_params = sum(p.numel() for p in model.parameters())
     if rank == 0:
         print(json.dumps({"config": name, "impl": "b200", "comm": args.comm, "parallel": par, "n_gpus": world, "batch_per_gpu": batch,
@@ -161,6 +185,8 @@ def run_lm_torch(name, args):
     ids = [torch.randint(0, cfg.vocab, (batch, cfg.seq_len), generator=g).pin_memory() for _ in range(2)]
     lab = [torch.randint(0, cfg.vocab, (batch, cfg.seq_len), generator=g).pin_memory() for _ in range(2)]
     ms, first, last = _time_steps(lambda i: stepper.step(ids[i % 2].to(dev, non_blocking=True), lab[i % 2].to(dev, non_blocking=True)), args, world, dev)
+    if args.kernel_table:
+        _kernel_table(lambda: stepper.step(ids[0].to(dev, non_blocking=True), lab[0].to(dev, non_blocking=True)), args.kernel_table, rank)
     if rank == 0:
         print(json.dumps({"config": name, "impl": "torch", "comm": "nccl", "parallel": par, "n_gpus": world, "batch_per_gpu": batch,
                           "seq_len": cfg.seq_len, "params_per_rank": sum(p.numel() for p in model.parameters()), "ms_per_step": ms,
@@ -344,6 +370,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "torch"], help="torch: the NCCL + cuBLAS library arm (moe_lm, mamba_lm)")
     ap.add_argument("--parallel", default="auto", choices=["auto", "dp", "tp", "ep"], help="layout for N > 1 (auto: the preset's)")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"], help="b200 arm: fused peer-memory kernels or NCCL calls")
+    ap.add_argument("--kernel-table", default="", help="after timing, profile one more step and write device time per kernel name here")
     ap.add_argument("--buckets", action="store_true", help="dp: bucketed gradient reduction overlapped with backward")
     args = ap.parse_args()
     if args.config == "mlp":

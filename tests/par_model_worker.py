@@ -32,7 +32,7 @@ def mamba_tp(args, rank, world, dev, dtype):
     from rust_neural_network_b200.models.mamba import MambaLM
     from rust_neural_network_b200.optim import Adam
     from rust_neural_network_b200.parallel.tp import TPContext
-    V, d, L, N, R, S, Bl = 256, 64, 2, 16, 8, 128, 2
+    V, d, L, N, R, S, Bl = 256, (64 if world <= 4 else 128), 2, 16, 8, 128, 2      # 32 inner channels per rank at least
     di = 2 * d
     M = world * Bl * S
     tp = TPContext(M, d, d, device=dev, backend=args.backend, max_allreduce_numel=M * (R + 2 * N))

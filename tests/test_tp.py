@@ -205,3 +205,13 @@ def test_expert_parallel_moe_lm_two_gpus(backend, port):
         pytest.skip("needs 2 GPUs")
     r0 = _run_model(2, ["--model", "moe_ep", "--device", "cuda", "--backend", backend], port)[0]
     _check_model(r0, "ep_losses", 8e-2, 5e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("model,key,port", [("mamba_tp", "tp_losses", 29666), ("moe_ep", "ep_losses", 29667)])
+def test_parallel_models_eight_gpus(model, key, port):
+    """The same two checks over all eight GPUs of a node: 8-way channel sharding, one expert per rank."""
+    if torch.cuda.device_count() < 8:
+        pytest.skip("needs 8 GPUs")
+    r0 = _run_model(8, ["--model", model, "--device", "cuda", "--backend", "fused"], port)[0]
+    _check_model(r0, key, 8e-2, 5e-2)

@@ -124,7 +124,7 @@ def cuda():
             torch.cuda.init()
             # load every tensor-core kernel variant and opt in to its shared-memory carve-out now,
             # from the importing thread, instead of lazily from an autograd worker thread
-            for name in ("b200_gemm_init", "b200_flash_fwd_init", "b200_flash_bwd_init", "b200_linattn_init"):
+            for name in ("b200_gemm_init", "b200_flash_fwd_init", "b200_flash_bwd_init", "b200_linattn_init", "b200_gemm_mx_init"):
                 fn = getattr(_cuda_lib, name)
                 fn.argtypes, fn.restype = [], c_int
                 rc = fn()

@@ -1,6 +1,7 @@
 """Single-kernel micro-benchmarks with roofline fractions.
 
     python -m rust_neural_network_b200.utils.kernel_bench gemm --m 65536 --n 2048 --k 512 [--bias --act gelu --residual]
+    python -m rust_neural_network_b200.utils.kernel_bench gemm_mx --m 8192 --n 8192 --k 8192 --kind mxfp8|nvfp4
     python -m rust_neural_network_b200.utils.kernel_bench flash_fwd --b 64 --s 1024 --h 8 --hd 64 --causal
     python -m rust_neural_network_b200.utils.kernel_bench flash_bwd ...
     python -m rust_neural_network_b200.utils.kernel_bench layernorm_bwd --rows 65536 --d 512
@@ -83,7 +84,7 @@ def time_fn(fn, iters=10, warmup=3):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "flash_fwd", "flash_bwd", "layernorm_bwd", "layernorm_fwd", "ce", "scan_fwd", "scan_bwd"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_mx", "flash_fwd", "flash_bwd", "layernorm_bwd", "layernorm_fwd", "ce", "scan_fwd", "scan_bwd"])
     for name, default in (("m", 65536), ("n", 2048), ("k", 512), ("b", 64), ("s", 1024), ("h", 8), ("hd", 64),
                           ("rows", 65536), ("d", 512), ("v", 32000), ("iters", 10)):
         ap.add_argument(f"--{name}", type=int, default=default)
@@ -95,6 +96,7 @@ def main(argv=None):
     ap.add_argument("--a-mn", action="store_true")
     ap.add_argument("--b-mn", action="store_true")
     ap.add_argument("--f32-out", action="store_true")
+    ap.add_argument("--kind", default="mxfp8", choices=["mxfp8", "nvfp4"], help="gemm_mx: block-scaled operand format")
     ap.add_argument("--bn", type=int, default=0, help="GEMM tile width override (64 / 128 / 256)")
     args = ap.parse_args(argv)
 
@@ -121,6 +123,16 @@ def main(argv=None):
         byts = 2.0 * (M * Kd + N * Kd) + (4.0 if args.f32_out else 2.0) * M * N * (2 if kw["want_aux"] else 1) + (2.0 * M * N if res is not None else 0) + (2.0 * M * N if aux_in is not None else 0)
         out.update(shape=[M, N, Kd], ms=ms, tflops=flops / ms / 1e9, frac_of_bf16_peak=flops / ms / 1e9 / pk["bf16_tflops"],
                    gbs=byts / ms / 1e6, frac_of_hbm_peak=byts / ms / 1e6 / pk["hbm_gbs"])
+    elif args.kernel == "gemm_mx":
+        from rust_neural_network_b200.ops import mx
+        M, N, Kd = args.m, args.n, args.k
+        qa = mx.quantize_mx(torch.randn(M, Kd, device=dev).bfloat16(), args.kind)
+        qb = mx.quantize_mx(torch.randn(N, Kd, device=dev).bfloat16(), args.kind)
+        ms = time_fn(lambda: mx.gemm_mx(qa, qb), args.iters)
+        ms_q = time_fn(lambda: mx.quantize_mx(torch.empty(M, Kd, device=dev, dtype=torch.bfloat16), args.kind), args.iters)
+        flops = 2.0 * M * N * Kd
+        out.update(shape=[M, N, Kd], kind=args.kind, ms=ms, tflops=flops / ms / 1e9, vs_bf16_peak=flops / ms / 1e9 / pk["bf16_tflops"],
+                   quantise_activations_ms=ms_q, nominal_dense_peak_tflops=4500.0 if args.kind == "mxfp8" else 9000.0)
     elif args.kernel in ("flash_fwd", "flash_bwd"):
         B, S, H, hd = args.b, args.s, args.h, args.hd
         qkv = (torch.randn(B, S, 3, H, hd, device=dev) * 0.5).bfloat16()

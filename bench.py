@@ -214,6 +214,7 @@ def main():
     ap.add_argument("--dp", default="fused", choices=["fused", "nccl"], help="data-parallel gradient path for N > 1")
     ap.add_argument("--global-batch", type=int, default=0, help="override the global batch (diagnostics; the headline configuration is 64)")
     ap.add_argument("--small", action="store_true", help="tiny configuration for smoke tests (NOT a valid bench number)")
+    ap.add_argument("--no-pair", action="store_true", help="bf16 GEMMs on single-CTA tiles only, no CTA pairs (diagnostics)")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch (diagnostics)")
     ap.add_argument("--no-torch-arm", action="store_true", help="skip the stock-PyTorch run that follows the measurement (the `torch_arm` / `vs_torch` keys)")
     args = ap.parse_args()
@@ -245,6 +246,8 @@ def main():
     nv.cuda()
     if args.no_pdl:
         nv.set_pdl(False)
+    if args.no_pair:
+        nv.set_gemm_pair(False)
 
     cfg = dict(CONFIG)
     if args.small:
@@ -353,7 +356,7 @@ def main():
                        "global_batch": cfg["global_batch"], "seq_len": S,
                        "parallelism": f"dp{world}" + (f"-{args.dp}" if world > 1 else ""),
                        "l2_policy": "inputs larger than L2 (multi-GB activation working set per step)",
-                       "cuda_graph": trainer._graph is not None, "pdl": not args.no_pdl, "small": bool(args.small)},
+                       "cuda_graph": trainer._graph is not None, "pdl": not args.no_pdl, "gemm_cta_pairs": not args.no_pair, "small": bool(args.small)},
             "clocks": sampler.summary(),
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4},

@@ -108,6 +108,8 @@ def run_lm(name, args):
         over["layers"] = args.layers
     if args.seq:
         over["seq_len"] = args.seq
+    if args.recompute_scan and name == "mamba_lm":
+        over["recompute_scan"] = True
     cfg = dataclasses.replace(PRESETS[name], **over)
     batch = args.batch or cfg.batch_per_gpu
     par = args.parallel if args.parallel != "auto" else (cfg.parallelism if world > 1 else "none")
@@ -370,6 +372,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "torch"], help="torch: the NCCL + cuBLAS library arm (moe_lm, mamba_lm)")
     ap.add_argument("--parallel", default="auto", choices=["auto", "dp", "tp", "ep"], help="layout for N > 1 (auto: the preset's)")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"], help="b200 arm: fused peer-memory kernels or NCCL calls")
+    ap.add_argument("--recompute-scan", action="store_true", help="mamba_lm: rebuild the scan checkpoints in the backward (less memory, one more forward scan per layer)")
     ap.add_argument("--kernel-table", default="", help="after timing, profile one more step and write device time per kernel name here")
     ap.add_argument("--buckets", action="store_true", help="dp: bucketed gradient reduction overlapped with backward")
     args = ap.parse_args()

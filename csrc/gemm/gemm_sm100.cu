@@ -101,11 +101,13 @@ __device__ __forceinline__ float act_bwd(float s, int act) {
   }
 }
 
-template <typename T, int BN, bool A_MN, bool B_MN>
+// CG = 2: a pair of CTAs on neighbouring SMs shares one 256 x BN tile; each CTA stages its own 128 rows of A and its own
+// half (BN / 2 rows) of B, so a K step moves 32 KB per SM instead of 48 KB for the same FLOPs per SM.
+template <typename T, int BN, bool A_MN, bool B_MN, int CG = 1>
 struct GemmSmem {
   static constexpr int BK = ElemTraits<T>::BK;
   static constexpr int A_BYTES = BM * TILE_K_BYTES;   // 16 KB
-  static constexpr int B_BYTES = BN * TILE_K_BYTES;
+  static constexpr int B_BYTES = (BN / CG) * TILE_K_BYTES;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_BYTES = EPI_WARPS * EPI_PANEL_BYTES;   // 32 KB
   static constexpr int BAR_BYTES = 256;
@@ -152,6 +154,30 @@ __device__ __forceinline__ void panel_store(uint8_t* sbuf, int lane, const float
     const uint4 v = *reinterpret_cast<const uint4*>(sbuf + P::off(row, c));
     if (row < rows_valid && c < chunks_valid) *reinterpret_cast<uint4*>(gpanel + (long long)row * ld + c * 8) = v;
   }
+}
+
+// Tensor maps of the bf16 outputs (C and the optional pre-activation copy), box {64 columns, 32 rows}: with them a warp
+// hands its 32 x 64 panel to the TMA engine as ONE store instead of reading it back from shared memory and issuing
+// 8 predicated 16-byte stores per thread.
+struct OutMaps {
+  CUtensorMap c, aux;
+  int use;              // 0: plain stores (fp32 / int32 outputs, unaligned C, narrow tiles)
+};
+
+// registers (row owner) -> bf16 panel in the 128-byte-swizzle layout -> one TMA store; rows and columns past the edge of
+// the tensor are clipped by the copy engine. The panel buffer is reused, so the previous store's read of it is awaited first.
+__device__ __forceinline__ void panel_store_tma(uint8_t* sbuf, int lane, const float (&f)[64], const CUtensorMap* tm, int col0, int row0, int b) {
+  if (lane == 0) tma_store_wait_read0();
+  __syncwarp();
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint4 o = make_uint4(pack_bf16x2(f[8 * c], f[8 * c + 1]), pack_bf16x2(f[8 * c + 2], f[8 * c + 3]),
+                         pack_bf16x2(f[8 * c + 4], f[8 * c + 5]), pack_bf16x2(f[8 * c + 6], f[8 * c + 7]));
+    *reinterpret_cast<uint4*>(sbuf + sw128_offset(lane, c)) = o;
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) { tma_store_3d(tm, sbuf, col0, row0, b); tma_store_commit(); }
 }
 
 // global (bf16, coalesced) -> row-owner registers: out[c] = 8 bf16 of this lane's row, chunk c
@@ -212,9 +238,13 @@ __device__ __forceinline__ bool peer_handshake(const TpParams& tp, uint32_t epoc
   return ok;
 }
 
-template <typename T, int BN, bool A_MN, bool B_MN, int TP>
-__device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const TpParams* tpp) {
-  using S = GemmSmem<T, BN, A_MN, B_MN>;
+template <typename T, int BN, bool A_MN, bool B_MN, int TP, int CG = 1>
+__device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const TpParams* tpp,
+                                          const OutMaps* om = nullptr) {
+  using S = GemmSmem<T, BN, A_MN, B_MN, CG>;
+  static_assert(CG == 1 || (CG == 2 && TP == TP_NONE && BN == 256), "CTA pairs: plain GEMM with 256-wide tiles only");
+  constexpr int BNL = BN / CG;                          // rows of B this CTA stages
+  const uint32_t crank = CG == 2 ? cluster_ctarank() : 0u;
   constexpr int BK = S::BK;
   constexpr int STAGES = S::STAGES;
   constexpr int ATOM = TILE_K_BYTES / sizeof(T);        // elements per 128-byte row
@@ -236,7 +266,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
   const int lane = threadIdx.x & 31;
   pdl_trigger();
 
-  const int m_blocks = (p.M + BM - 1) / BM;
+  const int m_blocks = (p.M + BM * CG - 1) / (BM * CG);      // row blocks of a tile: 128 rows, 256 for a CTA pair
   const int n_blocks = (p.N + BN - 1) / BN;
   const int num_kb = (p.K + BK - 1) / BK;
   const int kb_per_split = (num_kb + p.splits - 1) / p.splits;
@@ -244,8 +274,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
   const long long total_tiles = tiles_per_batch * p.batch;
   // TP_AG_GEMM reserves the first `copy_ctas` CTAs for pulling remote shards; the rest run the GEMM
   const int n_copy = (TP == TP_AG_GEMM) ? tpp->copy_ctas : 0;
-  const int cta = (int)blockIdx.x - n_copy;
-  const int n_ctas = (int)gridDim.x - n_copy;
+  const int cta = CG == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x - n_copy;          // CTA pairs walk the tiles together
+  const int n_ctas = CG == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x - n_copy;
   const int tp_shift = (TP == TP_AG_GEMM) ? tpp->rank * tpp->blocks_per_rank : 0;   // start with the local rows
   // The handshake epoch of a tensor-parallel call lives in device memory (one word per context) and is advanced by the
   // call's last CTA, so a CUDA-graph replay of the launch sees a fresh epoch every time.
@@ -253,14 +283,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], EPI_WARPS); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], EPI_WARPS * CG); }   // pair: both CTAs' epilogue warps arrive at the even CTA
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
   }
+  if constexpr (CG == 2) cluster_sync_all();            // the partner's barriers exist before anything is counted on them
   if (warp == 1) {
-    tmem_alloc(tmem_slot, TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (CG == 2) { tmem_alloc_pair(tmem_slot, TMEM_COLS); tmem_relinquish_pair(); }
+    else { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -335,6 +366,28 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, ST_TIMEOUT_TMA_EMPTY)) { ok = false; break; }
           uint8_t* sa = smem + stage * S::STAGE_BYTES;
           uint8_t* sb = sa + S::A_BYTES;
+          if constexpr (CG == 2) {
+            // both CTAs load their own halves; the bytes of both are counted on the even CTA's barrier, which its MMA thread waits on
+            const int arow = (mb * 2 + (int)crank) * BM, brow = nb * BN + (int)crank * BNL;
+            const uint32_t bar = cluster_map(smem_u32(&full_bar[stage]), 0);
+            if (crank == 0) mbar_expect_tx(&full_bar[stage], 2 * S::STAGE_BYTES);
+            if (!A_MN) {
+              tma_load_3d_pair(sa, &tmA, bar, kb * BK, arow, b);
+            } else {
+#pragma unroll
+              for (int a = 0; a < BM / ATOM; ++a)
+                tma_load_3d_pair(sa + a * (BK * TILE_K_BYTES), &tmA, bar, arow + a * ATOM, kb * BK, b);
+            }
+            if (!B_MN) {
+              tma_load_3d_pair(sb, &tmB, bar, kb * BK, brow, b);
+            } else {
+#pragma unroll
+              for (int a = 0; a < BNL / ATOM; ++a)
+                tma_load_3d_pair(sb + a * (BK * TILE_K_BYTES), &tmB, bar, brow + a * ATOM, kb * BK, b);
+            }
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            continue;
+          }
           mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
           if (!A_MN) {
             tma_load_3d(sa, &tmA, &full_bar[stage], kb * BK, mb * BM, b);
@@ -356,8 +409,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BM, BN, KindOf<T>::CF, KindOf<T>::AF, KindOf<T>::BF,
+    if (lane == 0 && crank == 0) {                       // of a CTA pair only the even CTA issues
+      constexpr uint32_t idesc = make_idesc(BM * CG, BN, KindOf<T>::CF, KindOf<T>::AF, KindOf<T>::BF,
                                             A_MN ? 1u : 0u, B_MN ? 1u : 0u);
       // K-major: 8-row groups 1024 B apart.  MN-major: 8-k-row groups 1024 B apart, 128B-row atoms
       // BK*128 B apart.
@@ -387,15 +440,28 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
             uint64_t da = make_sdesc_sw128(sa + k * A_KADV, A_LBO, A_SBO);
             uint64_t db = make_sdesc_sw128(sb + k * B_KADV, B_LBO, B_SBO);
             const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
-            if constexpr (KindOf<T>::v == KIND_TF32) umma_tf32(d_tmem, da, db, idesc, accum);
+            if constexpr (CG == 2) umma_f16_pair(d_tmem, da, db, idesc, accum);
+            else if constexpr (KindOf<T>::v == KIND_TF32) umma_tf32(d_tmem, da, db, idesc, accum);
             else if constexpr (KindOf<T>::v == KIND_I8) umma_i8(d_tmem, da, db, idesc, accum);
             else if constexpr (KindOf<T>::v == KIND_F8) umma_f8(d_tmem, da, db, idesc, accum);
             else umma_f16(d_tmem, da, db, idesc, accum);
           }
-          tc_commit(&empty_bar[stage]);   // stage reusable once these MMAs have read it
+          if constexpr (CG == 2) {          // the stage is free in BOTH CTAs once these MMAs have read it
+            tc_commit_pair(cluster_map(smem_u32(&empty_bar[stage]), 0));
+            tc_commit_pair(cluster_map(smem_u32(&empty_bar[stage]), 1));
+          } else {
+            tc_commit(&empty_bar[stage]);   // stage reusable once these MMAs have read it
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) tc_commit(&acc_full[as]);
+        if (ok) {
+          if constexpr (CG == 2) {
+            tc_commit_pair(cluster_map(smem_u32(&acc_full[as]), 0));
+            tc_commit_pair(cluster_map(smem_u32(&acc_full[as]), 1));
+          } else {
+            tc_commit(&acc_full[as]);
+          }
+        }
       }
     }
   } else {
@@ -409,6 +475,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
     uint8_t* sbuf = epi_smem + ew * EPI_PANEL_BYTES;
     const float alpha = p.alpha_ptr ? p.alpha * __ldg(p.alpha_ptr) : p.alpha;
     const bool staged = (p.out_mode == OUT_BF16) && p.vec_ok;       // coalesced bf16 path
+    const bool tma_out = staged && PW == 64 && TP != TP_GEMM_RS && om != nullptr && om->use;   // ... through the TMA engine
     bool ok = true;
     int it = 0;
     for (long long t = cta; t < total_tiles && ok; t += n_ctas, ++it) {
@@ -423,7 +490,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
       const uint32_t aphase = (it >> 1) & 1;
       if (!mbar_wait(&acc_full[as], aphase, p.status, ST_TIMEOUT_ACC_FULL)) { ok = false; break; }
       tc_fence_after_sync();
-      const int row0 = mb * BM + q * 32;          // first row of this warp's panel
+      const int row0 = (mb * CG + (int)crank) * BM + q * 32;          // first row of this warp's panel
       const int row = row0 + lane;
       const bool row_ok = row < p.M;
       const int rows_valid = min(32, p.M - row0);  // may be <= 0
@@ -498,7 +565,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         }
         if (p.aux_out) {          // bf16 copy of the pre-activation (dense layout of C)
           __nv_bfloat16* ap = reinterpret_cast<__nv_bfloat16*>(p.aux_out) + cbase + col0;
-          if (staged) panel_store<PW>(sbuf, lane, f, ap, p.ldc, rows_valid, chunks_valid);
+          if constexpr (PW == 64) {
+            if (tma_out) panel_store_tma(sbuf, lane, f, &om->aux, col0, row0, b);
+          }
+          if (tma_out) {}
+          else if (staged) panel_store<PW>(sbuf, lane, f, ap, p.ldc, rows_valid, chunks_valid);
           else if (row_ok) {
 #pragma unroll
             for (int j = 0; j < PW; ++j) if (j < cols_valid) ap[(long long)lane * p.ldc + j] = __float2bfloat16(f[j]);
@@ -516,6 +587,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
           const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + cbase + col0;
           if (staged) {
             uint4 u[PW / 8];
+            if (tma_out) { if (lane == 0) tma_store_wait_read0(); __syncwarp(); }
             panel_load<PW>(sbuf, lane, ap, p.ldc, rows_valid, chunks_valid, u);
             switch (p.dact) {
 #define B200_DACT_CASE(A) case A: { _Pragma("unroll") for (int j = 0; j < PW / 8; ++j) { \
@@ -535,6 +607,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
           const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(p.residual) + rbase + col0;
           if (staged && p.res_vec_ok) {
             uint4 u[PW / 8];
+            if (tma_out) { if (lane == 0) tma_store_wait_read0(); __syncwarp(); }
             panel_load<PW>(sbuf, lane, rp, p.ldr, rows_valid, chunks_valid, u);
 #pragma unroll
             for (int j = 0; j < PW / 8; ++j) {
@@ -557,7 +630,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
             const long long slot = ((long long)(tp_epoch & 1u) * tp.world + tp.rank) * rows_per_rank;
             cp = reinterpret_cast<__nv_bfloat16*>(tp.slots_peer[owner]) + (slot + (row0 - owner * rows_per_rank)) * p.ldc + col0;
           }
-          if (staged) panel_store<PW>(sbuf, lane, f, cp, p.ldc, rows_valid, chunks_valid);
+          if constexpr (PW == 64) {
+            if (tma_out) panel_store_tma(sbuf, lane, f, &om->c, col0, row0, b);
+          }
+          if (tma_out) {}
+          else if (staged) panel_store<PW>(sbuf, lane, f, cp, p.ldc, rows_valid, chunks_valid);
           else if (row_ok) {
 #pragma unroll
             for (int j = 0; j < PW; ++j) if (j < cols_valid) cp[(long long)lane * p.ldc + j] = __float2bfloat16(f[j]);
@@ -586,15 +663,21 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[as]);
+      if (lane == 0) {
+        if constexpr (CG == 2) mbar_arrive_cluster(cluster_map(smem_u32(&acc_empty[as]), 0));
+        else mbar_arrive(&acc_empty[as]);
+      }
     }
+    if (tma_out && lane == 0) tma_store_wait0();          // this warp's last stores have left shared memory and landed
   }
 
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();            // neither CTA leaves (or frees TMEM) while its partner may still use it
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if constexpr (CG == 2) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
   if constexpr (TP == TP_AG_GEMM) {
     // The last CTA of the grid tells every peer "my GEMM no longer reads my staging buffer" and waits for the
@@ -654,8 +737,17 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
 
 template <typename T, int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ GemmParams p) {
-  gemm_body<T, BN, A_MN, B_MN, TP_NONE>(tmA, tmB, p, nullptr);
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ GemmParams p,
+            const __grid_constant__ OutMaps om) {
+  gemm_body<T, BN, A_MN, B_MN, TP_NONE>(tmA, tmB, p, nullptr, &om);
+}
+
+// CTA-pair variant: bf16, 256 x 256 tile per pair, launched as clusters of two
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ GemmParams p,
+                 const __grid_constant__ OutMaps om) {
+  gemm_body<__nv_bfloat16, 256, A_MN, B_MN, TP_NONE, 2>(tmA, tmB, p, nullptr, &om);
 }
 
 // bf16, K-major x K-major (the Linear forward layout) fused with its neighbouring collective
@@ -687,6 +779,23 @@ static int gemm_set_attr() {
   return 0;
 }
 
+static int g_tma_store = -1;     // -1: from the environment on first use (B200NN_GEMM_TMA_STORE=0 turns it off)
+// Output maps for the bf16 store path; `use` stays 0 (plain stores) whenever a rule of the copy engine is not met.
+static void make_out_maps(OutMaps& om, const GemmParams& p, int BN) {
+  om.use = 0;
+  if (g_tma_store < 0) { const char* e = getenv("B200NN_GEMM_TMA_STORE"); g_tma_store = (e && e[0] == '0') ? 0 : 1; }
+  if (!g_tma_store || p.out_mode != OUT_BF16 || !p.vec_ok || BN < 128) return;
+  const unsigned long long ldb = (unsigned long long)p.ldc * 2, sb = (unsigned long long)p.strideC * 2;
+  if (ldb % 16 || (p.batch > 1 && sb % 16) || (reinterpret_cast<uintptr_t>(p.C) & 15)) return;
+  if (make_tmap_3d(&om.c, p.C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.M, p.batch, ldb, sb, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B)) return;
+  om.aux = om.c;
+  if (p.aux_out) {
+    if (reinterpret_cast<uintptr_t>(p.aux_out) & 15) return;
+    if (make_tmap_3d(&om.aux, p.aux_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.M, p.batch, ldb, sb, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B)) return;
+  }
+  om.use = 1;
+}
+
 template <typename T, int BN, bool A_MN, bool B_MN>
 static int launch_one(const GemmArgs& a, cudaStream_t stream, int num_sms) {
   using S = GemmSmem<T, BN, A_MN, B_MN>;
@@ -709,7 +818,60 @@ static int launch_one(const GemmArgs& a, cudaStream_t stream, int num_sms) {
   const long long tiles = m_blocks * n_blocks * p.splits * p.batch;
   int grid = (int)(tiles < num_sms ? tiles : num_sms);
   if (grid < 1) grid = 1;
-  cudaError_t e = launch_pdl(kfn, dim3(grid), dim3(GEMM_THREADS), S::TOTAL, stream, tmA, tmB, p);
+  OutMaps om;
+  om.c = tmA; om.aux = tmA;
+  make_out_maps(om, p, BN);
+  cudaError_t e = launch_pdl(kfn, dim3(grid), dim3(GEMM_THREADS), S::TOTAL, stream, tmA, tmB, p, om);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+static int g_pair_mode = -1;     // -1: from the environment on first use; 0: off; 1: where it pays; 2: wherever the shape allows
+static bool pair_enabled() {
+  if (g_pair_mode < 0) {
+    const char* e = getenv("B200NN_GEMM_PAIR");
+    g_pair_mode = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_pair_mode >= 1;
+}
+
+template <bool A_MN, bool B_MN>
+static int pair_set_attr() {
+  static bool done = false;
+  if (done) return 0;
+  (void)cudaGetLastError();
+  cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       GemmSmem<__nv_bfloat16, 256, A_MN, B_MN, 2>::TOTAL);
+  if (e != cudaSuccess) return (int)e;
+  done = true;
+  return 0;
+}
+
+// 256 x 256 tiles on CTA pairs. Worth it when there are enough pair tiles to fill the machine.
+template <bool A_MN, bool B_MN>
+static int launch_pair(const GemmArgs& a, cudaStream_t stream, int num_sms) {
+  using T = __nv_bfloat16;
+  using S = GemmSmem<T, 256, A_MN, B_MN, 2>;
+  constexpr int BK = S::BK, BN = 256;
+  constexpr int ATOM = TILE_K_BYTES / sizeof(T);
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!A_MN) rc = make_tmap_3d(&tmA, a.A, DT<T>::v, sizeof(T), a.K, a.M, a.batch, a.lda * sizeof(T), a.strideA * sizeof(T), BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  else       rc = make_tmap_3d(&tmA, a.A, DT<T>::v, sizeof(T), a.M, a.K, a.batch, a.lda * sizeof(T), a.strideA * sizeof(T), ATOM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return 100 + rc;
+  if (!B_MN) rc = make_tmap_3d(&tmB, a.B, DT<T>::v, sizeof(T), a.K, a.N, a.batch, a.ldb * sizeof(T), a.strideB * sizeof(T), BK, BN / 2, CU_TENSOR_MAP_SWIZZLE_128B);
+  else       rc = make_tmap_3d(&tmB, a.B, DT<T>::v, sizeof(T), a.N, a.K, a.batch, a.ldb * sizeof(T), a.strideB * sizeof(T), ATOM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return 200 + rc;
+  { int e = pair_set_attr<A_MN, B_MN>(); if (e) return 300 + e; }
+  GemmParams p = a.p;
+  const long long m_blocks = (p.M + 2 * BM - 1) / (2 * BM), n_blocks = (p.N + BN - 1) / BN;
+  const long long tiles = m_blocks * n_blocks * p.splits * p.batch;
+  const long long pairs = num_sms / 2;
+  int grid = 2 * (int)(tiles < pairs ? tiles : pairs);
+  OutMaps om;
+  om.c = tmA; om.aux = tmA;
+  make_out_maps(om, p, BN);
+  cudaError_t e = launch_pdl_cluster2(gemm_pair_kernel<A_MN, B_MN>, dim3(grid), dim3(GEMM_THREADS), S::TOTAL, stream, tmA, tmB, p, om);
   if (e == cudaSuccess) e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }
@@ -744,6 +906,18 @@ static int launch_tp(const GemmArgs& a, const TpParams& tp, cudaStream_t stream,
 
 template <typename T, int BN>
 static int launch_major(const GemmArgs& a, cudaStream_t s, int sms) {
+  if constexpr (BN == 256 && sizeof(T) == 2) {
+    // CTA pairs when the pair tiles fill the machine at least once (small problems keep the finer 128-row tiles)
+    const long long pair_tiles = (long long)((a.p.M + 255) / 256) * ((a.p.N + 255) / 256) * a.p.splits * a.p.batch;
+    // and the mainloop is long enough to matter (K >= 1024 per split: below that the tile is bound by its epilogue)
+    const bool pays = pair_tiles >= sms / 2 && a.K / (a.p.splits > 0 ? a.p.splits : 1) >= 1024;
+    if (pair_enabled() && a.p.M >= 256 && (pays || g_pair_mode == 2)) {
+      if (!a.a_mn && !a.b_mn) return launch_pair<false, false>(a, s, sms);
+      if (!a.a_mn && a.b_mn) return launch_pair<false, true>(a, s, sms);
+      if (a.a_mn && !a.b_mn) return launch_pair<true, false>(a, s, sms);
+      return launch_pair<true, true>(a, s, sms);
+    }
+  }
   if (!a.a_mn && !a.b_mn) return launch_one<T, BN, false, false>(a, s, sms);
   if (!a.a_mn && a.b_mn) return launch_one<T, BN, false, true>(a, s, sms);
   if (a.a_mn && !a.b_mn) return launch_one<T, BN, true, false>(a, s, sms);
@@ -761,12 +935,18 @@ extern "C" int b200_gemm_init() {
   e |= gemm_set_attr<__nv_bfloat16, BN, true, false>(); e |= gemm_set_attr<__nv_bfloat16, BN, true, true>();
   B200_INIT_BN(64) B200_INIT_BN(128) B200_INIT_BN(256)
 #undef B200_INIT_BN
+  e |= pair_set_attr<false, false>(); e |= pair_set_attr<false, true>(); e |= pair_set_attr<true, false>(); e |= pair_set_attr<true, true>();
   e |= gemm_set_attr<float, 128, false, false>();
   e |= gemm_set_attr<s8s8_t, 128, false, false>(); e |= gemm_set_attr<s8s8_t, 256, false, false>();
   e |= gemm_set_attr<u8s8_t, 128, false, false>(); e |= gemm_set_attr<u8s8_t, 256, false, false>();
   e |= gemm_set_attr<e4m3_t, 128, false, false>(); e |= gemm_set_attr<e4m3_t, 256, false, false>();
   return e;
 }
+
+// 0: single-CTA tiles only; 1: 256 x 256 tiles on CTA pairs where they pay (default); 2: wherever M >= 256 and the tile is 256 wide
+extern "C" int b200_gemm_set_pair(int mode) { b200::g_pair_mode = mode < 0 ? 0 : (mode > 2 ? 2 : mode); return 0; }
+
+extern "C" int b200_gemm_set_tma_store(int on) { b200::g_tma_store = on ? 1 : 0; return 0; }
 
 extern "C" int b200_gemm_launch(const b200::GemmArgs* args, int bn, int num_sms, cudaStream_t stream) {
   using namespace b200;

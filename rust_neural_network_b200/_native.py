@@ -148,6 +148,26 @@ def set_pdl(on: bool) -> None:
     fn(1 if on else 0)
 
 
+def set_gemm_pair(on: bool, force: bool = False) -> None:
+    """bf16 GEMMs with 256-wide tiles run as 256 x 256 tiles on pairs of CTAs (`cta_group::2`: one MMA across the tensor
+    cores of two neighbouring SMs, each staging half of the operands) where that pays: enough pair tiles to fill the
+    machine and at least 1024 of K per tile (shorter tiles are bound by their epilogue). On by default;
+    `B200NN_GEMM_PAIR=0` in the environment or `set_gemm_pair(False)` keeps single-CTA tiles; `force=True` takes the pair
+    kernel for every shape it can run (tests)."""
+    lib = _cuda_lib if _cuda_lib is not None else cuda()
+    fn = lib.b200_gemm_set_pair
+    fn.argtypes, fn.restype = [c_int], c_int
+    fn((2 if force else 1) if on else 0)
+
+
+def set_gemm_tma_store(on: bool) -> None:
+    """bf16 GEMM outputs leave the epilogue as TMA stores of 32 x 64 panels (default) or as per-thread 16-byte stores."""
+    lib = _cuda_lib if _cuda_lib is not None else cuda()
+    fn = lib.b200_gemm_set_tma_store
+    fn.argtypes, fn.restype = [c_int], c_int
+    fn(1 if on else 0)
+
+
 def register_sigs(sigs: dict) -> None:
     """Let other modules declare the signatures of kernels they own."""
     _EXTRA_SIGS.update(sigs)

@@ -69,6 +69,7 @@ class MambaLmConfig:
     seq_len: int = 4096
     batch_per_gpu: int = 8
     parallelism: str = "tp"
+    recompute_scan: bool = False     # rebuild the scan's state checkpoints in the backward instead of keeping them per layer
 
 
 @dataclasses.dataclass(frozen=True)
@@ -112,6 +113,6 @@ def build_model(name: str, device="cuda", tp=None, ep_group=None, ep_backend: st
         return m.to_device(dev, dt), cfg
     if name == "mamba_lm":
         from .models.mamba import MambaLM
-        m = MambaLM(cfg.vocab, cfg.d_model, cfg.layers, d_state=cfg.d_state, d_conv=cfg.d_conv, expand=cfg.expand, dt_rank=cfg.dt_rank, tp=tp)
+        m = MambaLM(cfg.vocab, cfg.d_model, cfg.layers, d_state=cfg.d_state, d_conv=cfg.d_conv, expand=cfg.expand, dt_rank=cfg.dt_rank, tp=tp, recompute_scan=cfg.recompute_scan)
         return m.to_device(dev, dt), cfg
     raise KeyError(name)

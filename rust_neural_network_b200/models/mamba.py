@@ -42,6 +42,7 @@ class MambaBlock(nn.Module):
         self.d_inner = expand * d_model
         self.standard = standard
         self.tp = tp
+        self.recompute_scan = False      # True: the scan's state checkpoints are rebuilt in the backward instead of kept
         di = self.d_inner
         if tp is not None:
             if not standard:
@@ -115,7 +116,7 @@ class MambaBlock(nn.Module):
         dt = F.linear(xp[:, :R], self.dt_up, None, "none", None)                     # [M, dl]
         b_vec, c_vec = xp[:, R:R + N].view(Bt, seq_len, N), xp[:, R + N:].view(Bt, seq_len, N)
         A = -torch.exp(self.a.float())
-        y = selective_scan(xa, dt.reshape(Bt, seq_len, dl), A, b_vec, c_vec, self.d_skip, z, self.dt_bias, True)
+        y = selective_scan(xa, dt.reshape(Bt, seq_len, dl), A, b_vec, c_vec, self.d_skip, z, self.dt_bias, True, self.recompute_scan)
         return TP.row_parallel(y.reshape(M, dl), self.out_proj, None, residual, tp)  # [rows_local, d_model]
 
     def forward(self, x):
@@ -128,12 +129,12 @@ class MambaBlock(nn.Module):
             dt = self.dt_up(self.proj_delta(xa))
             b_vec, c_vec = self.proj_b(xa), self.proj_c(xa)
             A = -torch.exp(self.a.float())
-            y = selective_scan(xa, dt, A, b_vec, c_vec, self.d_skip, z, self.dt_bias, True)
+            y = selective_scan(xa, dt, A, b_vec, c_vec, self.d_skip, z, self.dt_bias, True, self.recompute_scan)
         else:
             xa = causal_conv1d(xs, self.conv_weight, None, "silu")
             delta = self.proj_delta(xa)                                # softplus is applied inside the scan kernel
             b_vec, c_vec = self.proj_b(xa), self.proj_c(xa)
-            y = selective_scan(xa, delta, self.a, b_vec, c_vec, None, z, None, True)
+            y = selective_scan(xa, delta, self.a, b_vec, c_vec, None, z, None, True, self.recompute_scan)
         return self.out_proj(y)
 
     def parameters(self):
@@ -208,7 +209,7 @@ class MambaLM(nn.Module):
     per-rank gradients are partial sums over that rank's rows."""
 
     def __init__(self, vocab: int, d_model: int, num_layers: int, d_state: int = 16, d_conv: int = 4, expand: int = 2,
-                 dt_rank: int = 0, init_std: float = 0.02, tp=None, seed: int = 1234):
+                 dt_rank: int = 0, init_std: float = 0.02, tp=None, seed: int = 1234, recompute_scan: bool = False):
         init = nn.normal_init(init_std)
         self.tp = tp
         g = torch.Generator().manual_seed(seed) if tp is not None else None
@@ -216,6 +217,8 @@ class MambaLM(nn.Module):
         self.norms = [nn.LayerNorm(d_model) for _ in range(num_layers)]
         self.blocks = [MambaBlock(d_model, d_state, expand, d_conv, standard=True, dt_rank=dt_rank, init=init, tp=tp, generator=g)
                        for _ in range(num_layers)]
+        for b in self.blocks:
+            b.recompute_scan = recompute_scan
         self.ln_final = nn.LayerNorm(d_model)
         self.lm_head = nn.Linear(d_model, vocab, bias=False, init=init)
 

@@ -154,7 +154,8 @@ def scan_bwd_raw(dy, u, delta, A, Bm, Cm, Dskip, z, delta_bias, delta_softplus, 
 # ----------------------------------------------------------------------------- autograd
 class SelectiveScanFn(Function):
     @staticmethod
-    def forward(ctx, u, delta, A, Bm, Cm, Dskip, z, delta_bias, delta_softplus):
+    def forward(ctx, u, delta, A, Bm, Cm, Dskip, z, delta_bias, delta_softplus, recompute=False):
+        ctx.recompute = bool(recompute)
         if not u.is_cuda:
             ctx.cpu = True
             ctx.save_for_backward(u, delta, A, Bm, Cm, Dskip, z, delta_bias)
@@ -162,8 +163,10 @@ class SelectiveScanFn(Function):
             return selective_scan_ref(u, delta, A, Bm, Cm, Dskip, z, delta_bias, delta_softplus)
         ctx.cpu = False
         need = any(t is not None and t.requires_grad for t in (u, delta, A, Bm, Cm, Dskip, z, delta_bias))
+        # recompute: the state checkpoints (B x S/8 x D x N fp32, 4x the size of u) are not kept; the backward runs the
+        # forward kernel once more to rebuild them, so only one layer's checkpoints exist at a time
         y, hck = scan_fwd_raw(u, delta, A.detach(), Bm, Cm, Dskip.detach() if Dskip is not None else None, z,
-                              delta_bias.detach() if delta_bias is not None else None, delta_softplus, need)
+                              delta_bias.detach() if delta_bias is not None else None, delta_softplus, need and not ctx.recompute)
         ctx.save_for_backward(u, delta, A, Bm, Cm, Dskip, z, delta_bias, hck)
         ctx.softplus = delta_softplus
         return y
@@ -182,23 +185,28 @@ class SelectiveScanFn(Function):
             for t, orig in zip(ins, (u, delta, A, Bm, Cm, Dskip, z, delta_bias)):
                 g = next(it) if t is not None else None
                 outs.append(g.to(orig.dtype) if g is not None else None)
-            return (*outs, None)
+            return (*outs, None, None)
         u, delta, A, Bm, Cm, Dskip, z, delta_bias, hck = ctx.saved_tensors
+        if hck is None:
+            _, hck = scan_fwd_raw(u, delta, A.detach(), Bm, Cm, Dskip.detach() if Dskip is not None else None, z,
+                                  delta_bias.detach() if delta_bias is not None else None, ctx.softplus, True)
         du, ddelta, dA, dB, dC, dD, dz, ddb = scan_bwd_raw(dy, u, delta, A.detach(), Bm, Cm,
                                                            Dskip.detach() if Dskip is not None else None, z,
                                                            delta_bias.detach() if delta_bias is not None else None,
                                                            ctx.softplus, hck)
         return (du, ddelta.to(delta.dtype), dA.to(A.dtype), dB.to(Bm.dtype), dC.to(Cm.dtype),
-                dD.to(Dskip.dtype) if dD is not None else None, dz, ddb.to(delta_bias.dtype) if ddb is not None else None, None)
+                dD.to(Dskip.dtype) if dD is not None else None, dz, ddb.to(delta_bias.dtype) if ddb is not None else None, None, None)
 
 
-def selective_scan(u, delta, A, Bm, Cm, Dskip=None, z=None, delta_bias=None, delta_softplus=False):
+def selective_scan(u, delta, A, Bm, Cm, Dskip=None, z=None, delta_bias=None, delta_softplus=False, recompute=False):
+    """`recompute=True` trades one more forward scan in the backward pass for not keeping the state checkpoints of
+    every layer alive between forward and backward (4x the bytes of `u` per layer)."""
     if z is not None and u.is_cuda and A.shape[1] == 16:
         # the lane-per-state kernels (16 states) take no gate: y * silu(z) is one elementwise kernel on each side of them,
         # far cheaper than falling back to the thread-per-channel scan that fuses it
         from . import functional as F
-        return F.mul_silu(SelectiveScanFn.apply(u, delta, A, Bm, Cm, Dskip, None, delta_bias, delta_softplus), z.to(u.dtype))
-    return SelectiveScanFn.apply(u, delta, A, Bm, Cm, Dskip, z, delta_bias, delta_softplus)
+        return F.mul_silu(SelectiveScanFn.apply(u, delta, A, Bm, Cm, Dskip, None, delta_bias, delta_softplus, recompute), z.to(u.dtype))
+    return SelectiveScanFn.apply(u, delta, A, Bm, Cm, Dskip, z, delta_bias, delta_softplus, recompute)
 
 
 class CausalConv1dFn(Function):

@@ -102,11 +102,21 @@ class QuantizedTensor:
 class QuantizedLinear(nn.Module):
     def __init__(self, weight: QuantizedTensor, bias: Optional[torch.Tensor], in_features: int, out_features: int):
         self.weight, self.bias, self.in_features, self.out_features = weight, bias, in_features, out_features
+        self.mx = None          # block-scaled copy of the weight for the tensor-core path (from_linear(tensor_core=True))
 
     @staticmethod
-    def from_linear(layer: nn.Linear, format: QuantFormat, group_size: int = 0) -> "QuantizedLinear":
+    def from_linear(layer: nn.Linear, format: QuantFormat, group_size: int = 0, tensor_core: bool = False) -> "QuantizedLinear":
+        """`tensor_core=True` (NVFP4 only, in_features a multiple of 256) additionally stores the weight as e2m1 with ue4m3
+        block scales, and `forward` on a GPU then multiplies 4-bit operands on the tensor core (ops/mx.py) instead of
+        dequantising the weight to bf16."""
         b = layer.bias.detach().float().clone() if layer.bias is not None else None
-        return QuantizedLinear(QuantizedTensor.quantize(layer.weight, format, group_size), b, layer.weight.shape[1], layer.weight.shape[0])
+        q = QuantizedLinear(QuantizedTensor.quantize(layer.weight, format, group_size), b, layer.weight.shape[1], layer.weight.shape[0])
+        if tensor_core:
+            if format != QuantFormat.NVFP4 or layer.weight.shape[1] % 256 != 0:
+                raise ValueError("the tensor-core path takes NVFP4 weights with in_features a multiple of 256")
+            from .ops import mx
+            q.mx = mx.quantize_mx(layer.weight.detach(), "nvfp4")
+        return q
 
     def _rowwise_int8(self) -> bool:
         w = self.weight
@@ -114,7 +124,13 @@ class QuantizedLinear(nn.Module):
 
     def forward(self, x: torch.Tensor, out_dtype=torch.float32, act: str = "none") -> torch.Tensor:
         a = x.detach().reshape(-1, x.shape[-1])
-        if self._rowwise_int8():
+        if self.mx is not None and a.is_cuda:
+            from .ops import mx
+            y = mx.gemm_mx(mx.quantize_mx(a, "nvfp4"), self.mx, torch.float32)
+            if self.bias is not None:
+                y = y + self.bias
+            y = G.act_ref(y, act).to(out_dtype)
+        elif self._rowwise_int8():
             aq, a_scale = Q.quant_rows(a, "int8")
             wq = self.weight.data.view(torch.int8).view(self.out_features, self.in_features)
             y = G.gemm(aq, wq, row_scale=a_scale, col_scale=self.weight.scales, bias=self.bias, act=act, out_dtype=out_dtype)

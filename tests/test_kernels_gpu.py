@@ -364,3 +364,64 @@ def test_softmax_rows_forward_backward(dtype, rows, cols, causal):
     tol = 1e-5 if dtype == torch.float32 else 1e-2
     assert torch.allclose(y.float(), ref, atol=tol, rtol=tol)
     assert torch.allclose(x.grad.float(), xr.grad, atol=tol * 4, rtol=tol * 4)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(8192, 2048, 512), (5000, 1800, 192), (16384, 512, 2048)])
+def test_gemm_cta_pair_tiles(M, N, K, a_mn, b_mn):
+    """Shapes with enough 256 x 256 tiles to take the CTA-pair kernel (one MMA across two SMs), against the same product
+    on single-CTA tiles (must agree to the last bit: same K order, same fp32 accumulation) and against fp32."""
+    from rust_neural_network_b200 import _native as nv
+    torch.manual_seed(M + N + K)
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda").bfloat16()
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda").bfloat16()
+    bias = torch.randn(N, device="cuda")
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    nv.set_gemm_pair(True, force=True)
+    out = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, act="gelu", residual=res, bn=256)
+    out32 = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32, bn=256)
+    nv.set_gemm_pair(False)
+    one = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, act="gelu", residual=res, bn=256)
+    one32 = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32, bn=256)
+    nv.set_gemm_pair(True)
+    torch.cuda.synchronize(); nv.check_status()
+    assert torch.equal(out, one) and torch.equal(out32, one32)
+    ref = G.gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    assert rel_err(out32, ref) < 1e-5
+
+
+def test_gemm_cta_pair_split_k_and_batch():
+    from rust_neural_network_b200 import _native as nv
+    torch.manual_seed(11)
+    nv.set_gemm_pair(True, force=True)
+    a = torch.randn(4096, 2048, device="cuda").bfloat16()           # dW-like: A, B MN-major, long K, split-K with fp32 atomics
+    b = torch.randn(4096, 1024, device="cuda").bfloat16()
+    acc = torch.zeros(2048, 1024, device="cuda")
+    G.gemm(a, b, a_mn=True, b_mn=True, accumulate_into=acc, bn=256)
+    ref = a.float().t() @ b.float()
+    assert rel_err(acc, ref) < 1e-4
+    ab = torch.randn(6, 1024, 256, device="cuda").bfloat16()
+    bb = torch.randn(6, 2048, 256, device="cuda").bfloat16()
+    out = G.gemm(ab, bb, out_dtype=torch.float32, bn=256)
+    torch.cuda.synchronize(); nv.check_status()
+    nv.set_gemm_pair(True)
+    assert rel_err(out, ab.float() @ bb.float().transpose(1, 2)) < 1e-5
+
+
+@pytest.mark.parametrize("M,N,K", [(4096, 1536, 512), (1000, 520, 256), (300, 2048, 128)])
+def test_gemm_tma_store_epilogue_matches_plain_stores(M, N, K):
+    """bf16 outputs (C and the saved pre-activation) through TMA stores, ragged edges included, against per-thread stores."""
+    from rust_neural_network_b200 import _native as nv
+    torch.manual_seed(M)
+    a, b = torch.randn(M, K, device="cuda").bfloat16(), torch.randn(N, K, device="cuda").bfloat16()
+    bias, res = torch.randn(N, device="cuda"), torch.randn(M, N, device="cuda").bfloat16()
+    outs = []
+    for on in (True, False):
+        nv.set_gemm_tma_store(on)
+        y, aux = G.gemm(a, b, bias=bias, act="gelu", residual=res, want_aux=True)
+        outs.append((y.clone(), aux.clone()))
+    nv.set_gemm_tma_store(True)
+    torch.cuda.synchronize(); nv.check_status()
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    ref, _ = G.gemm_ref(a, b, bias=bias, act="gelu", residual=res, want_aux=True, out_dtype=torch.float32)
+    assert rel_err(outs[0][0], ref) < 1e-2

@@ -60,3 +60,19 @@ def test_mx_linear_layer():
         assert y.shape == (4, 60, 512) and y.dtype == torch.bfloat16
         assert _rel(y, ref) < tol
         assert lin.memory_bytes() < w.numel() * (1.1 if kind == "mxfp8" else 0.6) + 2048
+
+
+def test_quantized_linear_nvfp4_tensor_core_path():
+    from rust_neural_network_b200 import nn
+    from rust_neural_network_b200.quantize import QuantFormat, QuantizedLinear
+    torch.manual_seed(5)
+    lin = nn.Linear(512, 256).to_device("cuda", torch.float32)
+    x = torch.randn(40, 512, device="cuda")
+    ref = x @ lin.weight.t() + lin.bias
+    soft = QuantizedLinear.from_linear(lin, QuantFormat.NVFP4, 16)
+    hard = QuantizedLinear.from_linear(lin, QuantFormat.NVFP4, 16, tensor_core=True)
+    assert hard.mx is not None and soft.mx is None
+    ys, yh = soft.forward(x), hard.forward(x)
+    assert _rel(ys, ref) < 0.15 and _rel(yh, ref) < 0.2          # the second also quantises the activations to 4 bits
+    with pytest.raises(ValueError):
+        QuantizedLinear.from_linear(nn.Linear(100, 8).to_device("cuda", torch.float32), QuantFormat.NVFP4, 16, tensor_core=True)

@@ -72,3 +72,23 @@ def test_causal_conv1d(B, S, C, K, act, bias, dtype):
     assert rel_err(w.grad, wr.grad) < gtol
     if bias:
         assert rel_err(b.grad, br.grad) < gtol
+
+
+@pytest.mark.gpu
+def test_selective_scan_recompute_gives_identical_gradients():
+    """`recompute=True` keeps no state checkpoints and rebuilds them in the backward: same bits, less memory held."""
+    from rust_neural_network_b200.ops.scan import selective_scan
+    torch.manual_seed(0)
+    B, S, D, N = 2, 300, 128, 16
+    mk = lambda *s: (torch.randn(*s, device="cuda") * 0.5).bfloat16()
+    u, dl, z, Bm, Cm = mk(B, S, D), mk(B, S, D), mk(B, S, D), mk(B, S, N), mk(B, S, N)
+    A = -torch.arange(1, N + 1, device="cuda", dtype=torch.float32).repeat(D, 1)
+    Dk, db = torch.randn(D, device="cuda"), torch.randn(D, device="cuda") * 0.1
+    res = []
+    for rec in (False, True):
+        ins = [t.clone().requires_grad_(True) for t in (u, dl, A, Bm, Cm, Dk, z, db)]
+        y = selective_scan(ins[0], ins[1], ins[2], ins[3], ins[4], ins[5], ins[6], ins[7], True, rec)
+        y.float().square().sum().backward()
+        res.append([y.detach()] + [t.grad for t in ins])
+    for a, b in zip(*res):
+        assert torch.equal(a, b)

@@ -34,6 +34,26 @@ namespace b200 {
 
 constexpr int LA_C = 128;                    // tokens per chunk = rows of every product = TMEM lanes
 
+// Sequence-parallel exchange of the slice totals, done by the attention kernels themselves over NVLink peer memory.
+// The state pass of a rank (role 1) writes its total into its OWN symmetric buffer and then raises one flag per
+// (consumer rank, batch x head); the main pass (role 2) of a consumer waits for the flags of the ranks it depends on,
+// pulls their totals with plain peer loads in rank order (so every run sums in the same order), keeps the sum in
+// `prefix` and acknowledges. A total is double-buffered by call parity and is only overwritten once every consumer has
+// acknowledged the call two earlier. The call counter is a device word that the last CTA of the main pass advances,
+// so a captured graph replays with fresh epochs. All waits are bounded.
+constexpr int LA_MAX_WORLD = 8;
+struct LaExchange {
+  float* state[LA_MAX_WORLD];       // every rank's totals [2][B*H][hd*hd + hd] fp32 (peer-mapped)
+  uint32_t* flags[LA_MAX_WORLD];    // every rank's arrival flags [world][B*H] (peer-mapped): flags[c][r * BH + bh] = epoch
+  uint32_t* acks[LA_MAX_WORLD];     // every rank's release flags [world][B*H] (peer-mapped): acks[r][c * BH + bh] = epoch
+  float* prefix;                    // local [B*H][hd*hd + hd]: the sum the main pass started from (the backward needs it again)
+  uint32_t* words;                  // local: [0] calls so far, [1] retired CTAs of the main pass
+  long long wait_cycles;
+  int rank, world;                  // world <= 1: no exchange
+  int dir;                          // 0: sum over the LOWER ranks (forward states), 1: over the HIGHER ranks (backward)
+  int role;                         // 0: none, 1: publish this slice's total, 2: consume
+};
+
 struct LinAttnArgs {
   AttnTensor q, k, v, o;                     // bf16 [B, S, H, hd] (any strides, hd contiguous)
   AttnTensor dout, dq, dk, dv;               // backward
@@ -50,7 +70,83 @@ struct LinAttnArgs {
   int kind;                                  // 0: ELU + 1, 1: ReLU^2
   int state_only;                            // forward: only accumulate the state (reads K, V; writes s_out)
   uint32_t* status;
+  LaExchange sx;
 };
+
+__device__ __forceinline__ bool la_wait_flag(const uint32_t* f, uint32_t want, long long budget, uint32_t* status) {
+  const long long t0 = clock64();
+  for (;;) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+    if ((int32_t)(v - want) >= 0) return true;
+    if (clock64() - t0 > budget) { if (status) atomicCAS(status, 0u, (uint32_t)ST_TIMEOUT_PEER_FLAG); return false; }
+    __nanosleep(64);
+  }
+}
+__device__ __forceinline__ void la_set_flag(uint32_t* f, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t la_epoch(const LinAttnArgs& p) {
+  return (p.sx.role != 0 && p.sx.world > 1) ? *reinterpret_cast<volatile const uint32_t*>(p.sx.words) + 1u : 0u;
+}
+// Main pass: the state this (batch, head) starts from. Without an exchange that is `fallback` (the caller's s_in / ds_in).
+template <int HD>
+__device__ __forceinline__ const float* la_consume(const LinAttnArgs& p, int bh, uint32_t epoch, const float* fallback) {
+  const LaExchange& x = p.sx;
+  if (x.role != 2 || x.world <= 1) return fallback;
+  const int lo = x.dir == 0 ? 0 : x.rank + 1, hi = x.dir == 0 ? x.rank : x.world;       // the ranks whose totals flow in
+  if (lo >= hi) return nullptr;
+  constexpr int ST = HD * HD + HD;
+  const int BH = p.B * p.H, tid = threadIdx.x;
+  __shared__ int s_ok;
+  if (tid == 0) s_ok = 1;
+  __syncthreads();
+  if (tid >= lo && tid < hi && !la_wait_flag(x.flags[x.rank] + (size_t)tid * BH + bh, epoch, x.wait_cycles, p.status)) s_ok = 0;
+  __syncthreads();
+  float4* dst = reinterpret_cast<float4*>(x.prefix + (size_t)bh * ST);
+  const bool ok = s_ok != 0;
+  for (int i = tid; i < ST / 4; i += blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = lo; r < hi && ok; ++r) {
+      const float4 v = __ldcv(reinterpret_cast<const float4*>(x.state[r] + ((size_t)(epoch & 1u) * BH + bh) * ST) + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    dst[i] = acc;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid >= lo && tid < hi) la_set_flag(x.acks[tid] + (size_t)x.rank * BH + bh, epoch);        // "I have read your total"
+  return x.prefix;
+}
+// State pass: where this slice's totals go. With an exchange: this rank's symmetric buffer (after the consumers of the
+// call two earlier have released it); `la_publish_end` then raises the flags at the consumers.
+template <int HD>
+__device__ __forceinline__ float* la_publish_begin(const LinAttnArgs& p, int bh, uint32_t epoch, float* fallback) {
+  const LaExchange& x = p.sx;
+  if (x.role != 1 || x.world <= 1) return fallback;
+  constexpr int ST = HD * HD + HD;
+  const int BH = p.B * p.H, tid = threadIdx.x;
+  const int lo = x.dir == 0 ? x.rank + 1 : 0, hi = x.dir == 0 ? x.world : x.rank;       // the ranks that will read it
+  if (tid >= lo && tid < hi) la_wait_flag(x.acks[x.rank] + (size_t)tid * BH + bh, epoch - 2u, x.wait_cycles, p.status);
+  __syncthreads();
+  return x.state[x.rank] + (size_t)(epoch & 1u) * BH * ST;
+}
+__device__ __forceinline__ void la_publish_end(const LinAttnArgs& p, int bh, uint32_t epoch) {
+  const LaExchange& x = p.sx;
+  if (x.role != 1 || x.world <= 1) return;
+  const int BH = p.B * p.H, tid = threadIdx.x;
+  const int lo = x.dir == 0 ? x.rank + 1 : 0, hi = x.dir == 0 ? x.world : x.rank;
+  __threadfence_system();
+  __syncthreads();
+  if (tid >= lo && tid < hi) la_set_flag(x.flags[tid] + (size_t)x.rank * BH + bh, epoch);
+}
+// Main pass, last thing: the last CTA to get here advances the call counter.
+__device__ __forceinline__ void la_retire(const LinAttnArgs& p, uint32_t epoch) {
+  const LaExchange& x = p.sx;
+  if (x.role != 2 || x.world <= 1 || threadIdx.x != 0) return;
+  __threadfence();
+  if (atomicAdd(x.words + 1, 1u) == gridDim.x - 1) { x.words[1] = 0u; __threadfence(); x.words[0] = epoch; }
+}
 
 __device__ __forceinline__ float la_phi(float x, int kind) { return kind == 0 ? (x > 0.f ? x + 1.f : __expf(x)) : (x > 0.f ? x * x : 0.f); }
 // derivative of phi expressed through its value: ELU+1: 1 for x > 0 (phi > 1) else phi; ReLU^2: 2 sqrt(phi)
@@ -267,12 +363,14 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (HD == 64) for (int i = tid; i < L::ZERO / 16; i += 128) reinterpret_cast<uint4*>(sZero)[i] = make_uint4(0, 0, 0, 0);
   // state before the first token: TMEM (fp32) and the two bf16 operand tiles
   const size_t st_stride = (size_t)HD * HD + HD;
+  const uint32_t sx_epoch = la_epoch(p);
+  const float* s_in = la_consume<HD>(p, bh, sx_epoch, p.s_in);       // the caller's state, or the lower ranks' totals
   if (tid < HD) {
     float s0[HD];
 #pragma unroll
-    for (int i = 0; i < HD; ++i) s0[i] = p.s_in ? p.s_in[bh * st_stride + (size_t)tid * HD + i] : 0.f;
+    for (int i = 0; i < HD; ++i) s0[i] = s_in ? s_in[bh * st_stride + (size_t)tid * HD + i] : 0.f;
     la_write_hilo<HD>(sShi, sSlo, HD, tid, s0);
-    sz[tid] = p.s_in ? p.s_in[bh * st_stride + (size_t)HD * HD + tid] : 0.f;
+    sz[tid] = s_in ? s_in[bh * st_stride + (size_t)HD * HD + tid] : 0.f;
   }
   tc_fence_before_sync();
   fence_proxy_async_smem();
@@ -280,12 +378,12 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t trow = tmem_base + (uint32_t(warp * 32) << 16);
-  if (p.s_in) {                                     // TMEM accesses are warp-wide: every lane stores (rows >= HD: zeros)
+  if (s_in) {                                     // TMEM accesses are warp-wide: every lane stores (rows >= HD: zeros)
 #pragma unroll
     for (int c = 0; c < HD / 32; ++c) {
       uint32_t r[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) r[i] = tid < HD ? __float_as_uint(p.s_in[bh * st_stride + (size_t)tid * HD + c * 32 + i]) : 0u;
+      for (int i = 0; i < 32; ++i) r[i] = tid < HD ? __float_as_uint(s_in[bh * st_stride + (size_t)tid * HD + c * 32 + i]) : 0u;
       tmem_st_x32(trow + COL_S + c * 32, r);
     }
     tmem_st_wait();
@@ -307,7 +405,7 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (n_chunks > 1) load(sK + L::TILE, &tmK, &k_bar[1], 1);
   }
   bool ok = true;
-  const bool have_state0 = p.s_in != nullptr;
+  const bool have_state0 = s_in != nullptr;
   for (int c = 0; c < n_chunks; ++c) {
     const int st = c & 1;
     uint8_t* sKc = sK + st * L::TILE;
@@ -410,17 +508,20 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     tc_fence_before_sync();
     __syncthreads();
   }
-  if (ok && p.s_out) {
+  float* s_out = la_publish_begin<HD>(p, bh, sx_epoch, p.s_out);      // the caller's buffer, or this rank's slot of the exchange
+  if (ok && s_out) {
     tc_fence_after_sync();
     float srow[HD];
     la_tmem_row<HD>(trow + COL_S, srow);
     if (tid < HD) {
 #pragma unroll
       for (int i = 0; i < HD; i += 4)
-        *reinterpret_cast<float4*>(p.s_out + bh * st_stride + (size_t)tid * HD + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
-      p.s_out[bh * st_stride + (size_t)HD * HD + tid] = sz[tid];
+        *reinterpret_cast<float4*>(s_out + bh * st_stride + (size_t)tid * HD + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
+      s_out[bh * st_stride + (size_t)HD * HD + tid] = sz[tid];
     }
   }
+  la_publish_end(p, bh, sx_epoch);
+  la_retire(p, sx_epoch);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) { tc_fence_after_sync(); tmem_dealloc(tmem_base, 512); }
@@ -670,12 +771,14 @@ linattn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   if (warp == 0) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
   if (HD == 64) for (int i = tid; i < L::ZERO / 16; i += 128) reinterpret_cast<uint4*>(sZero)[i] = make_uint4(0, 0, 0, 0);
   const size_t st_stride = (size_t)HD * HD + HD;
+  const uint32_t sx_epoch = la_epoch(p);
+  const float* ds_in = la_consume<HD>(p, bh, sx_epoch, p.ds_in);     // the caller's dS, or the higher ranks' totals
   if (tid < HD) {
     float s0[HD];
 #pragma unroll
-    for (int i = 0; i < HD; ++i) s0[i] = p.ds_in ? p.ds_in[bh * st_stride + (size_t)tid * HD + i] : 0.f;
+    for (int i = 0; i < HD; ++i) s0[i] = ds_in ? ds_in[bh * st_stride + (size_t)tid * HD + i] : 0.f;
     la_write_hilo<HD>(sDhi, sDlo, HD, tid, s0);
-    sdz[tid] = p.ds_in ? p.ds_in[bh * st_stride + (size_t)HD * HD + tid] : 0.f;
+    sdz[tid] = ds_in ? ds_in[bh * st_stride + (size_t)HD * HD + tid] : 0.f;
   }
   tc_fence_before_sync();
   fence_proxy_async_smem();
@@ -683,12 +786,12 @@ linattn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t trow = tmem_base + (uint32_t(warp * 32) << 16);
-  if (p.ds_in) {
+  if (ds_in) {
 #pragma unroll
     for (int c = 0; c < HD / 32; ++c) {
       uint32_t r[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) r[i] = tid < HD ? __float_as_uint(p.ds_in[bh * st_stride + (size_t)tid * HD + c * 32 + i]) : 0u;
+      for (int i = 0; i < 32; ++i) r[i] = tid < HD ? __float_as_uint(ds_in[bh * st_stride + (size_t)tid * HD + c * 32 + i]) : 0u;
       tmem_st_x32(trow + COL_DS + c * 32, r);
     }
     tmem_st_wait();
@@ -709,7 +812,7 @@ linattn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   const uint32_t q_lbo = HD == 64 ? uint32_t(L::TILE) : uint32_t(LA_C * 128);
   if (tid == 0) load_all(n_chunks - 1);
   bool ok = true;
-  const bool have_state0 = p.ds_in != nullptr;
+  const bool have_state0 = ds_in != nullptr;
   uint32_t t_phase = 0;
   for (int it = 0; it < n_chunks; ++it) {
     const int c = n_chunks - 1 - it;
@@ -810,17 +913,20 @@ linattn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     tc_fence_before_sync();
     __syncthreads();
   }
-  if (ok && p.ds_out) {
+  float* ds_out = la_publish_begin<HD>(p, bh, sx_epoch, p.ds_out);
+  if (ok && ds_out) {
     tc_fence_after_sync();
     float srow[HD];
     la_tmem_row<HD>(trow + COL_DS, srow);
     if (tid < HD) {
 #pragma unroll
       for (int i = 0; i < HD; i += 4)
-        *reinterpret_cast<float4*>(p.ds_out + bh * st_stride + (size_t)tid * HD + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
-      p.ds_out[bh * st_stride + (size_t)HD * HD + tid] = sdz[tid];
+        *reinterpret_cast<float4*>(ds_out + bh * st_stride + (size_t)tid * HD + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
+      ds_out[bh * st_stride + (size_t)HD * HD + tid] = sdz[tid];
     }
   }
+  la_publish_end(p, bh, sx_epoch);
+  la_retire(p, sx_epoch);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) { tc_fence_after_sync(); tmem_dealloc(tmem_base, 512); }

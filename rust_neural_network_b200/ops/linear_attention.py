@@ -35,12 +35,23 @@ from .functional import matmul
 CHUNK = 128
 
 
+LA_MAX_WORLD = 8
+
+
+class LaExchange(C.Structure):
+    """Mirror of `LaExchange` in csrc/attention/linattn_sm100.cu: the in-kernel exchange of slice totals between the
+    ranks of a sequence-parallel group (role 1: publish, role 2: consume; dir 0: from lower ranks, 1: from higher)."""
+    _fields_ = [("state", C.c_void_p * LA_MAX_WORLD), ("flags", C.c_void_p * LA_MAX_WORLD), ("acks", C.c_void_p * LA_MAX_WORLD),
+                ("prefix", C.c_void_p), ("words", C.c_void_p), ("wait_cycles", C.c_longlong),
+                ("rank", C.c_int), ("world", C.c_int), ("dir", C.c_int), ("role", C.c_int)]
+
+
 class LinAttnArgs(C.Structure):
     _fields_ = [("q", nv.AttnTensor), ("k", nv.AttnTensor), ("v", nv.AttnTensor), ("o", nv.AttnTensor),
                 ("dout", nv.AttnTensor), ("dq", nv.AttnTensor), ("dk", nv.AttnTensor), ("dv", nv.AttnTensor), ("o_lo", nv.AttnTensor),
                 ("den", C.c_void_p), ("s_in", C.c_void_p), ("s_out", C.c_void_p), ("ds_in", C.c_void_p), ("ds_out", C.c_void_p),
                 ("B", C.c_int), ("H", C.c_int), ("S", C.c_int), ("hd", C.c_int), ("scale", C.c_float), ("eps", C.c_float),
-                ("kind", C.c_int), ("state_only", C.c_int), ("status", C.c_void_p)]
+                ("kind", C.c_int), ("state_only", C.c_int), ("status", C.c_void_p), ("sx", LaExchange)]
 
 
 nv.register_sigs({"b200_linattn": [C.POINTER(LinAttnArgs), C.c_int, C.c_void_p], "b200_linattn_init": []})
@@ -63,9 +74,14 @@ def fused_supported(q, causal) -> bool:
 
 @nv.traced("linear_attention")
 def _launch(which, q, k, v, scale, eps, kind, o=None, den=None, dout=None, dq=None, dk=None, dv=None, s_in=None, s_out=None,
-            ds_in=None, ds_out=None, state_only=False, o_lo=None):
+            ds_in=None, ds_out=None, state_only=False, o_lo=None, sx=None):
+    """`sx = (SPContext, dir, role)` lets the kernel itself exchange the slice totals with the other ranks (see
+    `LaExchange`); it returns the local buffer the consume pass leaves the summed state in."""
     B, S, H, d = q.shape
     a = LinAttnArgs()
+    prefix = None
+    if sx is not None:
+        prefix = sx[0].fill_exchange(a.sx, B * H, d * d + d, sx[1], sx[2])
     a.q, a.k, a.v = _attn_t(q), _attn_t(k), _attn_t(v)
     for name, t in (("o", o), ("dout", dout), ("dq", dq), ("dk", dk), ("dv", dv), ("o_lo", o_lo)):
         if t is not None:
@@ -76,6 +92,7 @@ def _launch(which, q, k, v, scale, eps, kind, o=None, den=None, dout=None, dq=No
     a.status = nv.status_word(q.device).data_ptr()
     nv.check(nv.cuda().b200_linattn(C.byref(a), which, nv.stream_ptr()), "linattn")
     nv.count_launch()
+    return prefix
 
 
 class FusedCausalLinearAttnFn(Function):
@@ -92,14 +109,22 @@ class FusedCausalLinearAttnFn(Function):
         o = torch.empty((B, S, H, d), dtype=torch.bfloat16, device=dev)
         den = torch.empty((B, H, S), dtype=torch.float32, device=dev)
         s_in = None
-        if sp is not None and sp.world > 1:
+        in_kernel = sp is not None and sp.world > 1 and sp.backend == "fused"
+        if sp is not None and sp.world > 1 and not in_kernel:
             tot = torch.empty((B * H, d * d + d), dtype=torch.float32, device=dev)
             _launch(0, q, k, v, scale, eps, kind, s_out=tot, state_only=True)
             s_in = sp._exchange(tot, 0)                         # sum of the lower ranks' totals
         # the backward needs more of O than its bf16 value (see csrc/attention/linattn_sm100.cu: o_lo): keep the remainder
         need_grad = any(t.requires_grad for t in (q, k, v))
         o_lo = torch.empty_like(o) if need_grad else None
-        _launch(0, q, k, v, scale, eps, kind, o=o, den=den, s_in=s_in, o_lo=o_lo)
+        if in_kernel:
+            # the state pass publishes this slice's total in peer-mapped memory, the main pass pulls the lower ranks' totals
+            # itself: two launches, no exchange kernel, and a (batch, head) starts as soon as ITS states have arrived
+            _launch(0, q, k, v, scale, eps, kind, state_only=True, sx=(sp, 0, 1))
+            pre = _launch(0, q, k, v, scale, eps, kind, o=o, den=den, o_lo=o_lo, sx=(sp, 0, 2))
+            s_in = pre.clone() if (sp.rank > 0 and need_grad) else None      # the buffer is reused by the next call
+        else:
+            _launch(0, q, k, v, scale, eps, kind, o=o, den=den, s_in=s_in, o_lo=o_lo)
         ctx.save_for_backward(q, k, v, o, den, s_in if s_in is not None else torch.empty(0), o_lo if o_lo is not None else torch.empty(0))
         ctx.cfg = (scale, eps, kind, sp)
         return o
@@ -115,6 +140,10 @@ class FusedCausalLinearAttnFn(Function):
         dq, dk, dv = torch.empty_like(o), torch.empty_like(o), torch.empty_like(o)
         _launch(1, q, k, v, scale, eps, kind, o=o, den=den, dout=dout, dq=dq, s_in=s_in, o_lo=o_lo)
         ds_in = None
+        if sp is not None and sp.world > 1 and sp.backend == "fused":
+            _launch(2, q, k, v, scale, eps, kind, o=o, den=den, dout=dout, state_only=True, o_lo=o_lo, sx=(sp, 1, 1))
+            _launch(2, q, k, v, scale, eps, kind, o=o, den=den, dout=dout, dk=dk, dv=dv, o_lo=o_lo, sx=(sp, 1, 2))
+            return dq, dk, dv, None, None, None, None
         if sp is not None and sp.world > 1:
             tot = torch.empty((B * H, d * d + d), dtype=torch.float32, device=q.device)
             _launch(2, q, k, v, scale, eps, kind, o=o, den=den, dout=dout, ds_out=tot, state_only=True, o_lo=o_lo)

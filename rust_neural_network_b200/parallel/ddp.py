@@ -76,20 +76,61 @@ def is_replicated(p: torch.Tensor, max_numel: int = REPLICATE_MAX_NUMEL) -> bool
     return p.dim() < 2 or p.numel() <= max_numel
 
 
+GUARD_BYTES = 256
+_GUARD_BYTE = 0xA5
+_LIVE_BUFFERS: "weakref.WeakSet" = None
+
+
 class SymmetricBuffer:
     """A tensor allocated in symmetric memory and mapped by every rank of the group.
     `ptrs[r]` is the address of rank r's copy in THIS process; `mc_ptr` is the NVLS multicast
-    address (0 when unavailable)."""
+    address (0 when unavailable).
 
-    def __init__(self, numel: int, dtype: torch.dtype, device, group=None):
+    Every allocation carries a guard band of `GUARD_BYTES` on each side of the payload, filled with a fixed byte. The
+    kernels that write through peer pointers are given the payload address only, so a store that runs past either end
+    of a peer's buffer (a wrong shard offset, a row count that does not match) lands in a guard band instead of in a
+    neighbouring allocation; `check()` / `check_canaries()` compare the bands with the pattern and name the buffer."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, device, group=None, name: str = ""):
+        import weakref
+
         import torch.distributed._symmetric_memory as symm_mem
+        global _LIVE_BUFFERS
         group = group or dist.group.WORLD
-        self.tensor = symm_mem.empty(numel, dtype=dtype, device=device)
-        self.tensor.zero_()
-        self.handle = symm_mem.rendezvous(self.tensor, group)
-        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        es = torch.empty((), dtype=dtype).element_size()
+        g = GUARD_BYTES // es
+        self.name = name or f"{dtype}[{numel}]"
+        self._raw = symm_mem.empty(numel + 2 * g, dtype=dtype, device=device)
+        self._raw.zero_()
+        raw_bytes = self._raw.view(torch.uint8)
+        raw_bytes[:GUARD_BYTES] = _GUARD_BYTE
+        raw_bytes[GUARD_BYTES + numel * es:] = _GUARD_BYTE
+        self.tensor = self._raw[g:g + numel]
+        self.handle = symm_mem.rendezvous(self._raw, group)
+        self.ptrs = [int(p) + GUARD_BYTES for p in self.handle.buffer_ptrs]
         mc = getattr(self.handle, "multicast_ptr", 0)
-        self.mc_ptr = int(mc) if mc else 0
+        self.mc_ptr = int(mc) + GUARD_BYTES if mc else 0
+        if _LIVE_BUFFERS is None:
+            _LIVE_BUFFERS = weakref.WeakSet()
+        _LIVE_BUFFERS.add(self)
+
+    def check(self) -> None:
+        """Raise if anything (this rank or a peer) wrote outside the payload of this rank's copy."""
+        b = self._raw.view(torch.uint8)
+        n = self.tensor.numel() * self.tensor.element_size()
+        front, back = b[:GUARD_BYTES], b[GUARD_BYTES + n:]
+        bad_f, bad_b = int((front != _GUARD_BYTE).sum()), int((back != _GUARD_BYTE).sum())
+        if bad_f or bad_b:
+            raise RuntimeError(f"symmetric buffer {self.name}: {bad_f} bytes before and {bad_b} bytes after the payload were overwritten")
+
+
+def check_canaries() -> int:
+    """Check the guard bands of every live symmetric buffer of this process; returns how many were checked."""
+    n = 0
+    for buf in list(_LIVE_BUFFERS or ()):
+        buf.check()
+        n += 1
+    return n
 
 
 # ----------------------------------------------------------------------------------------------- marks

@@ -61,6 +61,38 @@ class SPContext:
             dist.barrier(self.group)
             torch.cuda.synchronize()
 
+    def fill_exchange(self, sx, bh: int, st: int, direction: int, role: int) -> torch.Tensor:
+        """Fill the `LaExchange` block of a linear-attention launch: the kernels of csrc/attention/linattn_sm100.cu then
+        publish (role 1) / pull (role 2) the slice totals of `bh` (batch x head) states of `st` floats themselves.
+        One set of buffers per direction (0: forward states flow to higher ranks, 1: backward states to lower ranks),
+        allocated on first use - collectively, so every rank must make the same calls. Returns the local buffer the
+        consume pass leaves its summed state in."""
+        if self.backend != "fused":
+            raise RuntimeError("the in-kernel exchange needs the peer-memory backend")
+        if not hasattr(self, "_la"):
+            self._la = {}
+        ent = self._la.get(direction)
+        if ent is None or ent["bh"] < bh or ent["st"] != st:
+            if ent is not None:
+                raise ValueError("the exchange buffers of this context were sized for a smaller batch x heads or another head size")
+            from .ddp import SymmetricBuffer
+            ent = {"bh": bh, "st": st,
+                   "state": SymmetricBuffer(2 * bh * st, torch.float32, self.device, self.group, name=f"la_state{direction}"),
+                   "flags": SymmetricBuffer(self.world * bh, torch.int32, self.device, self.group, name=f"la_flags{direction}"),
+                   "acks": SymmetricBuffer(self.world * bh, torch.int32, self.device, self.group, name=f"la_acks{direction}"),
+                   "prefix": torch.zeros(bh * st, dtype=torch.float32, device=self.device),
+                   "words": torch.zeros(2, dtype=torch.int32, device=self.device)}
+            dist.barrier(self.group)
+            torch.cuda.synchronize()
+            self._la[direction] = ent
+        if ent["bh"] != bh:
+            raise ValueError("batch x heads must stay the same for one context (the flag arrays are indexed by it)")
+        for r in range(self.world):
+            sx.state[r], sx.flags[r], sx.acks[r] = ent["state"].ptrs[r], ent["flags"].ptrs[r], ent["acks"].ptrs[r]
+        sx.prefix, sx.words = ent["prefix"].data_ptr(), ent["words"].data_ptr()
+        sx.wait_cycles, sx.rank, sx.world, sx.dir, sx.role = self.wait_cycles, self.rank, self.world, direction, role
+        return ent["prefix"].view(bh, st)
+
     def _exchange(self, total: torch.Tensor, mode: int) -> torch.Tensor:
         if self.backend != "fused":
             parts = [torch.empty_like(total) for _ in range(self.world)]

@@ -175,6 +175,22 @@ def main():
         if args.ckpt:
             from rust_neural_network_b200.serialize import save_checkpoint
             save_checkpoint(os.path.join(args.ckpt, "single.rnnb"), ref, ropt)
+    if dev.type == "cuda":
+        from rust_neural_network_b200.parallel import ddp as D
+        torch.cuda.synchronize()
+        dist.barrier()                                            # every peer has finished writing into this rank's buffers
+        result["canaries_checked"] = D.check_canaries()
+        bufs = list(D._LIVE_BUFFERS or ())
+        if bufs:                                                  # the detector itself: a byte of a guard band changed on the host side
+            raw = bufs[0]._raw.view(torch.uint8)
+            keep = int(raw[3])
+            raw[3] = 0
+            try:
+                D.check_canaries()
+                result["canary_detects"] = False
+            except RuntimeError:
+                result["canary_detects"] = True
+            raw[3] = keep
     gathered = [None] * world
     dist.all_gather_object(gathered, result)
     if rank == 0:

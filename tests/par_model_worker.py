@@ -209,6 +209,11 @@ def main():
         dist.init_process_group("gloo")
         dtype = torch.float32
     out = {"mamba_tp": mamba_tp, "moe_ep": moe_ep}[args.model](args, rank, world, dev, dtype)
+    if torch.cuda.is_available() and dist.get_backend() == "nccl":
+        from rust_neural_network_b200.parallel.ddp import check_canaries
+        torch.cuda.synchronize()
+        dist.barrier()
+        out["canaries_checked"] = check_canaries()               # raises if any peer wrote outside a symmetric buffer's payload
     gathered = [None] * world
     dist.all_gather_object(gathered, out)
     if rank == 0:

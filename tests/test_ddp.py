@@ -99,6 +99,8 @@ def test_two_gpu_fused_variants(extra, port):
         assert r0["buckets"] >= 2
     if "--clip" in extra:
         assert r0["norm"] > 0.5
+    # guard bands around every symmetric buffer are intact on every rank, and the check notices a changed byte
+    assert all(r["canaries_checked"] >= 3 and r["canary_detects"] for r in ranks)
 
 
 @pytest.mark.gpu

@@ -208,6 +208,11 @@ def main():
                 out[f"sp_{tag}_{nm}_rel_err"] = rel(loc_in[i].grad, orc_in[i].grad[:, sl])
                 out[f"ref_{tag}_{nm}_rel_err"] = rel(ref_in[i].grad[:, sl], orc_in[i].grad[:, sl])
 
+    if torch.cuda.is_available() and dist.get_backend() == "nccl":
+        from rust_neural_network_b200.parallel.ddp import check_canaries
+        torch.cuda.synchronize()
+        dist.barrier()
+        out["canaries_checked"] = check_canaries()               # raises if any peer wrote outside a symmetric buffer's payload
     gathered = [None] * world
     dist.all_gather_object(gathered, out)
     if rank == 0:

@@ -204,8 +204,7 @@ class MoEExpertsFn(Function):
         xb = xbuf.view(E_local, cap, d)
         W1l, W2l = F.lp(W1), F.lp(W2)
         h, pre = gemm(xb, W1l, bias=b1.detach() if b1 is not None else None, act=act, want_aux=True)        # [E, cap, hid]
-        y = gemm(h, W2l, bias=b2.detach() if b2 is not None else None)                                       # [E, cap, d]
-        ybuf.view(E_local, cap, d).copy_(y)
+        y = gemm(h, W2l, bias=b2.detach() if b2 is not None else None, out=ybuf.view(E_local, cap, d))       # [E, cap, d], in the peers' reach
         xsave = xb.clone()
         ep.barrier(dev)                                           # every rank's expert outputs are in place
         out = torch.empty((T, d), dtype=torch.bfloat16, device=dev)
@@ -215,20 +214,21 @@ class MoEExpertsFn(Function):
         nv.count_launch(2)
         xbuf.zero_(); fill.zero_()
         ep.barrier(dev)                                           # peers have read my outputs; everyone's input buffers are clear
-        ctx.save_for_backward(dest, wc, xsave, h, pre, y, W1, b1, W2, b2)
+        ctx.save_for_backward(dest, wc, xsave, h, pre, W1, b1, W2, b2)
         ctx.cfg = (act, cap, ep, T, d, k, E_local, hid)
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        dest, wc, xb, h, pre, y, W1, b1, W2, b2 = ctx.saved_tensors
+        dest, wc, xb, h, pre, W1, b1, W2, b2 = ctx.saved_tensors
         act, cap, ep, T, d, k, E_local, hid = ctx.cfg
         world, rows, dev = ep.world, E_local * cap, dout.device
         lib = nv.cuda()
         ybuf, yptrs = ep.buffer("y", rows * d, torch.bfloat16, dev)
         dybuf, dyptrs = ep.buffer("dy", rows * d, torch.bfloat16, dev)
         dxbuf, dxptrs = ep.buffer("dx", rows * d, torch.bfloat16, dev)
-        ybuf.view(E_local, cap, d).copy_(y)
+        # the expert outputs are needed once more (d of the gate weights): recomputed from h straight into the shared buffer
+        gemm(h, F.lp(W2), bias=b2.detach() if b2 is not None else None, out=ybuf.view(E_local, cap, d))
         ep.barrier(dev)
         dw = torch.empty((T, k), dtype=torch.float32, device=dev)
         dc = dout.contiguous()
@@ -240,7 +240,7 @@ class MoEExpertsFn(Function):
         dh = gemm(dy, W2l, b_mn=True, aux_in=pre, dact=act)                                   # [E, cap, hid]
         dW2 = gemm(dy, h, a_mn=True, b_mn=True, out_dtype=torch.float32)                       # [E, d, hid]
         dW1 = gemm(dh, xb, a_mn=True, b_mn=True, out_dtype=torch.float32)                      # [E, hid, d]
-        dxb = gemm(dh, W1l, b_mn=True)                                                         # [E, cap, d]
+        gemm(dh, W1l, b_mn=True, out=dxbuf.view(E_local, cap, d))                               # [E, cap, d], pulled by the token owners
         db1 = db2 = None
         if b1 is not None:
             db1 = torch.zeros((E_local, hid), dtype=torch.float32, device=dev)
@@ -249,7 +249,6 @@ class MoEExpertsFn(Function):
             db2 = torch.zeros((E_local, d), dtype=torch.float32, device=dev)
             nv.check(lib.b200_colsum_batched(dy.data_ptr(), db2.data_ptr(), E_local, cap, d, d, cap * d, 1, nv.stream_ptr()), "colsum_batched")
         # adjoint of dispatch: pull the token gradients back from the owning ranks
-        dxbuf.view(E_local, cap, d).copy_(dxb)
         ep.barrier(dev)
         dx = torch.empty((T, d), dtype=torch.bfloat16, device=dev)
         nv.check(lib.b200_moe_gather_sum(_ptr_array(dxptrs), world, dest.data_ptr(), dx.data_ptr(), T, k, d, rows, nv.stream_ptr()), "moe_gather_sum")

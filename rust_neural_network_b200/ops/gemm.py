@@ -124,8 +124,10 @@ def _tma_ready(t: torch.Tensor) -> torch.Tensor:
 @nv.traced("gemm")
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias=None, act: str = "none",
          residual=None, aux_in=None, dact: str = "none", want_aux: bool = False, alpha: float = 1.0,
-         out_dtype=None, accumulate_into=None, splits: int = 0, bn: int = 0, alpha_t=None, row_scale=None, col_scale=None):
-    """See module docstring. Returns C (and the bf16 pre-activation when ``want_aux``).
+         out_dtype=None, accumulate_into=None, splits: int = 0, bn: int = 0, alpha_t=None, row_scale=None, col_scale=None,
+         out=None):
+    """See module docstring. Returns C (and the bf16 pre-activation when ``want_aux``). ``out`` (GPU only): write the
+    result into this tensor ([M, N] or [batch, M, N], unit inner stride, dtype of the result) instead of a new one.
 
     8-bit operands (int8 x int8, uint8 x int8, float8_e4m3fn x float8_e4m3fn; both K-major) run on the
     tensor cores' integer / fp8 kinds. ``row_scale`` ([M] or [batch, M] fp32) and ``col_scale`` ([N] fp32)
@@ -134,9 +136,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if not a.is_cuda:
         if alpha_t is not None:
             alpha = alpha * float(alpha_t)
-        return gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, act=act, residual=residual, aux_in=aux_in, dact=dact,
-                        alpha=alpha, out_dtype=out_dtype, accumulate_into=accumulate_into, want_aux=want_aux,
-                        row_scale=row_scale, col_scale=col_scale)
+        r = gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, act=act, residual=residual, aux_in=aux_in, dact=dact,
+                     alpha=alpha, out_dtype=out_dtype, accumulate_into=accumulate_into, want_aux=want_aux,
+                     row_scale=row_scale, col_scale=col_scale)
+        if out is not None:
+            out.copy_((r[0] if want_aux else r).reshape(out.shape))
+            r = (out, r[1]) if want_aux else out
+        return r
     lib = nv.cuda()
     kinds = {(torch.bfloat16, torch.bfloat16): GEMM_BF16, (torch.float32, torch.float32): GEMM_F32,
              (torch.int8, torch.int8): GEMM_S8S8, (torch.uint8, torch.int8): GEMM_U8S8,
@@ -178,7 +184,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
             out_mode = OUT_I32
         else:
             out_mode = OUT_F32 if odt == torch.float32 else OUT_BF16
-        out = None
+        if out is not None:
+            want = torch.int32 if out_mode == OUT_I32 else torch.float32 if out_mode == OUT_F32 else torch.bfloat16
+            if out.dtype != want or out.stride(-1) != 1 or out.numel() != batch * M * N:
+                raise ValueError("`out` must have the result's dtype, size and a unit inner stride")
+            if splits > 1:
+                raise ValueError("`out` and split-K do not go together (split-K accumulates into a zeroed fp32 buffer)")
+            splits = splits or 1
     # tile width and split-K
     sms = _num_sms(dev)
     if is_f32:

@@ -240,13 +240,21 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
     for (int g = 0; g < SC / 8; ++g) {
       float pp[8], ds[8];
+      // packed fp32 pairs for the exponent argument, dP - delta and the product: this loop is bound by instruction issue
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
+      for (int u = 0; u < 8; u += 2) {
         const int e = g * 8 + u;
-        float pr = ex2_approx(fmaf(__uint_as_float(sv[e]), p.scale_log2, -lse2));
-        if (MASK) { if (!row_ok || (CAUSAL && (kv0 + col0 + e > q_row))) pr = 0.f; }
-        pp[u] = pr;
-        ds[u] = pr * (__uint_as_float(dv[e]) - dlt);
+        float a0 = __uint_as_float(sv[e]), a1 = __uint_as_float(sv[e + 1]);
+        fma2_scalar(a0, a1, p.scale_log2, -lse2);
+        float p0 = ex2_approx(a0), p1 = ex2_approx(a1);
+        if (MASK) {
+          if (!row_ok || (CAUSAL && (kv0 + col0 + e > q_row))) p0 = 0.f;
+          if (!row_ok || (CAUSAL && (kv0 + col0 + e + 1 > q_row))) p1 = 0.f;
+        }
+        float d0 = __uint_as_float(dv[e]), d1 = __uint_as_float(dv[e + 1]);
+        add2(d0, d1, -dlt, -dlt);
+        mul2(d0, d1, p0, p1);
+        pp[u] = p0; pp[u + 1] = p1; ds[u] = d0; ds[u + 1] = d1;
       }
       const int cc = (col0 >> 3) + g;
       const int atom = cc >> 3, chunk = cc & 7;

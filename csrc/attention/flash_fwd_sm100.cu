@@ -173,10 +173,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (col >= p.Skv || (CAUSAL && col > q_row)) s[i] = -INFINITY;
       }
     }
-    // four independent chains: a 128-long dependent fmax chain would cost its latency 128 times over
+    // four independent chains of 3-input maxima: a 128-long dependent chain would cost its latency 128 times over
     float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
 #pragma unroll
-    for (int i = 4; i < BN; i += 4) { mx0 = fmaxf(mx0, s[i]); mx1 = fmaxf(mx1, s[i + 1]); mx2 = fmaxf(mx2, s[i + 2]); mx3 = fmaxf(mx3, s[i + 3]); }
+    for (int i = 4; i + 8 <= BN - 4; i += 8) {
+      mx0 = max3(mx0, s[i], s[i + 4]); mx1 = max3(mx1, s[i + 1], s[i + 5]);
+      mx2 = max3(mx2, s[i + 2], s[i + 6]); mx3 = max3(mx3, s[i + 3], s[i + 7]);
+    }
+    { mx0 = fmaxf(mx0, s[BN - 4]); mx1 = fmaxf(mx1, s[BN - 3]); mx2 = fmaxf(mx2, s[BN - 2]); mx3 = fmaxf(mx3, s[BN - 1]); }
     const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
     const float m_new = fmaxf(m_used, mx * c);
     const bool grow = m_new > m_used + 8.f;                     // also true on the first finite maximum (m_used = -inf)
@@ -198,12 +202,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       m_used = m_new;
     }
     const float m_ref = (m_used == -INFINITY) ? 0.f : m_used;
+    // exponent arguments and row sums as packed fp32 pairs: half the FMA / ADD instructions of the scalar form
     float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+    const float neg_m = -m_ref;
 #pragma unroll
     for (int i = 0; i < BN; i += 4) {
-      s[i] = ex2_approx(fmaf(s[i], c, -m_ref)); s[i + 1] = ex2_approx(fmaf(s[i + 1], c, -m_ref));
-      s[i + 2] = ex2_approx(fmaf(s[i + 2], c, -m_ref)); s[i + 3] = ex2_approx(fmaf(s[i + 3], c, -m_ref));
-      rs0 += s[i]; rs1 += s[i + 1]; rs2 += s[i + 2]; rs3 += s[i + 3];
+      fma2_scalar(s[i], s[i + 1], c, neg_m);
+      fma2_scalar(s[i + 2], s[i + 3], c, neg_m);
+      s[i] = ex2_approx(s[i]); s[i + 1] = ex2_approx(s[i + 1]); s[i + 2] = ex2_approx(s[i + 2]); s[i + 3] = ex2_approx(s[i + 3]);
+      add2(rs0, rs1, s[i], s[i + 1]);
+      add2(rs2, rs3, s[i + 2], s[i + 3]);
     }
     l_run += (rs0 + rs1) + (rs2 + rs3);
     // bf16 P tile into shared memory (K-major, 128B swizzle)

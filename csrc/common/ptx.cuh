@@ -358,6 +358,36 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// ----------------------------------------------------------------------------
+// Packed fp32 pairs (sm_100: one instruction, two lanes of the FMA pipe) and the 3-input maximum: the softmax loops of
+// the attention kernels are bound by instruction issue, and these halve the FMA / ADD / MAX count.
+// ----------------------------------------------------------------------------
+// (x, y) <- (x, y) * m + a
+__device__ __forceinline__ void fma2_scalar(float& x, float& y, float m, float a) {
+  asm("{\n\t.reg .b64 v, mm, aa;\n\t"
+      "mov.b64 v, {%0, %1};\n\tmov.b64 mm, {%2, %2};\n\tmov.b64 aa, {%3, %3};\n\t"
+      "fma.rn.f32x2 v, v, mm, aa;\n\t"
+      "mov.b64 {%0, %1}, v;\n\t}" : "+f"(x), "+f"(y) : "f"(m), "f"(a));
+}
+// (sx, sy) += (x, y)
+__device__ __forceinline__ void add2(float& sx, float& sy, float x, float y) {
+  asm("{\n\t.reg .b64 s, v;\n\t"
+      "mov.b64 s, {%0, %1};\n\tmov.b64 v, {%2, %3};\n\t"
+      "add.rn.f32x2 s, s, v;\n\t"
+      "mov.b64 {%0, %1}, s;\n\t}" : "+f"(sx), "+f"(sy) : "f"(x), "f"(y));
+}
+// (x, y) <- (x, y) * (a, b)
+__device__ __forceinline__ void mul2(float& x, float& y, float a, float b) {
+  asm("{\n\t.reg .b64 v, w;\n\t"
+      "mov.b64 v, {%0, %1};\n\tmov.b64 w, {%2, %3};\n\t"
+      "mul.rn.f32x2 v, v, w;\n\t"
+      "mov.b64 {%0, %1}, v;\n\t}" : "+f"(x), "+f"(y) : "f"(a), "f"(b));
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

@@ -284,26 +284,32 @@ layernorm_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, cons
 
 // bf16 rows whose length is a multiple of 256: every lane owns 8 contiguous columns per 256-column chunk and
 // moves them with one 16-byte load / store (4x fewer memory instructions than the 2-column variant above).
-template <int J2, int W>
+// SUMS: the kernel also accumulates the column sums of `dres` and of its own output into `sum_dres` / `sum_dx` (fp32 [d],
+// added to). In a pre-norm transformer block those are the bias gradients of the two projections whose outputs join
+// the residual stream on either side of this LayerNorm, so two column-sum kernels (and two more passes over
+// [rows, d] gradients) disappear.
+template <int J2, int W, bool SUMS = false>
 __global__ void __launch_bounds__(256)
 layernorm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
                          const float* __restrict__ mean_in, const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
                          float* __restrict__ dgamma, float* __restrict__ dbeta, const __nv_bfloat16* __restrict__ dres,
-                         long long rows, int d) {
-  extern __shared__ float sh[];   // [row groups][2][d]
+                         long long rows, int d, float* __restrict__ sum_dres = nullptr, float* __restrict__ sum_dx = nullptr) {
+  constexpr int NS = SUMS ? 4 : 2;
+  extern __shared__ float sh[];   // [row groups][NS][d]
   __shared__ float red[2][2][8];  // [row parity][s1 | s2][warp]
   pdl_trigger();
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int groups_per_block = (blockDim.x >> 5) / W, grp = warp / W, wi = warp % W;
   float gam[J2][8], adg[J2][8], adb[J2][8];
+  float adr[SUMS ? J2 : 1][8], ado[SUMS ? J2 : 1][8];
 #pragma unroll
   for (int j = 0; j < J2; ++j) {
     const int c = 8 * lane + 256 * (j * W + wi);
     const float4 g0 = *reinterpret_cast<const float4*>(gamma + c), g1 = *reinterpret_cast<const float4*>(gamma + c + 4);
     gam[j][0] = g0.x; gam[j][1] = g0.y; gam[j][2] = g0.z; gam[j][3] = g0.w; gam[j][4] = g1.x; gam[j][5] = g1.y; gam[j][6] = g1.z; gam[j][7] = g1.w;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) { adg[j][e] = 0.f; adb[j][e] = 0.f; }
+    for (int e = 0; e < 8; ++e) { adg[j][e] = 0.f; adb[j][e] = 0.f; if (SUMS) { adr[j][e] = 0.f; ado[j][e] = 0.f; } }
   }
   const float inv_d = 1.f / d;
   auto unpack8 = [](const uint4& u, float (&o)[8]) {
@@ -366,7 +372,11 @@ layernorm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat
         float rr[8];
         unpack8(ru[j], rr);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] += rr[e];
+        for (int e = 0; e < 8; ++e) { o[e] += rr[e]; if (SUMS) adr[j][e] += rr[e]; }
+      }
+      if (SUMS) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ado[j][e] += o[e];
       }
       uint4 ou;
       __nv_bfloat162 t0 = __floats2bfloat162_rn(o[0], o[1]), t1 = __floats2bfloat162_rn(o[2], o[3]);
@@ -376,18 +386,22 @@ layernorm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat
       *reinterpret_cast<uint4*>(dxr + c) = ou;
     }
   }
-  float* my = sh + (size_t)grp * 2 * d;
+  float* my = sh + (size_t)grp * NS * d;
 #pragma unroll
   for (int j = 0; j < J2; ++j) {
     const int c = 8 * lane + 256 * (j * W + wi);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) { my[c + e] = adg[j][e]; my[d + c + e] = adb[j][e]; }
+    for (int e = 0; e < 8; ++e) {
+      my[c + e] = adg[j][e]; my[d + c + e] = adb[j][e];
+      if (SUMS) { my[2 * d + c + e] = adr[j][e]; my[3 * d + c + e] = ado[j][e]; }
+    }
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < 2 * d; c += blockDim.x) {
+  for (int c = threadIdx.x; c < NS * d; c += blockDim.x) {
     float acc = 0.f;
-    for (int w = 0; w < groups_per_block; ++w) acc += sh[(size_t)w * 2 * d + c];
-    atomicAdd(c < d ? dgamma + c : dbeta + (c - d), acc);
+    for (int w = 0; w < groups_per_block; ++w) acc += sh[(size_t)w * NS * d + c];
+    float* dst = c < d ? dgamma + c : c < 2 * d ? dbeta + (c - d) : c < 3 * d ? sum_dres + (c - 2 * d) : sum_dx + (c - 3 * d);
+    if (c < 2 * d || (c < 3 * d ? sum_dres != nullptr : sum_dx != nullptr)) atomicAdd(dst, acc);
   }
 }
 
@@ -513,7 +527,7 @@ int b200_layernorm_bwd(const void* dy, const void* x, const float* gamma, const 
       const size_t sm = (size_t)gpb * 2 * d * sizeof(float); \
       long long gg = (rows + gpb - 1) / gpb; if (gg > 148 * 2) gg = 148 * 2; \
       if (sm + 256 > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); if (e != cudaSuccess) return (int)e; } \
-      launch_pdl(k, dim3((int)gg), dim3(block), sm, st, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, gamma, (const float*)mean, (const float*)rstd, (__nv_bfloat16*)dx, dgamma, dbeta, (const __nv_bfloat16*)dres, rows, d); }
+      launch_pdl(k, dim3((int)gg), dim3(block), sm, st, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, gamma, (const float*)mean, (const float*)rstd, (__nv_bfloat16*)dx, dgamma, dbeta, (const __nv_bfloat16*)dres, rows, d, (float*)nullptr, (float*)nullptr); }
     switch (d / 256) {
       case 1: B200_LNV(1, 1) break; case 2: B200_LNV(2, 1) break; case 3: B200_LNV(3, 1) break; case 4: B200_LNV(4, 1) break;
       case 6: B200_LNV(3, 2) break; case 8: B200_LNV(4, 2) break; case 12: B200_LNV(3, 4) break; default: B200_LNV(4, 4) break;
@@ -540,6 +554,27 @@ int b200_layernorm_bwd(const void* dy, const void* x, const float* gamma, const 
   }
   if (is_bf16) layernorm_bwd_kernel<__nv_bfloat16><<<(int)g, block, smem, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, gamma, mean, rstd, (__nv_bfloat16*)dx, dgamma, dbeta, (const __nv_bfloat16*)dres, rows, d);
   else layernorm_bwd_kernel<float><<<(int)g, block, smem, st>>>((const float*)dy, (const float*)x, gamma, mean, rstd, (float*)dx, dgamma, dbeta, (const float*)dres, rows, d);
+  return (int)cudaGetLastError();
+}
+
+// LayerNorm backward that also adds the column sums of `dres` and of dx (+ dres) into sum_dres / sum_dx (either may be
+// null). bf16 rows with d a multiple of 256 up to 1024 and 16-byte aligned operands; returns -1 otherwise (the caller
+// then takes b200_layernorm_bwd and separate column sums).
+int b200_layernorm_bwd_sums(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd, void* dx,
+                            float* dgamma, float* dbeta, const void* dres, long long rows, int d, float* sum_dres, float* sum_dx,
+                            cudaStream_t st) {
+  if (rows <= 0) return 0;
+  const bool aligned16 = ((uintptr_t)dy % 16 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)dx % 16 == 0) && (!dres || (uintptr_t)dres % 16 == 0) &&
+                         ((uintptr_t)gamma % 16 == 0);
+  if (!aligned16 || d % 256 != 0 || d > 1024) return -1;
+  const int block = 256, gpb = block / 32;
+  const size_t sm = (size_t)gpb * 4 * d * sizeof(float);
+  long long gg = (rows + gpb - 1) / gpb; if (gg > 148 * 2) gg = 148 * 2;
+#define B200_LNS(JJ) { auto k = layernorm_bwd_vec_kernel<JJ, 1, true>; \
+    if (sm + 256 > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); if (e != cudaSuccess) return (int)e; } \
+    launch_pdl(k, dim3((int)gg), dim3(block), sm, st, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, gamma, (const float*)mean, (const float*)rstd, (__nv_bfloat16*)dx, dgamma, dbeta, (const __nv_bfloat16*)dres, rows, d, sum_dres, sum_dx); }
+  switch (d / 256) { case 1: B200_LNS(1) break; case 2: B200_LNS(2) break; case 3: B200_LNS(3) break; default: B200_LNS(4) break; }
+#undef B200_LNS
   return (int)cudaGetLastError();
 }
 

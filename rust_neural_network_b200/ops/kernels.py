@@ -305,10 +305,12 @@ def add_layernorm_fwd(x2d, res2d, gamma, beta, eps):
 
 
 @nv.traced("norm")
-def layernorm_bwd(dy2d, x2d, gamma, mean, rstd, dres=None, dgamma=None, dbeta=None):
+def layernorm_bwd(dy2d, x2d, gamma, mean, rstd, dres=None, dgamma=None, dbeta=None, sum_dres=None, sum_dx=None):
     """Returns (dx [+ dres], dgamma, dbeta). `dres` is an optional gradient of the same shape that is
     added to dx in the same pass (the residual branch); dgamma/dbeta may be existing fp32
-    accumulators."""
+    accumulators. `sum_dres` / `sum_dx` (fp32 [d] accumulators, added to): column sums of `dres` and of the returned
+    gradient - the bias gradients of the projections on either side of a pre-norm block's LayerNorm - taken in the
+    same pass when the kernel supports the shape, by separate column-sum kernels otherwise."""
     rows, d = x2d.shape
     if not x2d.is_cuda:
         xh = (x2d.float() - mean[:, None]) * rstd[:, None]
@@ -322,6 +324,10 @@ def layernorm_bwd(dy2d, x2d, gamma, mean, rstd, dres=None, dgamma=None, dbeta=No
         dg, db = (g * xh).sum(0), g.sum(0)
         if dgamma is not None:
             dgamma.add_(dg); dbeta.add_(db); dg, db = dgamma, dbeta
+        if sum_dres is not None and dres is not None:
+            sum_dres.add_(dres.float().sum(0))
+        if sum_dx is not None:
+            sum_dx.add_(dx.sum(0))
         return dx.to(x2d.dtype), dg, db
     dy2d = dy2d.contiguous()
     dx = torch.empty_like(x2d)
@@ -330,8 +336,22 @@ def layernorm_bwd(dy2d, x2d, gamma, mean, rstd, dres=None, dgamma=None, dbeta=No
         dbeta = torch.zeros(d, dtype=torch.float32, device=x2d.device)
     if dres is not None:
         dres = dres.contiguous()
+    want_sums = (sum_dres is not None and dres is not None) or sum_dx is not None
+    if want_sums and x2d.dtype == torch.bfloat16:
+        rc = nv.cuda().b200_layernorm_bwd_sums(dy2d.data_ptr(), x2d.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
+                                               dgamma.data_ptr(), dbeta.data_ptr(), nv.ptr(dres), rows, d,
+                                               nv.ptr(sum_dres if dres is not None else None), nv.ptr(sum_dx), nv.stream_ptr())
+        if rc == 0:
+            nv.count_launch()
+            return dx, dgamma, dbeta
+        if rc != -1:
+            nv.check(rc, "layernorm_bwd_sums")
     nv.check(nv.cuda().b200_layernorm_bwd(dy2d.data_ptr(), x2d.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), nv.ptr(dres), rows, d, _isbf(x2d), nv.stream_ptr()), "layernorm_bwd")
     nv.count_launch()
+    if sum_dres is not None and dres is not None:
+        colsum(dres, out=sum_dres)
+    if sum_dx is not None:
+        colsum(dx, out=sum_dx)
     return dx, dgamma, dbeta
 
 

@@ -86,7 +86,10 @@ class TransformerBlockFn(Function):
             dy2 = dy2.contiguous()
         # ---- feed-forward
         dw2 = _wgrad(dy2, a, w2)
-        db2 = _bgrad(dy2, b2)
+        # the bias gradients of the two projections that feed the residual stream around the second LayerNorm (ff2: column
+        # sums of dy2; out-projection: column sums of what that LayerNorm's backward returns) come out of its backward pass
+        acc_b2 = b2.grad if (getattr(b2, "_fused_grad", False) and b2.grad is not None) else torch.zeros(d, dtype=torch.float32, device=dy2.device)
+        acc_bo = bo.grad if (getattr(bo, "_fused_grad", False) and bo.grad is not None) else torch.zeros(d, dtype=torch.float32, device=dy2.device)
         # (dy W2) * gelu'(pre): the product is a plain GEMM, the derivative and the bias gradient are one streaming pass
         fused_b1 = getattr(b1, "_fused_grad", False) and b1.grad is not None
         dpre, db1 = K.dact_colsum(gemm(dy2, lp(w2), b_mn=True), pre, "gelu", bias_grad=b1.grad if fused_b1 else None)
@@ -94,11 +97,13 @@ class TransformerBlockFn(Function):
         dh2 = gemm(dpre, lp(w1), b_mn=True)
         fused_ln2 = getattr(g2, "_fused_grad", False) and g2.grad is not None
         dy1, dg2, dbe2 = K.layernorm_bwd(dh2, y1, g2.detach(), mean2, rstd2, dres=dy2,
-                                         dgamma=g2.grad if fused_ln2 else None, dbeta=be2.grad if fused_ln2 else None)
+                                         dgamma=g2.grad if fused_ln2 else None, dbeta=be2.grad if fused_ln2 else None,
+                                         sum_dres=acc_b2, sum_dx=acc_bo)
+        db2 = None if acc_b2 is b2.grad else acc_b2
+        dbo = None if acc_bo is bo.grad else acc_bo
         # ---- attention
         o2 = o.view(T, d)
         dwo = _wgrad(dy1, o2, wo)
-        dbo = _bgrad(dy1, bo)
         do = gemm(dy1, lp(wo), b_mn=True).view(B, S, heads, hd)
         dqkv = torch.empty_like(qkv)
         qkv5, dqkv5 = qkv.view(B, S, 3, heads, hd), dqkv.view(B, S, 3, heads, hd)

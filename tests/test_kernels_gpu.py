@@ -425,3 +425,22 @@ def test_gemm_tma_store_epilogue_matches_plain_stores(M, N, K):
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
     ref, _ = G.gemm_ref(a, b, bias=bias, act="gelu", residual=res, want_aux=True, out_dtype=torch.float32)
     assert rel_err(outs[0][0], ref) < 1e-2
+
+
+@pytest.mark.parametrize("rows,d", [(1000, 512), (4096, 1024), (300, 768), (64, 2048)])
+def test_layernorm_bwd_with_fused_column_sums(rows, d):
+    """The backward that also returns the column sums of the residual gradient and of its own output (the bias gradients
+    on either side of a pre-norm LayerNorm) against the plain backward plus two column sums; d = 2048 takes the fallback."""
+    torch.manual_seed(rows + d)
+    x = torch.randn(rows, d, device=DEV).bfloat16()
+    dy, dres = torch.randn(rows, d, device=DEV).bfloat16(), torch.randn(rows, d, device=DEV).bfloat16()
+    g = torch.randn(d, device=DEV)
+    _, mean, rstd = K.layernorm_fwd(x, g, torch.zeros(d, device=DEV), 1e-5)
+    s_res, s_dx = torch.ones(d, device=DEV), torch.full((d,), 2.0, device=DEV)           # accumulators: added to
+    dx, dg, db = K.layernorm_bwd(dy, x, g, mean, rstd, dres=dres, sum_dres=s_res, sum_dx=s_dx)
+    dx0, dg0, db0 = K.layernorm_bwd(dy, x, g, mean, rstd, dres=dres)
+    assert torch.equal(dx, dx0)
+    assert torch.allclose(dg, dg0, rtol=1e-3, atol=1e-2) and torch.allclose(db, db0, rtol=1e-3, atol=1e-2)
+    assert torch.allclose(s_res - 1.0, dres.float().sum(0), rtol=1e-3, atol=2e-2)
+    # the fused sum is taken before the bf16 rounding of dx, the reference after it
+    assert torch.allclose(s_dx - 2.0, dx0.float().sum(0), rtol=1e-2, atol=0.5)

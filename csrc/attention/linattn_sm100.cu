@@ -98,13 +98,10 @@ __device__ __forceinline__ const float* la_consume(const LinAttnArgs& p, int bh,
   if (lo >= hi) return nullptr;
   constexpr int ST = HD * HD + HD;
   const int BH = p.B * p.H, tid = threadIdx.x;
-  __shared__ int s_ok;
-  if (tid == 0) s_ok = 1;
-  __syncthreads();
-  if (tid >= lo && tid < hi && !la_wait_flag(x.flags[x.rank] + (size_t)tid * BH + bh, epoch, x.wait_cycles, p.status)) s_ok = 0;
-  __syncthreads();
+  int good = 1;
+  if (tid >= lo && tid < hi && !la_wait_flag(x.flags[x.rank] + (size_t)tid * BH + bh, epoch, x.wait_cycles, p.status)) good = 0;
+  const bool ok = __syncthreads_and(good) != 0;
   float4* dst = reinterpret_cast<float4*>(x.prefix + (size_t)bh * ST);
-  const bool ok = s_ok != 0;
   for (int i = tid; i < ST / 4; i += blockDim.x) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int r = lo; r < hi && ok; ++r) {
@@ -329,12 +326,107 @@ struct LaSmem {
 };
 
 // ---------------------------------------------------------------------------------------------------- forward
+// Thread mapping of the forward kernel: 8 warps. Warp w owns tile rows / TMEM lanes 32 (w & 3) .. + 31 (the lanes a warp
+// may read) and column half w >> 2 of every row, so the elementwise work of a chunk is spread over twice the warps of a
+// row-per-thread mapping and every scheduler has two warps to switch between (the kernel is bound by instruction
+// latency, not by the tensor core: 4 k instructions per chunk and thread at ~5 cycles each with one warp per scheduler).
+constexpr int LA_FWD_THREADS = 256;
+
+// phi(scale * x) in place on this thread's half of its row (4 of the 8 16-byte chunks of every 64-column atom)
 template <int HD>
-__global__ void __launch_bounds__(128, 1)
+__device__ __forceinline__ void la_phi_half(uint8_t* tile, int row, int hf, int valid, float scale, int kind) {
+#pragma unroll
+  for (int a = 0; a < HD / 64; ++a)
+#pragma unroll
+    for (int c4 = 0; c4 < 4; ++c4) {
+      const int c = hf * 4 + c4;
+      uint4* p = reinterpret_cast<uint4*>(tile + a * (LA_C * 128) + sw128_offset(row, c));
+      uint4 u = *p;
+      uint32_t* w = &u.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(w[j]);
+        w[j] = row < valid ? pack_bf16x2(la_phi(f.x * scale, kind), la_phi(f.y * scale, kind)) : 0u;
+      }
+      *p = u;
+    }
+}
+// this thread's half of (row . z)
+template <int HD>
+__device__ __forceinline__ float la_dot_half(const uint8_t* tile, int row, int hf, const float* z) {
+  float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+  for (int a = 0; a < HD / 64; ++a)
+#pragma unroll
+    for (int c4 = 0; c4 < 4; ++c4) {
+      const int c = hf * 4 + c4;
+      const uint4 u = *reinterpret_cast<const uint4*>(tile + a * (LA_C * 128) + sw128_offset(row, c));
+      const uint32_t* w = &u.x;
+      const float* zz = z + a * 64 + c * 8;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16x2(w[j]); acc0 = fmaf(f.x, zz[2 * j], acc0); acc1 = fmaf(f.y, zz[2 * j + 1], acc1); }
+    }
+  return acc0 + acc1;
+}
+// 64 fp32 values = columns 64 hf .. of this thread's row of a [128][128] tile (atom hf) -> value and remainder tiles
+__device__ __forceinline__ void la_write_half128_hilo(uint8_t* hi, uint8_t* lo, int row, int hf, const float* v, bool with_lo) {
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    uint32_t h[4], l[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = v[g * 8 + 2 * j], b = v[g * 8 + 2 * j + 1];
+      h[j] = pack_bf16x2(a, b);
+      const float2 r = unpack_bf16x2(h[j]);
+      l[j] = pack_bf16x2(a - r.x, b - r.y);
+    }
+    const uint32_t off = hf * (LA_C * 128) + sw128_offset(row, g);
+    *reinterpret_cast<uint4*>(hi + off) = make_uint4(h[0], h[1], h[2], h[3]);
+    if (with_lo) *reinterpret_cast<uint4*>(lo + off) = make_uint4(l[0], l[1], l[2], l[3]);
+  }
+}
+// HD / 2 fp32 values = columns (HD / 2) hf .. of a state row -> value and remainder tiles ([rows][HD], atoms of `rows` rows)
+template <int HD>
+__device__ __forceinline__ void la_write_hilo_half(uint8_t* hi, uint8_t* lo, int rows, int row, int hf, const float* v) {
+#pragma unroll
+  for (int gg = 0; gg < HD / 16; ++gg) {
+    const int g = hf * (HD / 16) + gg;
+    uint32_t h[4], l[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = v[gg * 8 + 2 * j], b = v[gg * 8 + 2 * j + 1];
+      h[j] = pack_bf16x2(a, b);
+      const float2 r = unpack_bf16x2(h[j]);
+      l[j] = pack_bf16x2(a - r.x, b - r.y);
+    }
+    const uint32_t off = (g >> 3) * (rows * 128) + sw128_offset(row, g & 7);
+    *reinterpret_cast<uint4*>(hi + off) = make_uint4(h[0], h[1], h[2], h[3]);
+    *reinterpret_cast<uint4*>(lo + off) = make_uint4(l[0], l[1], l[2], l[3]);
+  }
+}
+// partial column sum: rows [r0, r0 + n) of column k
+__device__ __forceinline__ float la_colsum_rows(const uint8_t* tile, int k, int r0, int n) {
+  const uint8_t* base = tile + (k >> 6) * (LA_C * 128) + (k & 7) * 2;
+  const int chunk = (k & 63) >> 3;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll 4
+  for (int r = r0; r < r0 + n; r += 4) {
+    s0 += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(base + sw128_offset(r, chunk)));
+    s1 += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(base + sw128_offset(r + 1, chunk)));
+    s2 += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(base + sw128_offset(r + 2, chunk)));
+    s3 += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(base + sw128_offset(r + 3, chunk)));
+  }
+  return (s0 + s1) + (s2 + s3);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(LA_FWD_THREADS, 1)
 linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const LinAttnArgs p) {
   using L = LaSmem<HD>;
   constexpr int KA = HD / 64;
+  constexpr int HH = HD / 2;                  // columns of a HD-wide row per thread
+  constexpr int ZP = LA_FWD_THREADS / HD;     // row groups of the column sums of K~ (4 or 2)
   constexpr uint32_t COL_A = 0, COL_NUM = 128, COL_S = 256;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
@@ -346,11 +438,14 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint8_t* sSlo = sShi + L::ST;
   uint8_t* sPlo = HD == 64 ? sSlo + L::ST : sQ;
   float* sz = reinterpret_cast<float*>(sSlo + L::ST + L::PLO);      // [HD]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sz + HD);
+  float* s_part = sz + HD;                    // [2][128]: the halves' shares of a row's denominator
+  float* s_zk = s_part + 2 * LA_C;            // [ZP][HD]: partial column sums of K~
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_zk + LA_FWD_THREADS);
   uint64_t* q_bar = bars; uint64_t* k_bar = bars + 1; uint64_t* v_bar = bars + 3; uint64_t* a_bar = bars + 4; uint64_t* b_bar = bars + 5;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int quad = warp & 3, hf = warp >> 2, row = quad * 32 + lane;
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
   const int n_chunks = (p.S + LA_C - 1) / LA_C;
   const bool full = !p.state_only;
@@ -364,7 +459,7 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
   }
   if (warp == 0) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
-  if (HD == 64) for (int i = tid; i < L::ZERO / 16; i += 128) reinterpret_cast<uint4*>(sZero)[i] = make_uint4(0, 0, 0, 0);
+  if (HD == 64) for (int i = tid; i < L::ZERO / 16; i += LA_FWD_THREADS) reinterpret_cast<uint4*>(sZero)[i] = make_uint4(0, 0, 0, 0);
   // state before the first token: TMEM (fp32) and the two bf16 operand tiles
   const size_t st_stride = (size_t)HD * HD + HD;
   const uint32_t sx_epoch = la_epoch(p);
@@ -381,13 +476,13 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t trow = tmem_base + (uint32_t(warp * 32) << 16);
-  if (s_in) {                                     // TMEM accesses are warp-wide: every lane stores (rows >= HD: zeros)
+  const uint32_t trow = tmem_base + (uint32_t(quad * 32) << 16);
+  if (s_in && hf == 0) {                             // TMEM accesses are warp-wide: every lane stores (rows >= HD: zeros)
 #pragma unroll
     for (int c = 0; c < HD / 32; ++c) {
       uint32_t r[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) r[i] = tid < HD ? __float_as_uint(s_in[bh * st_stride + (size_t)tid * HD + c * 32 + i]) : 0u;
+      for (int i = 0; i < 32; ++i) r[i] = row < HD ? __float_as_uint(s_in[bh * st_stride + (size_t)row * HD + c * 32 + i]) : 0u;
       tmem_st_x32(trow + COL_S + c * 32, r);
     }
     tmem_st_wait();
@@ -418,8 +513,8 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (full && !mbar_wait(q_bar, c & 1, p.status, ST_TIMEOUT_TMA_FULL)) ok = false;
     if (ok && !mbar_wait(&k_bar[st], (c >> 1) & 1, p.status, ST_TIMEOUT_TMA_FULL)) ok = false;
     if (__syncthreads_or(!ok)) { ok = false; break; }
-    if (full) la_phi_tile<HD>(sQ, tid, LA_C, p.scale, p.kind);
-    la_phi_tile<HD>(sKc, tid, valid, p.scale, p.kind);
+    if (full) la_phi_half<HD>(sQ, row, hf, LA_C, p.scale, p.kind);
+    la_phi_half<HD>(sKc, row, hf, valid, p.scale, p.kind);
     fence_proxy_async_smem();
     __syncthreads();
     float den = p.eps;
@@ -431,30 +526,28 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         la_mma_pw<HD, HD>(tmem_base + COL_NUM, sQ, sSlo, HD * 128, true);
         tc_commit(a_bar);                                                             // covers every reader of Q~
       }
-      // Q~ . z in fp32 while the tensor core works
-      float qrow[HD];
-      la_read_row<HD>(sQ, tid, qrow);
-#pragma unroll
-      for (int i = 0; i < HD; ++i) den = fmaf(qrow[i], sz[i], den);
+      // this half's share of Q~ . z in fp32 while the tensor core works
+      float part = la_dot_half<HD>(sQ, row, hf, sz);
       if (!mbar_wait(a_bar, c & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
       if (__syncthreads_or(!ok)) { ok = false; break; }
       tc_fence_after_sync();
       if (HD == 64 && tid == 0 && c + 1 < n_chunks) load(sQ, &tmQ, q_bar, c + 1);  // Q~ has been consumed
-      float a[LA_C];
-      la_tmem_row<LA_C>(trow + COL_A, a);
+      float a[64];
+      la_tmem_row<64>(trow + COL_A + hf * 64, a);
       float r0 = 0.f, r1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < LA_C; i += 2) {
-        if (i > tid) a[i] = 0.f;
-        if (i + 1 > tid) a[i + 1] = 0.f;
+      for (int i = 0; i < 64; i += 2) {
+        if (hf * 64 + i > row) a[i] = 0.f;
+        if (hf * 64 + i + 1 > row) a[i + 1] = 0.f;
         r0 += a[i]; r1 += a[i + 1];
       }
-      den += r0 + r1;
-      la_write_row128_hilo(sP, sPlo, tid, a, rem);
+      s_part[hf * LA_C + row] = part + (r0 + r1);
+      la_write_half128_hilo(sP, sPlo, row, hf, a, rem);
       tc_fence_before_sync();
       fence_proxy_async_smem();
     }
     __syncthreads();
+    if (full) den += s_part[row] + s_part[LA_C + row];        // both halves add in the same order
     if (tid == 0) {
       ok = mbar_wait(v_bar, c & 1, p.status, ST_TIMEOUT_TMA_FULL);
       if (ok) {
@@ -467,9 +560,8 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc_commit(b_bar);
       }
     }
-    // z += colsum(K~) while the products run; the new z is first read after the barrier below
-    float zk = 0.f;
-    if (tid < HD) zk = la_colsum<HD>(sKc, tid);
+    // z += colsum(K~) while the products run: ZP row groups per column, combined after the barrier below
+    s_zk[tid] = la_colsum_rows(sKc, tid % HD, (tid / HD) * (LA_C / ZP), LA_C / ZP);
     if (!mbar_wait(b_bar, c & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
     if (__syncthreads_or(!ok)) { ok = false; break; }
     tc_fence_after_sync();
@@ -479,15 +571,15 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (c + 2 < n_chunks) load(sKc, &tmK, &k_bar[st], c + 2);
     }
     if (full) {
-      float num[HD];
-      la_tmem_row<HD>(trow + COL_NUM, num);
-      const int tok = c * LA_C + tid;
+      float num[HH];
+      la_tmem_row<HH>(trow + COL_NUM + hf * HH, num);
+      const int tok = c * LA_C + row;
       if (tok < p.S) {
         const float inv = 1.f / den;
-        __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.o.ptr) + (long long)b * p.o.sb + (long long)tok * p.o.ss + (long long)h * p.o.sh;
-        __nv_bfloat16* lp = p.o_lo.ptr ? reinterpret_cast<__nv_bfloat16*>(p.o_lo.ptr) + (long long)b * p.o_lo.sb + (long long)tok * p.o_lo.ss + (long long)h * p.o_lo.sh : nullptr;
+        __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.o.ptr) + (long long)b * p.o.sb + (long long)tok * p.o.ss + (long long)h * p.o.sh + hf * HH;
+        __nv_bfloat16* lp = p.o_lo.ptr ? reinterpret_cast<__nv_bfloat16*>(p.o_lo.ptr) + (long long)b * p.o_lo.sb + (long long)tok * p.o_lo.ss + (long long)h * p.o_lo.sh + hf * HH : nullptr;
 #pragma unroll
-        for (int i = 0; i < HD; i += 8) {
+        for (int i = 0; i < HH; i += 8) {
           uint32_t hi[4], lo[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -499,29 +591,34 @@ linattn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           *reinterpret_cast<uint4*>(op + i) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
           if (lp) *reinterpret_cast<uint4*>(lp + i) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
         }
-        if (p.den) p.den[((long long)b * p.H + h) * p.S + tok] = den;
+        if (p.den && hf == 0) p.den[((long long)b * p.H + h) * p.S + tok] = den;
       }
     }
-    if (tid < HD) sz[tid] += zk;
-    if (full && c + 1 < n_chunks) {                                           // operand copies of the new state
-      float srow[HD];
-      la_tmem_row<HD>(trow + COL_S, srow);
-      if (tid < HD) la_write_hilo<HD>(sShi, sSlo, HD, tid, srow);
+    if (tid < HD) {
+      float zk = 0.f;
+#pragma unroll
+      for (int g = 0; g < ZP; ++g) zk += s_zk[g * HD + tid];
+      sz[tid] += zk;
+    }
+    if (full && c + 1 < n_chunks && quad * 32 < HD) {                         // operand copies of the new state (warps that own state rows)
+      float srow[HH];
+      la_tmem_row<HH>(trow + COL_S + hf * HH, srow);
+      if (row < HD) la_write_hilo_half<HD>(sShi, sSlo, HD, row, hf, srow);
       fence_proxy_async_smem();
     }
     tc_fence_before_sync();
     __syncthreads();
   }
   float* s_out = la_publish_begin<HD>(p, bh, sx_epoch, p.s_out);      // the caller's buffer, or this rank's slot of the exchange
-  if (ok && s_out) {
+  if (ok && s_out && hf == 0) {
     tc_fence_after_sync();
     float srow[HD];
     la_tmem_row<HD>(trow + COL_S, srow);
-    if (tid < HD) {
+    if (row < HD) {
 #pragma unroll
       for (int i = 0; i < HD; i += 4)
-        *reinterpret_cast<float4*>(s_out + bh * st_stride + (size_t)tid * HD + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
-      s_out[bh * st_stride + (size_t)HD * HD + tid] = sz[tid];
+        *reinterpret_cast<float4*>(s_out + bh * st_stride + (size_t)row * HD + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
+      s_out[bh * st_stride + (size_t)HD * HD + row] = sz[row];
     }
   }
   la_publish_end(p, bh, sx_epoch);
@@ -939,6 +1036,8 @@ linattn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 
 // ---------------------------------------------------------------------------------------------------- host side
 template <int HD> constexpr int la_fwd_smem() { return 4 * LaSmem<HD>::TILE + LaSmem<HD>::ZERO + LaSmem<HD>::PT + LaSmem<HD>::PLO + 2 * LaSmem<HD>::ST + HD * 4 + 128; }
+// the forward kernel also keeps [2][128] denominator shares and 256 partial column sums
+template <int HD> constexpr int la_fwd8_smem() { return la_fwd_smem<HD>() + 2 * LA_C * 4 + LA_FWD_THREADS * 4; }
 template <int HD> constexpr int la_dkv_smem() { return 4 * LaSmem<HD>::TILE + LaSmem<HD>::ZERO + LaSmem<HD>::PT + 2 * LaSmem<HD>::ST + (HD + LA_C) * 4 + 128; }
 
 static int la_maps(const LinAttnArgs& a, CUtensorMap* tq, CUtensorMap* tk, CUtensorMap* tv) {
@@ -954,7 +1053,7 @@ static int la_set_attrs() {
   static bool done = false;
   if (done) return 0;
   (void)cudaGetLastError();
-  if (cudaFuncSetAttribute(linattn_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, la_fwd_smem<HD>()) != cudaSuccess) return 1;
+  if (cudaFuncSetAttribute(linattn_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, la_fwd8_smem<HD>()) != cudaSuccess) return 1;
   if (cudaFuncSetAttribute(linattn_bwd_dq_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, la_fwd_smem<HD>()) != cudaSuccess) return 1;
   if (cudaFuncSetAttribute(linattn_bwd_dkv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, la_dkv_smem<HD>()) != cudaSuccess) return 1;
   done = true;
@@ -969,7 +1068,7 @@ static int la_launch(const LinAttnArgs& a, int which, cudaStream_t st) {
   if (int rc = la_maps(a, need_q ? &tq : nullptr, &tk, &tv)) return rc;
   if (!need_q) tq = tk;
   const unsigned grid = (unsigned)(a.B * a.H);
-  if (which == 0) linattn_fwd_kernel<HD><<<grid, 128, la_fwd_smem<HD>(), st>>>(tq, tk, tv, a);
+  if (which == 0) linattn_fwd_kernel<HD><<<grid, LA_FWD_THREADS, la_fwd8_smem<HD>(), st>>>(tq, tk, tv, a);
   else if (which == 1) linattn_bwd_dq_kernel<HD><<<grid, 128, la_fwd_smem<HD>(), st>>>(tk, tv, a);
   else linattn_bwd_dkv_kernel<HD><<<grid, 128, la_dkv_smem<HD>(), st>>>(tq, tk, tv, a);
   const cudaError_t e = cudaGetLastError();

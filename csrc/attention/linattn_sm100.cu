@@ -689,12 +689,94 @@ __device__ __forceinline__ void la_store_dphi(const AttnTensor& x, const AttnTen
   }
 }
 
-// ---------------------------------------------------------------------------------------------------- backward 1: dQ
+// ---------------------------------------------------------------------------------------------------- backward helpers (8 warps)
+// This thread's half of one token: G = dO / D for HD / 2 columns (bf16 tile row), returns its share of -(G . O).
+// Tokens past the end give zeros.
 template <int HD>
-__global__ void __launch_bounds__(128, 1)
+__device__ __forceinline__ float la_load_g_half(const LinAttnArgs& p, int b, int h, int tok, uint8_t* sG, int row, int hf) {
+  constexpr int HH = HD / 2;
+  uint32_t g[HH / 2];
+  float dden = 0.f;
+  if (tok < p.S) {
+    const __nv_bfloat16* dp = reinterpret_cast<const __nv_bfloat16*>(p.dout.ptr) + (long long)b * p.dout.sb + (long long)tok * p.dout.ss + (long long)h * p.dout.sh + hf * HH;
+    const __nv_bfloat16* op = reinterpret_cast<const __nv_bfloat16*>(p.o.ptr) + (long long)b * p.o.sb + (long long)tok * p.o.ss + (long long)h * p.o.sh + hf * HH;
+    const __nv_bfloat16* lp = p.o_lo.ptr ? reinterpret_cast<const __nv_bfloat16*>(p.o_lo.ptr) + (long long)b * p.o_lo.sb + (long long)tok * p.o_lo.ss + (long long)h * p.o_lo.sh + hf * HH : nullptr;
+    const float inv = 1.f / p.den[((long long)b * p.H + h) * p.S + tok];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < HH; i += 8) {
+      const uint4 du = *reinterpret_cast<const uint4*>(dp + i), ou = *reinterpret_cast<const uint4*>(op + i);
+      const uint4 lu = lp ? *reinterpret_cast<const uint4*>(lp + i) : make_uint4(0, 0, 0, 0);
+      const uint32_t* dw = &du.x; const uint32_t* ow = &ou.x; const uint32_t* lw = &lu.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 d2 = unpack_bf16x2(dw[j]), o2 = unpack_bf16x2(ow[j]), l2 = unpack_bf16x2(lw[j]);
+        // the SAME rounded G enters G V^T on the tensor core and the dot product here; O carries its remainder
+        const uint32_t gp = pack_bf16x2(d2.x * inv, d2.y * inv);
+        const float2 gr = unpack_bf16x2(gp);
+        g[(i >> 1) + j] = gp;
+        dot = fmaf(gr.x, o2.x + l2.x, dot); dot = fmaf(gr.y, o2.y + l2.y, dot);
+      }
+    }
+    dden = -dot;
+  } else {
+#pragma unroll
+    for (int i = 0; i < HH / 2; ++i) g[i] = 0u;
+  }
+#pragma unroll
+  for (int gi = 0; gi < HH / 8; ++gi) {
+    const int gc = hf * (HH / 8) + gi;                 // 16-byte chunk of the full row
+    *reinterpret_cast<uint4*>(sG + (gc >> 3) * (LA_C * 128) + sw128_offset(row, gc & 7)) =
+        make_uint4(g[gi * 4], g[gi * 4 + 1], g[gi * 4 + 2], g[gi * 4 + 3]);
+  }
+  return dden;
+}
+// grad[i] <- scale * phi'(scale * x_i) * grad[i] for this thread's HD / 2 columns of a token, stored as bf16
+template <int HD>
+__device__ __forceinline__ void la_store_dphi_half(const AttnTensor& x, const AttnTensor& dx, int b, int h, int tok, int hf, const float* grad, float scale, int kind) {
+  constexpr int HH = HD / 2;
+  const __nv_bfloat16* xp = reinterpret_cast<const __nv_bfloat16*>(x.ptr) + (long long)b * x.sb + (long long)tok * x.ss + (long long)h * x.sh + hf * HH;
+  __nv_bfloat16* gp = reinterpret_cast<__nv_bfloat16*>(dx.ptr) + (long long)b * dx.sb + (long long)tok * dx.ss + (long long)h * dx.sh + hf * HH;
+#pragma unroll
+  for (int i = 0; i < HH; i += 8) {
+    const uint4 xu = *reinterpret_cast<const uint4*>(xp + i);
+    const uint32_t* xw = &xu.x;
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x2 = unpack_bf16x2(xw[j]);
+      const float a = x2.x * scale, c = x2.y * scale;
+      const float da = kind == 0 ? (a > 0.f ? 1.f : __expf(a)) : (a > 0.f ? 2.f * a : 0.f);
+      const float dc = kind == 0 ? (c > 0.f ? 1.f : __expf(c)) : (c > 0.f ? 2.f * c : 0.f);
+      o[j] = pack_bf16x2(grad[i + 2 * j] * da * scale, grad[i + 2 * j + 1] * dc * scale);
+    }
+    *reinterpret_cast<uint4*>(gp + i) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+// partial weighted column sum: sum over rows [r0, r0 + n) of w[r] * tile(r, k)
+__device__ __forceinline__ float la_colsum_w_rows(const uint8_t* tile, int k, const float* w, int r0, int n) {
+  const uint8_t* base = tile + (k >> 6) * (LA_C * 128) + (k & 7) * 2;
+  const int chunk = (k & 63) >> 3;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll 4
+  for (int r = r0; r < r0 + n; r += 4) {
+    s0 = fmaf(w[r], __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(base + sw128_offset(r, chunk))), s0);
+    s1 = fmaf(w[r + 1], __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(base + sw128_offset(r + 1, chunk))), s1);
+    s2 = fmaf(w[r + 2], __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(base + sw128_offset(r + 2, chunk))), s2);
+    s3 = fmaf(w[r + 3], __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(base + sw128_offset(r + 3, chunk))), s3);
+  }
+  return (s0 + s1) + (s2 + s3);
+}
+
+// ---------------------------------------------------------------------------------------------------- backward 1: dQ
+// Same 8-warp mapping as the forward: warp w owns rows 32 (w & 3) .. and column half w >> 2.
+template <int HD>
+__global__ void __launch_bounds__(LA_FWD_THREADS, 1)
 linattn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const LinAttnArgs p) {
   using L = LaSmem<HD>;
   constexpr int KA = HD / 64;
+  constexpr int HH = HD / 2;
+  constexpr int ZP = LA_FWD_THREADS / HD;
   constexpr uint32_t COL_A = 0, COL_DQ = 128, COL_S = 256;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sG = smem;
@@ -706,11 +788,15 @@ linattn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   uint8_t* sSlo = sShi + L::ST;
   uint8_t* sPlo = HD == 64 ? sSlo + L::ST : sG;
   float* sz = reinterpret_cast<float*>(sSlo + L::ST + L::PLO);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sz + HD);
+  float* s_part = sz + HD;                    // [2][128]: the halves' shares of dden; later in the chunk: partial column sums
+  float* s_zk = s_part;                       // (two barriers lie between the last read of one use and the first write of the other)
+  float* s_dden = s_part + 2 * LA_C;          // [128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_dden + LA_C);
   uint64_t* k_bar = bars; uint64_t* v_bar = bars + 2; uint64_t* a_bar = bars + 3; uint64_t* b_bar = bars + 4;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int quad = warp & 3, hf = warp >> 2, row = quad * 32 + lane;
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
   const int n_chunks = (p.S + LA_C - 1) / LA_C;
   const bool rem = p.kind == 0;                // see the forward kernel
@@ -721,7 +807,7 @@ linattn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
   }
   if (warp == 0) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
-  if (HD == 64) for (int i = tid; i < L::ZERO / 16; i += 128) reinterpret_cast<uint4*>(sZero)[i] = make_uint4(0, 0, 0, 0);
+  if (HD == 64) for (int i = tid; i < L::ZERO / 16; i += LA_FWD_THREADS) reinterpret_cast<uint4*>(sZero)[i] = make_uint4(0, 0, 0, 0);
   const size_t st_stride = (size_t)HD * HD + HD;
   if (tid < HD) {
     float s0[HD];
@@ -735,13 +821,13 @@ linattn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t trow = tmem_base + (uint32_t(warp * 32) << 16);
-  if (p.s_in) {
+  const uint32_t trow = tmem_base + (uint32_t(quad * 32) << 16);
+  if (p.s_in && hf == 0) {
 #pragma unroll
     for (int c = 0; c < HD / 32; ++c) {
       uint32_t r[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) r[i] = tid < HD ? __float_as_uint(p.s_in[bh * st_stride + (size_t)tid * HD + c * 32 + i]) : 0u;
+      for (int i = 0; i < 32; ++i) r[i] = row < HD ? __float_as_uint(p.s_in[bh * st_stride + (size_t)row * HD + c * 32 + i]) : 0u;
       tmem_st_x32(trow + COL_S + c * 32, r);
     }
     tmem_st_wait();
@@ -767,13 +853,14 @@ linattn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     const int st = c & 1;
     uint8_t* sKc = sK + st * L::TILE;
     const int valid = min(LA_C, p.S - c * LA_C);
-    const int tok = c * LA_C + tid;
-    // G and dden of this thread's token come straight from global memory while the TMA tiles land
-    const float dden = la_load_g<HD>(p, b, h, tok, sG, tid);
+    const int tok = c * LA_C + row;
+    // this half of G and its share of dden come straight from global memory while the TMA tiles land
+    s_part[hf * LA_C + row] = la_load_g_half<HD>(p, b, h, tok, sG, row, hf);
     if (!mbar_wait(&k_bar[st], (c >> 1) & 1, p.status, ST_TIMEOUT_TMA_FULL)) ok = false;
     if (ok && !mbar_wait(v_bar, c & 1, p.status, ST_TIMEOUT_TMA_FULL)) ok = false;
     if (__syncthreads_or(!ok)) { ok = false; break; }
-    la_phi_tile<HD>(sKc, tid, valid, p.scale, p.kind);
+    const float dden = s_part[row] + s_part[LA_C + row];
+    la_phi_half<HD>(sKc, row, hf, valid, p.scale, p.kind);
     fence_proxy_async_smem();
     __syncthreads();
     if (tid == 0) {
@@ -787,11 +874,11 @@ linattn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     if (__syncthreads_or(!ok)) { ok = false; break; }
     tc_fence_after_sync();
     {
-      float a[LA_C];
-      la_tmem_row<LA_C>(trow + COL_A, a);
+      float a[64];
+      la_tmem_row<64>(trow + COL_A + hf * 64, a);
 #pragma unroll
-      for (int i = 0; i < LA_C; ++i) a[i] = i > tid ? 0.f : a[i] + dden;
-      la_write_row128_hilo(sP, sPlo, tid, a, rem);
+      for (int i = 0; i < 64; ++i) a[i] = (hf * 64 + i > row) ? 0.f : a[i] + dden;
+      la_write_half128_hilo(sP, sPlo, row, hf, a, rem);
     }
     tc_fence_before_sync();
     fence_proxy_async_smem();
@@ -803,8 +890,7 @@ linattn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       la_mma_xTw<HD>(tmem_base + COL_S, sKc, k_lbo[st], sV, have_state0 || c > 0);    // S += K~^T V
       tc_commit(b_bar);
     }
-    float zk = 0.f;
-    if (tid < HD) zk = la_colsum<HD>(sKc, tid);
+    s_zk[tid] = la_colsum_rows(sKc, tid % HD, (tid / HD) * (LA_C / ZP), LA_C / ZP);
     if (!mbar_wait(b_bar, c & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
     if (__syncthreads_or(!ok)) { ok = false; break; }
     tc_fence_after_sync();
@@ -813,20 +899,25 @@ linattn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       if (c + 2 < n_chunks) load(sKc, &tmK, &k_bar[st], c + 2);
     }
     {
-      float dq[HD];
-      la_tmem_row<HD>(trow + COL_DQ, dq);
+      float dq[HH];
+      la_tmem_row<HH>(trow + COL_DQ + hf * HH, dq);
       if (tok < p.S) {
 #pragma unroll
-        for (int i = 0; i < HD; ++i) dq[i] = fmaf(dden, sz[i], dq[i]);               // z of the chunks before this one
-        la_store_dphi<HD>(p.q, p.dq, b, h, tok, dq, p.scale, p.kind);
+        for (int i = 0; i < HH; ++i) dq[i] = fmaf(dden, sz[hf * HH + i], dq[i]);      // z of the chunks before this one
+        la_store_dphi_half<HD>(p.q, p.dq, b, h, tok, hf, dq, p.scale, p.kind);
       }
     }
     __syncthreads();                                                                  // every thread has read the old z
-    if (tid < HD) sz[tid] += zk;
-    if (c + 1 < n_chunks) {
-      float srow[HD];
-      la_tmem_row<HD>(trow + COL_S, srow);
-      if (tid < HD) la_write_hilo<HD>(sShi, sSlo, HD, tid, srow);
+    if (tid < HD) {
+      float zk = 0.f;
+#pragma unroll
+      for (int g = 0; g < ZP; ++g) zk += s_zk[g * HD + tid];
+      sz[tid] += zk;
+    }
+    if (c + 1 < n_chunks && quad * 32 < HD) {
+      float srow[HH];
+      la_tmem_row<HH>(trow + COL_S + hf * HH, srow);
+      if (row < HD) la_write_hilo_half<HD>(sShi, sSlo, HD, row, hf, srow);
       fence_proxy_async_smem();
     }
     tc_fence_before_sync();
@@ -839,11 +930,13 @@ linattn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
 
 // ---------------------------------------------------------------------------------------------------- backward 2: dK, dV
 template <int HD>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(LA_FWD_THREADS, 1)
 linattn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const LinAttnArgs p) {
   using L = LaSmem<HD>;
   constexpr int KA = HD / 64;
+  constexpr int HH = HD / 2;
+  constexpr int ZP = LA_FWD_THREADS / HD;
   constexpr uint32_t COL_T = 0, COL_DV = 128, COL_DK = 128 + HD, COL_DS = 128 + 2 * HD;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
@@ -856,11 +949,14 @@ linattn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   uint8_t* sDlo = sDhi + L::ST;
   float* sdz = reinterpret_cast<float*>(sDlo + L::ST);     // [HD]
   float* sdden = sdz + HD;                                  // [128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sdden + LA_C);
+  float* s_part = sdden + LA_C;                             // [2][128] dden shares; later in the chunk: partial column sums
+  float* s_zk = s_part;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_part + 2 * LA_C);
   uint64_t* ld_bar = bars; uint64_t* t_bar = bars + 1; uint64_t* u_bar = bars + 2; uint64_t* b_bar = bars + 3;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int quad = warp & 3, hf = warp >> 2, row = quad * 32 + lane;
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
   const int n_chunks = (p.S + LA_C - 1) / LA_C;
   const bool full = !p.state_only;               // state_only: only dS / dz of this slice (reads Q, dO, O)
@@ -871,7 +967,7 @@ linattn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
   }
   if (warp == 0) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
-  if (HD == 64) for (int i = tid; i < L::ZERO / 16; i += 128) reinterpret_cast<uint4*>(sZero)[i] = make_uint4(0, 0, 0, 0);
+  if (HD == 64) for (int i = tid; i < L::ZERO / 16; i += LA_FWD_THREADS) reinterpret_cast<uint4*>(sZero)[i] = make_uint4(0, 0, 0, 0);
   const size_t st_stride = (size_t)HD * HD + HD;
   const uint32_t sx_epoch = la_epoch(p);
   const float* ds_in = la_consume<HD>(p, bh, sx_epoch, p.ds_in);     // the caller's dS, or the higher ranks' totals
@@ -887,13 +983,13 @@ linattn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t trow = tmem_base + (uint32_t(warp * 32) << 16);
-  if (ds_in) {
+  const uint32_t trow = tmem_base + (uint32_t(quad * 32) << 16);
+  if (ds_in && hf == 0) {
 #pragma unroll
     for (int c = 0; c < HD / 32; ++c) {
       uint32_t r[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) r[i] = tid < HD ? __float_as_uint(ds_in[bh * st_stride + (size_t)tid * HD + c * 32 + i]) : 0u;
+      for (int i = 0; i < 32; ++i) r[i] = row < HD ? __float_as_uint(ds_in[bh * st_stride + (size_t)row * HD + c * 32 + i]) : 0u;
       tmem_st_x32(trow + COL_DS + c * 32, r);
     }
     tmem_st_wait();
@@ -919,13 +1015,13 @@ linattn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   for (int it = 0; it < n_chunks; ++it) {
     const int c = n_chunks - 1 - it;
     const int valid = min(LA_C, p.S - c * LA_C);
-    const int tok = c * LA_C + tid;
-    const float dden = la_load_g<HD>(p, b, h, tok, sG, tid);
-    sdden[tid] = dden;
+    const int tok = c * LA_C + row;
+    s_part[hf * LA_C + row] = la_load_g_half<HD>(p, b, h, tok, sG, row, hf);
     if (!mbar_wait(ld_bar, it & 1, p.status, ST_TIMEOUT_TMA_FULL)) ok = false;
     if (__syncthreads_or(!ok)) { ok = false; break; }
-    la_phi_tile<HD>(sQ, tid, LA_C, p.scale, p.kind);
-    if (full) la_phi_tile<HD>(sK, tid, valid, p.scale, p.kind);
+    if (hf == 0) sdden[row] = s_part[row] + s_part[LA_C + row];
+    la_phi_half<HD>(sQ, row, hf, LA_C, p.scale, p.kind);
+    if (full) la_phi_half<HD>(sK, row, hf, valid, p.scale, p.kind);
     fence_proxy_async_smem();
     __syncthreads();
     if (full) {
@@ -943,11 +1039,11 @@ linattn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     if (__syncthreads_or(!ok)) { ok = false; break; }
     tc_fence_after_sync();
     {
-      float a[LA_C];
-      la_tmem_row<LA_C>(trow + COL_T, a);
+      float a[64];
+      la_tmem_row<64>(trow + COL_T + hf * 64, a);
 #pragma unroll
-      for (int i = 0; i < LA_C; ++i) if (i < tid) a[i] = 0.f;                        // keep queries at or after this key
-      la_write_row128(sP, tid, a);
+      for (int i = 0; i < 64; ++i) if (hf * 64 + i < row) a[i] = 0.f;                // keep queries at or after this key
+      la_write_half128_hilo(sP, sP, row, hf, a, false);
     }
     tc_fence_before_sync();
     fence_proxy_async_smem();
@@ -965,11 +1061,11 @@ linattn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     if (__syncthreads_or(!ok)) { ok = false; break; }
     tc_fence_after_sync();
     {
-      float a[LA_C];
-      la_tmem_row<LA_C>(trow + COL_T, a);
+      float a[64];
+      la_tmem_row<64>(trow + COL_T + hf * 64, a);
 #pragma unroll
-      for (int i = 0; i < LA_C; ++i) a[i] = i < tid ? 0.f : a[i] + sdden[i];
-      la_write_row128(sP, tid, a);
+      for (int i = 0; i < 64; ++i) a[i] = (hf * 64 + i < row) ? 0.f : a[i] + sdden[hf * 64 + i];
+      la_write_half128_hilo(sP, sP, row, hf, a, false);
     }
     tc_fence_before_sync();
     fence_proxy_async_smem();
@@ -981,50 +1077,55 @@ linattn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       la_mma_xTw<HD>(tmem_base + COL_DS, sQ, q_lbo, sG, have_state0 || it > 0);       // dS += Q~^T G
       tc_commit(b_bar);
     }
-    float dzk = 0.f;
-    if (tid < HD) dzk = la_colsum_w<HD>(sQ, tid, sdden);                              // dz += Q~^T dden, fp32
+    // dz += Q~^T dden in fp32: ZP row groups per column, combined after the barriers below
+    s_zk[tid] = la_colsum_w_rows(sQ, tid % HD, sdden, (tid / HD) * (LA_C / ZP), LA_C / ZP);
     if (!mbar_wait(b_bar, it & 1, p.status, ST_TIMEOUT_ACC_FULL)) ok = false;
     if (__syncthreads_or(!ok)) { ok = false; break; }
     tc_fence_after_sync();
     if (tid == 0 && c > 0) load_all(c - 1);
     if (full) {
-      float g[HD];
-      la_tmem_row<HD>(trow + COL_DV, g);
+      float g[HH];
+      la_tmem_row<HH>(trow + COL_DV + hf * HH, g);
       if (tok < p.S) {
-        __nv_bfloat16* vp = reinterpret_cast<__nv_bfloat16*>(p.dv.ptr) + (long long)b * p.dv.sb + (long long)tok * p.dv.ss + (long long)h * p.dv.sh;
+        __nv_bfloat16* vp = reinterpret_cast<__nv_bfloat16*>(p.dv.ptr) + (long long)b * p.dv.sb + (long long)tok * p.dv.ss + (long long)h * p.dv.sh + hf * HH;
 #pragma unroll
-        for (int i = 0; i < HD; i += 8)
+        for (int i = 0; i < HH; i += 8)
           *reinterpret_cast<uint4*>(vp + i) = make_uint4(pack_bf16x2(g[i], g[i + 1]), pack_bf16x2(g[i + 2], g[i + 3]),
                                                          pack_bf16x2(g[i + 4], g[i + 5]), pack_bf16x2(g[i + 6], g[i + 7]));
       }
-      la_tmem_row<HD>(trow + COL_DK, g);
+      la_tmem_row<HH>(trow + COL_DK + hf * HH, g);
       if (tok < p.S) {
 #pragma unroll
-        for (int i = 0; i < HD; ++i) g[i] += sdz[i];                                   // dz of the chunks after this one
-        la_store_dphi<HD>(p.k, p.dk, b, h, tok, g, p.scale, p.kind);
+        for (int i = 0; i < HH; ++i) g[i] += sdz[hf * HH + i];                         // dz of the chunks after this one
+        la_store_dphi_half<HD>(p.k, p.dk, b, h, tok, hf, g, p.scale, p.kind);
       }
     }
     __syncthreads();                                                                  // every thread has read the old dz
-    if (tid < HD) sdz[tid] += dzk;
-    if (full && c > 0) {
-      float srow[HD];
-      la_tmem_row<HD>(trow + COL_DS, srow);
-      if (tid < HD) la_write_hilo<HD>(sDhi, sDlo, HD, tid, srow);
+    if (tid < HD) {
+      float dzk = 0.f;
+#pragma unroll
+      for (int g = 0; g < ZP; ++g) dzk += s_zk[g * HD + tid];
+      sdz[tid] += dzk;
+    }
+    if (full && c > 0 && quad * 32 < HD) {
+      float srow[HH];
+      la_tmem_row<HH>(trow + COL_DS + hf * HH, srow);
+      if (row < HD) la_write_hilo_half<HD>(sDhi, sDlo, HD, row, hf, srow);
       fence_proxy_async_smem();
     }
     tc_fence_before_sync();
     __syncthreads();
   }
   float* ds_out = la_publish_begin<HD>(p, bh, sx_epoch, p.ds_out);
-  if (ok && ds_out) {
+  if (ok && ds_out && hf == 0) {
     tc_fence_after_sync();
     float srow[HD];
     la_tmem_row<HD>(trow + COL_DS, srow);
-    if (tid < HD) {
+    if (row < HD) {
 #pragma unroll
       for (int i = 0; i < HD; i += 4)
-        *reinterpret_cast<float4*>(ds_out + bh * st_stride + (size_t)tid * HD + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
-      ds_out[bh * st_stride + (size_t)HD * HD + tid] = sdz[tid];
+        *reinterpret_cast<float4*>(ds_out + bh * st_stride + (size_t)row * HD + i) = make_float4(srow[i], srow[i + 1], srow[i + 2], srow[i + 3]);
+      ds_out[bh * st_stride + (size_t)HD * HD + row] = sdz[row];
     }
   }
   la_publish_end(p, bh, sx_epoch);
@@ -1038,7 +1139,9 @@ linattn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 template <int HD> constexpr int la_fwd_smem() { return 4 * LaSmem<HD>::TILE + LaSmem<HD>::ZERO + LaSmem<HD>::PT + LaSmem<HD>::PLO + 2 * LaSmem<HD>::ST + HD * 4 + 128; }
 // the forward kernel also keeps [2][128] denominator shares and 256 partial column sums
 template <int HD> constexpr int la_fwd8_smem() { return la_fwd_smem<HD>() + 2 * LA_C * 4 + LA_FWD_THREADS * 4; }
-template <int HD> constexpr int la_dkv_smem() { return 4 * LaSmem<HD>::TILE + LaSmem<HD>::ZERO + LaSmem<HD>::PT + 2 * LaSmem<HD>::ST + (HD + LA_C) * 4 + 128; }
+// dQ: [2][128] dden shares (reused for the partial column sums) + [128] dden; dK / dV: the same shares beside its [128] dden
+template <int HD> constexpr int la_dq8_smem() { return la_fwd_smem<HD>() + 3 * LA_C * 4; }
+template <int HD> constexpr int la_dkv_smem() { return 4 * LaSmem<HD>::TILE + LaSmem<HD>::ZERO + LaSmem<HD>::PT + 2 * LaSmem<HD>::ST + (HD + LA_C) * 4 + 2 * LA_C * 4 + 128; }
 
 static int la_maps(const LinAttnArgs& a, CUtensorMap* tq, CUtensorMap* tk, CUtensorMap* tv) {
   const auto BF = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -1054,7 +1157,7 @@ static int la_set_attrs() {
   if (done) return 0;
   (void)cudaGetLastError();
   if (cudaFuncSetAttribute(linattn_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, la_fwd8_smem<HD>()) != cudaSuccess) return 1;
-  if (cudaFuncSetAttribute(linattn_bwd_dq_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, la_fwd_smem<HD>()) != cudaSuccess) return 1;
+  if (cudaFuncSetAttribute(linattn_bwd_dq_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, la_dq8_smem<HD>()) != cudaSuccess) return 1;
   if (cudaFuncSetAttribute(linattn_bwd_dkv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, la_dkv_smem<HD>()) != cudaSuccess) return 1;
   done = true;
   return 0;
@@ -1069,8 +1172,8 @@ static int la_launch(const LinAttnArgs& a, int which, cudaStream_t st) {
   if (!need_q) tq = tk;
   const unsigned grid = (unsigned)(a.B * a.H);
   if (which == 0) linattn_fwd_kernel<HD><<<grid, LA_FWD_THREADS, la_fwd8_smem<HD>(), st>>>(tq, tk, tv, a);
-  else if (which == 1) linattn_bwd_dq_kernel<HD><<<grid, 128, la_fwd_smem<HD>(), st>>>(tk, tv, a);
-  else linattn_bwd_dkv_kernel<HD><<<grid, 128, la_dkv_smem<HD>(), st>>>(tq, tk, tv, a);
+  else if (which == 1) linattn_bwd_dq_kernel<HD><<<grid, LA_FWD_THREADS, la_dq8_smem<HD>(), st>>>(tk, tv, a);
+  else linattn_bwd_dkv_kernel<HD><<<grid, LA_FWD_THREADS, la_dkv_smem<HD>(), st>>>(tq, tk, tv, a);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }

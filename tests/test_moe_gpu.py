@@ -95,8 +95,11 @@ def test_linear_attention_gpu(causal, kind):
     o = linear_attention(q, k, v, 0.5, 1e-6, causal, kind)
     qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
     r = linear_attention_ref(qr, kr, vr, 0.5, 1e-6, causal, kind)
-    assert rel_err(o, r) < 3e-2
+    assert rel_err(o, r) < 8e-3                         # measured 1.6e-3 .. 3.4e-3
     g = torch.randn_like(r)
     (o.float() * g).sum().backward(); (r * g).sum().backward()
-    for a, b in ((q, qr), (k, kr), (v, vr)):
-        assert rel_err(a.grad, b.grad) < 6e-2
+    # measured: dk, dv 3.4e-3 .. 4.5e-3 everywhere; dq 4e-3 .. 8.5e-3, and 2.0e-2 for the non-causal ELU + 1 form
+    # (bf16 features near 1 in a difference of nearly equal sums)
+    for name, a, b in (("dq", q, qr), ("dk", k, kr), ("dv", v, vr)):
+        tol = 3e-2 if (name == "dq" and kind == "elu") else 1e-2
+        assert rel_err(a.grad, b.grad) < tol, (name, rel_err(a.grad, b.grad))

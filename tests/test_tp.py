@@ -34,9 +34,13 @@ def test_fused_tp_and_ep_on_two_gpus():
         for nm in ("fwd", "dx", "dW1", "db1", "dW2", "db2"):                      # sharded MLP with autograd vs fp32 unsharded
             assert r[f"tpmlp_{nm}_rel_err"] < 3e-2, (nm, r[f"tpmlp_{nm}_rel_err"])
         for tag in ("causal", "full"):
-            # against the fp32 oracle the sequence-sharded run is as accurate as the unsharded bf16 run
+            # against the fp32 oracle: absolute bounds (the causal form runs on the fused kernels with the exchange inside
+            # them), and the sequence-sharded run is as accurate as the unsharded bf16 run
             for nm in ("fwd", "dq", "dk", "dv"):
-                assert r[f"sp_{tag}_{nm}_rel_err"] < 1.5 * r[f"ref_{tag}_{nm}_rel_err"] + 1e-2, (tag, nm, r)
+                # dq of the non-causal form: composed bf16 GEMMs with a bf16 global state, 7 % at these sizes
+                bound = 1e-2 if nm == "fwd" else ((5e-2 if tag == "causal" else 1e-1) if nm == "dq" else 1.5e-2)
+                assert r[f"sp_{tag}_{nm}_rel_err"] < bound, (tag, nm, r[f"sp_{tag}_{nm}_rel_err"])
+                assert r[f"sp_{tag}_{nm}_rel_err"] < 1.5 * r[f"ref_{tag}_{nm}_rel_err"] + 5e-3, (tag, nm, r)
 
 
 def _cpu_tp_rank(rank, world, port, q):

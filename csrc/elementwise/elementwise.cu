@@ -295,11 +295,13 @@ dact_colsum_kernel(__nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restric
 // batched column sum: out[z, c] += sum_r x[z, r, c]  (per-expert bias gradients)
 template <typename T>
 __global__ void colsum_batched_kernel(const T* __restrict__ x, float* __restrict__ out, long long rows, int cols,
-                                      long long ld, long long bs) {
+                                      long long ld, long long bs, const int* __restrict__ rows_valid) {
   int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= cols) return;
   const T* xp = x + blockIdx.z * bs;
+  if (rows_valid) { const long long rv = ((long long)rows_valid[blockIdx.z] + 127) / 128 * 128; if (rv < rows) rows = rv; }   // ragged groups: whole 128-row tiles
   long long r0 = (long long)blockIdx.y * 256, r1 = r0 + 256; if (r1 > rows) r1 = rows;
+  if (r0 >= r1) return;
   float acc = 0.f;
   for (long long r = r0; r < r1; ++r) acc += to_f(xp[r * ld + c]);
   atomicAdd(out + (long long)blockIdx.z * cols + c, acc);
@@ -575,12 +577,13 @@ int b200_colsum(const void* x, float* out, long long rows, int cols, long long l
   return (int)cudaGetLastError();
 }
 
+// rows_valid (optional, device int [batch]): only the first rows_valid[z] rows, rounded up to 128, of batch z are summed
 int b200_colsum_batched(const void* x, float* out, int batch, long long rows, int cols, long long ld, long long bs,
-                        int is_bf16, cudaStream_t st) {
+                        int is_bf16, const int* rows_valid, cudaStream_t st) {
   if (rows <= 0 || cols <= 0 || batch <= 0) return 0;
   dim3 grid((cols + 127) / 128, (unsigned)((rows + 255) / 256), batch);
-  if (is_bf16) colsum_batched_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, out, rows, cols, ld, bs);
-  else colsum_batched_kernel<float><<<grid, 128, 0, st>>>((const float*)x, out, rows, cols, ld, bs);
+  if (is_bf16) colsum_batched_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, out, rows, cols, ld, bs, rows_valid);
+  else colsum_batched_kernel<float><<<grid, 128, 0, st>>>((const float*)x, out, rows, cols, ld, bs, rows_valid);
   return (int)cudaGetLastError();
 }
 

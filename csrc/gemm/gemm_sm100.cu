@@ -270,6 +270,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
   const int n_blocks = (p.N + BN - 1) / BN;
   const int num_kb = (p.K + BK - 1) / BK;
   const int kb_per_split = (num_kb + p.splits - 1) / p.splits;
+  // ragged groups: is the row tile of batch `bb` in use, and where does its K loop end
+  auto tile_skipped = [&](int bb, int mb_) -> bool { return p.m_valid != nullptr && mb_ * (BM * CG) >= __ldg(p.m_valid + bb); };
+  auto kb_end = [&](int bb) -> int {
+    if (p.k_valid == nullptr) return num_kb;
+    const int kv = min(p.K, ((__ldg(p.k_valid + bb) + 127) / 128) * 128);
+    return (kv + BK - 1) / BK;
+  };
   const long long tiles_per_batch = (long long)m_blocks * n_blocks * p.splits;
   const long long total_tiles = tiles_per_batch * p.batch;
   // TP_AG_GEMM reserves the first `copy_ctas` CTAs for pulling remote shards; the rest run the GEMM
@@ -353,8 +360,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         const int split = (int)(r / ((long long)m_blocks * n_blocks));
         r %= (long long)m_blocks * n_blocks;
         const int mb = ((int)(r / n_blocks) + tp_shift) % m_blocks, nb = (int)(r % n_blocks);
+        if (tile_skipped(b, mb)) continue;
         const int kb0 = split * kb_per_split;
-        const int kb1 = min(kb0 + kb_per_split, num_kb);
+        const int kb1 = min(kb0 + kb_per_split, kb_end(b));
         if constexpr (TP == TP_AG_GEMM) {
           // rows of another rank: wait until the gather CTAs have landed this row block
           if (mb / tpp->blocks_per_rank != tpp->rank) {
@@ -419,12 +427,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
       constexpr uint32_t A_KADV = A_MN ? UMMA_K * TILE_K_BYTES : UMMA_K_BYTES;
       constexpr uint32_t B_KADV = B_MN ? UMMA_K * TILE_K_BYTES : UMMA_K_BYTES;
       int stage = 0; uint32_t phase = 0; bool ok = true;
-      int it = 0;
-      for (long long t = cta; t < total_tiles && ok; t += n_ctas, ++it) {
+      int it = 0;                                   // tiles this CTA really computes (skipped ones use no accumulator)
+      for (long long t = cta; t < total_tiles && ok; t += n_ctas) {
+        const int b = (int)(t / tiles_per_batch);
         long long r = t % tiles_per_batch;
         const int split = (int)(r / ((long long)m_blocks * n_blocks));
+        r %= (long long)m_blocks * n_blocks;
+        if (tile_skipped(b, ((int)(r / n_blocks) + tp_shift) % m_blocks)) continue;
         const int kb0 = split * kb_per_split;
-        const int kb1 = min(kb0 + kb_per_split, num_kb);
+        const int kb1 = min(kb0 + kb_per_split, kb_end(b));
         const int as = it & 1;
         const uint32_t aphase = (it >> 1) & 1;
         if (!mbar_wait(&acc_empty[as], aphase ^ 1, p.status, ST_TIMEOUT_ACC_EMPTY)) { ok = false; break; }
@@ -462,6 +473,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
             tc_commit(&acc_full[as]);
           }
         }
+        ++it;
       }
     }
   } else {
@@ -478,14 +490,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
     const bool tma_out = staged && PW == 64 && TP != TP_GEMM_RS && om != nullptr && om->use;   // ... through the TMA engine
     bool ok = true;
     int it = 0;
-    for (long long t = cta; t < total_tiles && ok; t += n_ctas, ++it) {
+    for (long long t = cta; t < total_tiles && ok; t += n_ctas) {
       const int b = (int)(t / tiles_per_batch);
       long long r = t % tiles_per_batch;
       const int split = (int)(r / ((long long)m_blocks * n_blocks));
       r %= (long long)m_blocks * n_blocks;
       const int mb = ((int)(r / n_blocks) + tp_shift) % m_blocks, nb = (int)(r % n_blocks);
+      if (tile_skipped(b, mb)) continue;
       const int kb0 = split * kb_per_split;
-      const bool has_k = kb0 < min(kb0 + kb_per_split, num_kb);
+      const bool has_k = kb0 < min(kb0 + kb_per_split, kb_end(b));
       const int as = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
       if (!mbar_wait(&acc_full[as], aphase, p.status, ST_TIMEOUT_ACC_FULL)) { ok = false; break; }
@@ -667,6 +680,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         if constexpr (CG == 2) mbar_arrive_cluster(cluster_map(smem_u32(&acc_empty[as]), 0));
         else mbar_arrive(&acc_empty[as]);
       }
+      ++it;
     }
     if (tma_out && lane == 0) tma_store_wait0();          // this warp's last stores have left shared memory and landed
   }

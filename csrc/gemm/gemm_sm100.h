@@ -26,6 +26,9 @@ struct GemmParams {
   const float* row_scale;  // 8-bit kinds: fp32 dequantisation scale per row of A ([batch*M]) or null
   const float* col_scale;  // 8-bit kinds: fp32 dequantisation scale per column (row of B, [N]) or null
   uint32_t* status;        // device word, receives a non-zero code on a bounded-wait expiry
+  // Grouped (batched) products over ragged groups, e.g. the tokens routed to each expert: device arrays [batch] or null.
+  const int* m_valid;      // rows of A (and C) in use per batch: row tiles wholly past it are skipped (their C rows are not written)
+  const int* k_valid;      // contraction length in use per batch, rounded up to 128: the K loop stops there
 };
 
 // Tensor-parallel extension: the GEMM fused with the collective next to it, over NVLink peer memory.

@@ -28,6 +28,7 @@ class GemmParams(C.Structure):
         ("vec_ok", c_int), ("res_vec_ok", c_int),
         ("row_scale", c_void_p), ("col_scale", c_void_p),
         ("status", c_void_p),
+        ("m_valid", c_void_p), ("k_valid", c_void_p),
     ]
 
 
@@ -65,7 +66,7 @@ _SIGS = {
     "b200_transpose": [c_void_p, c_void_p, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_int, c_int, c_void_p],
     "b200_colsum": [c_void_p, c_void_p, c_ll, c_int, c_ll, c_int, c_void_p],
     "b200_dact_colsum": [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_ll, c_ll, c_int, c_void_p],
-    "b200_colsum_batched": [c_void_p, c_void_p, c_int, c_ll, c_int, c_ll, c_ll, c_int, c_void_p],
+    "b200_colsum_batched": [c_void_p, c_void_p, c_int, c_ll, c_int, c_ll, c_ll, c_int, c_void_p, c_void_p],
     "b200_reduce": [c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p],
     "b200_dropout": [c_void_p, c_void_p, c_ll, c_float, c_ull, c_int, c_void_p],
     "b200_softmax_fwd": [c_void_p, c_void_p, c_ll, c_int, c_float, c_int, c_int, c_void_p],

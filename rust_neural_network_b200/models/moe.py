@@ -203,8 +203,11 @@ class MoEExpertsFn(Function):
         ep.barrier(dev)                                           # all remote rows have landed
         xb = xbuf.view(E_local, cap, d)
         W1l, W2l = F.lp(W1), F.lp(W2)
-        h, pre = gemm(xb, W1l, bias=b1.detach() if b1 is not None else None, act=act, want_aux=True)        # [E, cap, hid]
-        y = gemm(h, W2l, bias=b2.detach() if b2 is not None else None, out=ybuf.view(E_local, cap, d))       # [E, cap, d], in the peers' reach
+        # rows in use per local expert: the expert GEMMs skip the 128-row tiles past them (the capacity padding costs
+        # nothing), and nothing downstream reads the rows they leave unwritten
+        counts = fill[:E_local].clamp(max=cap) if x.is_cuda else None
+        h, pre = gemm(xb, W1l, bias=b1.detach() if b1 is not None else None, act=act, want_aux=True, m_valid=counts)   # [E, cap, hid]
+        y = gemm(h, W2l, bias=b2.detach() if b2 is not None else None, out=ybuf.view(E_local, cap, d), m_valid=counts)  # [E, cap, d], in the peers' reach
         xsave = xb.clone()
         ep.barrier(dev)                                           # every rank's expert outputs are in place
         out = torch.empty((T, d), dtype=torch.bfloat16, device=dev)
@@ -214,13 +217,14 @@ class MoEExpertsFn(Function):
         nv.count_launch(2)
         xbuf.zero_(); fill.zero_()
         ep.barrier(dev)                                           # peers have read my outputs; everyone's input buffers are clear
-        ctx.save_for_backward(dest, wc, xsave, h, pre, W1, b1, W2, b2)
+        ctx.save_for_backward(dest, wc, xsave, h, pre, W1, b1, W2, b2, counts if counts is not None else torch.empty(0))
         ctx.cfg = (act, cap, ep, T, d, k, E_local, hid)
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        dest, wc, xb, h, pre, W1, b1, W2, b2 = ctx.saved_tensors
+        dest, wc, xb, h, pre, W1, b1, W2, b2, counts = ctx.saved_tensors
+        counts = counts if counts.numel() else None
         act, cap, ep, T, d, k, E_local, hid = ctx.cfg
         world, rows, dev = ep.world, E_local * cap, dout.device
         lib = nv.cuda()
@@ -228,7 +232,7 @@ class MoEExpertsFn(Function):
         dybuf, dyptrs = ep.buffer("dy", rows * d, torch.bfloat16, dev)
         dxbuf, dxptrs = ep.buffer("dx", rows * d, torch.bfloat16, dev)
         # the expert outputs are needed once more (d of the gate weights): recomputed from h straight into the shared buffer
-        gemm(h, F.lp(W2), bias=b2.detach() if b2 is not None else None, out=ybuf.view(E_local, cap, d))
+        gemm(h, F.lp(W2), bias=b2.detach() if b2 is not None else None, out=ybuf.view(E_local, cap, d), m_valid=counts)
         ep.barrier(dev)
         dw = torch.empty((T, k), dtype=torch.float32, device=dev)
         dc = dout.contiguous()
@@ -237,17 +241,17 @@ class MoEExpertsFn(Function):
         ep.barrier(dev)
         dy = dybuf.view(E_local, cap, d)
         W1l, W2l = F.lp(W1), F.lp(W2)
-        dh = gemm(dy, W2l, b_mn=True, aux_in=pre, dact=act)                                   # [E, cap, hid]
-        dW2 = gemm(dy, h, a_mn=True, b_mn=True, out_dtype=torch.float32)                       # [E, d, hid]
-        dW1 = gemm(dh, xb, a_mn=True, b_mn=True, out_dtype=torch.float32)                      # [E, hid, d]
-        gemm(dh, W1l, b_mn=True, out=dxbuf.view(E_local, cap, d))                               # [E, cap, d], pulled by the token owners
+        dh = gemm(dy, W2l, b_mn=True, aux_in=pre, dact=act, m_valid=counts)                   # [E, cap, hid]
+        dW2 = gemm(dy, h, a_mn=True, b_mn=True, out_dtype=torch.float32, k_valid=counts)       # [E, d, hid]
+        dW1 = gemm(dh, xb, a_mn=True, b_mn=True, out_dtype=torch.float32, k_valid=counts)      # [E, hid, d]
+        gemm(dh, W1l, b_mn=True, out=dxbuf.view(E_local, cap, d), m_valid=counts)               # [E, cap, d], pulled by the token owners
         db1 = db2 = None
         if b1 is not None:
             db1 = torch.zeros((E_local, hid), dtype=torch.float32, device=dev)
-            nv.check(lib.b200_colsum_batched(dh.data_ptr(), db1.data_ptr(), E_local, cap, hid, hid, cap * hid, 1, nv.stream_ptr()), "colsum_batched")
+            nv.check(lib.b200_colsum_batched(dh.data_ptr(), db1.data_ptr(), E_local, cap, hid, hid, cap * hid, 1, nv.ptr(counts), nv.stream_ptr()), "colsum_batched")
         if b2 is not None:
             db2 = torch.zeros((E_local, d), dtype=torch.float32, device=dev)
-            nv.check(lib.b200_colsum_batched(dy.data_ptr(), db2.data_ptr(), E_local, cap, d, d, cap * d, 1, nv.stream_ptr()), "colsum_batched")
+            nv.check(lib.b200_colsum_batched(dy.data_ptr(), db2.data_ptr(), E_local, cap, d, d, cap * d, 1, nv.ptr(counts), nv.stream_ptr()), "colsum_batched")
         # adjoint of dispatch: pull the token gradients back from the owning ranks
         ep.barrier(dev)
         dx = torch.empty((T, d), dtype=torch.bfloat16, device=dev)

@@ -125,9 +125,12 @@ def _tma_ready(t: torch.Tensor) -> torch.Tensor:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias=None, act: str = "none",
          residual=None, aux_in=None, dact: str = "none", want_aux: bool = False, alpha: float = 1.0,
          out_dtype=None, accumulate_into=None, splits: int = 0, bn: int = 0, alpha_t=None, row_scale=None, col_scale=None,
-         out=None):
+         out=None, m_valid=None, k_valid=None):
     """See module docstring. Returns C (and the bf16 pre-activation when ``want_aux``). ``out`` (GPU only): write the
     result into this tensor ([M, N] or [batch, M, N], unit inner stride, dtype of the result) instead of a new one.
+    ``m_valid`` / ``k_valid`` (int32 [batch] on the device) make a batched product ragged, as the groups of tokens routed
+    to each expert are: row tiles of 128 wholly past ``m_valid[b]`` are skipped (those rows of the result are NOT
+    written), and the contraction stops at ``k_valid[b]`` rounded up to 128 (rows up to there must hold finite values).
 
     8-bit operands (int8 x int8, uint8 x int8, float8_e4m3fn x float8_e4m3fn; both K-major) run on the
     tensor cores' integer / fp8 kinds. ``row_scale`` ([M] or [batch, M] fp32) and ``col_scale`` ([N] fp32)
@@ -139,6 +142,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         r = gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, act=act, residual=residual, aux_in=aux_in, dact=dact,
                      alpha=alpha, out_dtype=out_dtype, accumulate_into=accumulate_into, want_aux=want_aux,
                      row_scale=row_scale, col_scale=col_scale)
+        # (m_valid / k_valid only skip work whose operands are zero or whose results are never read: nothing to do on CPU)
         if out is not None:
             out.copy_((r[0] if want_aux else r).reshape(out.shape))
             r = (out, r[1]) if want_aux else out
@@ -271,6 +275,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
             raise ValueError("col_scale needs one value per row of B")
     p.row_scale, p.col_scale = nv.ptr(row_scale), nv.ptr(col_scale)
     p.status = nv.status_word(dev).data_ptr()
+    for name, t in (("m_valid", m_valid), ("k_valid", k_valid)):
+        if t is not None and (t.dtype != torch.int32 or t.numel() != batch or not t.is_cuda):
+            raise ValueError(f"{name} must be an int32 device tensor with one entry per batch")
+    p.m_valid, p.k_valid = nv.ptr(m_valid), nv.ptr(k_valid)
     args.A, args.lda, args.strideA, args.a_mn = a3.data_ptr(), a3.stride(1), a3.stride(0), int(a_mn)
     args.B, args.ldb, args.strideB, args.b_mn = b3.data_ptr(), b3.stride(1), b3.stride(0), int(b_mn)
     args.M, args.N, args.K, args.batch, args.dtype = M, N, K, batch, kind

@@ -444,3 +444,36 @@ def test_layernorm_bwd_with_fused_column_sums(rows, d):
     assert torch.allclose(s_res - 1.0, dres.float().sum(0), rtol=1e-3, atol=2e-2)
     # the fused sum is taken before the bf16 rounding of dx, the reference after it
     assert torch.allclose(s_dx - 2.0, dx0.float().sum(0), rtol=1e-2, atol=0.5)
+
+
+def test_gemm_ragged_groups():
+    """Batched GEMM over ragged groups (the tokens routed to each expert): row tiles past `m_valid` are skipped, the K loop
+    of a weight-gradient product stops at `k_valid` rounded up to 128, and skipped tiles may hold anything."""
+    from rust_neural_network_b200 import _native as nv
+    torch.manual_seed(21)
+    E, cap, d, hid = 6, 640, 256, 384
+    counts = torch.tensor([640, 0, 130, 128, 511, 1], dtype=torch.int32, device=DEV)
+    x = torch.randn(E, cap, d, device=DEV).bfloat16()
+    for e in range(E):
+        x[e, int(counts[e]):] = 0                                   # rows past the count are zero, as a dispatch buffer is
+    w = torch.randn(E, hid, d, device=DEV).bfloat16()
+    bias = torch.randn(E, hid, device=DEV)
+    out = torch.full((E, cap, hid), float("nan"), device=DEV, dtype=torch.bfloat16)
+    G.gemm(x, w, bias=bias, act="silu", out=out, m_valid=counts)
+    ref = G.gemm_ref(x, w, bias=bias, act="silu", out_dtype=torch.float32)
+    for e in range(E):
+        n = int(counts[e]); tiles = (n + 127) // 128 * 128
+        assert rel_err(out[e, :tiles], ref[e, :tiles]) < 1e-2 or tiles == 0
+        assert bool(torch.isnan(out[e, tiles:]).all())              # skipped tiles were not touched
+    # weight gradient: dy^T h over the rows in use; rows past the computed tiles hold NaN on purpose
+    dy = torch.randn(E, cap, hid, device=DEV).bfloat16()
+    for e in range(E):
+        dy[e, int(counts[e]):] = 0
+    hbuf = out.clone()                                               # NaN in the skipped tiles
+    dW = G.gemm(dy, hbuf, a_mn=True, b_mn=True, out_dtype=torch.float32, k_valid=counts)       # [E, hid(dy cols), hid]
+    torch.cuda.synchronize(); nv.check_status()
+    assert bool(torch.isfinite(dW).all())
+    h_clean = torch.nan_to_num(hbuf.float(), nan=0.0)
+    refW = dy.float().transpose(1, 2) @ h_clean
+    assert rel_err(dW, refW) < 1e-2
+    assert float(dW[1].abs().max()) == 0.0                          # an empty group contributes nothing

@@ -164,6 +164,13 @@ struct OutMaps {
   int use;              // 0: plain stores (fp32 / int32 outputs, unaligned C, narrow tiles)
 };
 
+// GEMM -> reduce-scatter: one map per rank over ITS slot buffer [2 * world][rows_per_rank][N] (peer-mapped), so that a
+// panel crosses NVLink as one bulk store instead of 256 16-byte stores (no load, and nothing multicast, goes that way)
+struct PeerMaps {
+  CUtensorMap m[TP_MAX_WORLD];
+  int use;
+};
+
 // registers (row owner) -> bf16 panel in the 128-byte-swizzle layout -> one TMA store; rows and columns past the edge of
 // the tensor are clipped by the copy engine. The panel buffer is reused, so the previous store's read of it is awaited first.
 __device__ __forceinline__ void panel_store_tma(uint8_t* sbuf, int lane, const float (&f)[64], const CUtensorMap* tm, int col0, int row0, int b) {
@@ -238,9 +245,11 @@ __device__ __forceinline__ bool peer_handshake(const TpParams& tp, uint32_t epoc
   return ok;
 }
 
-template <typename T, int BN, bool A_MN, bool B_MN, int TP, int CG = 1>
+// KEEP_PERMIT: the kernel will allocate tensor memory again after this body (a fused kernel that runs two products):
+// the allocation permit is then not given up here (no allocation is legal after `relinquish_alloc_permit`).
+template <typename T, int BN, bool A_MN, bool B_MN, int TP, int CG = 1, bool KEEP_PERMIT = false>
 __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, const TpParams* tpp,
-                                          const OutMaps* om = nullptr) {
+                                          const OutMaps* om = nullptr, const PeerMaps* pm = nullptr) {
   using S = GemmSmem<T, BN, A_MN, B_MN, CG>;
   static_assert(CG == 1 || (CG == 2 && TP == TP_NONE && BN == 256), "CTA pairs: plain GEMM with 256-wide tiles only");
   constexpr int BNL = BN / CG;                          // rows of B this CTA stages
@@ -271,10 +280,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
   const int num_kb = (p.K + BK - 1) / BK;
   const int kb_per_split = (num_kb + p.splits - 1) / p.splits;
   // ragged groups: is the row tile of batch `bb` in use, and where does its K loop end
-  auto tile_skipped = [&](int bb, int mb_) -> bool { return p.m_valid != nullptr && mb_ * (BM * CG) >= __ldg(p.m_valid + bb); };
+  auto tile_skipped = [&](int bb, int mb_) -> bool { return p.m_valid != nullptr && mb_ * (BM * CG) >= *reinterpret_cast<volatile const int*>(p.m_valid + bb); };
   auto kb_end = [&](int bb) -> int {
     if (p.k_valid == nullptr) return num_kb;
-    const int kv = min(p.K, ((__ldg(p.k_valid + bb) + 127) / 128) * 128);
+    const int kv = min(p.K, ((*reinterpret_cast<volatile const int*>(p.k_valid + bb) + 127) / 128) * 128);
     return (kv + BK - 1) / BK;
   };
   const long long tiles_per_batch = (long long)m_blocks * n_blocks * p.splits;
@@ -298,7 +307,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
   if constexpr (CG == 2) cluster_sync_all();            // the partner's barriers exist before anything is counted on them
   if (warp == 1) {
     if constexpr (CG == 2) { tmem_alloc_pair(tmem_slot, TMEM_COLS); tmem_relinquish_pair(); }
-    else { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+    else { tmem_alloc(tmem_slot, TMEM_COLS); if constexpr (!KEEP_PERMIT) tmem_relinquish(); }
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -312,6 +321,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
     // peer's staging buffer - posted NVLink stores, 8 x 16 bytes in flight per thread - followed by a
     // release of the row block's flag AT THE PEER.
     const TpParams& tp = *tpp;
+    uint32_t mover_phase = 0;
     const long long row_bytes = (long long)p.K * 2;                      // bf16 rows, K % 8 == 0
     const long long blk_vec = (long long)BM * row_bytes / 16;            // 16-byte vectors per row block
     constexpr int UNROLL = 8;
@@ -319,6 +329,51 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
     // shrinks when there are fewer row blocks than 4 per gather CTA, so that every gather CTA has work
     const int GROUP = max(1, min(4, tp.blocks_per_rank / max(n_copy, 1)));
     const int n_groups = (tp.blocks_per_rank + GROUP - 1) / GROUP;
+    const bool bulk = pm != nullptr && (pm->use & 2) != 0;
+    if (bulk) {
+      // Bulk movers: lane 0 of each of the first MOVERS warps owns one 32 KB buffer of this CTA's (otherwise idle) stage
+      // memory and runs load (local staging -> shared) / store (shared -> every peer's staging) chains through the copy
+      // engine: no registers in the data path and ~200 KB in flight per CTA.
+      constexpr int MOVERS = STAGES < 6 ? STAGES : 6, CH = 32 * 1024;       // one load barrier and (at least) 32 KB of stage memory each
+      for (int jg = (int)blockIdx.x; jg < n_groups; jg += n_copy) {
+        const int j0 = jg * GROUP;
+        const int nblk = min(GROUP, tp.blocks_per_rank - j0);
+        const int mbg = tp.rank * tp.blocks_per_rank + j0;
+        const long long boff = (long long)mbg * BM * row_bytes;
+        const long long grp_bytes = (long long)nblk * BM * row_bytes;        // multiple of 16
+        if (lane == 0 && warp < MOVERS) {
+          uint8_t* buf = smem + warp * CH;
+          uint64_t* bar = &full_bar[warp];
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(tp.stage_peer[tp.rank]) + boff;
+          bool okm = true;
+          for (long long off = (long long)warp * CH; off < grp_bytes && okm; off += (long long)MOVERS * CH) {
+            const uint32_t n = (uint32_t)min((long long)CH, grp_bytes - off);
+            mbar_expect_tx(bar, n);
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_u32(buf)), "l"(reinterpret_cast<uint64_t>(src + off)), "r"(n), "r"(smem_u32(bar)) : "memory");
+            okm = mbar_wait(bar, mover_phase, p.status, ST_TIMEOUT_TMA_FULL);
+            mover_phase ^= 1;
+            if (!okm) break;
+            for (int rr = 1; rr < tp.world; ++rr) {
+              const int peer = (tp.rank + rr) % tp.world;                    // stagger the peers
+              uint8_t* dst = reinterpret_cast<uint8_t*>(tp.stage_peer[peer]) + boff + off;
+              asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                           ::"l"(reinterpret_cast<uint64_t>(dst)), "r"(smem_u32(buf)), "r"(n) : "memory");
+            }
+            tma_store_commit();
+            tma_store_wait_read0();                                          // the buffer may be refilled
+          }
+          tma_store_wait0();                                                 // this mover's stores have landed
+          fence_proxy_async_all();
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0)
+          for (int rr = 1; rr < tp.world; ++rr)
+            for (int q = 0; q < nblk; ++q) st_release_sys_u32(tp.ready_peer[(tp.rank + rr) % tp.world] + mbg + q, tp_epoch);
+        __syncthreads();
+      }
+    } else
     for (int jg = (int)blockIdx.x; jg < n_groups; jg += n_copy) {
       const int j0 = jg * GROUP;
       const int nblk = min(GROUP, tp.blocks_per_rank - j0);
@@ -488,6 +543,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
     const float alpha = p.alpha_ptr ? p.alpha * __ldg(p.alpha_ptr) : p.alpha;
     const bool staged = (p.out_mode == OUT_BF16) && p.vec_ok;       // coalesced bf16 path
     const bool tma_out = staged && PW == 64 && TP != TP_GEMM_RS && om != nullptr && om->use;   // ... through the TMA engine
+    const bool rs_tma = staged && PW == 64 && TP == TP_GEMM_RS && pm != nullptr && pm->use;    // partial tiles to their owners, ditto
     bool ok = true;
     int it = 0;
     for (long long t = cta; t < total_tiles && ok; t += n_ctas) {
@@ -645,8 +701,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
           }
           if constexpr (PW == 64) {
             if (tma_out) panel_store_tma(sbuf, lane, f, &om->c, col0, row0, b);
+            if constexpr (TP == TP_GEMM_RS) {
+              if (rs_tma) {
+                const TpParams& tp = *tpp;
+                const int owner = mb / tp.blocks_per_rank;
+                panel_store_tma(sbuf, lane, f, &pm->m[owner], col0, row0 - owner * tp.blocks_per_rank * BM, (int)(tp_epoch & 1u) * tp.world + tp.rank);
+              }
+            }
           }
-          if (tma_out) {}
+          if (tma_out || rs_tma) {}
           else if (staged) panel_store<PW>(sbuf, lane, f, cp, p.ldc, rows_valid, chunks_valid);
           else if (row_ok) {
 #pragma unroll
@@ -682,7 +745,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
       }
       ++it;
     }
-    if (tma_out && lane == 0) tma_store_wait0();          // this warp's last stores have left shared memory and landed
+    if ((tma_out || rs_tma) && lane == 0) {               // this warp's last stores have left shared memory and landed
+      tma_store_wait0();
+      if (rs_tma) { fence_proxy_async_all(); __threadfence_system(); }
+    }
   }
 
   tc_fence_before_sync();
@@ -693,6 +759,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
     if constexpr (CG == 2) tmem_dealloc_pair(tmem_base, TMEM_COLS);
     else tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (threadIdx.x == 0) {                               // a kernel may run this body again (fused expert layer): leave no live barrier behind
+    for (int i = 0; i < 2 * STAGES + 4; ++i) mbar_inval(&bars[i]);
+  }
+  __syncthreads();
   if constexpr (TP == TP_AG_GEMM) {
     // The last CTA of the grid tells every peer "my GEMM no longer reads my staging buffer" and waits for the
     // same from them: when this kernel ends, the next call may push into any peer's staging buffer.
@@ -764,12 +834,136 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   gemm_body<__nv_bfloat16, 256, A_MN, B_MN, TP_NONE, 2>(tmA, tmB, p, nullptr, &om);
 }
 
+// ---------------------------------------------------------------------------- expert-parallel MoE layer, forward, ONE kernel
+// dispatch (token rows stored into the owning rank's expert buffers over NVLink, slots claimed with remote atomics)
+// -> cross-rank barrier -> grouped GEMM 1 (+bias, activation, saved pre-activation) over the real per-expert counts
+// -> grid barrier -> grouped GEMM 2 into the peer-visible output buffer -> cross-rank barrier -> combine (weighted sum of
+// the k expert rows of every token, read from the owners over NVLink) while the input buffer is saved for the backward
+// and cleared -> cross-rank barrier. One persistent launch of one CTA per SM: the barriers inside it need every CTA
+// resident. No host synchronisation, no NCCL; every wait is bounded by a clock budget and reports through the status word.
+constexpr int MOEF_MAX_RANKS = 8;
+struct MoeFusedArgs {
+  const __nv_bfloat16* x; const int* idx; int* dest;        // [T, d], [T, k] expert ids, [T, k] global row ids (out)
+  void* xbuf[MOEF_MAX_RANKS]; int* fill[MOEF_MAX_RANKS];     // every rank's expert input buffer [E_local, cap, d] and slot counters [E_local]
+  const void* ybuf[MOEF_MAX_RANKS];                          // every rank's expert output buffer [E_local, cap, d]
+  uint32_t* bar_flags[MOEF_MAX_RANKS];                       // cross-rank barrier flags (shared with the barrier kernel of the backward)
+  uint32_t* bar_words;                                       // local: [0] cross-rank barriers passed so far
+  uint32_t* sync;                                            // local: [0] CTA arrivals, [1] barrier generation
+  const float* w; __nv_bfloat16* out;                        // [T, k] gate weights, [T, d] result
+  __nv_bfloat16* xsave;                                      // copy of this rank's expert inputs for the weight gradient
+  int* counts_out;                                           // [E_local] rows in use per local expert (for the backward)
+  long long tokens, rows_per_rank, wait_cycles;
+  int k, d, E_local, cap, rank, world;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ void moef_barrier(const MoeFusedArgs& a, uint32_t gen, uint32_t epoch, bool cross) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();                                  // this CTA's stores, peer stores included, are out
+    const uint32_t old = atomicAdd(a.sync, 1u);
+    if (old % gridDim.x == gridDim.x - 1) {                  // the last CTA to arrive speaks for the rank
+      if (cross && a.world > 1) {
+        for (int r = 0; r < a.world; ++r) st_release_sys_u32(a.bar_flags[r] + a.rank, epoch);
+        for (int r = 0; r < a.world; ++r)
+          if (!wait_flag<true>(a.bar_flags[a.rank] + r, epoch, a.wait_cycles, a.status, ST_TIMEOUT_PEER_FLAG)) break;
+      }
+      if (cross) { __threadfence_system(); a.bar_words[0] = epoch; }
+      __threadfence();
+      st_release_gpu_u32(a.sync + 1, gen);
+    }
+    wait_flag<false>(a.sync + 1, gen, 2 * a.wait_cycles, a.status, ST_TIMEOUT_GENERIC);
+    __threadfence();
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+moe_fused_fwd_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ GemmParams p1,
+                     const __grid_constant__ OutMaps om1, const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
+                     const __grid_constant__ GemmParams p2, const __grid_constant__ OutMaps om2, const __grid_constant__ MoeFusedArgs a) {
+  const uint32_t gen0 = *reinterpret_cast<volatile const uint32_t*>(a.sync + 1);
+  const uint32_t ep0 = *reinterpret_cast<volatile const uint32_t*>(a.bar_words);
+  const int lane = threadIdx.x & 31;
+  const long long warp_g = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const long long row_vec = a.d / 8;                         // 16-byte vectors per row
+  // ---- dispatch: one warp per (token, choice)
+  for (long long wid = warp_g; wid < a.tokens * a.k; wid += n_warps) {
+    const long long t = wid / a.k;
+    const int e = a.idx[wid];
+    const int owner = e / a.E_local, el = e % a.E_local;
+    int slot = 0;
+    if (lane == 0) slot = atomicAdd_system(a.fill[owner] + el, 1);
+    slot = __shfl_sync(0xffffffffu, slot, 0);
+    if (slot >= a.cap) { if (lane == 0) a.dest[wid] = -1; continue; }
+    if (lane == 0) a.dest[wid] = (owner * a.E_local + el) * a.cap + slot;
+    const uint4* src = reinterpret_cast<const uint4*>(a.x + t * a.d);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.xbuf[owner]) + ((long long)el * a.cap + slot) * a.d);
+    for (long long i = lane; i < row_vec; i += 32) dst[i] = src[i];
+  }
+  moef_barrier(a, gen0 + 1, ep0 + 1, true);                  // every rank's rows and slot counts have landed
+  fence_proxy_async_all();                                   // ... and are visible to the TMA loads below
+  gemm_body<__nv_bfloat16, 256, false, false, TP_NONE, 1, true>(tmA1, tmB1, p1, nullptr, &om1);
+  moef_barrier(a, gen0 + 2, 0u, false);                      // all of h is written
+  fence_proxy_async_all();
+  gemm_body<__nv_bfloat16, 256, false, false, TP_NONE, 1>(tmA2, tmB2, p2, nullptr, &om2);
+  moef_barrier(a, gen0 + 3, ep0 + 2, true);                  // every rank's expert outputs are in place
+  // ---- combine: one warp per token; rows may live on a peer
+  for (long long t = warp_g; t < a.tokens; t += n_warps) {
+    for (long long c = lane; c < row_vec; c += 32) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int j = 0; j < a.k; ++j) {
+        const int r = a.dest[t * a.k + j];
+        if (r < 0) continue;
+        const float wj = a.w[t * a.k + j];
+        const int owner = (int)(r / a.rows_per_rank);
+        const long long lr = r % a.rows_per_rank;
+        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.ybuf[owner]) + lr * a.d) + c);
+        const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { const float2 f = __bfloat1622float2(hh[q]); acc[2 * q] += wj * f.x; acc[2 * q + 1] += wj * f.y; }
+      }
+      uint4 o;
+      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) oh[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+      *(reinterpret_cast<uint4*>(a.out + t * a.d) + c) = o;
+    }
+  }
+  // ---- keep the expert inputs for the weight gradient and clear the buffer for the next layer (rows in use, rounded up to
+  //      the 128-row tiles the backward's K loop covers; rows past a count are zero already and are saved as zeros)
+  {
+    uint4* xb = reinterpret_cast<uint4*>(a.xbuf[a.rank]);
+    uint4* xs = reinterpret_cast<uint4*>(a.xsave);
+    const int* fill = a.fill[a.rank];
+    const long long total_rows = (long long)a.E_local * a.cap;
+    for (long long row = warp_g; row < total_rows; row += n_warps) {
+      const int e = (int)(row / a.cap), r = (int)(row % a.cap);
+      const int cnt = min(*reinterpret_cast<volatile const int*>(fill + e), a.cap);
+      if (r >= (cnt + 127) / 128 * 128) continue;
+      for (long long i = lane; i < row_vec; i += 32) {
+        const uint4 v = xb[row * row_vec + i];
+        if (xs) xs[row * row_vec + i] = v;
+        xb[row * row_vec + i] = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  }
+  moef_barrier(a, gen0 + 4, 0u, false);                      // every CTA has read the slot counts
+  if (blockIdx.x == 0)
+    for (int e = threadIdx.x; e < a.E_local; e += blockDim.x) {
+      int* f = a.fill[a.rank] + e;
+      a.counts_out[e] = min(*reinterpret_cast<volatile int*>(f), a.cap);
+      *f = 0;
+    }
+  moef_barrier(a, gen0 + 5, ep0 + 3, true);                  // peers have read my outputs; everyone's input buffers are clear
+}
+
 // bf16, K-major x K-major (the Linear forward layout) fused with its neighbouring collective
 template <int BN, int TP>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ GemmParams p,
-               const __grid_constant__ TpParams tp) {
-  gemm_body<__nv_bfloat16, BN, false, false, TP>(tmA, tmB, p, &tp);
+               const __grid_constant__ TpParams tp, const __grid_constant__ PeerMaps pm) {
+  gemm_body<__nv_bfloat16, BN, false, false, TP>(tmA, tmB, p, &tp, nullptr, &pm);
 }
 
 // ---------------------------------------------------------------------------- host side
@@ -913,7 +1107,27 @@ static int launch_tp(const GemmArgs& a, const TpParams& tp, cudaStream_t stream,
   // every CTA must be resident at once (CTAs wait on one another): one CTA per SM, grid <= SM count
   int grid = num_sms;
   if (TP == TP_AG_GEMM && grid - tp.copy_ctas < 1) return -6;
-  gemm_tp_kernel<BN, TP><<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, a.p, tp);
+  PeerMaps pm;
+  pm.use = 0;
+  for (int r = 0; r < TP_MAX_WORLD; ++r) pm.m[r] = tmA;
+  if (TP == TP_AG_GEMM) {
+    static int tp_bulk = -1;
+    if (tp_bulk < 0) { const char* e = getenv("B200NN_TP_BULK_GATHER"); tp_bulk = (e && e[0] == '0') ? 0 : 1; }
+    if (tp_bulk && S::STAGE_BYTES >= 32 * 1024) pm.use = 2;
+  }
+  if (TP == TP_GEMM_RS && BN >= 128) {
+    static int tp_tma = -1;
+    if (tp_tma < 0) { const char* e = getenv("B200NN_TP_TMA_STORE"); tp_tma = (e && e[0] == '0') ? 0 : 1; }
+    const unsigned long long rows_per_rank = (unsigned long long)tp.blocks_per_rank * BM, nb = (unsigned long long)a.p.N * 2;
+    if (tp_tma && a.p.N % 8 == 0) {
+      pm.use = 1;
+      for (int r = 0; r < tp.world; ++r)
+        if ((reinterpret_cast<uintptr_t>(tp.slots_peer[r]) & 15) ||
+            make_tmap_3d(&pm.m[r], tp.slots_peer[r], DT<T>::v, sizeof(T), a.p.N, rows_per_rank, 2ull * tp.world, nb, rows_per_rank * nb, 64, 32,
+                         CU_TENSOR_MAP_SWIZZLE_128B)) { pm.use = 0; break; }
+    }
+  }
+  gemm_tp_kernel<BN, TP><<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, a.p, tp, pm);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }
@@ -1010,3 +1224,37 @@ extern "C" int b200_gemm_tp_launch(const b200::GemmArgs* args, const b200::TpPar
   return -2;
 }
 
+// One launch for the forward of an expert-parallel MoE layer (see moe_fused_fwd_kernel). g1 / g2 describe the two grouped
+// GEMMs exactly as b200_gemm_launch would take them (bf16, both operands K-major, 256-wide tiles, no split-K, batch =
+// local experts, m_valid = this rank's slot counters).
+extern "C" int b200_moe_fused_fwd(const b200::GemmArgs* g1, const b200::GemmArgs* g2, const b200::MoeFusedArgs* fa, int num_sms, cudaStream_t stream) {
+  using namespace b200;
+  using T = __nv_bfloat16;
+  using S = GemmSmem<T, 256, false, false>;
+  constexpr int BK = S::BK, BN = 256;
+  if (fa->world < 1 || fa->world > MOEF_MAX_RANKS || fa->d % 8) return -1;
+  const GemmArgs* gs[2] = {g1, g2};
+  CUtensorMap tmA[2], tmB[2];
+  OutMaps om[2];
+  for (int i = 0; i < 2; ++i) {
+    const GemmArgs& a = *gs[i];
+    if (a.dtype != GEMM_BF16 || a.a_mn || a.b_mn || a.p.splits != 1 || a.p.out_mode != OUT_BF16) return -3;
+    int rc = make_tmap_3d(&tmA[i], a.A, DT<T>::v, sizeof(T), a.K, a.M, a.batch, a.lda * sizeof(T), a.strideA * sizeof(T), BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return 100 + rc;
+    rc = make_tmap_3d(&tmB[i], a.B, DT<T>::v, sizeof(T), a.K, a.N, a.batch, a.ldb * sizeof(T), a.strideB * sizeof(T), BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return 200 + rc;
+    om[i].c = tmA[i]; om[i].aux = tmA[i];
+    make_out_maps(om[i], a.p, BN);
+  }
+  static bool attr_done = false;
+  if (!attr_done) {
+    (void)cudaGetLastError();
+    cudaError_t e = cudaFuncSetAttribute(moe_fused_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) return 300 + (int)e;
+    attr_done = true;
+  }
+  // every CTA must be resident at once (CTAs wait on one another): one CTA per SM, grid = SM count, the same for every launch
+  moe_fused_fwd_kernel<<<num_sms, GEMM_THREADS, S::TOTAL, stream>>>(tmA[0], tmB[0], g1->p, om[0], tmA[1], tmB[1], g2->p, om[1], *fa);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}

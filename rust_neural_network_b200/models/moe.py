@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 from typing import List, Optional
 
 import torch
@@ -145,6 +146,30 @@ class EPContext:
         e = self._bufs[k]
         return e[0], e[1]
 
+    def _barrier_state(self, device):
+        """(flag addresses on every rank, local epoch words, wait budget in cycles) of the device-side barrier; one set per
+        context, shared by the barrier kernel and by the barriers inside the fused layer kernel."""
+        if self._bar is None:
+            hz = torch.cuda.get_device_properties(device).clock_rate * 1000
+            words = torch.zeros(4, dtype=torch.int32, device=device)
+            if self.world == 1:
+                flags = torch.zeros(64, dtype=torch.int32, device=device)
+                self._bar = (flags, [flags.data_ptr()], words, int(self.wait_seconds * hz))
+            else:
+                from ..parallel.ddp import SymmetricBuffer
+                flags = SymmetricBuffer(64, torch.int32, device, self.group, name="ep_barrier_flags")
+                import torch.distributed as dist
+                dist.barrier(self.group)
+                torch.cuda.synchronize()
+                self._bar = (flags, flags.ptrs, words, int(self.wait_seconds * hz))
+        return self._bar[1], self._bar[2], self._bar[3]
+
+    def fused_sync(self, device):
+        """Local words of the fused layer kernel's grid barrier: [0] CTA arrivals, [1] generation."""
+        if getattr(self, "_sync", None) is None:
+            self._sync = torch.zeros(4, dtype=torch.int32, device=device)
+        return self._sync
+
     def barrier(self, device=None):
         if self.world == 1:
             return
@@ -153,19 +178,60 @@ class EPContext:
             torch.cuda.current_stream().synchronize()
             dist.barrier(self.group)
             return
-        if self._bar is None:
-            from ..parallel.ddp import SymmetricBuffer
-            flags = SymmetricBuffer(64, torch.int32, device, self.group)
-            words = torch.zeros(4, dtype=torch.int32, device=device)
-            hz = torch.cuda.get_device_properties(device).clock_rate * 1000
-            import torch.distributed as dist
-            dist.barrier(self.group)
-            torch.cuda.synchronize()
-            self._bar = (flags, words, int(self.wait_seconds * hz))
-        flags, words, cycles = self._bar
-        nv.check(nv.cuda().b200_ep_barrier(_ptr_array(flags.ptrs), self.world, self.rank, words.data_ptr(), cycles,
+        ptrs, words, cycles = self._barrier_state(device)
+        nv.check(nv.cuda().b200_ep_barrier(_ptr_array(ptrs), self.world, self.rank, words.data_ptr(), cycles,
                                            nv.status_word(device).data_ptr(), nv.stream_ptr()), "ep_barrier")
         nv.count_launch()
+
+
+_FUSED_LAYER = os.environ.get("B200NN_MOE_FUSED_LAYER", "1") != "0"
+
+
+class MoeFusedArgs(C.Structure):
+    """Mirror of `MoeFusedArgs` in csrc/gemm/gemm_sm100.cu (the one-kernel forward of an expert-parallel layer)."""
+    _fields_ = [("x", C.c_void_p), ("idx", C.c_void_p), ("dest", C.c_void_p),
+                ("xbuf", C.c_void_p * 8), ("fill", C.c_void_p * 8), ("ybuf", C.c_void_p * 8), ("bar_flags", C.c_void_p * 8),
+                ("bar_words", C.c_void_p), ("sync", C.c_void_p), ("w", C.c_void_p), ("out", C.c_void_p), ("xsave", C.c_void_p),
+                ("counts_out", C.c_void_p), ("tokens", C.c_longlong), ("rows_per_rank", C.c_longlong), ("wait_cycles", C.c_longlong),
+                ("k", C.c_int), ("d", C.c_int), ("E_local", C.c_int), ("cap", C.c_int), ("rank", C.c_int), ("world", C.c_int),
+                ("status", C.c_void_p)]
+
+
+def _fused_layer_forward(ep, xc, idx, w, W1, b1, W2, b2, act, cap, xbuf, xptrs, fill, fptrs, ybuf, yptrs, dest):
+    """Forward of the routed experts as ONE kernel launch: dispatch, cross-rank barrier, both grouped GEMMs over the real
+    per-expert counts, barrier, combine, clearing of the input buffer, closing barrier (csrc/gemm/gemm_sm100.cu:
+    moe_fused_fwd_kernel). Returns the output and the tensors the backward needs."""
+    from ..ops.gemm import _num_sms
+    T, d = xc.shape
+    k = idx.shape[1]
+    E_local, hid = W1.shape[0], W1.shape[1]
+    dev = xc.device
+    xb = xbuf.view(E_local, cap, d)
+    fill_l = fill[:E_local]
+    g1, bn1, h, pre, keep1 = gemm(xb, F.lp(W1), bias=b1.detach() if b1 is not None else None, act=act, want_aux=True, m_valid=fill_l,
+                                  bn=256, _prepare=True)
+    g2, bn2, _, _, keep2 = gemm(h, F.lp(W2), bias=b2.detach() if b2 is not None else None, out=ybuf.view(E_local, cap, d), m_valid=fill_l,
+                                bn=256, _prepare=True)
+    out = torch.empty((T, d), dtype=torch.bfloat16, device=dev)
+    xsave = torch.empty((E_local, cap, d), dtype=torch.bfloat16, device=dev)
+    counts = torch.empty(E_local, dtype=torch.int32, device=dev)
+    wc = w.float().contiguous()
+    flag_ptrs, words, cycles = ep._barrier_state(dev)
+    a = MoeFusedArgs()
+    a.x, a.idx, a.dest = xc.data_ptr(), idx.data_ptr(), dest.data_ptr()
+    for r in range(ep.world):
+        a.xbuf[r], a.fill[r], a.ybuf[r], a.bar_flags[r] = xptrs[r], fptrs[r], yptrs[r], flag_ptrs[r]
+    a.bar_words, a.sync = words.data_ptr(), ep.fused_sync(dev).data_ptr()
+    a.w, a.out, a.xsave, a.counts_out = wc.data_ptr(), out.data_ptr(), xsave.data_ptr(), counts.data_ptr()
+    a.tokens, a.rows_per_rank, a.wait_cycles = T, E_local * cap, cycles
+    a.k, a.d, a.E_local, a.cap, a.rank, a.world = k, d, E_local, cap, ep.rank, ep.world
+    a.status = nv.status_word(dev).data_ptr()
+    fn = nv.cuda().b200_moe_fused_fwd
+    fn.argtypes, fn.restype = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p], C.c_int
+    nv.check(fn(C.addressof(g1), C.addressof(g2), C.addressof(a), _num_sms(dev), nv.stream_ptr()), "moe_fused_fwd")
+    nv.count_launch()
+    del keep1, keep2
+    return out, (dest, wc, xsave, h, pre, W1, b1, W2, b2, counts)
 
 
 class MoEExpertsFn(Function):
@@ -198,6 +264,11 @@ class MoEExpertsFn(Function):
         dest = torch.empty((T, k), dtype=torch.int32, device=dev)
         lib = nv.cuda()
         xc = x.contiguous()
+        if ep.backend == "fused" and x.is_cuda and _FUSED_LAYER and d % 8 == 0:
+            out, saved = _fused_layer_forward(ep, xc, idx, w, W1, b1, W2, b2, act, cap, xbuf, xptrs, fill, fptrs, ybuf, yptrs, dest)
+            ctx.save_for_backward(*saved)
+            ctx.cfg = (act, cap, ep, T, d, k, E_local, hid)
+            return out
         nv.check(lib.b200_moe_dispatch(xc.data_ptr(), idx.data_ptr(), dest.data_ptr(), _ptr_array(xptrs), _ptr_array(fptrs), world,
                                        T, k, d, E_local, cap, nv.stream_ptr()), "moe_dispatch")
         ep.barrier(dev)                                           # all remote rows have landed

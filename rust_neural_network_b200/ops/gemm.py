@@ -125,7 +125,7 @@ def _tma_ready(t: torch.Tensor) -> torch.Tensor:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias=None, act: str = "none",
          residual=None, aux_in=None, dact: str = "none", want_aux: bool = False, alpha: float = 1.0,
          out_dtype=None, accumulate_into=None, splits: int = 0, bn: int = 0, alpha_t=None, row_scale=None, col_scale=None,
-         out=None, m_valid=None, k_valid=None):
+         out=None, m_valid=None, k_valid=None, _prepare: bool = False):
     """See module docstring. Returns C (and the bf16 pre-activation when ``want_aux``). ``out`` (GPU only): write the
     result into this tensor ([M, N] or [batch, M, N], unit inner stride, dtype of the result) instead of a new one.
     ``m_valid`` / ``k_valid`` (int32 [batch] on the device) make a batched product ragged, as the groups of tokens routed
@@ -282,6 +282,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     args.A, args.lda, args.strideA, args.a_mn = a3.data_ptr(), a3.stride(1), a3.stride(0), int(a_mn)
     args.B, args.ldb, args.strideB, args.b_mn = b3.data_ptr(), b3.stride(1), b3.stride(0), int(b_mn)
     args.M, args.N, args.K, args.batch, args.dtype = M, N, K, batch, kind
+    if _prepare:
+        # a fused kernel runs this product itself: hand back the filled launch record, the tile width, the results and
+        # everything the record points at (kept alive by the caller until the launch has been issued)
+        res = out3[0] if (squeeze and out.dim() == 3) else out
+        return args, bn, res, (aux[0] if (aux is not None and squeeze) else aux), (a3, b3, bias, residual, aux_in, row_scale, col_scale, m_valid, k_valid, out3)
     rc = lib.b200_gemm_launch(C.byref(args), bn, sms, nv.stream_ptr())
     nv.check(rc, "b200_gemm_launch")
     nv.count_launch()

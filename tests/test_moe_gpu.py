@@ -61,6 +61,40 @@ def test_routed_experts_match_dense_loop(act):
         assert rel_err(a.grad, b.grad) < 3e-2
 
 
+def test_one_kernel_layer_equals_the_separate_kernels(monkeypatch):
+    """The forward of the routed experts as one launch (dispatch, barriers, both grouped GEMMs, combine inside one
+    persistent kernel) against the same layer as separate launches: the outputs agree to the last bit (every token's row
+    goes through the same arithmetic whatever slot it lands in), the gradients up to the summation order over rows."""
+    torch.manual_seed(3)
+    T, d, hid, E, k = 700, 256, 512, 8, 2
+    x = (torch.randn(T, d, device="cuda") * 0.5).bfloat16()
+    logits = torch.randn(T, E, device="cuda")
+    wv, idx = torch.topk(torch.softmax(logits, -1), k, dim=-1)
+    idx = idx.int().contiguous()
+    g = torch.randn(T, d, device="cuda").bfloat16()
+    res = []
+    for fused in (True, False):
+        monkeypatch.setattr(M, "_FUSED_LAYER", fused)
+        torch.manual_seed(5)
+        W1 = (torch.randn(E, hid, d, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+        b1 = (torch.randn(E, hid, device="cuda") * 0.1).requires_grad_(True)
+        W2 = (torch.randn(E, d, hid, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+        b2 = (torch.randn(E, d, device="cuda") * 0.1).requires_grad_(True)
+        xi = x.clone().requires_grad_(True)
+        wi = wv.clone().requires_grad_(True)
+        for _ in range(2):                                   # twice: the second call finds the buffers as the first left them
+            xi.grad = wi.grad = W1.grad = b1.grad = W2.grad = b2.grad = None
+            out = M.MoEExpertsFn.apply(xi, idx, wi, W1, b1, W2, b2, "silu", 256, None)
+            out.backward(g)
+        res.append([t.detach().float().clone() for t in (out, xi.grad, wi.grad, W1.grad, b1.grad, W2.grad, b2.grad)])
+    assert torch.equal(res[0][0], res[1][0])
+    assert torch.equal(res[0][1], res[1][1])
+    for a, b in zip(res[0][2:], res[1][2:]):
+        assert rel_err(a, b) < 2e-3
+    ref = M.moe_experts_ref(x, idx, wv, W1.detach(), b1.detach(), W2.detach(), b2.detach(), "silu")
+    assert rel_err(res[0][0], ref) < 2e-2
+
+
 def test_capacity_drops_are_consistent():
     torch.manual_seed(2)
     T, d, hid, E, k = 256, 64, 64, 4, 1

@@ -292,7 +292,25 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
   const int n_copy = (TP == TP_AG_GEMM) ? tpp->copy_ctas : 0;
   const int cta = CG == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x - n_copy;          // CTA pairs walk the tiles together
   const int n_ctas = CG == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x - n_copy;
-  const int tp_shift = (TP == TP_AG_GEMM) ? tpp->rank * tpp->blocks_per_rank : 0;   // start with the local rows
+  // Row-block order of a tensor-parallel call. all-gather -> GEMM starts with the local rows (the others are still
+  // arriving). GEMM -> reduce-scatter starts with the rows of the NEXT rank: every rank then stores into a different
+  // owner at any moment; with one common order all ranks would write to owner 0 first, then to owner 1, ..., and the
+  // NVLink ingress of one GPU at a time would carry the traffic of all of them.
+  const int tp_shift = (TP == TP_AG_GEMM) ? tpp->rank * tpp->blocks_per_rank
+                     : (TP == TP_GEMM_RS) ? ((tpp->rank + 1) % tpp->world) * tpp->blocks_per_rank : 0;
+  // q-th row block a CTA works on -> row block of the matrix. all-gather -> GEMM: the local rows, then the peers' rows
+  // interleaved (block g of rank+1, block g of rank+2, ..., block g+1 of rank+1, ...): that is the order in which the
+  // gather CTAs of the peers deliver them, each of them sending its blocks to all its peers at the same pace.
+  auto row_block = [&](int q) -> int {
+    if constexpr (TP == TP_AG_GEMM) {
+      const int bpr = tpp->blocks_per_rank, w = tpp->world;
+      if (q < bpr || w <= 1) return (q + tp_shift) % m_blocks;
+      const int qq = q - bpr;
+      return ((tpp->rank + 1 + qq % (w - 1)) % w) * bpr + qq / (w - 1);
+    } else {
+      return (q + tp_shift) % m_blocks;
+    }
+  };
   // The handshake epoch of a tensor-parallel call lives in device memory (one word per context) and is advanced by the
   // call's last CTA, so a CUDA-graph replay of the launch sees a fresh epoch every time.
   const uint32_t tp_epoch = (TP != TP_NONE) ? *reinterpret_cast<volatile const uint32_t*>(tpp->epoch_ptr) + 1u : 0u;
@@ -414,7 +432,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         long long r = t % tiles_per_batch;
         const int split = (int)(r / ((long long)m_blocks * n_blocks));
         r %= (long long)m_blocks * n_blocks;
-        const int mb = ((int)(r / n_blocks) + tp_shift) % m_blocks, nb = (int)(r % n_blocks);
+        const int mb = row_block((int)(r / n_blocks)), nb = (int)(r % n_blocks);
         if (tile_skipped(b, mb)) continue;
         const int kb0 = split * kb_per_split;
         const int kb1 = min(kb0 + kb_per_split, kb_end(b));
@@ -488,7 +506,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
         long long r = t % tiles_per_batch;
         const int split = (int)(r / ((long long)m_blocks * n_blocks));
         r %= (long long)m_blocks * n_blocks;
-        if (tile_skipped(b, ((int)(r / n_blocks) + tp_shift) % m_blocks)) continue;
+        if (tile_skipped(b, row_block((int)(r / n_blocks)))) continue;
         const int kb0 = split * kb_per_split;
         const int kb1 = min(kb0 + kb_per_split, kb_end(b));
         const int as = it & 1;
@@ -551,7 +569,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensor
       long long r = t % tiles_per_batch;
       const int split = (int)(r / ((long long)m_blocks * n_blocks));
       r %= (long long)m_blocks * n_blocks;
-      const int mb = ((int)(r / n_blocks) + tp_shift) % m_blocks, nb = (int)(r % n_blocks);
+      const int mb = row_block((int)(r / n_blocks)), nb = (int)(r % n_blocks);
       if (tile_skipped(b, mb)) continue;
       const int kb0 = split * kb_per_split;
       const bool has_k = kb0 < min(kb0 + kb_per_split, kb_end(b));

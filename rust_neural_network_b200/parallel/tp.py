@@ -18,6 +18,7 @@ kernels are measured against, and the path CPU (gloo) ranks take.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import math
 from typing import Optional
 
@@ -67,7 +68,8 @@ class TPContext:
         self.max_rows, self.max_k, self.max_n = max_rows, max_k, max_n
         # gather CTAs of the all-gather -> GEMM kernel: 32 of the 148 measured best on 2 GPUs; with more ranks the per-rank GEMM
         # shrinks and the push grows, so more CTAs push
-        self.copy_ctas = copy_ctas if copy_ctas > 0 else (32 if self.world <= 2 else 64)
+        env_c = int(os.environ.get("B200NN_TP_COPY_CTAS", "0"))            # gather CTAs of all-gather -> GEMM (0: by world size)
+        self.copy_ctas = copy_ctas if copy_ctas > 0 else (env_c if env_c > 0 else (32 if self.world <= 2 else 64))
         if self.backend == "fused":
             from .ddp import SymmetricBuffer
             if max_rows % (self.world * BM) != 0:

@@ -107,12 +107,18 @@ def save_model(model) -> bytes:
     return serialize([(f"param_{i}", p) for i, p in enumerate(model.parameters())])
 
 
-def save_model_named(named: Sequence[Tuple[str, torch.Tensor]]) -> bytes:
-    return serialize(named)
+def save_model_named(model, names: Sequence[str] | None = None) -> bytes:
+    """`save_model` with the caller's names: `names[i]` for parameter i, `param_i` where the list is short
+    (src/serialize.rs:107-122). A list of (name, tensor) pairs in place of the model is written as it is."""
+    if names is None and not hasattr(model, "parameters"):
+        return serialize(model)
+    names = list(names or [])
+    return serialize([(names[i] if i < len(names) else f"param_{i}", p) for i, p in enumerate(model.parameters())])
 
 
-def load_model(model, buf: bytes) -> None:
-    """Assign checkpoint tensors to the model's parameters in order; count and shapes must match."""
+def load_model(model, buf: bytes) -> int:
+    """Assign checkpoint tensors to the model's parameters in order; count and shapes must match. Returns how many
+    tensors were loaded (src/serialize.rs:125-141)."""
     loaded = deserialize(buf, requires_grad=False)
     params = model.parameters()
     if len(loaded) != len(params):
@@ -122,6 +128,7 @@ def load_model(model, buf: bytes) -> None:
             if tuple(t.shape) != tuple(p.shape):
                 raise SerializationError(f"shape mismatch for {name}: {tuple(t.shape)} vs {tuple(p.shape)}")
             p.copy_(t.to(p.device))
+    return len(loaded)
 
 
 def write_file(path: str, buf: bytes) -> None:

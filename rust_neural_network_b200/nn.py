@@ -17,6 +17,7 @@ import torch
 
 from .ops import functional as F
 from .ops import kernels as K
+from .tensor import Tensor as _Wrapped
 
 Parameter = torch.nn.Parameter
 
@@ -25,11 +26,39 @@ def _param(t: torch.Tensor) -> Parameter:
     return Parameter(t.float().contiguous(), requires_grad=True)
 
 
+def _rewrap(out):
+    if isinstance(out, torch.Tensor):
+        return _Wrapped(out)
+    if isinstance(out, tuple):
+        return tuple(_rewrap(o) for o in out)
+    return out
+
+
+def _accepts_wrapped(f):
+    import functools
+
+    @functools.wraps(f)
+    def forward(self, *a, **kw):
+        for v in a:
+            if isinstance(v, _Wrapped):
+                return _rewrap(f(self, *[u.t if isinstance(u, _Wrapped) else u for u in a], **kw))
+        return f(self, *a, **kw)
+    return forward
+
+
 class Module:
     """Base class. Sub-modules and parameters are discovered through `children()` / `own_parameters()`
     overrides or, by default, by scanning instance attributes in definition order."""
 
     training: bool = True
+
+    def __init_subclass__(cls, **kw):
+        """Every `forward` also takes the reference-shaped `Tensor` wrapper (src/nn.rs:12 `fn forward(&self, x: &Tensor)`):
+        wrapped inputs are unwrapped, and the result then comes back wrapped."""
+        super().__init_subclass__(**kw)
+        f = cls.__dict__.get("forward")
+        if f is not None:
+            cls.forward = _accepts_wrapped(f)
 
     def forward(self, x):
         raise NotImplementedError

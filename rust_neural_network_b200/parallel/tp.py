@@ -66,10 +66,11 @@ class TPContext:
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.backend = backend if self.device.type == "cuda" else "nccl"
         self.max_rows, self.max_k, self.max_n = max_rows, max_k, max_n
-        # gather CTAs of the all-gather -> GEMM kernel: 32 of the 148 measured best on 2 GPUs; with more ranks the per-rank GEMM
-        # shrinks and the push grows, so more CTAs push
-        env_c = int(os.environ.get("B200NN_TP_COPY_CTAS", "0"))            # gather CTAs of all-gather -> GEMM (0: by world size)
-        self.copy_ctas = copy_ctas if copy_ctas > 0 else (env_c if env_c > 0 else (32 if self.world <= 2 else 64))
+        # gather CTAs of the all-gather -> GEMM kernel, 0: chosen per call. Measured: 32 of the 148 is best on 2 GPUs; on 8 GPUs
+        # 64 is best while the push is small (59 MB: 0.185 ms against 0.201 with 32: latency, more chains in flight) and 32 once
+        # it is large (940 MB: 1.82 ms against 2.08 with 64: the links are full either way and the tiles want the SMs)
+        env_c = int(os.environ.get("B200NN_TP_COPY_CTAS", "0"))
+        self.copy_ctas = copy_ctas if copy_ctas > 0 else env_c
         if self.backend == "fused":
             from .ddp import SymmetricBuffer
             if max_rows % (self.world * BM) != 0:
@@ -116,10 +117,16 @@ class TPContext:
         off = half * self.max_rows * self.max_k
         return self.stage.tensor[off: off + m * k].view(m, k)
 
-    def _tp(self, mode: int, rows_local: int) -> TpParams:
+    def _gather_ctas(self, rows_local: int, k: int) -> int:
+        if self.copy_ctas > 0:
+            return self.copy_ctas
+        pushed = rows_local * k * 2 * (self.world - 1)
+        return 32 if (self.world <= 2 or pushed >= (256 << 20)) else 64
+
+    def _tp(self, mode: int, rows_local: int, k: int = 0) -> TpParams:
         tp = TpParams()
         tp.mode, tp.rank, tp.world = mode, self.rank, self.world
-        tp.copy_ctas = self.copy_ctas if (mode == TP_AG_GEMM and self.world > 1) else 0
+        tp.copy_ctas = self._gather_ctas(rows_local, k) if (mode == TP_AG_GEMM and self.world > 1) else 0
         tp.blocks_per_rank = rows_local // BM
         tp.epoch_ptr, tp.wait_cycles = self.local.data_ptr() + 8, self.wait_cycles
         tp.go = self.local.data_ptr()
@@ -153,7 +160,7 @@ class TPContext:
             mine.copy_(x_shard)
         half = self.ag_calls & 1
         self.ag_calls += 1
-        tp = self._tp(TP_AG_GEMM, rows_local)
+        tp = self._tp(TP_AG_GEMM, rows_local, k)
         for r in range(self.world):
             tp.stage_peer[r] = self.stage.ptrs[r] + half * self.max_rows * self.max_k * 2
         out = torch.empty(m, n, dtype=torch.bfloat16, device=self.device)

@@ -26,7 +26,7 @@ _EXPORTS = {
     "distill": "DistillConfig DistillResult Distiller ProgressiveDistiller",
     "distributed": "average_gradients clip_gradients flatten_gradients recv_message ring_all_reduce_simulated ring_all_reduce_all send_message "
                    "sync_gradients unflatten_gradients DistributedConfig DistributedWorker Message MessageType TcpStore HeartbeatMonitor",
-    "error": "RustNnError ShapeMismatch DimensionError InvalidArgument EmptyTensor SerializationError IoError DeviceError NumericalError",
+    "error": "RustNnError ShapeMismatch InvalidNdims InvalidInput IndexOutOfBounds EmptyTensor Serialization DataLoad DimensionError InvalidArgument SerializationError IoError DeviceError NumericalError",
     "finetune": "FastTrainConfig FastTrainer LoraAdapter LrSchedule TrainPoint",
     "fused": "fused_linear sparse_topk_route FusedActivation",
     "gpu": "gpu_add gpu_attention gpu_linear gpu_matmul gpu_mul gpu_relu has_gpu GpuBackend",

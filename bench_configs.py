@@ -111,7 +111,7 @@ def run_lm(name, args):
     if args.recompute_scan and name == "mamba_lm":
         over["recompute_scan"] = True
     cfg = dataclasses.replace(PRESETS[name], **over)
-    batch = args.batch or cfg.batch_per_gpu
+    batch = args.batch or getattr(cfg, "batch_per_gpu", 0) or cfg.global_batch // world
     par = args.parallel if args.parallel != "auto" else (cfg.parallelism if world > 1 else "none")
     if world == 1:
         par = "none"
@@ -360,7 +360,7 @@ def run_attention_sp(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("config", choices=["mlp", "ref_mlp", "moe_lm", "mamba_lm", "attention", "attention_sp"])
+    ap.add_argument("config", choices=["mlp", "ref_mlp", "looped_lm", "moe_lm", "mamba_lm", "attention", "attention_sp"])
     ap.add_argument("--batch", type=int, default=0)
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="override the preset's layer count (diagnostics)")

@@ -20,6 +20,13 @@ template <> __device__ __forceinline__ void sf<__nv_bfloat16>(__nv_bfloat16* p, 
 
 template <typename T, int N> struct alignas(sizeof(T) * N) PackL { T v[N]; };
 
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+constexpr float kLog2e = 1.4426950408889634f;
+
 __device__ __forceinline__ void online_combine(float& m, float& s, float m2, float s2) {
   float nm = fmaxf(m, m2);
   if (nm == -INFINITY) { s = 0.f; m = nm; return; }
@@ -31,7 +38,7 @@ __device__ __forceinline__ void online_combine(float& m, float& s, float m2, flo
 // write (softmax - onehot) * grad_scale. Per-row loss goes to loss_rows; the mean is accumulated
 // into loss_sum with one atomic per row. Labels < 0 (ignore) contribute nothing.
 template <typename T>
-__global__ void ce_label_kernel(const T* __restrict__ logits, const long long* __restrict__ labels,
+__global__ void __launch_bounds__(512, 3) ce_label_kernel(const T* __restrict__ logits, const long long* __restrict__ labels,
                                 T* __restrict__ dlogits, float* __restrict__ loss_rows, float* __restrict__ loss_sum,
                                 int V, long long ld, float grad_scale, float loss_scale) {
   constexpr int N = 16 / sizeof(T);
@@ -44,7 +51,26 @@ __global__ void ce_label_kernel(const T* __restrict__ logits, const long long* _
   float m = -INFINITY, s = 0.f;
   const bool vec = (ld % N == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0);
   const int nv = vec ? V / N : 0;
-  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+  int i = threadIdx.x;
+  // four packets per thread in flight: with one, a 512-thread block keeps 8 KB outstanding and the pass runs at ~4 TB/s
+  for (; i + 3 * (int)blockDim.x < nv; i += 4 * blockDim.x) {
+    P p[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) p[u] = reinterpret_cast<const P*>(xr)[i + u * blockDim.x];
+    float lm = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int j = 0; j < N; ++j) lm = fmaxf(lm, lf(&p[u].v[j]));
+    float ls = 0.f;
+    const float nl = -lm * kLog2e;
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int j = 0; j < N; ++j) ls += ex2f(fmaf(lf(&p[u].v[j]), kLog2e, nl));
+    online_combine(m, s, lm, ls);
+  }
+  for (; i < nv; i += blockDim.x) {
     P p = reinterpret_cast<const P*>(xr)[i];
     float lm = -INFINITY;
 #pragma unroll
@@ -83,23 +109,26 @@ __global__ void ce_label_kernel(const T* __restrict__ logits, const long long* _
   }
   if (!dlogits) return;
   T* dr = dlogits + row * ld;
-  const float inv_s = 1.f / s;
   const float gs = valid ? grad_scale : 0.f;
-  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
-    P p = reinterpret_cast<const P*>(xr)[i], o;
+  // softmax * gs as one exponential: 2^(x log2e - (m log2e + log2 s - log2 gs)); an ignored row (gs = 0) gets 2^-inf = 0.
+  // The label's element is rewritten by thread 0 after the row is out (it kept x[label] from before the first write).
+  const float c2 = valid ? m * kLog2e + log2f(s) - log2f(grad_scale) : INFINITY;
+  auto grad_packet = [&](const P& p, int idx) {
+    P o;
 #pragma unroll
-    for (int j = 0; j < N; ++j) {
-      float pr = __expf(lf(&p.v[j]) - m) * inv_s;
-      if ((long long)i * N + j == label) pr -= 1.f;
-      sf(&o.v[j], pr * gs);
-    }
-    reinterpret_cast<P*>(dr)[i] = o;
+    for (int j = 0; j < N; ++j) sf(&o.v[j], ex2f(fmaf(lf(&p.v[j]), kLog2e, -c2)));
+    reinterpret_cast<P*>(dr)[idx] = o;
+  };
+  i = threadIdx.x;
+  for (; i + (int)blockDim.x < nv; i += 2 * blockDim.x) {            // the re-read hits L2; two packets in flight per thread
+    const P p0 = reinterpret_cast<const P*>(xr)[i], p1 = reinterpret_cast<const P*>(xr)[i + blockDim.x];
+    grad_packet(p0, i);
+    grad_packet(p1, i + blockDim.x);
   }
-  for (int c = nv * N + threadIdx.x; c < V; c += blockDim.x) {
-    float pr = __expf(lf(xr + c) - m) * inv_s;
-    if (c == label) pr -= 1.f;
-    sf(dr + c, pr * gs);
-  }
+  for (; i < nv; i += blockDim.x) grad_packet(reinterpret_cast<const P*>(xr)[i], i);
+  for (int c = nv * N + threadIdx.x; c < V; c += blockDim.x) sf(dr + c, ex2f(fmaf(lf(xr + c), kLog2e, -c2)));
+  __syncthreads();
+  if (threadIdx.x == 0 && valid) sf(dr + label, ex2f(fmaf(x_label, kLog2e, -c2)) - gs);
 }
 
 // dense targets (one-hot or soft): loss_row = -sum_c t_c * log(max(softmax_c, 1e-12)); grad = (p*sum(t) - t)*scale

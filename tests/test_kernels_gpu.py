@@ -322,7 +322,8 @@ def test_sgd_rmsprop_muon():
 
 # ----------------------------------------------------------------------------- attention
 @pytest.mark.parametrize("causal", [False, True])
-@pytest.mark.parametrize("B,S,H,hd", [(2, 256, 2, 64), (1, 200, 3, 64), (2, 384, 2, 128), (1, 1024, 1, 64), (1, 130, 1, 128)])
+@pytest.mark.parametrize("B,S,H,hd", [(2, 256, 2, 64), (1, 200, 3, 64), (2, 384, 2, 128), (1, 1024, 1, 64), (1, 130, 1, 128),
+                                      (2, 200, 8, 64), (2, 136, 16, 128)])   # 256-row delta tiles that straddle two batches
 def test_flash_forward_backward(B, S, H, hd, causal):
     torch.manual_seed(0)
     qkv = (torch.randn(B, S, 3, H, hd, device=DEV) * 0.8).bfloat16()

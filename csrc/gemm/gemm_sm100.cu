@@ -1153,10 +1153,15 @@ static int launch_tp(const GemmArgs& a, const TpParams& tp, cudaStream_t stream,
 template <typename T, int BN>
 static int launch_major(const GemmArgs& a, cudaStream_t s, int sms) {
   if constexpr (BN == 256 && sizeof(T) == 2) {
-    // CTA pairs when the pair tiles fill the machine at least once (small problems keep the finer 128-row tiles)
-    const long long pair_tiles = (long long)((a.p.M + 255) / 256) * ((a.p.N + 255) / 256) * a.p.splits * a.p.batch;
+    // CTA pairs when they occupy (nearly) as many SMs as the 128-row tiles would: a pair tile is two CTAs, so a split-K
+    // weight gradient whose 128-row tiles were sized to fill the machine keeps its CTA count and moves a third less
+    // operand traffic from L2 per FLOP
+    const int sp = a.p.splits > 0 ? a.p.splits : 1;
+    const long long pair_tiles = (long long)((a.p.M + 255) / 256) * ((a.p.N + 255) / 256) * sp * a.p.batch;
+    const long long single_tiles = (long long)((a.p.M + 127) / 128) * ((a.p.N + 255) / 256) * sp * a.p.batch;
+    const long long want = single_tiles < sms ? single_tiles : sms;
     // and the mainloop is long enough to matter (K >= 1024 per split: below that the tile is bound by its epilogue)
-    const bool pays = pair_tiles >= sms / 2 && a.K / (a.p.splits > 0 ? a.p.splits : 1) >= 1024;
+    const bool pays = 2 * pair_tiles * 100 >= want * 85 && a.K / sp >= 1024;
     if (pair_enabled() && a.p.M >= 256 && (pays || g_pair_mode == 2)) {
       if (!a.a_mn && !a.b_mn) return launch_pair<false, false>(a, s, sms);
       if (!a.a_mn && a.b_mn) return launch_pair<false, true>(a, s, sms);

@@ -259,6 +259,19 @@ dact_colsum_kernel(__nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restric
       gv = make_uint4(gw[0], gw[1], gw[2], gw[3]);
     };
     long long r = r0 + warp;
+    for (; r + 24 < r1; r += 32) {                   // four rows of both operands in flight per lane
+      uint4 gv[4], sv[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        gv[j] = *reinterpret_cast<const uint4*>(g + (r + 8 * j) * ld_g + c0);
+        sv[j] = __ldg(reinterpret_cast<const uint4*>(saved + (r + 8 * j) * ld_s + c0));
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        one(gv[j], sv[j]);
+        *reinterpret_cast<uint4*>(g + (r + 8 * j) * ld_g + c0) = gv[j];
+      }
+    }
     for (; r + 8 < r1; r += 16) {
       uint4 gv[2], sv[2];
 #pragma unroll

@@ -143,6 +143,66 @@ __global__ void binary_kernel(const T* __restrict__ a, const T* __restrict__ b, 
   }
 }
 
+// Mamba output gate on row-strided bf16 matrices (the gate z is a column slice of the fused input projection's output,
+// so its rows are 2 x cols apart): out = y * silu(z), and its backward in one pass over g, y, z:
+// dy = g * silu(z), dz = g * y * silu'(z). 16-byte packets, four per thread in flight.
+__device__ __forceinline__ void gate_unpack(const uint4& u, float (&f)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) { f[2 * k] = __uint_as_float(w[k] << 16); f[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u); }
+}
+__device__ __forceinline__ uint4 gate_pack(const float (&f)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) { const __nv_bfloat162 t = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]); w[k] = *reinterpret_cast<const uint32_t*>(&t); }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <bool BWD>
+__global__ void __launch_bounds__(256)
+gate_kernel(const __nv_bfloat16* __restrict__ g, long long ld_g, const __nv_bfloat16* __restrict__ y, long long ld_y,
+            const __nv_bfloat16* __restrict__ z, long long ld_z, __nv_bfloat16* __restrict__ o0, long long ld_0,
+            __nv_bfloat16* __restrict__ o1, long long ld_1, unsigned rows, unsigned ppr) {
+  pdl_trigger();
+  pdl_wait();
+  const unsigned total = rows * ppr, stride = gridDim.x * blockDim.x;
+  for (unsigned k0 = blockIdx.x * blockDim.x + threadIdx.x; k0 < total; k0 += 4 * stride) {
+    uint4 a[4], b[4], c[4];
+    long long r[4]; unsigned col[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const unsigned k = k0 + u * stride;
+      r[u] = k / ppr; col[u] = (k - (unsigned)r[u] * ppr) * 8;
+      if (k < total) {
+        b[u] = __ldg(reinterpret_cast<const uint4*>(y + r[u] * ld_y + col[u]));
+        c[u] = __ldg(reinterpret_cast<const uint4*>(z + r[u] * ld_z + col[u]));
+        if (BWD) a[u] = __ldg(reinterpret_cast<const uint4*>(g + r[u] * ld_g + col[u]));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (k0 + u * stride >= total) continue;
+      float fy[8], fz[8], r0[8], r1[8];
+      gate_unpack(b[u], fy); gate_unpack(c[u], fz);
+      if (BWD) {
+        float fg[8];
+        gate_unpack(a[u], fg);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float sg = __fdividef(1.f, 1.f + __expf(-fz[e])), sl = fz[e] * sg;
+          r0[e] = fg[e] * sl;                                              // d y
+          r1[e] = fg[e] * fy[e] * sg * (1.f + fz[e] * (1.f - sg));          // d z
+        }
+        *reinterpret_cast<uint4*>(o0 + r[u] * ld_0 + col[u]) = gate_pack(r0);
+        *reinterpret_cast<uint4*>(o1 + r[u] * ld_1 + col[u]) = gate_pack(r1);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) r0[e] = fy[e] * fz[e] * __fdividef(1.f, 1.f + __expf(-fz[e]));
+        *reinterpret_cast<uint4*>(o0 + r[u] * ld_0 + col[u]) = gate_pack(r0);
+      }
+    }
+  }
+}
+
 // cast kernels
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ x, TO* __restrict__ y, long long n, float scale) {
@@ -542,6 +602,23 @@ int b200_binary(const void* a, const void* b, void* y, long long n, int op, long
   long long work = (b_period && (b_period % vw || n % vw)) ? n : n / vw + 1;
   if (is_bf16) launch_pdl(binary_kernel<__nv_bfloat16>, dim3(grid_for(work, 256)), dim3(256), 0, st, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, n, op, b_period);
   else launch_pdl(binary_kernel<float>, dim3(grid_for(work, 256)), dim3(256), 0, st, (const float*)a, (const float*)b, (float*)y, n, op, b_period);
+  return (int)cudaGetLastError();
+}
+
+// Gate forward (g == nullptr: o0 = y * silu(z)) or backward (o0 = d y, o1 = d z). bf16, cols % 8 == 0, every leading
+// dimension % 8 == 0, 16-byte aligned bases, fewer than 2^31 packets; -1 otherwise (the caller composes elementwise kernels).
+int b200_gate(const void* g, long long ld_g, const void* y, long long ld_y, const void* z, long long ld_z, void* o0, long long ld_0,
+              void* o1, long long ld_1, long long rows, int cols, cudaStream_t st) {
+  if (rows <= 0 || cols <= 0) return 0;
+  const bool bwd = g != nullptr;
+  if (cols % 8 || ld_y % 8 || ld_z % 8 || ld_0 % 8 || (bwd && (ld_g % 8 || ld_1 % 8))) return -1;
+  if (((uintptr_t)y | (uintptr_t)z | (uintptr_t)o0 | (uintptr_t)g | (uintptr_t)o1) & 15) return -1;
+  const long long packets = rows * (cols / 8);
+  if (packets >= (1LL << 31) - 4LL * 148 * 16 * 256) return -1;
+  const dim3 grid(grid_for((packets + 3) / 4, 256));
+  const __nv_bfloat16 *gp = (const __nv_bfloat16*)g, *yp = (const __nv_bfloat16*)y, *zp = (const __nv_bfloat16*)z;
+  if (bwd) launch_pdl(gate_kernel<true>, grid, dim3(256), 0, st, gp, ld_g, yp, ld_y, zp, ld_z, (__nv_bfloat16*)o0, ld_0, (__nv_bfloat16*)o1, ld_1, (unsigned)rows, (unsigned)(cols / 8));
+  else launch_pdl(gate_kernel<false>, grid, dim3(256), 0, st, gp, ld_g, yp, ld_y, zp, ld_z, (__nv_bfloat16*)o0, ld_0, (__nv_bfloat16*)o1, ld_1, (unsigned)rows, (unsigned)(cols / 8));
   return (int)cudaGetLastError();
 }
 

@@ -66,6 +66,7 @@ _SIGS = {
     "b200_transpose": [c_void_p, c_void_p, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_int, c_int, c_void_p],
     "b200_colsum": [c_void_p, c_void_p, c_ll, c_int, c_ll, c_int, c_void_p],
     "b200_dact_colsum": [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_ll, c_ll, c_int, c_void_p],
+    "b200_gate": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_ll, c_int, c_void_p],
     "b200_colsum_batched": [c_void_p, c_void_p, c_int, c_ll, c_int, c_ll, c_ll, c_int, c_void_p, c_void_p],
     "b200_reduce": [c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p],
     "b200_dropout": [c_void_p, c_void_p, c_ll, c_float, c_ull, c_int, c_void_p],

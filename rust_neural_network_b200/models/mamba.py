@@ -110,7 +110,8 @@ class MambaBlock(nn.Module):
         xz = TP.column_parallel(x_s, self.in_proj, None, tp)                        # [M, 2 dl]
         M = xz.shape[0]
         Bt = M // seq_len
-        xs, z = xz[:, :dl].view(Bt, seq_len, dl), xz[:, dl:].view(Bt, seq_len, dl)
+        xs, z = TP.split_cols(xz, dl)
+        xs, z = xs.view(Bt, seq_len, dl), z.view(Bt, seq_len, dl)
         xa = causal_conv1d(xs, self.conv_weight, self.conv_bias, "silu")            # [Bt, S, dl]
         xp = TP.row_parallel_all_reduce(xa.reshape(M, dl), self.x_proj, tp)             # [M, R + 2N] identical on all ranks
         dt = F.linear(xp[:, :R], self.dt_up, None, "none", None)                     # [M, dl]

@@ -183,15 +183,12 @@ class MulSiluFn(Function):
     @staticmethod
     def forward(ctx, y, z):
         ctx.save_for_backward(y, z)
-        return K.binary(y, z, "mul_silu")
+        return K.gate_fwd(y, z)
 
     @staticmethod
     def backward(ctx, g):
         y, z = ctx.saved_tensors
-        g = g.contiguous()
-        dy = K.binary(g, z, "mul_silu")
-        dz = K.binary(K.binary(g, y, "mul"), z, "silu_bwd")
-        return dy, dz
+        return K.gate_bwd(g, y, z)
 
 
 def mul_silu(y, z): return MulSiluFn.apply(y, z)

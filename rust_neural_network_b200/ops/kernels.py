@@ -142,6 +142,61 @@ def colsum(x2d, out=None):
     return out
 
 
+def _rows2d(t):
+    """Any tensor whose last dimension has unit stride and whose leading dimensions collapse into rows a fixed distance
+    apart -> (tensor, rows, cols, row stride); anything else is made contiguous first."""
+    cols = t.shape[-1]
+    if t.dim() >= 2 and t.stride(-1) == 1:
+        ld, ok, expect = t.stride(-2), True, t.stride(-2) * t.shape[-2]
+        for d in range(t.dim() - 3, -1, -1):
+            if t.shape[d] != 1 and t.stride(d) != expect:
+                ok = False
+                break
+            expect = t.stride(d) * t.shape[d] if t.shape[d] != 1 else expect
+        if ok:
+            return t, t.numel() // cols, cols, ld
+    t = t.contiguous()
+    return t, t.numel() // cols, cols, cols
+
+
+def _gate_ok(*ts):
+    return all(t.is_cuda and t.dtype == torch.bfloat16 for t in ts) and ts[0].shape[-1] % 8 == 0
+
+
+def gate_fwd(y, z):
+    """y * silu(z) (the Mamba output gate); `z` may be a column slice (rows a fixed distance apart)."""
+    if _gate_ok(y, z) and y.shape == z.shape:
+        y2, rows, cols, ld_y = _rows2d(y)
+        z2, _, _, ld_z = _rows2d(z)
+        out = torch.empty(y.shape, dtype=y.dtype, device=y.device)
+        rc = nv.cuda().b200_gate(None, 0, y2.data_ptr(), ld_y, z2.data_ptr(), ld_z, out.data_ptr(), cols, None, 0, rows, cols, nv.stream_ptr())
+        if rc == 0:
+            nv.count_launch()
+            return out
+        if rc != -1:
+            nv.check(rc, "gate")
+    return binary(y, z, "mul_silu")
+
+
+def gate_bwd(g, y, z):
+    """(d y, d z) of out = y * silu(z) for the incoming gradient g, in one pass."""
+    if _gate_ok(g, y, z) and g.shape == y.shape == z.shape:
+        g2, rows, cols, ld_g = _rows2d(g)
+        y2, _, _, ld_y = _rows2d(y)
+        z2, _, _, ld_z = _rows2d(z)
+        dy = torch.empty(y.shape, dtype=y.dtype, device=y.device)
+        dz = torch.empty(y.shape, dtype=y.dtype, device=y.device)
+        rc = nv.cuda().b200_gate(g2.data_ptr(), ld_g, y2.data_ptr(), ld_y, z2.data_ptr(), ld_z, dy.data_ptr(), cols, dz.data_ptr(), cols,
+                                 rows, cols, nv.stream_ptr())
+        if rc == 0:
+            nv.count_launch()
+            return dy, dz
+        if rc != -1:
+            nv.check(rc, "gate")
+    g = g.contiguous()
+    return binary(g, z, "mul_silu"), binary(binary(g, y, "mul"), z, "silu_bwd")
+
+
 def dact_colsum(g, saved, act, bias_grad=None, want_bias_grad=True):
     """In place g *= act'(saved) for act in {"relu", "gelu", "silu"} (saved = the pre-activation) and, in the same
     pass, the column sums of the result (the bias gradient), added into `bias_grad` when given. Returns (g, dbias).

@@ -81,6 +81,10 @@ class TPContext:
             # readable (e.g. for the weight gradient that follows) until the call after the next one
             self.stage = SymmetricBuffer(2 * max_rows * max_k, torch.bfloat16, dev, self.group)
             self.ag_calls = 0
+            # `keep_gathered` copies a call's gathered rows out of the staging half on this stream, beside whatever the
+            # main stream runs next; the next all-gather call (or the consumer of the copy) waits for it
+            self.side = torch.cuda.Stream(dev)
+            self._copy_done = None
             self.slots = SymmetricBuffer(2 * self.world * self.rows_per_rank * max_n, torch.bfloat16, dev, self.group)
             self.flags = SymmetricBuffer(2 * TP_MAX_WORLD + max_rows // BM, torch.int32, dev, self.group)   # handshake words, then ready[m_blocks]
             # go, done_ctr, call epoch. The epoch is a DEVICE word that each call's last CTA advances, so a captured launch
@@ -155,6 +159,7 @@ class TPContext:
             return (*res, xg) if want_aux else (res, xg)
         if rows_local % BM != 0 or k % 8 != 0 or n % 8 != 0:
             raise ValueError("fused all_gather_gemm needs rows_local % 128 == 0 and K, N % 8 == 0")
+        self.join_copy()                 # peers push into the other half's predecessor once this call's kernel has run
         mine = self.ag_input(rows_local, k)
         if x_shard.data_ptr() != mine.data_ptr():
             mine.copy_(x_shard)
@@ -170,6 +175,30 @@ class TPContext:
         if return_gathered:
             res = (*res, self._stage_view(half, rows_local, k))
         return res if len(res) > 1 else res[0]
+
+    def join_copy(self) -> None:
+        """Main stream waits for the outstanding `keep_gathered` copy, if any."""
+        if getattr(self, "_copy_done", None) is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._copy_done)
+            self._copy_done = None
+
+    def keep_gathered(self, xg: torch.Tensor):
+        """A private copy of a call's gathered rows (a view of a staging half, which the call after the next one
+        overwrites) for the backward pass. On the fused path the copy runs on a side stream, so the 2 x M x K bytes move
+        while the main stream computes; returns (copy, event to wait for before reading it or None)."""
+        if self.backend != "fused":
+            return xg, None              # a fresh tensor already (torch.cat of the gathered shards)
+        keep = torch.empty_like(xg)
+        main = torch.cuda.current_stream(self.device)
+        fork = torch.cuda.Event()
+        fork.record(main)
+        self.side.wait_event(fork)
+        with torch.cuda.stream(self.side):
+            keep.copy_(xg)
+            done = torch.cuda.Event()
+            done.record(self.side)
+        self._copy_done = done
+        return keep, done
 
     # ------------------------------------------------------------------ GEMM -> reduce-scatter
     def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, bias=None, residual=None) -> torch.Tensor:
@@ -277,7 +306,9 @@ class _ColumnParallelFn(torch.autograd.Function):
             y, xg = tpc.all_gather_gemm(x_shard, W, bias=bias, act=act, return_gathered=True)
             pre = y if act == "relu" else None
         # the gathered input is needed for the weight gradient long after the staging half has been reused
-        ctx.save_for_backward(xg.clone(), w, b if b is not None else torch.empty(0), pre if pre is not None else torch.empty(0))
+        need = any(ctx.needs_input_grad[:3])          # False under no_grad: nothing is kept then
+        keep, ctx.keep_done = tpc.keep_gathered(xg) if need else (torch.empty(0), None)
+        ctx.save_for_backward(keep, w, b if b is not None else torch.empty(0), pre if pre is not None else torch.empty(0))
         ctx.tpc, ctx.act = tpc, act
         return y
 
@@ -287,6 +318,10 @@ class _ColumnParallelFn(torch.autograd.Function):
         from ..ops.functional import compute_weight
         xg, w, b, pre = ctx.saved_tensors
         tpc, act = ctx.tpc, ctx.act
+        if ctx.keep_done is not None:
+            torch.cuda.current_stream(dy.device).wait_event(ctx.keep_done)
+            if tpc._copy_done is ctx.keep_done:
+                tpc._copy_done = None
         dy = dy.contiguous()
         db = None
         if act != "none":
@@ -342,6 +377,31 @@ class _RowParallelAllReduceFn(torch.autograd.Function):
         dh = G.gemm(g, compute_weight(w, g), b_mn=True) if ctx.needs_input_grad[0] else None
         dw = _wgrad(g, h, w) if ctx.needs_input_grad[1] else None
         return dh, dw, None
+
+
+class _SplitColsFn(torch.autograd.Function):
+    """(x[:, :n], x[:, n:]) as views; the backward writes both gradients into one buffer (two strided copies) where
+    autograd's own slice backward would fill two zero matrices of x's size, copy into them and add them."""
+
+    @staticmethod
+    def forward(ctx, x, n):
+        ctx.n, ctx.shape, ctx.dt = n, x.shape, x.dtype
+        return x[:, :n], x[:, n:]
+
+    @staticmethod
+    def backward(ctx, g1, g2):
+        dev = (g1 if g1 is not None else g2).device
+        out = torch.empty(ctx.shape, dtype=ctx.dt, device=dev)
+        for g, sl in ((g1, out[:, :ctx.n]), (g2, out[:, ctx.n:])):
+            if g is None:
+                sl.zero_()
+            else:
+                sl.copy_(g)
+        return out, None
+
+
+def split_cols(x: torch.Tensor, n: int):
+    return _SplitColsFn.apply(x, n)
 
 
 def row_parallel_all_reduce(h: torch.Tensor, w: torch.Tensor, tpc: "TPContext") -> torch.Tensor:

@@ -478,3 +478,23 @@ def test_gemm_ragged_groups():
     refW = dy.float().transpose(1, 2) @ h_clean
     assert rel_err(dW, refW) < 1e-2
     assert float(dW[1].abs().max()) == 0.0                          # an empty group contributes nothing
+
+
+@pytest.mark.parametrize("rows,cols,sliced", [(1000, 512, True), (4096, 2048, True), (300, 64, False), (77, 24, True)])
+def test_gate_forward_backward_on_column_slices(rows, cols, sliced):
+    """y * silu(z) and its two gradients in one pass each, with z (and g) taken as column slices of a wider matrix."""
+    torch.manual_seed(rows)
+    wide = torch.randn(rows, 2 * cols, device=DEV).bfloat16()
+    z = wide[:, cols:] if sliced else wide[:, cols:].contiguous()
+    y = torch.randn(rows, cols, device=DEV).bfloat16()
+    gw = torch.randn(rows, cols + 8, device=DEV).bfloat16()
+    g = gw[:, :cols] if sliced else gw[:, :cols].contiguous()
+    out = K.gate_fwd(y, z)
+    dy, dz = K.gate_bwd(g, y, z)
+    yf, zf, gf = (t.float().requires_grad_(True) for t in (y, z, g))
+    ref = yf * torch.nn.functional.silu(zf)
+    ref.backward(gf.detach())
+    assert rel_err(out, ref) < 5e-3
+    assert rel_err(dy, yf.grad) < 5e-3 and rel_err(dz, zf.grad) < 5e-3
+    o3 = K.gate_fwd(y.view(1, rows, cols), z.view(1, rows, cols) if not sliced else wide.view(1, rows, 2 * cols)[:, :, cols:])
+    assert torch.equal(o3.view(rows, cols), out)

@@ -392,3 +392,31 @@ def test_distributed_worker_standalone_step_and_rendezvous_timeout():
     assert l1 < l0
     with pytest.raises(TimeoutError):
         dist.DistributedWorker.connect(0, 2, master_port=0, timeout=0.3)   # the peer never joins
+
+
+def test_split_cols_backward_fills_one_buffer():
+    """The (x, z) split of a fused projection: views forward, both gradients written into one matrix backward; a missing
+    gradient becomes zeros."""
+    from rust_neural_network_b200.parallel.tp import split_cols
+    x = torch.randn(6, 10, requires_grad=True)
+    a, b = split_cols(x, 4)
+    assert a.shape == (6, 4) and b.shape == (6, 6) and a.data_ptr() == x.data_ptr()
+    ga, gb = torch.randn(6, 4), torch.randn(6, 6)
+    (a * ga).sum().backward(retain_graph=True)
+    assert torch.equal(x.grad[:, :4], ga) and float(x.grad[:, 4:].abs().sum()) == 0.0
+    x.grad = None
+    ((a * ga).sum() + (b * gb).sum()).backward()
+    assert torch.equal(x.grad, torch.cat([ga, gb], 1))
+
+
+def test_rows2d_accepts_column_slices_and_collapsible_batches():
+    from rust_neural_network_b200.ops.kernels import _rows2d
+    wide = torch.zeros(4, 6, 32)
+    t, rows, cols, ld = _rows2d(wide[:, :, 16:])                    # a column slice: rows 32 apart
+    assert (rows, cols, ld) == (24, 16, 32) and t.data_ptr() == wide[:, :, 16:].data_ptr()
+    t, rows, cols, ld = _rows2d(wide[:, ::2, :16])                  # every other row: still one row stride
+    assert (rows, cols, ld) == (12, 16, 64)
+    t, rows, cols, ld = _rows2d(wide.transpose(0, 1)[:, :, :16])    # batches that do not collapse: copied
+    assert (rows, cols, ld) == (24, 16, 16) and t.is_contiguous()
+    t, rows, cols, ld = _rows2d(torch.zeros(8, 5).t())              # no unit inner stride: copied
+    assert (rows, cols, ld) == (5, 8, 8)

@@ -176,3 +176,8 @@ class NativeBackend(BlasBackend):
     def sgemm(self, transa, transb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc):
         return sgemm(transa, transb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc)
 
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

@@ -88,3 +88,8 @@ class CompiledMLP:
 
     def biases(self) -> List[torch.Tensor]:
         return [l.bias for l in self.model.layers if isinstance(l, nn.Linear)]
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

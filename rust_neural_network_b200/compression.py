@@ -330,3 +330,8 @@ def automl_search(model, inputs, targets, loss_fn, target_compression: float) ->
             strategies.extend(CompressionStrategy.None_() for _ in range(i + 1, len(params)))
             break
     return CompressionRecipe(strategies, current, 1.0 - base * 0.1)
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

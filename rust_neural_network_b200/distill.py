@@ -138,3 +138,8 @@ class ProgressiveDistiller:
             results.append(r)
             teacher = r.student
         return results
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

@@ -216,3 +216,8 @@ class FastTrainer:
 
     def model(self):
         return self._model
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

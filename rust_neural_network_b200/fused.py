@@ -51,3 +51,8 @@ def sparse_topk_route(gating_logits: torch.Tensor, batch: int, num_experts: int,
     vals, idx = torch.topk(logits.float(), k, dim=-1)
     w = torch.softmax(vals, dim=-1)
     return idx.reshape(-1), w.reshape(-1)
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

@@ -7,3 +7,8 @@ NVIDIA_PTX_KERNEL = _src(_K.Nvidia)          # the CUDA source of the sm_100a GE
 AMD_HIP_KERNEL = _src(_K.Amd)                # no such kernel in this build: a one-line comment
 APPLE_MSL_KERNEL = _src(_K.Apple)
 
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals(), imported=True)

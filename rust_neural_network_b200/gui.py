@@ -163,3 +163,8 @@ def launch(html: str, path: str, open_viewer: bool = False) -> None:
         exe = shutil.which(opener)
         if exe:
             subprocess.Popen([exe, path], stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

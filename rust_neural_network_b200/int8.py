@@ -103,3 +103,8 @@ def igemm(a: torch.Tensor, b: torch.Tensor, m: int, k: int, n: int) -> torch.Ten
     if not a2.is_cuda:
         return igemm_scalar(a2, b2, m, k, n)
     return G.gemm(a2.contiguous(), b2.t().contiguous(), out_dtype=torch.int32)
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

@@ -18,3 +18,8 @@ class KernelKind(enum.IntEnum):
     @staticmethod
     def from_u8(v: int) -> "KernelKind":
         return KernelKind.Relu2 if v == 1 else KernelKind.Elu
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals(), imported=True)

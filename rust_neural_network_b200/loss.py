@@ -56,3 +56,8 @@ class HuberLoss(Loss):
 
     def forward(self, pred, target):
         return F.pointwise_loss(pred, target, "huber", self.delta, "mean")
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

@@ -355,3 +355,8 @@ class OffloadModel:
         ram, ssd = self.store.tier_counts()
         return (f"OffloadModel memory: {ram + ssd} tensors (RAM: {ram}, SSD: {ssd}), RAM: {self.ram_usage() / 1024 / 1024:.1f} MB, "
                 f"SSD: {self.ssd_usage() / 1024 / 1024:.1f} MB")
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

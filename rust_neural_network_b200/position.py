@@ -235,3 +235,8 @@ class PositionalEncoding:
 
     def parameters(self):
         return self.impl.parameters() if isinstance(self.impl, LearnedPE) else []
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

@@ -96,3 +96,8 @@ class RotorQuant(nn.Module):
 
     def parameters(self):
         return []
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

@@ -32,3 +32,8 @@ class SelfImprover:
             total += self.self_train_step(x)
             n += 1
         return total / n if n else 0.0
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

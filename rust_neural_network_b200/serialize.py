@@ -270,3 +270,8 @@ class _CallableModule(_types.ModuleType):
 
 
 _sys.modules[__name__].__class__ = _CallableModule
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

@@ -54,3 +54,8 @@ def simd_features() -> str:
         p = torch.cuda.get_device_properties(torch.cuda.current_device())
         return f"CUDA sm_{p.major}{p.minor} ({p.name}): {p.multi_processor_count} SMs, tcgen05 tensor cores, 16-byte vector loads"
     return "CPU reference path (PyTorch); CUDA kernels compiled for sm_100a"
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

@@ -144,3 +144,8 @@ class TernaryModel:
 
 def ternarize(tensor: torch.Tensor) -> TernaryTensor:
     return TernaryTensor.quantize(tensor)
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

@@ -149,3 +149,8 @@ class Trainer:
         if not losses:
             return 0.0
         return float(torch.stack([l.float() for l in losses]).mean())
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

@@ -1,0 +1,75 @@
+"""The reference's public functions take its `Tensor` (rust-nn src/activations.rs:6-65, src/loss.rs, src/quantize.rs:85,
+src/int8.rs:40, src/fused.rs:60, ...). Here every such entry point accepts the reference-shaped wrapper as well as a
+`torch.Tensor`, and answers in kind."""
+import torch
+
+import rust_neural_network_b200 as rn
+from rust_neural_network_b200.tensor import Tensor as T
+
+
+def _same(a, b, tol=1e-6):
+    a = a.t if isinstance(a, T) else a
+    b = b.t if isinstance(b, T) else b
+    return torch.allclose(a.float(), b.float(), atol=tol)
+
+
+def test_activations_take_and_return_the_wrapper():
+    x = T.from_vec([1.0, -2.0, 3.0, 0.5], [2, 2])
+    for name in ("relu", "sigmoid", "tanh", "gelu", "softmax"):
+        f = getattr(rn.activations, name)
+        out = f(x)
+        assert isinstance(out, T), name
+        raw = f(x.t)
+        assert isinstance(raw, torch.Tensor) and _same(out, raw), name
+
+
+def test_losses_and_trainer():
+    torch.manual_seed(0)
+    lin = rn.Linear(8, 3)
+    x, y = T.randn([4, 8]), T.randn([4, 3])
+    loss = rn.MSELoss()(lin(x), y)
+    assert isinstance(loss, T) and _same(loss, rn.MSELoss()(lin(x.t), y.t))
+    loss.backward()
+    assert lin.weight.grad is not None
+    onehot = T(torch.nn.functional.one_hot(torch.tensor([0, 1, 2, 0]), 3).float())
+    assert isinstance(rn.CrossEntropyLoss()(lin(x), onehot), T)
+    tr = rn.Trainer(lin, rn.Adam(lin.parameters(), lr=1e-2), rn.MSELoss())
+    first = float(T(tr.train_step(x, y)).t)
+    for _ in range(20):
+        last = float(T(tr.train_step(x, y)).t)
+    assert last < first
+
+
+def test_quantisers_and_compression_take_the_wrapper():
+    torch.manual_seed(1)
+    x = T.randn([8, 16])
+    q = rn.quantize.QuantizedTensor.quantize(x, rn.quantize.QuantFormat.INT8, 0)
+    assert q.quantization_error(x) < 0.05 and tuple(q.dequantize().shape) == (8, 16)
+    assert rn.int8.Int8Weights.quantize(x).quantization_error(x) < 0.01
+    assert rn.ternary.TernaryTensor.quantize(x).compression_ratio() > 5
+    assert isinstance(rn.quant.RotorQuant.new(6, 4).quantize(T.randn([5, 6])), T)
+    assert rn.compression.SparseMatrix.from_dense(x, 0.5).sparsity() > 0.0
+    assert isinstance(rn.distill.softmax_temp(x, 2.0), T)
+
+
+def test_io_and_tools_take_the_wrapper(tmp_path):
+    x = T.from_vec([1.0, 2.0, 3.0, 4.0], [2, 2])
+    blob = rn.serialize.serialize([("w", x)])
+    (name, back), = rn.deserialize(blob)
+    assert name == "w" and _same(back, x)
+    s = rn.offload.SsdTensor.write(x, str(tmp_path))
+    assert _same(s.load(), x)
+    assert "<td" in rn.gui.tensor_heatmap_html(x, 10)
+    y = rn.fused.fused_linear(x, T.from_vec([1.0, 0.0, 0.0, 1.0], [2, 2]), None)
+    assert isinstance(y, T) and _same(y, x)
+    c, _ = rn.gpu_kernels.kernel_matmul(x, x)
+    assert isinstance(c, T) and _same(c, x.t @ x.t, 1e-2)
+    o = rn.linear_attention.linear_attention_forward(T.randn([1, 4, 2]), T.randn([1, 4, 2]), T.randn([1, 4, 2]), 1, 4, 2, 1.0, 1e-6, False, 0)
+    assert isinstance(o, T) and list(o.shape()) == [1, 4, 2]
+
+
+def test_plain_tensors_pass_through_untouched():
+    x = torch.randn(3, 3)
+    assert type(rn.activations.relu(x)) is torch.Tensor
+    assert type(rn.fused.fused_linear(x, x, None)) is torch.Tensor
+    assert type(rn.MSELoss()(x, x)) is torch.Tensor

@@ -455,3 +455,8 @@ def parse_rust_file(path: str, source: str) -> FileNode:
             if name:
                 node.exports.append(name)
     return node
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

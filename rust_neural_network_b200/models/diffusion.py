@@ -118,3 +118,8 @@ class DDPM(nn.Module):
 
     def parameters(self):
         return self.denoise.parameters()
+
+
+from .._compat import install as _install  # noqa: E402
+
+_install(globals())

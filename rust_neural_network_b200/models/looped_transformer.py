@@ -264,3 +264,8 @@ def _add(a, b):
 
 def _add_row(a, row):
     return _AddRowFn.apply(a, row)
+
+
+from .._compat import accept_wrapped as _accept_wrapped  # noqa: E402
+
+LoopedTransformer.forward_with_loops = _accept_wrapped(LoopedTransformer.forward_with_loops)   # (output, loops used) for a wrapped input too

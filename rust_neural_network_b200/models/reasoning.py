@@ -117,3 +117,8 @@ class MarkovianRSA(nn.Module):
 
     def parameters(self):
         return self.aggregation_layer.parameters()
+
+
+from .._compat import install as _install  # noqa: E402
+
+_install(globals())

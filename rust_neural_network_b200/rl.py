@@ -341,3 +341,8 @@ class ChainEnv(Environment):
 
     def observation_dim(self): return self.n
     def num_actions(self): return 2
+
+
+from ._compat import install as _install  # noqa: E402
+
+_install(globals())

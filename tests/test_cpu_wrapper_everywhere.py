@@ -73,3 +73,16 @@ def test_plain_tensors_pass_through_untouched():
     assert type(rn.activations.relu(x)) is torch.Tensor
     assert type(rn.fused.fused_linear(x, x, None)) is torch.Tensor
     assert type(rn.MSELoss()(x, x)) is torch.Tensor
+
+
+def test_model_side_methods_take_the_wrapper():
+    from rust_neural_network_b200.models.diffusion import DDPM, ScheduleType
+    torch.manual_seed(2)
+    d = DDPM(3, 16, 100, ScheduleType.Linear)
+    xt = d.q_sample(T.from_vec([1.0, 2.0, 3.0], [1, 3]), 0, T.zeros([1, 3]))
+    assert isinstance(xt, T) and abs(xt.get([0, 0]) - 1.0) < 0.05
+    assert isinstance(d.predict_noise(T.randn([2, 3]), 5), T)
+    assert d.train_batch(rn.Adam(d.parameters(), lr=1e-2), T.randn([8, 3])) >= 0.0
+    y, loops = rn.LoopedTransformer(4, 8, 2, 16, 2, 3).forward_with_loops(T.randn([1, 3, 4]))
+    assert isinstance(y, T) and y.shape() == [1, 3, 2] and loops == 3
+    assert isinstance(rn.TreeOfThoughts(4, 2, 2, 1).score(T.randn([2, 4])), T)

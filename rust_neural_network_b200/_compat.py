@@ -17,6 +17,14 @@ import torch
 from .tensor import Tensor as _W
 
 
+class NewMixin:
+    """`Type.new(...)`: the reference's spelling of a constructor call (`Linear::new(2, 8, true)`)."""
+
+    @classmethod
+    def new(cls, *args, **kwargs):
+        return cls(*args, **kwargs)
+
+
 def _has_wrapped(args, kwargs) -> bool:
     for v in args:
         if isinstance(v, _W):

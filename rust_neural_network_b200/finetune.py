@@ -186,6 +186,7 @@ class FastTrainer:
                 return lr
 
             for x, y in loader:
+                x, y = _unwrap(x), _unwrap(y)
                 x = x.to(dev, non_blocking=True); y = y.to(dev, non_blocking=True)
                 loss = loss_fn(self._model(x), y)
                 loss.backward()
@@ -218,6 +219,6 @@ class FastTrainer:
         return self._model
 
 
-from ._compat import install as _install  # noqa: E402
+from ._compat import install as _install, unwrap as _unwrap  # noqa: E402
 
 _install(globals())

@@ -11,7 +11,9 @@ import torch
 from .ops import functional as F
 
 
-class Loss:
+from ._compat import NewMixin as _NewMixin  # noqa: E402
+
+class Loss(_NewMixin):
     def forward(self, pred, target):
         raise NotImplementedError
 

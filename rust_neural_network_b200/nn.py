@@ -18,6 +18,7 @@ import torch
 from .ops import functional as F
 from .ops import kernels as K
 from .tensor import Tensor as _Wrapped
+from ._compat import NewMixin as _NewMixin
 
 Parameter = torch.nn.Parameter
 
@@ -46,7 +47,7 @@ def _accepts_wrapped(f):
     return forward
 
 
-class Module:
+class Module(_NewMixin):
     """Base class. Sub-modules and parameters are discovered through `children()` / `own_parameters()`
     overrides or, by default, by scanning instance attributes in definition order."""
 
@@ -210,6 +211,8 @@ class Sequential(Module):
         self.layers: List[Module] = list(layers)
 
     def add(self, m: Module) -> "Sequential":
+        if isinstance(m, type):              # `.add(ReLU)`: the reference's unit structs are written without parentheses
+            m = m()
         self.layers.append(m)
         return self
 

@@ -20,6 +20,8 @@ from .ops.gemm import gemm
 _ALIGN = 64   # elements; keeps every parameter 256-byte aligned inside the flat buffers
 
 
+from ._compat import NewMixin as _NewMixin  # noqa: E402
+
 class FlatParams:
     """Flat fp32 master / grad buffers and a flat bf16 shadow for a list of parameters.
 
@@ -99,7 +101,7 @@ class FlatParams:
             p._lp_version = p._version
 
 
-class Optimizer:
+class Optimizer(_NewMixin):
     """`step()` consumes the gradients, `zero_grad()` clears them (src/optim.rs:5-9)."""
 
     def __init__(self, params, lr: float):

@@ -134,6 +134,10 @@ class Tensor:
         self.t.requires_grad_(flag)
         return self
 
+    def clone(self) -> "Tensor":
+        """Another handle on the same storage, as cloning the reference's `Arc`-backed tensor gives (src/tensor.rs:34-40)."""
+        return Tensor(self.t)
+
     def zero_grad(self) -> None:
         if self.t.grad is not None:
             self.t.grad.zero_()

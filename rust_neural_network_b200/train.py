@@ -15,11 +15,17 @@ import torch
 from . import _native as nv
 
 
-class SimpleDataLoader:
+from ._compat import NewMixin as _NewMixin, unwrap as _unwrap  # noqa: E402
+
+class SimpleDataLoader(_NewMixin):
     """Splits `inputs` / `targets` along dim 0 into batches of `batch_size`; no shuffle; the last
     batch may be short (src/train.rs:21-107)."""
 
     def __init__(self, inputs: torch.Tensor, targets: torch.Tensor, batch_size: int):
+        from .tensor import Tensor as _W
+        self._wrapped = isinstance(inputs, _W) or isinstance(targets, _W)      # built from wrappers: batches come out wrapped
+        inputs = inputs.t if isinstance(inputs, _W) else inputs
+        targets = targets.t if isinstance(targets, _W) else targets
         if inputs.shape[0] != targets.shape[0]:
             raise ValueError("inputs and targets must have the same number of rows")
         self.inputs, self.targets, self.batch_size = inputs, targets, max(1, int(batch_size))
@@ -33,10 +39,16 @@ class SimpleDataLoader:
     def __iter__(self) -> Iterator[Tuple[torch.Tensor, torch.Tensor]]:
         n = self.inputs.shape[0]
         for i in range(0, n, self.batch_size):
-            yield self.inputs[i:i + self.batch_size], self.targets[i:i + self.batch_size]
+            x, y = self.inputs[i:i + self.batch_size], self.targets[i:i + self.batch_size]
+            if self._wrapped:
+                from .tensor import Tensor as _W
+                x, y = _W(x), _W(y)
+            yield x, y
+
+    __init__._accepts_wrapped = True           # unwraps by itself (it has to remember that it did)
 
 
-class Trainer:
+class Trainer(_NewMixin):
     """`Trainer(model, optimizer, loss_fn)`; if `loss_fn` is None the model must expose
     `loss(inputs, targets)` (the fused LM head + cross-entropy path)."""
 
@@ -45,6 +57,8 @@ class Trainer:
         """`logger`: a `utils.metrics.MetricsLogger`; every `log_every` steps one record (step, loss, ms per step since the
         last record measured with CUDA events, tokens/s when `tokens_per_step` is given, kernel launches per step) is
         appended. Reading the loss for the record synchronises, so leave `logger` off in timed runs."""
+        if isinstance(loss_fn, type):          # `Trainer::new(model, optimizer, MSELoss)`: a unit struct in the reference
+            loss_fn = loss_fn()
         self.model, self.optimizer, self.loss_fn = model, optimizer, loss_fn
         self.logger, self.log_every, self.tokens_per_step = logger, max(1, int(log_every)), int(tokens_per_step)
         self._log_event = None
@@ -145,6 +159,7 @@ class Trainer:
     def train_epoch(self, loader) -> float:
         losses = []
         for x, y in loader:
+            x, y = _unwrap(x), _unwrap(y)                          # a loader built from `Tensor` wrappers yields wrappers
             losses.append(self.train_step(x, y).clone())
         if not losses:
             return 0.0

@@ -86,3 +86,39 @@ def test_model_side_methods_take_the_wrapper():
     y, loops = rn.LoopedTransformer(4, 8, 2, 16, 2, 3).forward_with_loops(T.randn([1, 3, 4]))
     assert isinstance(y, T) and y.shape() == [1, 3, 2] and loops == 3
     assert isinstance(rn.TreeOfThoughts(4, 2, 2, 1).score(T.randn([2, 4])), T)
+
+
+def test_the_reference_xor_example_line_by_line():
+    """rust-nn examples/xor.rs with `::new` constructors, unit-struct layers and losses, and `Tensor` everywhere."""
+    from rust_neural_network_b200 import Adam, Linear, MSELoss, ReLU, Sequential, SimpleDataLoader, Tensor, Trainer
+    torch.manual_seed(0)
+    inputs = Tensor.from_vec([0.0, 0.0, 0.0, 1.0, 1.0, 0.0, 1.0, 1.0], [4, 2])
+    targets = Tensor.from_vec([0.0, 1.0, 1.0, 0.0], [4, 1])
+    model = Sequential.new().add(Linear.new(2, 8, True)).add(ReLU).add(Linear.new(8, 1, True))
+    trainer = Trainer.new(model, Adam.new(model.parameters(), 0.01), MSELoss)
+    losses = [trainer.train_epoch(SimpleDataLoader.new(inputs.clone(), targets.clone(), 4)) for _ in range(200)]
+    assert losses[-1] < 0.5 * losses[0]
+    out = model.forward(inputs)
+    assert isinstance(out, Tensor) and out.shape() == [4, 1]
+
+
+def test_the_reference_library_usage_loop():
+    """rust-nn examples/library_usage.rs: a hand-written loop over a loader built from wrappers yields wrappers."""
+    from rust_neural_network_b200 import Adam, Linear, MSELoss, ReLU, Sequential, SimpleDataLoader, Tensor
+    torch.manual_seed(1)
+    model = Sequential.new().add(Linear.new(10, 32, True)).add(ReLU).add(Linear.new(32, 5, True))
+    optimizer = Adam.new(model.parameters(), 0.01)
+    loss_fn = MSELoss()
+    loader = SimpleDataLoader.new(Tensor.randn([32, 10]), Tensor.randn([32, 5]), 8)
+    seen = 0
+    for batch_x, batch_y in loader:
+        assert isinstance(batch_x, Tensor) and batch_x.shape() == [8, 10]
+        optimizer.zero_grad()
+        loss = loss_fn.forward(model.forward(batch_x), batch_y)
+        loss.backward()
+        optimizer.step()
+        assert float(loss.data()) > 0.0
+        seen += 1
+    assert seen == 4
+    raw = SimpleDataLoader(torch.randn(5, 2), torch.randn(5, 1), 2)          # torch tensors in, torch tensors out
+    assert all(type(x) is torch.Tensor for x, _ in raw) and len(raw) == 3

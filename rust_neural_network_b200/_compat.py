@@ -74,6 +74,8 @@ def accept_wrapped(fn):
 
 
 def _wrap_class(cls) -> None:
+    if not hasattr(cls, "new"):                      # `Type.new(...)` for classes that do not spell it out
+        cls.new = classmethod(lambda c, *a, **k: c(*a, **k))
     for name, attr in list(cls.__dict__.items()):
         if name.startswith("_") and name not in ("__init__", "__call__"):
             continue

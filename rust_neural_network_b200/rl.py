@@ -296,6 +296,8 @@ class BanditEnv(Environment):
     @staticmethod
     def make_deterministic(k): return BanditEnv(k, deterministic=True)
     @staticmethod
+    def deterministic(k): return BanditEnv(k, deterministic=True)      # the reference's name (src/rl.rs); instances carry the flag under the same name
+    @staticmethod
     def sparse(k): return BanditEnv(k, deterministic=True, probs=[1.0] + [0.0] * (k - 1) if k > 0 else [])
 
     def reset(self): return [1.0]

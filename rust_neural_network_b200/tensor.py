@@ -35,6 +35,15 @@ class FusedAct(enum.Enum):
     Sigmoid = "sigmoid"
     Tanh = "tanh"
 
+    def to_u8(self) -> int:
+        """Identity 0, Relu 1 as in the reference (src/tensor.rs:134-152); the activations it does not have follow."""
+        return list(FusedAct).index(self)
+
+    @staticmethod
+    def from_u8(v: int) -> "FusedAct":
+        members = list(FusedAct)
+        return members[v] if 0 <= v < len(members) else FusedAct.Identity
+
 
 class KernelKind(enum.IntEnum):
     Elu = 0

@@ -25,6 +25,23 @@ class NewMixin:
         return cls(*args, **kwargs)
 
 
+class _Alias:
+    """Read access to a field under the reference's name. A non-data descriptor: an instance attribute of the same name
+    (set by the class or by the user) takes precedence, so adding an alias can never break an assignment."""
+
+    def __init__(self, fn):
+        self.fn = fn
+
+    def __get__(self, obj, owner=None):
+        return self if obj is None else self.fn(obj)
+
+
+def alias_fields(cls, **fields) -> None:
+    """`alias_fields(LayerNorm, num_features="n")`: `ln.num_features` reads `ln.n`; a callable computes the value."""
+    for ref_name, ours in fields.items():
+        setattr(cls, ref_name, _Alias((lambda self, _o=ours: getattr(self, _o)) if isinstance(ours, str) else ours))
+
+
 def _has_wrapped(args, kwargs) -> bool:
     for v in args:
         if isinstance(v, _W):

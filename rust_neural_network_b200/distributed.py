@@ -409,3 +409,10 @@ class DistributedWorker:
             clip_gradients(params, self.config.grad_clip)
         optimizer.step()
         return float(loss.detach()) / max(inputs.shape[0], 1)
+
+
+from ._compat import alias_fields as _alias_fields  # noqa: E402
+
+# src/distributed.rs:382-388: the ring's sockets. Here the ring runs over the C++ TCP store, so the "connections" are the
+# store handle (None until `connect`) in both directions.
+_alias_fields(DistributedWorker, right_conn=lambda self: self.store, left_conn=lambda self: self.store)

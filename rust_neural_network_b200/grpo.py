@@ -460,3 +460,7 @@ def parse_rust_file(path: str, source: str) -> FileNode:
 from ._compat import install as _install  # noqa: E402
 
 _install(globals())
+
+from ._compat import alias_fields as _alias_fields  # noqa: E402
+
+_alias_fields(StructureEdge, **{"from": "from_"})                          # `from` is a keyword here: getattr(edge, "from")

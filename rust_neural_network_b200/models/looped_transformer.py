@@ -269,3 +269,12 @@ def _add_row(a, row):
 from .._compat import accept_wrapped as _accept_wrapped  # noqa: E402
 
 LoopedTransformer.forward_with_loops = _accept_wrapped(LoopedTransformer.forward_with_loops)   # (output, loops used) for a wrapped input too
+
+from .._compat import alias_fields as _alias_fields  # noqa: E402
+
+# src/looped_transformer.rs:60-70, 150-157, 380-388
+_alias_fields(MultiHeadAttention, num_heads="heads", head_dim=lambda self: self.d_model // self.heads, attention="kind")
+_alias_fields(TransformerBlock, d_model=lambda self: self.attn.d_model, ff_dim=lambda self: self.ff1.weight.shape[0],
+              ff=lambda self: nn.Sequential(self.ff1, nn.GELU(), self.ff2))
+_alias_fields(Transformer, d_model=lambda self: self.blocks[0].attn.d_model, num_heads=lambda self: self.blocks[0].attn.heads,
+              ff_dim=lambda self: self.blocks[0].ff1.weight.shape[0])

@@ -282,3 +282,8 @@ class MambaLM(nn.Module):
         for n, b in zip(self.norms, self.blocks):
             ps += n.parameters() + b.parameters()
         return ps + self.ln_final.parameters() + self.lm_head.parameters()
+
+
+from .._compat import alias_fields as _alias_fields  # noqa: E402
+
+_alias_fields(Mamba, d_model=lambda self: self.blocks[0].d_model)          # src/mamba.rs:137-141

@@ -621,3 +621,28 @@ class MoETransformerLM(nn.Module):
 
     def forward(self, ids):
         return self.lm_head(self.hidden(ids)[0])
+
+
+class _ExpertView(nn.Module):
+    """Expert `e` of a routed layer on its own: `forward(x) = act(x W1[e]^T + b1[e]) W2[e]^T + b2[e]` on views of the
+    layer's stacked expert weights (the reference keeps a `Vec<Sequential>`, src/nn.rs:391-394; here the experts are
+    rows of four stacked tensors so that one grouped GEMM serves them all)."""
+
+    def __init__(self, moe, e: int):
+        self._moe, self.index = moe, e
+
+    def parameters(self):
+        m, e = self._moe, self.index
+        return [m.W1[e], m.b1[e], m.W2[e], m.b2[e]]
+
+    def forward(self, x):
+        from ..ops.gemm import act_ref
+        w1, b1, w2, b2 = self.parameters()
+        h = act_ref(x.float() @ w1.float().t() + b1.float(), self._moe.act)
+        return (h @ w2.float().t() + b2.float()).to(x.dtype)
+
+
+from .._compat import alias_fields as _alias_fields  # noqa: E402
+
+_alias_fields(_RoutedMoE, experts=lambda self: [_ExpertView(self, e) for e in range(self.W1.shape[0])],
+              shared_expert=lambda self: self.shared[0] if len(self.shared) == 1 else (self.shared or None))

@@ -457,3 +457,13 @@ def __getattr__(name):
         return getattr(moe, name)
     raise AttributeError(name)
 
+
+# field names of the reference's structs (src/nn.rs:226-233, 573-576, 636-641, 690-697) beside this package's own
+from ._compat import alias_fields as _alias_fields  # noqa: E402
+
+_alias_fields(BatchNorm1D, num_features="n")
+_alias_fields(LayerNorm, num_features="n")
+_alias_fields(CSA, compression_layer="compression", group_size="group")
+_alias_fields(HCA, compression_layer="compression", group_size="group")
+_alias_fields(FakeQuantize, num_bits="bits")
+_alias_fields(RNNCell, weight_ih="w_ih", weight_hh="w_hh")

@@ -326,3 +326,8 @@ class LinearAttention:
 
 
 LinearAttentionLayer = LinearAttention
+
+
+from .._compat import alias_fields as _alias_fields  # noqa: E402
+
+_alias_fields(LinearAttention, kernel="kind")                              # src/linear_attention.rs:640-646

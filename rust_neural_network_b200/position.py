@@ -97,7 +97,9 @@ class RoPE:
 
     @staticmethod
     def yarn(head_dim: int, max_seq_len: int, base: float, scale: float) -> "RoPE":
-        return RoPE(head_dim, max_seq_len, base, _inv=inv_freq_yarn(head_dim, base, scale))
+        r = RoPE(head_dim, max_seq_len, base, _inv=inv_freq_yarn(head_dim, base, scale))
+        r._yarn_scale = float(scale)
+        return r
 
     def apply(self, x):
         if x.shape[-1] != self.head_dim:
@@ -240,3 +242,9 @@ class PositionalEncoding:
 from ._compat import install as _install  # noqa: E402
 
 _install(globals())
+
+from ._compat import alias_fields as _alias_fields  # noqa: E402
+
+# src/position.rs:82-90, 184-195: `scale` is the YaRN factor the tables were built with (1.0 without YaRN), `base` the rotary base
+_alias_fields(RoPE, scale=lambda self: getattr(self, "_yarn_scale", 1.0))
+_alias_fields(CARoPE, base=lambda self: 10000.0)

@@ -122,3 +122,29 @@ def test_the_reference_library_usage_loop():
     assert seen == 4
     raw = SimpleDataLoader(torch.randn(5, 2), torch.randn(5, 1), 2)          # torch tensors in, torch tensors out
     assert all(type(x) is torch.Tensor for x, _ in raw) and len(raw) == 3
+
+
+def test_reference_field_names_read_this_packages_fields():
+    from rust_neural_network_b200 import nn, position
+    from rust_neural_network_b200.models import looped_transformer as LT
+    assert nn.LayerNorm(4).num_features == 4 and nn.BatchNorm1D(6).num_features == 6
+    csa = nn.CSA(8, 2)
+    assert csa.group_size == 2 and csa.compression_layer is csa.compression
+    assert position.RoPE.new(8, 16).scale == 1.0 and position.RoPE.yarn(8, 16, 10000.0, 4.0).scale == 4.0
+    mha = LT.MultiHeadAttention(8, 2)
+    assert (mha.num_heads, mha.head_dim) == (2, 4)
+    blk = LT.TransformerBlock(8, 2, 16)
+    assert (blk.d_model, blk.ff_dim) == (8, 16) and blk.ff.parameters()[0] is blk.ff1.weight
+    ln = nn.LayerNorm(4)
+    ln.num_features = 7                                              # an alias never blocks an assignment
+    assert ln.num_features == 7 and ln.n == 4
+
+
+def test_expert_views_compose_to_the_layer():
+    """`moe.experts[e]` is expert e on its own: with every expert selected, the layer equals the gate-weighted sum."""
+    torch.manual_seed(3)
+    moe = rn.NormalMoE(8, 16, 4, top_k=4)
+    x = torch.randn(5, 8)
+    w = torch.softmax(moe.gate(x).detach().float(), -1)
+    want = sum(w[:, e:e + 1] * moe.experts[e](x).float() for e in range(4))
+    assert len(moe.experts) == 4 and torch.allclose(moe(x).detach().float(), want.detach(), atol=1e-4)

@@ -354,3 +354,18 @@ def test_gpu_surface_cpu(tmp_path):
         assert torch.allclose(gpu.gpu_attention(q, q, q, 0.3), torch.softmax(q @ q.t() * 0.3, -1) @ q, atol=1e-5)
         assert torch.equal(gpu.gpu_relu(torch.tensor([-1.0, 2.0])), torch.tensor([0.0, 2.0]))
         assert torch.equal(gpu.gpu_add(a, a), a + a) and torch.equal(gpu.gpu_mul(a, a), a * a)
+
+
+def test_core_ops_bench_runs_every_group_on_cpu():
+    """benches/core_ops.py (the counterpart of the reference's criterion groups) runs end to end on the CPU path."""
+    import importlib.util
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benches", "core_ops.py")
+    spec = importlib.util.spec_from_file_location("core_ops_bench", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert set(mod.GROUPS) == {"matmul", "simd_matmul", "attention", "gemm_train", "int8_vs_fp32", "blas_sgemm", "dropout",
+                               "fused_linear", "elementwise", "backward"}
+    b = mod.Bench("cpu", 1, 1)
+    for fn in mod.GROUPS.values():
+        fn(b, True)
+    assert len(b.rows) >= 20 and all(t > 0 for _, _, t in b.rows)

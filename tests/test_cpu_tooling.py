@@ -369,3 +369,15 @@ def test_core_ops_bench_runs_every_group_on_cpu():
     for fn in mod.GROUPS.values():
         fn(b, True)
     assert len(b.rows) >= 20 and all(t > 0 for _, _, t in b.rows)
+
+
+@pytest.mark.parametrize("script,args", [("basic.py", []), ("xor.py", []), ("bench_train.py", ["--scale", "0.01"]), ("bench_compiled.py", ["--iters", "2"])])
+def test_examples_run_on_cpu(script, args):
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    r = subprocess.run([sys.executable, os.path.join(root, "examples", script), *args], capture_output=True, text=True, timeout=600,
+                       cwd=os.path.join(root, "examples"), env=env)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert r.stdout.strip()

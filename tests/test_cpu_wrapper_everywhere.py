@@ -148,3 +148,44 @@ def test_expert_views_compose_to_the_layer():
     w = torch.softmax(moe.gate(x).detach().float(), -1)
     want = sum(w[:, e:e + 1] * moe.experts[e](x).float() for e in range(4))
     assert len(moe.experts) == 4 and torch.allclose(moe(x).detach().float(), want.detach(), atol=1e-4)
+
+
+def test_compat_layer_rules():
+    from rust_neural_network_b200._compat import accept_wrapped, alias_fields, rewrap, unwrap
+
+    @accept_wrapped
+    def f(a, pairs=(), scale=1.0, *, extra=None):
+        total = a * scale
+        for _, t in pairs:
+            total = total + t
+        return (total + extra, [total]) if extra is not None else total
+
+    x, y = T.from_vec([1.0, 2.0], [2]), T.from_vec([10.0, 20.0], [2])
+    assert type(f(x.t)) is torch.Tensor                                   # nothing wrapped: untouched
+    out = f(x, [("w", y)], 2.0)                                           # wrappers inside (name, tensor) pairs count
+    assert isinstance(out, T) and out.data().tolist() == [12.0, 24.0]
+    a, (b,) = f(x.t, extra=y)                                             # a wrapped keyword argument, a nested result
+    assert isinstance(a, T) and isinstance(b, T) and a.data().tolist() == [11.0, 22.0]
+    assert accept_wrapped(f) is f                                         # wrapping twice is a no-op
+    p = torch.nn.Parameter(torch.zeros(2))
+    assert rewrap(p) is p and unwrap([x, (y, 3)])[1][1] == 3              # parameters stay parameters; other values pass through
+
+    class Box:
+        def __init__(self):
+            self.n = 5
+    alias_fields(Box, size="n", double=lambda self: 2 * self.n)
+    bx = Box()
+    assert (bx.size, bx.double) == (5, 10)
+    bx.size = 9                                                            # an instance attribute wins
+    assert bx.size == 9 and bx.n == 5
+
+
+def test_gathered_rows_are_kept_without_a_copy_off_the_fused_path():
+    """`TPContext.keep_gathered` on the NCCL / gloo path: the gathered tensor is already private, no copy, no event."""
+    from rust_neural_network_b200.parallel.tp import TPContext
+    ctx = TPContext.__new__(TPContext)
+    ctx.backend = "nccl"
+    xg = torch.randn(4, 3)
+    kept, done = ctx.keep_gathered(xg)
+    assert kept is xg and done is None
+    ctx.join_copy()                                                        # nothing outstanding: a no-op
